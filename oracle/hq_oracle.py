@@ -1,0 +1,618 @@
+"""CPU oracle for the hybrid-precision attention hot path.
+
+TEST INFRASTRUCTURE ONLY.  This module is a numpy restatement of the reference
+algorithm (jerrysfls/HyQuant).  It is imported by ``tests/``, by
+``__graft_entry__.smoke()`` and by the ``cpu_baseline`` / ``--impl reference``
+legs of ``bench.py`` as the *checker* and as the timed CPU baseline.  Nothing in
+the product package imports it; the product path has no CPU fallback.
+
+Pinning status
+--------------
+* quantise / pack / dequantise, decode attention (PyTorch fallback semantics),
+  vertical-line selection, freeze (cache reorganisation), staging append /
+  flush: PINNED — checked against outputs of the reference's own functions
+  executed on CPU (``tests/golden/make_golden.py`` imports the reference and
+  writes ``tests/golden/*.npz``; ``tests/test_oracle_golden.py`` replays them).
+* rest/vertical reorder + per-query-block counts of the hybrid prefill
+  (``reorder_kv_for_vertical``): PINNED the same way (it is eager PyTorch).
+* per-block INT8 quantiser and the hybrid prefill kernel itself: PARITY
+  UNPINNED — the reference implements them only as Triton GPU kernels that
+  cannot execute in a GPU-less container, and the reference ships no golden
+  vectors.  They are restated from the source text.
+
+bf16 tensors are represented as float32 arrays holding bf16-exact values
+(see :func:`bf16_round`); fp16 tensors as ``np.float16``.
+
+Every function cites the reference file:line it follows (paths relative to the
+reference project root).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+import numpy as np
+
+LOG2E = 1.44269504          # src/ops/decode_d_stage.py:17
+GROUP_SIZE = 128            # src/ops/decode_d_stage.py:19 (staging flush threshold)
+FP8_P_OFFSET = 8.807        # vendor/sageattention/csrc/qattn/attn_utils.cuh:30
+E4M3_MAX = 448.0
+
+
+# ----------------------------------------------------------------------------
+# dtype helpers
+# ----------------------------------------------------------------------------
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """Round fp32 to the nearest bf16 (ties to even); result stays float32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = x.view(np.uint32).astype(np.uint64)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    out = r.astype(np.uint32).view(np.float32)
+    return np.where(np.isnan(x), x, out).astype(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 (bf16-exact or not) -> uint16 bf16 bit patterns (RNE)."""
+    return (bf16_round(x).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def e4m3_round(x: np.ndarray) -> np.ndarray:
+    """Round fp32 to FP8 E4M3 (saturating, ties to even); result stays float32.
+
+    Follows ``cvt.rn.satfinite.e4m3x2.f32`` as used by
+    vendor/sageattention/csrc/numeric_conversion.cuh:46-61.
+    """
+    x = np.asarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x).astype(np.float64), E4M3_MAX)
+    # exponent of the value, clamped to the subnormal exponent (-6)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    e = np.maximum(e, -6.0)
+    step = np.exp2(e - 3.0)             # 3 mantissa bits
+    q = np.rint(a / step) * step        # np.rint is round-half-even
+    q = np.minimum(q, E4M3_MAX)
+    return (np.sign(x) * q).astype(np.float32)
+
+
+# ----------------------------------------------------------------------------
+# a1/a2 — per-token symmetric quantiser (src/ops/decode_d_stage.py:50-149)
+# ----------------------------------------------------------------------------
+
+def pack_int4(q: np.ndarray) -> np.ndarray:
+    """[..., D] int8 in [-8, 7] -> [..., D/2] int8.  decode_d_stage.py:104-111.
+
+    Even channel in the low nibble, odd channel in the high nibble,
+    two's-complement nibbles.
+    """
+    u = q.astype(np.int16) & 0x0F
+    return (u[..., 0::2] | (u[..., 1::2] << 4)).astype(np.uint8).view(np.int8)
+
+
+def unpack_int4(packed: np.ndarray) -> np.ndarray:
+    """[..., D/2] int8 -> [..., D] float32, sign-extended.  decode_d_stage.py:114-123."""
+    x = packed.view(np.uint8).astype(np.int32)
+    lo = ((x & 0x0F) ^ 8) - 8
+    hi = (((x >> 4) & 0x0F) ^ 8) - 8
+    out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), dtype=np.float32)
+    out[..., 0::2] = lo
+    out[..., 1::2] = hi
+    return out
+
+
+def pack_int2(q: np.ndarray) -> np.ndarray:
+    """decode_d_stage.py:126-133."""
+    u = q.astype(np.int16) & 0x03
+    return (u[..., 0::4] | (u[..., 1::4] << 2) | (u[..., 2::4] << 4) | (u[..., 3::4] << 6)).astype(np.uint8).view(np.int8)
+
+
+def unpack_int2(packed: np.ndarray) -> np.ndarray:
+    """decode_d_stage.py:136-149."""
+    x = packed.view(np.uint8).astype(np.int32)
+    out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 4,), dtype=np.float32)
+    for i in range(4):
+        out[..., i::4] = (((x >> (2 * i)) & 3) ^ 2) - 2
+    return out
+
+
+def quantize_per_token(x: np.ndarray, nbits: int = 4,
+                       reciprocal_scale: bool = False) -> Tuple[np.ndarray, np.ndarray]:
+    """Per-token symmetric quantisation.  decode_d_stage.py:50-77.
+
+    ``scale = half(max(|x|, 1e-5) / q_max)`` and the *rounded* fp16 scale is
+    what divides ``x`` (:66-68).  ``round`` is half-to-even (torch.round).
+
+    ``reciprocal_scale=True`` reproduces CUDA-eager PyTorch, whose
+    tensor/python-scalar division multiplies by the fp32 reciprocal of the
+    scalar instead of dividing; the default reproduces CPU-eager PyTorch (a
+    true IEEE division), which is what the golden vectors pin.
+    """
+    if nbits not in (2, 4, 8):
+        raise ValueError(f"nbits must be 2, 4, or 8, got {nbits}")
+    q_max = 2 ** (nbits - 1) - 1
+    q_min = -(2 ** (nbits - 1))
+    x_f = np.asarray(x, dtype=np.float32)
+    amax = np.maximum(np.abs(x_f).max(axis=-1), np.float32(1e-5)).astype(np.float32)
+    if reciprocal_scale:
+        s32 = amax * (np.float32(1.0) / np.float32(q_max))
+    else:
+        s32 = amax / np.float32(q_max)
+    scale = s32.astype(np.float16)
+    q = np.clip(np.rint(x_f / scale.astype(np.float32)[..., None]), q_min, q_max).astype(np.int8)
+    if nbits == 8:
+        return q, scale
+    if nbits == 4:
+        return pack_int4(q), scale
+    return pack_int2(q), scale
+
+
+def dequantize_per_token(packed: np.ndarray, scale: np.ndarray, nbits: int = 4) -> np.ndarray:
+    """decode_d_stage.py:80-101 — returns fp16 like the reference."""
+    if nbits == 8:
+        q = packed.astype(np.float32)
+    elif nbits == 4:
+        q = unpack_int4(packed)
+    elif nbits == 2:
+        q = unpack_int2(packed)
+    else:
+        raise ValueError(f"nbits must be 2, 4, or 8, got {nbits}")
+    return (q * scale.astype(np.float32)[..., None]).astype(np.float16)
+
+
+# ----------------------------------------------------------------------------
+# a4 — vertical-line selection (src/patch/_common.py:144-190)
+# ----------------------------------------------------------------------------
+
+def topk_desc(scores: np.ndarray, k: int) -> np.ndarray:
+    """Indices of the k largest entries along the last axis, sorted by
+    descending score; ties broken towards the LOWER index (the build's
+    definition — torch.topk leaves tie order unspecified, _common.py:189)."""
+    order = np.argsort(-scores, axis=-1, kind="stable")
+    return order[..., :k].astype(np.int64)
+
+
+def vertical_scores(query_states: np.ndarray, key_states: np.ndarray,
+                    window_size: int, kv_repeat: int = 1) -> Optional[np.ndarray]:
+    """q_mean . K_prefix^T  ->  [B, H_Q, P] float32.  _common.py:161-185."""
+    batch, num_heads, query_len, head_dim = query_states.shape
+    key_len = key_states.shape[2]
+    prefix_len = max(0, key_len - window_size)
+    if prefix_len == 0:
+        return None
+    tail_len = min(window_size, query_len)
+    q_mean = query_states[:, :, query_len - tail_len:, :].astype(np.float32).mean(axis=2)   # [B,H,D]
+    key_prefix = key_states[:, :, :prefix_len, :].astype(np.float32)
+    if kv_repeat <= 1 or key_states.shape[1] == num_heads:
+        return np.einsum("bhd,bhpd->bhp", q_mean, key_prefix, optimize=True).astype(np.float32)
+    h_kv = key_states.shape[1]
+    assert num_heads == h_kv * kv_repeat
+    q_g = q_mean.reshape(batch, h_kv, kv_repeat, head_dim)
+    s = np.einsum("bhrd,bhpd->bhrp", q_g, key_prefix, optimize=True)
+    return s.reshape(batch, num_heads, prefix_len).astype(np.float32)
+
+
+def vertical_topk_count(prefix_len: int, top_ratio: float) -> int:
+    """_common.py:187-188."""
+    return min(max(1, int(math.ceil(prefix_len * top_ratio))), prefix_len)
+
+
+def compute_vertical_indices(query_states: np.ndarray, key_states: np.ndarray,
+                             window_size: int, top_ratio: float, kv_repeat: int = 1) -> np.ndarray:
+    """_common.py:144-190 -> [B, H_Q, top_k] int64 (descending score)."""
+    s = vertical_scores(query_states, key_states, window_size, kv_repeat)
+    if s is None:
+        return np.empty(query_states.shape[:2] + (0,), dtype=np.int64)
+    return topk_desc(s, vertical_topk_count(s.shape[-1], top_ratio))
+
+
+# ----------------------------------------------------------------------------
+# a3/a5/a6 — the four-segment cache (src/ops/d_stage_kv_cache.py:36-357)
+# ----------------------------------------------------------------------------
+
+@dataclass
+class LayerCache:
+    """State of one layer after ``freeze`` (KV-head granularity, BH = B*H_KV)."""
+    B: int
+    H_KV: int
+    D: int
+    k_bits: int
+    v_bits: int
+    k_quant_packed: np.ndarray      # [BH, N_q, D_packed] int8
+    v_quant_packed: np.ndarray
+    k_scale: np.ndarray             # [BH, N_q] fp16
+    v_scale: np.ndarray
+    k_topk: np.ndarray              # [BH, T, D]  (descending-score order)
+    v_topk: np.ndarray
+    k_window: np.ndarray            # [BH, W, D]
+    v_window: np.ndarray
+    staging_k: np.ndarray           # [BH, 128, D]
+    staging_v: np.ndarray
+    staging_ptr: int = 0
+    seq_len: int = 0
+    vidx: Optional[np.ndarray] = field(default=None)   # [B, H_KV, T] for inspection
+
+
+def freeze(keys: np.ndarray, values: np.ndarray, query_tail: Optional[np.ndarray],
+           kv_repeat: int, window_size: int, top_ratio: float,
+           k_bits: int = 4, v_bits: int = 4, use_vert: bool = True,
+           round_fn=None, vidx_override: Optional[np.ndarray] = None) -> LayerCache:
+    """Prefill -> decode transition.  d_stage_kv_cache.py:106-189.
+
+    ``keys/values`` [B, H_KV, N, D]; ``query_tail`` [B, H_Q, <=W, D] (what
+    ``save_query_tail`` kept, :97-100).  ``round_fn`` rounds the group-mean of
+    the queries to the input dtype (identity for fp32, :func:`bf16_round` for
+    bf16 inputs, :131-133).
+
+    Quirk kept from the reference: ``compute_vertical_indices`` is handed the
+    already-sliced prefix and subtracts the window a second time, so candidates
+    are positions [0, N-2W) (:134-136 with _common.py:162-163).
+    """
+    B, H_KV, N, D = keys.shape
+    BH = B * H_KV
+    W = min(window_size, N)
+    prefix_len = N - W
+    k_window = keys[:, :, N - W:, :].reshape(BH, W, D).copy()
+    v_window = values[:, :, N - W:, :].reshape(BH, W, D).copy()
+    vidx = None
+    pk = {8: D, 4: D // 2, 2: D // 4}
+    if prefix_len > 0:
+        k_prefix = keys[:, :, :prefix_len, :]
+        v_prefix = values[:, :, :prefix_len, :]
+        if use_vert and query_tail is not None and kv_repeat >= 1:
+            q_kv = query_tail.reshape(B, H_KV, kv_repeat, -1, D).astype(np.float32).mean(axis=2)
+            if round_fn is not None:
+                q_kv = round_fn(q_kv)
+            if vidx_override is not None:
+                # bf16 inputs: the reference scores in bf16 and torch.topk's tie
+                # order is unspecified, so the selection itself is taken as given
+                vidx = np.asarray(vidx_override, dtype=np.int64)
+            else:
+                vidx = compute_vertical_indices(q_kv, k_prefix, window_size, top_ratio)   # [B,H_KV,T]
+            T = vidx.shape[-1]
+            k_topk = np.take_along_axis(k_prefix, vidx[..., None], axis=2).reshape(BH, T, D)
+            v_topk = np.take_along_axis(v_prefix, vidx[..., None], axis=2).reshape(BH, T, D)
+            keep = np.ones((B, H_KV, prefix_len), dtype=bool)
+            np.put_along_axis(keep, vidx, False, axis=2)
+            # ascending original position with the top-k rows removed (:148-160)
+            k_compact = k_prefix[keep].reshape(BH, prefix_len - T, D)
+            v_compact = v_prefix[keep].reshape(BH, prefix_len - T, D)
+        else:
+            k_topk = np.zeros((BH, 0, D), dtype=keys.dtype)
+            v_topk = np.zeros((BH, 0, D), dtype=keys.dtype)
+            k_compact = k_prefix.reshape(BH, prefix_len, D)
+            v_compact = v_prefix.reshape(BH, prefix_len, D)
+        kq, ks = quantize_per_token(k_compact, k_bits)
+        vq, vs = quantize_per_token(v_compact, v_bits)
+    else:
+        kq = np.zeros((BH, 0, pk[k_bits]), dtype=np.int8)
+        vq = np.zeros((BH, 0, pk[v_bits]), dtype=np.int8)
+        ks = np.zeros((BH, 0), dtype=np.float16)
+        vs = np.zeros((BH, 0), dtype=np.float16)
+        k_topk = np.zeros((BH, 0, D), dtype=keys.dtype)
+        v_topk = np.zeros((BH, 0, D), dtype=keys.dtype)
+    return LayerCache(
+        B=B, H_KV=H_KV, D=D, k_bits=k_bits, v_bits=v_bits,
+        k_quant_packed=kq, v_quant_packed=vq, k_scale=ks, v_scale=vs,
+        k_topk=np.ascontiguousarray(k_topk), v_topk=np.ascontiguousarray(v_topk),
+        k_window=k_window, v_window=v_window,
+        staging_k=np.zeros((BH, GROUP_SIZE, D), dtype=keys.dtype),
+        staging_v=np.zeros((BH, GROUP_SIZE, D), dtype=keys.dtype),
+        staging_ptr=0, seq_len=N, vidx=vidx,
+    )
+
+
+def flush_staging(c: LayerCache) -> None:
+    """d_stage_kv_cache.py:209-217 — quantise all 128 slots, append to the prefix."""
+    kp, ks = quantize_per_token(c.staging_k, c.k_bits)
+    vp, vs = quantize_per_token(c.staging_v, c.v_bits)
+    c.k_quant_packed = np.concatenate([c.k_quant_packed, kp], axis=1)
+    c.v_quant_packed = np.concatenate([c.v_quant_packed, vp], axis=1)
+    c.k_scale = np.concatenate([c.k_scale, ks], axis=1)
+    c.v_scale = np.concatenate([c.v_scale, vs], axis=1)
+    c.staging_ptr = 0
+
+
+def append_staging(c: LayerCache, key_states: np.ndarray, value_states: np.ndarray) -> None:
+    """d_stage_kv_cache.py:195-207 — key/value [B, H_KV, S, D]."""
+    B, H_KV, S, D = key_states.shape
+    k = key_states.reshape(B * H_KV, S, D)
+    v = value_states.reshape(B * H_KV, S, D)
+    for i in range(S):
+        c.staging_k[:, c.staging_ptr, :] = k[:, i, :]
+        c.staging_v[:, c.staging_ptr, :] = v[:, i, :]
+        c.staging_ptr += 1
+        if c.staging_ptr >= GROUP_SIZE:
+            flush_staging(c)
+    c.seq_len += S
+
+
+def _softmax_lastaxis(s: np.ndarray) -> np.ndarray:
+    m = s.max(axis=-1, keepdims=True)
+    e = np.exp(s - m)
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def decode_attention_fallback(q: np.ndarray, c: LayerCache, kv_repeat: int,
+                              round_fn=None, sm_scale: Optional[float] = None) -> np.ndarray:
+    """The reference's PyTorch fallback.  d_stage_kv_cache.py:306-354.
+
+    q [B, H_Q, 1, D] -> [B, H_Q, 1, D] float32.  Dequantised K/V are rounded to
+    fp16 first (decode_d_stage.py:101) and then cast to the query dtype
+    (``round_fn``: identity for fp32 queries, bf16_round for bf16 queries).
+    """
+    B, H_KV, D = c.B, c.H_KV, c.D
+    H_Q = H_KV * kv_repeat
+    rf = (lambda a: a) if round_fn is None else round_fn
+    segs_k, segs_v = [], []
+    if c.k_quant_packed.shape[1] > 0:
+        segs_k.append(rf(dequantize_per_token(c.k_quant_packed, c.k_scale, c.k_bits).astype(np.float32)))
+        segs_v.append(rf(dequantize_per_token(c.v_quant_packed, c.v_scale, c.v_bits).astype(np.float32)))
+    if c.k_topk.shape[1] > 0:
+        segs_k.append(c.k_topk.astype(np.float32)); segs_v.append(c.v_topk.astype(np.float32))
+    if c.staging_ptr > 0:
+        segs_k.append(c.staging_k[:, :c.staging_ptr].astype(np.float32))
+        segs_v.append(c.staging_v[:, :c.staging_ptr].astype(np.float32))
+    segs_k.append(c.k_window.astype(np.float32)); segs_v.append(c.v_window.astype(np.float32))
+    k_all = np.concatenate(segs_k, axis=1).reshape(B, H_KV, -1, D)
+    v_all = np.concatenate(segs_v, axis=1).reshape(B, H_KV, -1, D)
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    qg = q.astype(np.float32).reshape(B, H_KV, kv_repeat, D)
+    scores = np.einsum("bhrd,bhnd->bhrn", qg, k_all, optimize=True) * np.float32(sm_scale)
+    p = _softmax_lastaxis(scores.astype(np.float32))
+    out = np.einsum("bhrn,bhnd->bhrd", p, v_all, optimize=True)
+    return out.reshape(B, H_Q, 1, D).astype(np.float32)
+
+
+def decode_attention_exact(q: np.ndarray, c: LayerCache, kv_repeat: int,
+                           sm_scale: Optional[float] = None) -> np.ndarray:
+    """float64 attention over the *stored* cache contents, K/V = code * scale
+    without the fallback's fp16 rounding — the math of the reference's Triton
+    kernel (decode_d_stage.py:617-618, 653, 664-666) taken to infinite
+    precision.  Used as the tight yardstick for the CUDA kernel."""
+    B, H_KV, D = c.B, c.H_KV, c.D
+    H_Q = H_KV * kv_repeat
+    unp = {4: unpack_int4, 2: unpack_int2, 8: lambda a: a.astype(np.float32)}
+    segs_k, segs_v = [], []
+    if c.k_quant_packed.shape[1] > 0:
+        segs_k.append(unp[c.k_bits](c.k_quant_packed).astype(np.float64) * c.k_scale.astype(np.float64)[..., None])
+        segs_v.append(unp[c.v_bits](c.v_quant_packed).astype(np.float64) * c.v_scale.astype(np.float64)[..., None])
+    if c.k_topk.shape[1] > 0:
+        segs_k.append(c.k_topk.astype(np.float64)); segs_v.append(c.v_topk.astype(np.float64))
+    if c.staging_ptr > 0:
+        segs_k.append(c.staging_k[:, :c.staging_ptr].astype(np.float64))
+        segs_v.append(c.staging_v[:, :c.staging_ptr].astype(np.float64))
+    segs_k.append(c.k_window.astype(np.float64)); segs_v.append(c.v_window.astype(np.float64))
+    k_all = np.concatenate(segs_k, axis=1).reshape(B, H_KV, -1, D)
+    v_all = np.concatenate(segs_v, axis=1).reshape(B, H_KV, -1, D)
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    qg = q.astype(np.float64).reshape(B, H_KV, kv_repeat, D)
+    scores = np.einsum("bhrd,bhnd->bhrn", qg, k_all, optimize=True) * sm_scale
+    p = _softmax_lastaxis(scores)
+    out = np.einsum("bhrn,bhnd->bhrd", p, v_all, optimize=True)
+    return out.reshape(B, H_Q, 1, D)
+
+
+# ----------------------------------------------------------------------------
+# a9 — log-sum-exp merge of softmax partials (decode_d_stage.py:746-782)
+# ----------------------------------------------------------------------------
+
+def lse_merge(m: np.ndarray, l: np.ndarray, acc: np.ndarray) -> np.ndarray:
+    """Merge S partials.  m, l: [S, ...]; acc: [S, ..., D]; base-2 maxima.
+
+    ``M = max m_s; out = sum 2^(m_s-M) acc_s / sum 2^(m_s-M) l_s`` (:764-781).
+    """
+    M = m.max(axis=0)
+    w = np.exp2(m - M[None])
+    num = (w[..., None] * acc).sum(axis=0)
+    den = (w * l).sum(axis=0)
+    return num / den[..., None]
+
+
+def decode_partials(q: np.ndarray, k_all: np.ndarray, v_all: np.ndarray, sm_scale: float):
+    """Un-normalised softmax partial (m, l, acc) of one shard in base 2,
+    float64: m = max(s*log2e), l = sum 2^(s-m), acc = sum 2^(s-m) v."""
+    s = np.einsum("...rd,...nd->...rn", q.astype(np.float64), k_all.astype(np.float64)) * (sm_scale * LOG2E)
+    if s.shape[-1] == 0:
+        return (np.full(s.shape[:-1], -np.inf), np.zeros(s.shape[:-1]),
+                np.zeros(s.shape[:-1] + (v_all.shape[-1],)))
+    m = s.max(axis=-1)
+    p = np.exp2(s - m[..., None])
+    return m, p.sum(axis=-1), np.einsum("...rn,...nd->...rd", p, v_all.astype(np.float64))
+
+
+# ----------------------------------------------------------------------------
+# a12 — per-block INT8 quantiser (vendor/sageattention/triton/quant_per_block.py:21-101)
+# PARITY UNPINNED (Triton-only in the reference).
+# ----------------------------------------------------------------------------
+
+def quant_per_block_int8(x: np.ndarray, blk: int, sm_scale: float = 1.0) -> Tuple[np.ndarray, np.ndarray]:
+    """x [B, H, L, D] -> int8 same shape + fp32 scales [B, H, ceil(L/blk)].
+
+    ``scale = max|x*sm| / 127`` (no epsilon); ``x/scale + 0.5*sign`` truncated
+    towards zero = round-half-away (:41-45).
+    """
+    B, H, L, D = x.shape
+    nb = (L + blk - 1) // blk
+    xs = x.astype(np.float32) * np.float32(sm_scale)
+    pad = nb * blk - L
+    xp = np.pad(xs, ((0, 0), (0, 0), (0, pad), (0, 0))) if pad else xs
+    xb = xp.reshape(B, H, nb, blk, D)
+    scale = (np.abs(xb).max(axis=(3, 4)) / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        y = xb / scale[..., None, None]
+    y = y + np.float32(0.5) * np.where(y >= 0, np.float32(1), np.float32(-1))
+    q = np.trunc(y)
+    q = np.nan_to_num(q, nan=0.0).astype(np.int8).reshape(B, H, nb * blk, D)[:, :, :L]
+    return q, scale
+
+
+def per_block_int8(q: np.ndarray, k: np.ndarray, km: Optional[np.ndarray] = None,
+                   sm_scale: Optional[float] = None, round_fn=None):
+    """quant_per_block.py:49-101 with BLKQ=128, BLKK=64, HND layout.
+
+    K minus its mean is formed in the input dtype (:53-54) -> ``round_fn``.
+    """
+    D = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if km is not None:
+        k = k.astype(np.float32) - km.astype(np.float32)
+        if round_fn is not None:
+            k = round_fn(k)
+    qi, qs = quant_per_block_int8(q, 128, sm_scale * LOG2E)
+    ki, ks = quant_per_block_int8(k, 64, 1.0)
+    return qi, qs, ki, ks
+
+
+# ----------------------------------------------------------------------------
+# a11 — hybrid prefill (src/ops/sage_unified.py:398-622)
+# ----------------------------------------------------------------------------
+
+def window_lo_aligned(block_start: np.ndarray, window_size: int,
+                      block_n: int = 64) -> np.ndarray:
+    """sage_unified.py:483-485, 538-544: ``floor(max(0, s-(W-1))/64)*64``."""
+    return (np.maximum(block_start - (window_size - 1), 0) // block_n) * block_n
+
+
+def reorder_kv_for_vertical(k: np.ndarray, v: np.ndarray, vertical_indices: np.ndarray,
+                            window_size: int):
+    """sage_unified.py:499-547.  k, v [BH, N, D]; vertical_indices [B, H, T].
+
+    Returns k_rest, v_rest, k_vert, v_vert, n_rest_valid [BH, N] i32,
+    n_vert_valid [BH, N] i32, R, V.
+    """
+    BH, N, D = k.shape
+    B, H, VLEN = vertical_indices.shape
+    prefix_len = max(0, N - window_size)
+    if prefix_len == 0:
+        e = np.zeros((BH, 0, D), dtype=k.dtype)
+        z = np.zeros((BH, N), dtype=np.int32)
+        return e, e, e, e, z, z, 0, 0
+    vid = np.clip(vertical_indices.reshape(BH, VLEN).astype(np.int64), 0, prefix_len - 1)
+    vid_sorted = np.sort(vid, axis=1)
+    vert_mask = np.zeros((BH, prefix_len), dtype=bool)
+    np.put_along_axis(vert_mask, vid_sorted, True, axis=1)
+    rest_mask = ~vert_mask
+    rest_counts = rest_mask.sum(axis=1)
+    R = int(rest_counts.max())
+    # stable argsort of -mask puts the kept positions first, in position order
+    order = np.argsort(-(rest_mask.astype(np.int32)), axis=1, kind="stable")
+    rest_indices = np.sort(order[:, :R].astype(np.int64), axis=1)
+    k_rest = np.take_along_axis(k, np.clip(rest_indices, 0, N - 1)[..., None], axis=1)
+    v_rest = np.take_along_axis(v, np.clip(rest_indices, 0, N - 1)[..., None], axis=1)
+    k_vert = np.take_along_axis(k, np.clip(vid_sorted, 0, N - 1)[..., None], axis=1)
+    v_vert = np.take_along_axis(v, np.clip(vid_sorted, 0, N - 1)[..., None], axis=1)
+    pos = np.arange(N, dtype=np.int64)
+    wla = window_lo_aligned((pos // 128) * 128, window_size)
+    n_rest_valid = np.stack([np.searchsorted(rest_indices[i], wla, side="left") for i in range(BH)]).astype(np.int32)
+    n_vert_valid = np.stack([np.searchsorted(vid_sorted[i], wla, side="left") for i in range(BH)]).astype(np.int32)
+    return k_rest, v_rest, k_vert, v_vert, n_rest_valid, n_vert_valid, R, VLEN
+
+
+def _online_block(acc, l_i, m_i, qk, v, p_round, pv_round):
+    """One flash block: sage_unified.py:342-353 / :93-105."""
+    m_ij = np.maximum(m_i, qk.max(axis=1))
+    p = np.exp2(qk - m_ij[:, None]).astype(np.float32)
+    alpha = np.exp2(m_i - m_ij).astype(np.float32)
+    l_i = l_i * alpha + p.sum(axis=1, dtype=np.float32)
+    acc = acc * alpha[:, None]
+    acc = acc + pv_round(p_round(p).astype(np.float32) @ v.astype(np.float32))
+    return acc, l_i, m_ij
+
+
+def hybrid_prefill_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray,
+                             vertical_indices: np.ndarray, window_size: int = 256,
+                             sm_scale: Optional[float] = None, smooth_k: bool = True,
+                             round_fn=None) -> np.ndarray:
+    """Restatement of ``sage_vertical_attention_v2`` (sage_unified.py:550-622)
+    with the kernel ``_attn_fwd_vertical_v2`` (:398-496).  PARITY UNPINNED.
+
+    q [B, H_q, N, D], k/v [B, H_kv, N, D] (float32 holding input-dtype-exact
+    values), vertical_indices [B, H_q, T] int64.  ``round_fn`` rounds to the
+    input dtype.  INT8 QK for the rest, fp16 QK for vertical + window, fp16 P,
+    fp16-rounded PV products (``tl.dot(..., out_dtype=fp16)`` :351-352),
+    m0=-1e6, l0=1 (:457-458), count masks add -1e6 (:341,380), causal -inf (:92).
+    """
+    f16 = lambda a: np.asarray(a, dtype=np.float32).astype(np.float16).astype(np.float32)
+    rf = (lambda a: a) if round_fn is None else round_fn
+    B, H_q, N, D = q.shape
+    H_kv = k.shape[1]
+    g = H_q // H_kv
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    sml = sm_scale * LOG2E
+    km = rf(k.astype(np.float32).mean(axis=2, keepdims=True)) if smooth_k else None
+    q_int8, q_scale, _, _ = per_block_int8(q, k, km=km, sm_scale=sm_scale, round_fn=rf)
+    k_sm = rf(k.astype(np.float32) - km) if km is not None else k.astype(np.float32)
+    q_scaled = f16(rf(q.astype(np.float32) * np.float32(sml)))
+    k_raw = f16(np.repeat(k_sm, g, axis=1))
+    v16 = f16(np.repeat(v.astype(np.float32), g, axis=1))
+    BH = B * H_q
+    k3, v3 = k_raw.reshape(BH, N, D), v16.reshape(BH, N, D)
+    k_rest, v_rest, k_vert, v_vert, nrv, nvv, R, V = reorder_kv_for_vertical(k3, v3, vertical_indices, window_size)
+    if R > 0:
+        kr_i8, kr_sc = quant_per_block_int8(k_rest.reshape(B, H_q, R, D), 64, 1.0)
+        kr_i8 = kr_i8.reshape(BH, R, D); kr_sc = kr_sc.reshape(BH, -1)
+    out = np.zeros((BH, N, D), dtype=np.float32)
+    BM, BN = 128, 64
+    for bh in range(BH):
+        qi = q_int8.reshape(BH, N, D)[bh].astype(np.float32)
+        qs = q_scale.reshape(BH, -1)[bh]
+        qr = q_scaled.reshape(BH, N, D)[bh]
+        for sm_ in range(0, N, BM):
+            rows = np.arange(sm_, min(sm_ + BM, N))
+            nr, nv = nrv[bh, rows], nvv[bh, rows]
+            m_i = np.full(len(rows), -1.0e6, dtype=np.float32)
+            l_i = np.ones(len(rows), dtype=np.float32)
+            acc = np.zeros((len(rows), D), dtype=np.float32)
+            for s0 in range(0, int(-(-nr.max() // BN) * BN) if R > 0 else 0, BN):
+                cols = np.arange(s0, min(s0 + BN, R))
+                qk = (qi[rows] @ kr_i8[bh, cols].astype(np.float32).T) * (qs[sm_ // BM] * kr_sc[bh, s0 // BN])
+                qk = qk + np.where(cols[None, :] < nr[:, None], 0.0, -1.0e6).astype(np.float32)
+                acc, l_i, m_i = _online_block(acc, l_i, m_i, qk.astype(np.float32), v_rest[bh, cols], f16, f16)
+            for s0 in range(0, int(-(-nv.max() // BN) * BN) if V > 0 else 0, BN):
+                cols = np.arange(s0, min(s0 + BN, V))
+                qk = qr[rows] @ k_vert[bh, cols].T
+                qk = qk + np.where(cols[None, :] < nv[:, None], 0.0, -1.0e6).astype(np.float32)
+                acc, l_i, m_i = _online_block(acc, l_i, m_i, qk.astype(np.float32), v_vert[bh, cols], f16, f16)
+            wla = int(window_lo_aligned(np.array(sm_), window_size))
+            for s0 in range(wla, min(sm_ + BM, N), BN):
+                cols = np.arange(s0, min(s0 + BN, N))
+                qk = qr[rows] @ k3[bh, cols].T
+                with np.errstate(invalid="ignore"):
+                    qk = qk + np.where(rows[:, None] >= cols[None, :], 0.0, -np.inf).astype(np.float32)
+                acc, l_i, m_i = _online_block(acc, l_i, m_i, qk.astype(np.float32), v3[bh, cols], f16, f16)
+            out[bh, rows] = acc / l_i[:, None]
+    return rf(out.reshape(B, H_q, N, D))
+
+
+def dense_causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray,
+                           sm_scale: Optional[float] = None) -> np.ndarray:
+    """float64 causal softmax(QK^T)V with GQA — the yardstick the prefill
+    tolerances (max-abs 2e-2, rel-MSE 1e-4) are measured against."""
+    B, H_q, N, D = q.shape
+    H_kv = k.shape[1]
+    g = H_q // H_kv
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    out = np.empty((B, H_q, N, D), dtype=np.float64)
+    mask = np.tril(np.ones((N, N), dtype=bool))
+    for b in range(B):
+        for h in range(H_q):
+            s = (q[b, h].astype(np.float64) @ k[b, h // g].astype(np.float64).T) * sm_scale
+            s = np.where(mask, s, -np.inf)
+            out[b, h] = _softmax_lastaxis(s) @ v[b, h // g].astype(np.float64)
+    return out
+
+
+def rel_mse(a: np.ndarray, b: np.ndarray) -> float:
+    a = np.asarray(a, dtype=np.float64); b = np.asarray(b, dtype=np.float64)
+    return float(((a - b) ** 2).sum() / max((b ** 2).sum(), 1e-30))
