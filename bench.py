@@ -1,0 +1,398 @@
+#!/usr/bin/env python
+"""Benchmark of the hybrid-precision decode attention path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (per GPU): decode attention at Llama-3.1-8B shapes — batch 1, 32 query /
+8 KV heads, head_dim 128, prefix 32768, window 128, rho 5 % (1632 BF16
+vertical-line tokens, 31008 INT4 tokens), 64 live staging tokens, K4V4 with
+per-token scales.  One *step* is one generated token: 32 decode-attention calls,
+one per layer, each over its own cache (32 x 40 MB = 1.3 GB > L2, so no call
+re-reads a cache that is still in L2).  Inputs are seeded synthetic tensors with
+the outlier / vertical-line structure of ``hyquant_b200.synth``.
+
+Reported metric: achieved HBM throughput in GB/s = algorithmic bytes per call x
+calls / device time (whole job, summed over GPUs), with the per-call and
+per-token latencies beside it.  ``value`` times the kernels with every input
+resident in HBM; ``e2e`` drives the reference-named cache API per layer with the
+new token's q/k/v coming from pinned host memory and the attention output read
+back to the host inside the timed region.
+
+``--impl reference`` times the CPU restatement of the reference's own PyTorch
+fallback path (oracle/hq_oracle.py) on the host cores, on one layer call per
+step of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+B, H_Q, H_KV, D = 1, 32, 8, 128
+N_PREFIX, W, RHO, STAGING = 32768, 128, 0.05, 64
+LAYERS = 32
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(bh_kv, bh_q, n_quant, n_bf16):
+    """Bytes one decode call must move: INT4 token = 64+64 B codes + 2+2 B scales,
+    BF16 token = 256+256 B, plus q read and out written (2 x 256 B per query head)."""
+    return bh_kv * (132 * n_quant + 512 * n_bf16) + 512 * bh_q
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------
+# workload construction (device)
+# ---------------------------------------------------------------------------
+
+def build_layer(hq, torch, seed, n_prefix, device, b=B, h_q=H_Q, h_kv=H_KV, staging=STAGING):
+    """Seeded K/V/Q -> vertical selection over [0, N-W) -> frozen four-segment cache."""
+    from hyquant_b200.synth import gen_torch
+    t = gen_torch(b, h_q, h_kv, n_prefix, D, W, RHO, seed, n_qry=256, device=device)
+    layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+    layer.update_prefill(t["k"], t["v"])
+    layer.save_query_tail(t["q"])
+    r = h_q // h_kv
+    # vertical lines from the 256 pooled queries, KV-group mean, candidates [0, N-W)
+    pooled = t["q"].float().mean(dim=2, keepdim=True).reshape(b, h_kv, r, 1, D).mean(dim=2).to(t["k"].dtype)
+    vidx = hq.compute_vertical_indices(pooled, t["k"], W, RHO, kv_repeat=1)
+    layer.freeze(kv_repeat=r, vertical_indices=vidx)
+    g = torch.Generator(device=device); g.manual_seed(seed + 7)
+    for _ in range(staging):
+        kn = torch.randn(b, h_kv, 1, D, generator=g, device=device).to(torch.bfloat16)
+        vn = torch.randn(b, h_kv, 1, D, generator=g, device=device).to(torch.bfloat16)
+        layer.append_staging(kn, vn)
+    return layer, t["q_decode"]
+
+
+def layer_bytes(layer, h_q_total):
+    n_bf16 = layer.k_topk.shape[1] + layer._staging_ptr + layer.k_window.shape[1]
+    return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16)
+
+
+def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None):
+    """K steps of (one decode launch per layer), device-timed; returns ms total, launches.
+    ``flush``: a buffer larger than L2 that is rewritten before every step (outside the
+    timed events) when the step's own caches do not exceed L2."""
+    r = H_Q // H_KV
+    plans = []
+    outs = []
+    for layer, q in zip(layers, qs):
+        q2 = q.reshape(-1, D)
+        plans.append((layer._decode_plan(q2, r), q2))
+        outs.append(torch.empty_like(q2))
+    for _ in range(warmup):
+        for (p, q2), o in zip(plans, outs):
+            p.run(q2, out=o)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            for (p, q2), o in zip(plans, outs):
+                p.run(q2, out=o)
+        e1.record()
+        torch.cuda.synchronize()
+        total = e0.elapsed_time(e1)
+    else:
+        evs = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for (p, q2), o in zip(plans, outs):
+                p.run(q2, out=o)
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        total = sum(a.elapsed_time(b) for a, b in evs)
+    if dist is not None:
+        dist.barrier()
+    return total, steps * len(plans)
+
+
+def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
+    """Per layer and step: q/k/v of the new token from pinned host memory -> device,
+    append to staging (flush when full), decode attention, output back to the host."""
+    r = H_Q // H_KV
+    n = len(layers)
+    g = torch.Generator(); g.manual_seed(seed)
+    tot = steps + warmup
+    hq_ = torch.randn(tot, n, B, H_Q, 1, D, generator=g).to(torch.bfloat16).pin_memory()
+    hk_ = torch.randn(tot, n, B, H_KV, 1, D, generator=g).to(torch.bfloat16).pin_memory()
+    hv_ = torch.randn(tot, n, B, H_KV, 1, D, generator=g).to(torch.bfloat16).pin_memory()
+    hout = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16).pin_memory()
+    dev = layers[0].k_window.device
+
+    def one_step(s):
+        for li, layer in enumerate(layers):
+            q = hq_[s, li].to(dev, non_blocking=True)
+            k = hk_[s, li].to(dev, non_blocking=True)
+            v = hv_[s, li].to(dev, non_blocking=True)
+            layer.append_staging(k, v)
+            o = layer.decode_attention(q, r)
+            hout[li].copy_(o, non_blocking=True)
+        torch.cuda.synchronize()      # the step's result is on the host
+
+    for s in range(warmup):
+        one_step(s)
+    if dist is not None:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for s in range(warmup, tot):
+        one_step(s)
+    e1.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    h2d = n * (B * H_Q * D + 2 * B * H_KV * D) * 2
+    d2h = n * B * H_Q * D * 2
+    return max(e0.elapsed_time(e1), wall_ms), h2d, d2h
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (oracle port of the reference's PyTorch fallback)
+# ---------------------------------------------------------------------------
+
+def build_cpu_layer(seed=1015, n_prefix=N_PREFIX):
+    from hyquant_b200.synth import gen_numpy, n_vertical
+    from oracle import hq_oracle as orc
+    case = gen_numpy(B, H_Q, H_KV, n_prefix, D, W, RHO, seed, n_qry=256)
+    k, v, q = orc.bf16_round(case.k), orc.bf16_round(case.v), orc.bf16_round(case.q)
+    r = H_Q // H_KV
+    pooled = q.mean(axis=2, keepdims=True).reshape(B, H_KV, r, 1, D).mean(axis=2)
+    vidx = orc.compute_vertical_indices(pooled, k, W, RHO)
+    c = orc.freeze(k, v, q, r, W, RHO, round_fn=orc.bf16_round, vidx_override=vidx)
+    rng = np.random.Generator(np.random.PCG64(seed + 7))
+    for _ in range(STAGING):
+        orc.append_staging(c, orc.bf16_round(rng.standard_normal((B, H_KV, 1, D), dtype=np.float32)),
+                           orc.bf16_round(rng.standard_normal((B, H_KV, 1, D), dtype=np.float32)))
+    return c, orc.bf16_round(case.q_decode)
+
+
+def time_cpu_calls(calls, warmup):
+    """Seconds per decode-attention call of the reference's CPU path (torch-CPU
+    restatement, fp32, all intra-op threads), and the call's algorithmic bytes."""
+    import torch
+    from oracle import hq_oracle_torch as ot
+    torch.set_num_threads(os.cpu_count() or 1)
+    c, qd = build_cpu_layer()
+    r = H_Q // H_KV
+    segs = ot.from_numpy_cache(c)
+    q = torch.from_numpy(qd)
+    for _ in range(warmup):
+        ot.decode_attention_fallback(q, *segs, B, H_KV, r)
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        ot.decode_attention_fallback(q, *segs, B, H_KV, r)
+    dt = (time.perf_counter() - t0) / calls
+    nbytes = algorithmic_bytes(B * H_KV, B * H_Q, c.k_quant_packed.shape[1],
+                               c.k_topk.shape[1] + c.staging_ptr + c.k_window.shape[1])
+    return dt, nbytes, torch.get_num_threads()
+
+
+CONFIG = {"workload": "decode attention, Llama-3.1-8B shapes (B=1, 32q/8kv, d=128), prefix 32768, W=128, rho=5%, "
+                      "staging 64, K4V4 per-token scales, 32 layer caches per token",
+          "l2_policy": "inputs larger than L2 (32 distinct 40 MB caches per step = 1.3 GB)",
+          "parallelism": "one replica of the workload per GPU (KV-head groups are independent; no collective)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    calls = max(1, args.steps)
+    dt, nbytes, cores = time_cpu_calls(calls, max(1, min(args.warmup, 2)))
+    gbs = nbytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": calls, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": CONFIG,
+        "us_per_call": dt * 1e6,
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "one layer's decode-attention call per step (1/32 of a token) of the same 32K workload, "
+                                   "torch-CPU restatement of the reference's PyTorch fallback in fp32, intra-op threads = cores"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import hyquant_b200 as hq
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist_.init_process_group("nccl", device_id=dev)
+        dist = dist_
+    layers, qs = [], []
+    for li in range(LAYERS):
+        layer, qd = build_layer(hq, torch, 1015 + 100 * rank + li, N_PREFIX, dev)
+        layers.append(layer); qs.append(qd)
+    call_bytes = layer_bytes(layers[0], B * H_Q)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist)
+    clocks = sampler.stop()
+    e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, args.warmup, 99 + rank, dist)
+    e2e_bytes = sum(layer_bytes(l, B * H_Q) for l in layers)     # staging has grown by then; close enough per step
+
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    ms_per_step = ms / args.steps
+    us_per_call = ms_per_step * 1e3 / LAYERS
+    gbs_one = call_bytes / (us_per_call * 1e-6) / 1e9
+    value = gbs_one * world
+    e2e_val = e2e_bytes / (e2e_ms / args.steps * 1e-3) / 1e9 * world
+    peak, peak_src = measured_peak()
+
+    sweep = []
+    if rank == 0 and not args.no_sweep:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # 2 x L2
+        for n in (1024, 2048, 4096, 8192, 16384, 32768):
+            ncache = 16
+            ls, qq = zip(*[build_layer(hq, torch, 5000 + n + i, n, dev) for i in range(ncache)])
+            m, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush)
+            us = m * 1e3 / cnt
+            bts = layer_bytes(ls[0], B * H_Q)
+            sweep.append({"prefix": n, "us_per_call": round(us, 3), "gbps": round(bts / us / 1e3, 1),
+                          "bytes": bts, "caches": len(ls), "l2": "flushed before each pass over the caches"})
+            del ls, qq
+        del flush
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            dt, nb, cores = time_cpu_calls(5, 1)
+            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                   "sample": "5 decode-attention calls of one layer of the same 32K workload (torch-CPU restatement of "
+                             "the reference's PyTorch fallback in fp32, intra-op threads = cores)", "ms_per_call": dt * 1e3}
+        line = {
+            "metric": "decode_attn_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": CONFIG,
+            "us_per_call": us_per_call, "us_per_token_32_layers": ms_per_step * 1e3,
+            "bytes_per_call": call_bytes, "frac_of_8TBps": gbs_one / 8000.0,
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps,
+                    "path": "DStageLayerCache.append_staging + decode_attention per layer, q/k/v from pinned host, out to host"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src,
+                         "kernel": "hq::decode_splitk_kernel<1>", "algorithmic_bytes_per_launch": call_bytes},
+            "cpu_baseline": cpu,
+            "sweep": sweep,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch of the decode kernel from an ncu capture of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

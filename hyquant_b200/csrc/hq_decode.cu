@@ -1,0 +1,680 @@
+// Split-K decode attention over the four-segment KV cache, one launch.
+//
+//   segments per (batch, kv-head):  INT4 prefix (64 B K + 64 B V + 2x fp16 scale
+//   per token) | BF16 vertical-line tokens | BF16 staging | BF16 window
+//
+// Roofline: HBM-bound.  Algorithmic bytes per call
+//   BH_KV * (132 * n_quant + 512 * (n_topk + n_staging + n_window)) + 512 * BH_Q.
+//
+// Work decomposition.  Each head's tokens are cut into ~4 KB "units" (32 INT4
+// tokens, or 8 BF16 tokens), so units are balanced in BYTES across segment
+// kinds.  A CTA owns a contiguous range of one head's units; its 8 warps take
+// units round-robin.  Every warp runs its own 3-slot ring: lane 0 issues 1-D
+// bulk copies (TMA engine, mbarrier complete_tx) for the units ahead, the warp
+// consumes the current one straight from shared memory.  No CTA-wide barrier
+// is needed in the main loop.
+//
+// Math.  Scores are computed transposed, S^T = K Q^T, with tokens on the MMA M
+// axis and the kv-group's query heads on the N axis (N = 8 per tile, so GQA
+// ratios 4 and 8 fit one tile and 16 two tiles).  INT4 codes are expanded to
+// fp16 in registers with the 0x6400 magic-number trick (exact for -8..7) and
+// fed to mma.sync.m16n8k16.f16; the per-token K scale multiplies the fp32 score
+// afterwards, the per-token V scale is folded into P before the PV product.
+// BF16 segments use mma.sync bf16.  All segments share one online softmax in
+// base 2 with a lazily updated reference maximum.  O^T = V^T P^T accumulates in
+// fp32 registers.  Warps merge through shared memory, CTAs through a fp32
+// workspace with an atomic ticket: the last CTA of a head does the
+// log-sum-exp merge and writes the output, so there is no second launch.
+#include "hq_common.cuh"
+
+namespace hq {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kSlots = 3;
+constexpr int kSlotBytes = 4096;          // K 2048 | V 2048
+constexpr int kUnitQ = 32;                // INT4 tokens per unit
+constexpr int kUnitB = 8;                 // BF16 tokens per unit
+constexpr float kLazyRescale = 4.0f;      // rescale only if the max grows by > 2^4
+constexpr int kWsHeaderBytes = 256;       // [0] status word
+
+struct DecodeParams {
+  const __nv_bfloat16* q; int64_t q_stride;
+  const uint8_t* k_packed; const uint8_t* v_packed; int64_t kp_stride_bh, vp_stride_bh;
+  const __half* k_scale; const __half* v_scale; int64_t ks_stride_bh, vs_stride_bh;
+  const __nv_bfloat16* kseg[3]; const __nv_bfloat16* vseg[3]; int64_t kseg_stride[3], vseg_stride[3];
+  int nseg[3];                            // tokens in topk / staging / window
+  int n_quant;
+  int uq;                                 // INT4 units
+  int useg[3];                            // BF16 units per segment
+  int units;                              // total units per head
+  int nsplit;
+  int R;                                  // kv_repeat
+  int out_dtype;
+  float sml;                              // sm_scale * log2(e)
+  void* out; int64_t out_stride;
+  float* pm; float* pl; float* pacc;      // partial mode outputs (or null)
+  int* status; int* counters;             // workspace
+  float* ws_m; float* ws_l; float* ws_acc;
+};
+
+struct Unit {
+  const uint8_t* k; const uint8_t* v;
+  int kind;       // 0 = INT4, 1 = BF16
+  int ntok;       // valid tokens
+  int tok0;       // first token within its segment
+};
+
+__device__ __forceinline__ Unit unit_of(const DecodeParams& p, int head, int u) {
+  Unit r;
+  if (u < p.uq) {
+    r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, p.n_quant - r.tok0);
+    r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * 64;
+    r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * 64;
+    return r;
+  }
+  u -= p.uq;
+  int s = 0;
+  if (u >= p.useg[0]) { u -= p.useg[0]; s = 1; if (u >= p.useg[1]) { u -= p.useg[1]; s = 2; } }
+  r.kind = 1; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, p.nseg[s] - r.tok0);
+  r.k = reinterpret_cast<const uint8_t*>(p.kseg[s] + head * p.kseg_stride[s] + (int64_t)r.tok0 * 128);
+  r.v = reinterpret_cast<const uint8_t*>(p.vseg[s] + head * p.vseg_stride[s] + (int64_t)r.tok0 * 128);
+  return r;
+}
+
+// ---- register-level helpers -------------------------------------------------
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Each 16-bit lane of w carries four two's-complement nibbles.  Result k is the
+// fp16x2 (lane_lo nibble k, lane_hi nibble k) with the exact integer values.
+__device__ __forceinline__ void cvt_nibbles_f16(uint32_t w, uint32_t (&h)[4]) {
+  const uint32_t w8 = w >> 8;
+  const __half2 c1032 = u32_as_h2(0x64086408u);
+  const __half2 c16th = u32_as_h2(0x2C002C00u);     // 1/16
+  const __half2 cm72 = u32_as_h2(0xD480D480u);      // -72
+  h[0] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_xor(w, 0x000F000Fu, 0x64086408u)), c1032));
+  h[1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_xor(w, 0x00F000F0u, 0x64806480u)), c16th, cm72));
+  h[2] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_xor(w8, 0x000F000Fu, 0x64086408u)), c1032));
+  h[3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_xor(w8, 0x00F000F0u, 0x64806480u)), c16th, cm72));
+}
+
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16_1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return h2_as_u32(h);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float group_max(float v) {   // over the 8 lanes sharing lane%4
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+  return v;
+}
+__device__ __forceinline__ float group_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 16);
+  return v;
+}
+
+// Online-softmax bookkeeping shared by both unit kinds.  `mx` is the group-wide
+// maximum of the new scores for this thread's two heads of tile nt.
+template <int NT>
+__device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m_ref)[NT][2], float (&l_part)[NT][2],
+                                             float (&O)[NT][8][4]) {
+  bool need = false;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) need |= (mx[nt][j] > m_ref[nt][j] + kLazyRescale);
+  if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float nm = fmaxf(m_ref[nt][j], mx[nt][j]);
+        const float alpha = (nm == -INFINITY) ? 1.0f : ex2f(m_ref[nt][j] - nm);   // m_ref=-inf -> 0
+        m_ref[nt][j] = nm;
+        l_part[nt][j] *= alpha;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) { O[nt][mt][j] *= alpha; O[nt][mt][2 + j] *= alpha; }
+      }
+  }
+}
+
+// ---- the kernel -------------------------------------------------------------
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1)
+decode_splitk_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  // layout: ring [kWarps][kSlots][4096] | fragH [NT*1024 u32 = NT*4 KB]... see offsets below
+  uint8_t* ring = smem;
+  uint32_t* fragH = reinterpret_cast<uint32_t*>(smem + kWarps * kSlots * kSlotBytes);   // [NT][8][2][32]
+  uint32_t* fragB = fragH + NT * 512;                                                    // [NT][8][2][32]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fragB + NT * 512);                        // [kWarps][kSlots]
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int head = blockIdx.x / p.nsplit;
+  const int split = blockIdx.x - head * p.nsplit;
+  const int u_begin = (int)(((int64_t)split * p.units) / p.nsplit);
+  const int u_end = (int)(((int64_t)(split + 1) * p.units) / p.nsplit);
+  const int n_my = (u_end - u_begin - warp + kWarps - 1) / kWarps;   // units u_begin + warp + 8 i
+  uint8_t* my_ring = ring + warp * (kSlots * kSlotBytes);
+  uint64_t* my_bar = bars + warp * kSlots;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) mbar_init(&my_bar[s], 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+
+  auto issue = [&](int i) {   // lane 0 only
+    const Unit un = unit_of(p, head, u_begin + warp + kWarps * i);
+    const int slot = i % kSlots;
+    const uint32_t bytes = un.kind == 0 ? (uint32_t)un.ntok * 64u : (uint32_t)un.ntok * 256u;
+    uint8_t* dst = my_ring + slot * kSlotBytes;
+    mbar_expect_tx(&my_bar[slot], 2 * bytes);
+    bulk_g2s(dst, un.k, bytes, &my_bar[slot]);
+    bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
+  };
+  if (lane == 0) {
+    for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
+  }
+
+  // ---- query fragments: B operands of S^T = K Q^T, permuted along the channel
+  // axis to match the order in which channels fall out of the K loads.
+  {
+    const int heads = NT * 8;
+    for (int e = tid; e < NT * 512; e += kThreads) {
+      const int l = e & 31, r = (e >> 5) & 1, c = (e >> 6) & 7, nt = e >> 9;
+      const int gg = l >> 2, tt = l & 3, i = c >> 1, odd = c & 1;
+      const int hd = nt * 8 + gg;
+      // INT4 path: word i of thread tt covers channels 32 tt + 8 i + m (nibble m);
+      // register r of MMA chunk c pairs nibbles (2*odd + r, 2*odd + r + 4).
+      const int chA = 32 * tt + 8 * i + 2 * odd + r, chB = chA + 4;
+      // BF16 path: 16-byte chunk j = 4 i + tt covers channels 8 j .. 8 j + 7.
+      const int cbA = 8 * (4 * i + tt) + 4 * odd + 2 * r, cbB = cbA + 1;
+      float qa = 0.f, qb = 0.f, ra = 0.f, rb = 0.f;
+      if (hd < p.R) {
+        const __nv_bfloat16* qrow = p.q + (int64_t)(head * p.R + hd) * p.q_stride;
+        qa = __bfloat162float(qrow[chA]); qb = __bfloat162float(qrow[chB]);
+        ra = __bfloat162float(qrow[cbA]); rb = __bfloat162float(qrow[cbB]);
+      }
+      qa = fminf(fmaxf(qa, -65504.f), 65504.f); qb = fminf(fmaxf(qb, -65504.f), 65504.f);
+      fragH[e] = pack_f16x2(qa, qb);
+      fragB[e] = pack_bf16x2(ra, rb);
+      (void)heads;
+    }
+  }
+  __syncthreads();
+
+  float O[NT][8][4];
+  float m_ref[NT][2], l_part[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) { m_ref[nt][j] = -INFINITY; l_part[nt][j] = 0.f; }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) O[nt][mt][x] = 0.f;
+  }
+
+  bool failed = false;
+  int i = 0;
+
+  // ======================= INT4 units =======================================
+  {
+    uint32_t Qh[NT][8][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) Qh[nt][c][r] = fragH[((nt * 8 + c) * 2 + r) * 32 + lane];
+
+    // per-lane packed (k_scale, v_scale) of token `lane` of the upcoming unit
+    auto load_scales = [&](int ii) -> uint32_t {
+      if (ii >= n_my) return 0u;
+      const int u = u_begin + warp + kWarps * ii;
+      if (u >= p.uq) return 0u;
+      const int tok = u * kUnitQ + lane;
+      if (tok >= p.n_quant) return 0u;
+      const uint16_t ks = __half_as_ushort(p.k_scale[head * p.ks_stride_bh + tok]);
+      const uint16_t vs = __half_as_ushort(p.v_scale[head * p.vs_stride_bh + tok]);
+      return (uint32_t)ks | ((uint32_t)vs << 16);
+    };
+    uint32_t sc_cur = load_scales(0);
+
+    for (; i < n_my; ++i) {
+      const int u = u_begin + warp + kWarps * i;
+      if (u >= p.uq) break;
+      const int ntok = min(kUnitQ, p.n_quant - u * kUnitQ);
+      const uint32_t sc_next = load_scales(i + 1);
+      const int slot = i % kSlots;
+      if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
+      const uint8_t* Ks = my_ring + slot * kSlotBytes;
+      const uint8_t* Vs = Ks + 2048;
+
+      float s[2][NT][4];
+      float vsc[2][2];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int tokA = 16 * ch + g, tokB = tokA + 8;
+        const uint4 ka = *reinterpret_cast<const uint4*>(Ks + tokA * 64 + t * 16);
+        const uint4 kb = *reinterpret_cast<const uint4*>(Ks + tokB * 64 + t * 16);
+        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w};
+        const uint32_t wb[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int x = 0; x < 4; ++x) s[ch][nt][x] = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          uint32_t ha[4], hb[4];
+          cvt_nibbles_f16(wa[w], ha);
+          cvt_nibbles_f16(wb[w], hb);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
+            mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
+          }
+        }
+        const uint32_t scA = __shfl_sync(0xffffffffu, sc_cur, tokA);
+        const uint32_t scB = __shfl_sync(0xffffffffu, sc_cur, tokB);
+        const float ksA = __half2float(__ushort_as_half((uint16_t)(scA & 0xFFFFu))) * p.sml;
+        const float ksB = __half2float(__ushort_as_half((uint16_t)(scB & 0xFFFFu))) * p.sml;
+        vsc[ch][0] = __half2float(__ushort_as_half((uint16_t)(scA >> 16)));
+        vsc[ch][1] = __half2float(__ushort_as_half((uint16_t)(scB >> 16)));
+        const bool okA = tokA < ntok, okB = tokB < ntok;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          s[ch][nt][0] = okA ? s[ch][nt][0] * ksA : -INFINITY;
+          s[ch][nt][1] = okA ? s[ch][nt][1] * ksA : -INFINITY;
+          s[ch][nt][2] = okB ? s[ch][nt][2] * ksB : -INFINITY;
+          s[ch][nt][3] = okB ? s[ch][nt][3] * ksB : -INFINITY;
+        }
+      }
+      // one online-softmax step for the 32 tokens
+      float mx[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          mx[nt][j] = group_max(fmaxf(fmaxf(s[0][nt][j], s[0][nt][2 + j]), fmaxf(s[1][nt][j], s[1][nt][2 + j])));
+      lazy_rescale<NT>(mx, m_ref, l_part, O);
+
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t pb[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float pr[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float mu = m_ref[nt][x & 1];
+            pr[x] = ex2f(s[ch][nt][x] - (mu == -INFINITY ? 0.f : mu));
+          }
+          l_part[nt][0] += pr[0] + pr[2];
+          l_part[nt][1] += pr[1] + pr[3];
+          const uint32_t pa = pack_f16x2(pr[0] * vsc[ch][0], pr[1] * vsc[ch][0]);   // token g
+          const uint32_t pq = pack_f16x2(pr[2] * vsc[ch][1], pr[3] * vsc[ch][1]);   // token g + 8
+          pb[nt][0] = movmatrix_trans(pa);    // (tokens 2t, 2t+1 ; head g)
+          pb[nt][1] = movmatrix_trans(pq);    // (tokens 2t+8, 2t+9 ; head g)
+        }
+        const uint8_t* vrow = Vs + (16 * ch + 2 * t) * 64 + 8 * g;
+        const uint2 vA = *reinterpret_cast<const uint2*>(vrow);
+        const uint2 vB = *reinterpret_cast<const uint2*>(vrow + 64);
+        const uint2 vC = *reinterpret_cast<const uint2*>(vrow + 8 * 64);
+        const uint2 vD = *reinterpret_cast<const uint2*>(vrow + 9 * 64);
+        const uint32_t wA[2] = {vA.x, vA.y}, wB[2] = {vB.x, vB.y}, wC[2] = {vC.x, vC.y}, wD[2] = {vD.x, vD.y};
+#pragma unroll
+        for (int w = 0; w < 2; ++w)
+#pragma unroll
+          for (int hl = 0; hl < 2; ++hl) {
+            const uint32_t sel = hl ? 0x7632u : 0x5410u;
+            uint32_t hab[4], hcd[4];
+            cvt_nibbles_f16(prmt(wA[w], wB[w], sel), hab);
+            cvt_nibbles_f16(prmt(wC[w], wD[w], sel), hcd);
+            const int pidx = 2 * w + hl;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
+              mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+            }
+          }
+      }
+      sc_cur = sc_next;
+      __syncwarp();
+      if (lane == 0 && i + kSlots < n_my) { fence_proxy_async_smem(); issue(i + kSlots); }
+    }
+  }
+
+  // ======================= BF16 units =======================================
+  if (!failed && i < n_my) {
+    uint32_t Qb[NT][8][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) Qb[nt][c][r] = fragB[((nt * 8 + c) * 2 + r) * 32 + lane];
+
+    for (; i < n_my; ++i) {
+      const Unit un = unit_of(p, head, u_begin + warp + kWarps * i);
+      const int slot = i % kSlots;
+      if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
+      uint8_t* Ks = my_ring + slot * kSlotBytes;
+      uint8_t* Vs = Ks + 2048;
+      if (un.ntok < kUnitB) {   // stale bytes past the copied rows must not reach the MMA as NaN/Inf
+        const int n16 = (kUnitB - un.ntok) * 16;
+        for (int x = lane; x < n16; x += 32) {
+          reinterpret_cast<uint4*>(Ks + un.ntok * 256)[x] = make_uint4(0, 0, 0, 0);
+          reinterpret_cast<uint4*>(Vs + un.ntok * 256)[x] = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      float s[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) s[nt][x] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint4 kk = *reinterpret_cast<const uint4*>(Ks + g * 256 + (4 * w + t) * 16);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16_16816(s[nt], kk.x, 0u, kk.y, 0u, Qb[nt][2 * w][0], Qb[nt][2 * w][1]);
+          mma_bf16_16816(s[nt], kk.z, 0u, kk.w, 0u, Qb[nt][2 * w + 1][0], Qb[nt][2 * w + 1][1]);
+        }
+      }
+      const bool ok = g < un.ntok;
+      float mx[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          s[nt][j] = ok ? s[nt][j] * p.sml : -INFINITY;
+          mx[nt][j] = group_max(s[nt][j]);
+        }
+      lazy_rescale<NT>(mx, m_ref, l_part, O);
+      uint32_t pb[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float m0 = m_ref[nt][0] == -INFINITY ? 0.f : m_ref[nt][0];
+        const float m1 = m_ref[nt][1] == -INFINITY ? 0.f : m_ref[nt][1];
+        const float p0 = ex2f(s[nt][0] - m0), p1 = ex2f(s[nt][1] - m1);
+        l_part[nt][0] += p0;
+        l_part[nt][1] += p1;
+        pb[nt] = movmatrix_trans(pack_bf16x2(p0, p1));     // (tokens 2t, 2t+1 ; head g)
+      }
+      const uint8_t* va = Vs + (2 * t) * 256 + 32 * g;
+      const uint4 a0 = *reinterpret_cast<const uint4*>(va);
+      const uint4 a1 = *reinterpret_cast<const uint4*>(va + 16);
+      const uint4 b0 = *reinterpret_cast<const uint4*>(va + 256);
+      const uint4 b1 = *reinterpret_cast<const uint4*>(va + 256 + 16);
+      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        const uint32_t r0 = prmt(wa[mt], wb[mt], 0x5410u);   // channel 16g+2mt   of tokens (2t, 2t+1)
+        const uint32_t r1 = prmt(wa[mt], wb[mt], 0x7632u);   // channel 16g+2mt+1
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16_1688(O[nt][mt], r0, r1, pb[nt]);
+      }
+      __syncwarp();
+      if (lane == 0 && i + kSlots < n_my) { fence_proxy_async_smem(); issue(i + kSlots); }
+    }
+  }
+  if (failed && lane == 0) atomicOr(p.status, 1);
+
+  // ======================= merge the warps ===================================
+  __syncthreads();   // every ring slot is drained (each issued unit was waited for) unless `failed`
+  float* mrg_m = reinterpret_cast<float*>(smem);                 // [kWarps][NT*8]
+  float* mrg_l = mrg_m + kWarps * NT * 8;                        // [kWarps][NT*8]
+  float* mrg_o = mrg_l + kWarps * NT * 8;                        // [kWarps][NT*8][128]
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int hd = nt * 8 + 2 * t + j;
+      const float lsum = group_sum(l_part[nt][j]);
+      if (g == 0) { mrg_m[warp * NT * 8 + hd] = m_ref[nt][j]; mrg_l[warp * NT * 8 + hd] = lsum; }
+      float* orow = mrg_o + ((size_t)(warp * NT * 8 + hd)) * 128 + 16 * g;
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt)
+        *reinterpret_cast<float2*>(orow + 2 * mt) = make_float2(O[nt][mt][j], O[nt][mt][2 + j]);
+    }
+  __syncthreads();
+
+  const int d = tid & 127;
+  const bool single = (p.nsplit == 1);
+  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = mrg_m[w * NT * 8 + hd];
+      const float wt = (mw == -INFINITY) ? 0.f : ex2f(mw - M);
+      acc += wt * mrg_o[((size_t)(w * NT * 8 + hd)) * 128 + d];
+      l += wt * mrg_l[w * NT * 8 + hd];
+    }
+    const int64_t qrow = (int64_t)head * p.R + hd;
+    if (single) {
+      if (p.pacc) {
+        p.pacc[qrow * 128 + d] = acc;
+        if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
+      } else {
+        store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
+      }
+    } else {
+      const int64_t prow = ((int64_t)head * p.nsplit + split) * p.R + hd;
+      p.ws_acc[prow * 128 + d] = acc;
+      if (d == 0) { p.ws_m[prow] = M; p.ws_l[prow] = l; }
+    }
+  }
+  if (single) return;
+
+  // ======================= merge the splits (last CTA of the head) ===========
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&p.counters[head], 1);
+    s_last = (ticket == p.nsplit - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* sm_m = reinterpret_cast<float*>(smem);            // [nsplit * R]
+  float* sm_l = sm_m + p.nsplit * p.R;
+  const int64_t base = (int64_t)head * p.nsplit * p.R;
+  for (int x = tid; x < p.nsplit * p.R; x += kThreads) {
+    sm_m[x] = __ldcg(p.ws_m + base + x);
+    sm_l[x] = __ldcg(p.ws_l + base + x);
+  }
+  __syncthreads();
+  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, sm_m[s2 * p.R + hd]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll 4
+    for (int s2 = 0; s2 < p.nsplit; ++s2) {
+      const float ms = sm_m[s2 * p.R + hd];
+      const float wt = (ms == -INFINITY) ? 0.f : ex2f(ms - M);
+      acc += wt * __ldcg(p.ws_acc + (base + (int64_t)s2 * p.R + hd) * 128 + d);
+      l += wt * sm_l[s2 * p.R + hd];
+    }
+    const int64_t qrow = (int64_t)head * p.R + hd;
+    if (p.pacc) {
+      p.pacc[qrow * 128 + d] = acc;
+      if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
+    } else {
+      store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
+    }
+  }
+  if (tid == 0) p.counters[head] = 0;   // ready for the next launch on this workspace
+}
+
+// ---- host side ---------------------------------------------------------------
+
+static size_t decode_smem_bytes(int NT) {
+  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)kWarps * kSlots * 8;
+}
+
+static int max_ctas() { return 4 * sm_count(); }
+
+static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace hq
+
+extern "C" int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes) {
+  using namespace hq;
+  HQ_REQUIRE(bytes && BH_KV > 0 && kv_repeat > 0 && kv_repeat <= 16, HQ_ERR_INVALID,
+             "hq_decode_workspace_bytes: BH_KV>0 and 1<=kv_repeat<=16 required");
+  const int64_t ctas = (int64_t)BH_KV + max_ctas();
+  *bytes = kWsHeaderBytes + align_up((int64_t)BH_KV * 4, 256) + ctas * kv_repeat * (128 + 2) * 4 + 256;
+  return HQ_OK;
+}
+
+extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(a != nullptr, HQ_ERR_INVALID, "hq_decode_splitk: null args");
+  HQ_REQUIRE(a->struct_bytes == (int32_t)sizeof(hq_decode_args), HQ_ERR_INVALID,
+             "hq_decode_splitk: struct_bytes %d != %d", a->struct_bytes, (int)sizeof(hq_decode_args));
+  HQ_REQUIRE(a->head_dim == 128, HQ_ERR_UNSUPPORTED, "hq_decode_splitk: head_dim %d (only 128 is built)", a->head_dim);
+  HQ_REQUIRE(a->kv_repeat >= 1 && a->kv_repeat <= 16, HQ_ERR_UNSUPPORTED,
+             "hq_decode_splitk: kv_repeat %d outside 1..16", a->kv_repeat);
+  HQ_REQUIRE(a->BH_KV >= 0 && a->n_quant >= 0 && a->n_topk >= 0 && a->n_staging >= 0 && a->n_window >= 0,
+             HQ_ERR_INVALID, "hq_decode_splitk: negative size");
+  if (a->BH_KV == 0) return HQ_OK;
+  HQ_REQUIRE(a->q != nullptr, HQ_ERR_INVALID, "hq_decode_splitk: q is null");
+  const bool partial = a->partial_acc != nullptr;
+  HQ_REQUIRE(partial ? (a->partial_m && a->partial_l) : (a->out != nullptr), HQ_ERR_INVALID,
+             "hq_decode_splitk: output pointer(s) missing");
+  HQ_REQUIRE(a->out_dtype == HQ_BF16 || a->out_dtype == HQ_F16 || a->out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,
+             "hq_decode_splitk: out_dtype %d", a->out_dtype);
+
+  DecodeParams p{};
+  p.q = (const __nv_bfloat16*)a->q; p.q_stride = a->q_stride;
+  p.n_quant = a->n_quant;
+  if (a->n_quant > 0) {
+    HQ_REQUIRE(a->k_packed && a->v_packed && a->k_scale && a->v_scale, HQ_ERR_INVALID, "hq_decode_splitk: null INT4 segment");
+    HQ_REQUIRE(aligned16(a->k_packed) && aligned16(a->v_packed) && a->kp_stride_bh % 16 == 0 && a->vp_stride_bh % 16 == 0,
+               HQ_ERR_ALIGNMENT, "hq_decode_splitk: packed K/V must be 16-byte aligned with 16-byte head strides");
+  }
+  p.k_packed = (const uint8_t*)a->k_packed; p.v_packed = (const uint8_t*)a->v_packed;
+  p.kp_stride_bh = a->kp_stride_bh; p.vp_stride_bh = a->vp_stride_bh;
+  p.k_scale = (const __half*)a->k_scale; p.v_scale = (const __half*)a->v_scale;
+  p.ks_stride_bh = a->ks_stride_bh; p.vs_stride_bh = a->vs_stride_bh;
+  const void* ks[3] = {a->k_topk, a->k_staging, a->k_window};
+  const void* vs[3] = {a->v_topk, a->v_staging, a->v_window};
+  const int64_t kst[3] = {a->kt_stride_bh, a->kg_stride_bh, a->kw_stride_bh};
+  const int64_t vst[3] = {a->vt_stride_bh, a->vg_stride_bh, a->vw_stride_bh};
+  const int ns[3] = {a->n_topk, a->n_staging, a->n_window};
+  p.uq = (a->n_quant + kUnitQ - 1) / kUnitQ;
+  p.units = p.uq;
+  for (int s = 0; s < 3; ++s) {
+    p.nseg[s] = ns[s];
+    p.useg[s] = (ns[s] + kUnitB - 1) / kUnitB;
+    p.units += p.useg[s];
+    p.kseg[s] = (const __nv_bfloat16*)ks[s]; p.vseg[s] = (const __nv_bfloat16*)vs[s];
+    p.kseg_stride[s] = kst[s]; p.vseg_stride[s] = vst[s];
+    if (ns[s] > 0) {
+      HQ_REQUIRE(ks[s] && vs[s], HQ_ERR_INVALID, "hq_decode_splitk: null BF16 segment %d", s);
+      HQ_REQUIRE(aligned16(ks[s]) && aligned16(vs[s]) && kst[s] % 8 == 0 && vst[s] % 8 == 0, HQ_ERR_ALIGNMENT,
+                 "hq_decode_splitk: BF16 segment %d must be 16-byte aligned with head strides multiple of 8", s);
+    }
+  }
+  p.R = a->kv_repeat;
+  p.out_dtype = a->out_dtype;
+  p.sml = a->sm_scale * 1.44269504f;
+  p.out = a->out; p.out_stride = a->out_stride;
+  p.pm = a->partial_m; p.pl = a->partial_l; p.pacc = a->partial_acc;
+
+  // splits: one wave of CTAs (2 per SM), at least ~2 units per warp
+  const int sms = sm_count();
+  int nsplit = a->num_splits;
+  if (nsplit <= 0) {
+    const int by_grid = (2 * sms) / a->BH_KV;
+    const int by_work = (p.units + kWarps - 1) / kWarps;
+    nsplit = by_grid < by_work ? by_grid : by_work;
+  }
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > p.units && p.units > 0) nsplit = p.units;
+  if ((int64_t)nsplit * a->BH_KV > (int64_t)a->BH_KV + max_ctas()) nsplit = (int)(((int64_t)a->BH_KV + max_ctas()) / a->BH_KV);
+  if (nsplit < 1) nsplit = 1;
+  p.nsplit = nsplit;
+
+  int64_t need = 0;
+  hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
+  HQ_REQUIRE(a->workspace && a->workspace_bytes >= need, HQ_ERR_WORKSPACE,
+             "hq_decode_splitk: workspace of %lld bytes needed, %lld given", (long long)need, (long long)a->workspace_bytes);
+  HQ_REQUIRE(((uintptr_t)a->workspace & 255) == 0, HQ_ERR_ALIGNMENT, "hq_decode_splitk: workspace must be 256-byte aligned");
+  uint8_t* ws = (uint8_t*)a->workspace;
+  p.status = (int*)ws;
+  p.counters = (int*)(ws + kWsHeaderBytes);
+  float* f = (float*)(ws + kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256));
+  const int64_t rows = (int64_t)a->BH_KV * nsplit * a->kv_repeat;
+  p.ws_m = f; p.ws_l = f + rows; p.ws_acc = f + 2 * rows;
+  // keep ws_acc 16-byte aligned
+  p.ws_acc = (float*)(((uintptr_t)p.ws_acc + 15) & ~(uintptr_t)15);
+
+  const int NT = a->kv_repeat <= 8 ? 1 : 2;
+  const size_t smem = decode_smem_bytes(NT);
+  // the split-merge staging (2 * nsplit * R floats) reuses the ring
+  HQ_REQUIRE((size_t)2 * nsplit * a->kv_repeat * 4 <= (size_t)kWarps * kSlots * kSlotBytes, HQ_ERR_UNSUPPORTED,
+             "hq_decode_splitk: too many splits (%d)", nsplit);
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((unsigned)(a->BH_KV * nsplit)), block(kThreads);
+  if (NT == 1) {
+    static thread_local int attr_dev1 = -1;
+    int dev = 0; HQ_CUDA(cudaGetDevice(&dev));
+    if (attr_dev1 != dev) {
+      HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_dev1 = dev;
+    }
+    decode_splitk_kernel<1><<<grid, block, smem, st>>>(p);
+  } else {
+    static thread_local int attr_dev2 = -1;
+    int dev = 0; HQ_CUDA(cudaGetDevice(&dev));
+    if (attr_dev2 != dev) {
+      HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_dev2 = dev;
+    }
+    decode_splitk_kernel<2><<<grid, block, smem, st>>>(p);
+  }
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}

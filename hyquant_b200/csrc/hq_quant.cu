@@ -1,0 +1,73 @@
+// Per-token symmetric INT4 quantise + nibble pack (flush of the staging buffer
+// and the quantisation step of the prefill->decode reorganisation).
+//
+// HBM-bound: reads 256 B (bf16) per token, writes 64 B codes + 2 B scale.  One
+// warp owns one token row at a time; lane l holds channels 4l..4l+3, so the
+// warp's loads are one 256-byte line and its stores one 64-byte line.
+#include "hq_quant.cuh"
+
+namespace hq {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_pack_int4_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_stride_n, int BH, int n,
+                       uint8_t* __restrict__ packed, int64_t packed_stride_bh,
+                       __half* __restrict__ scale, int64_t scale_stride_bh,
+                       int64_t dst_off, int scale_mode) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t rows = (int64_t)BH * n;
+  for (int64_t r = warp0; r < rows; r += nwarps) {
+    const int bh = (int)(r / n);
+    const int tok = (int)(r - (int64_t)bh * n);
+    const T* src = x + bh * x_stride_bh + tok * x_stride_n + lane * 4;
+    float v[4];
+    load4(src, v);
+    uint16_t code;
+    __half s = quant_row_int4(v, scale_mode, code);
+    uint8_t* prow = packed + bh * packed_stride_bh + (dst_off + tok) * 64;
+    reinterpret_cast<uint16_t*>(prow)[lane] = code;
+    if (lane == 0) scale[bh * scale_stride_bh + dst_off + tok] = s;
+  }
+}
+
+}  // namespace hq
+
+extern "C" int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
+                                  int BH, int n, void* packed, int64_t packed_stride_bh,
+                                  void* scale, int64_t scale_stride_bh,
+                                  int64_t dst_token_offset, int scale_mode, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(BH >= 0 && n >= 0 && dst_token_offset >= 0, HQ_ERR_INVALID, "hq_quant_pack_int4: negative size");
+  if (BH == 0 || n == 0) return HQ_OK;
+  HQ_REQUIRE(x && packed && scale, HQ_ERR_INVALID, "hq_quant_pack_int4: null pointer");
+  HQ_REQUIRE(scale_mode == 0 || scale_mode == 1, HQ_ERR_INVALID, "hq_quant_pack_int4: scale_mode must be 0 or 1");
+  const int esz = in_dtype == HQ_F32 ? 4 : 2;
+  HQ_REQUIRE(((uintptr_t)x % (4 * esz)) == 0 && (x_stride_bh % 4) == 0 && (x_stride_n % 4) == 0, HQ_ERR_ALIGNMENT,
+             "hq_quant_pack_int4: x rows must be aligned to 4 elements");
+  HQ_REQUIRE(((uintptr_t)packed % 2) == 0 && (packed_stride_bh % 2) == 0, HQ_ERR_ALIGNMENT,
+             "hq_quant_pack_int4: packed rows must be 2-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows = (int64_t)BH * n;
+  const int warps_per_block = 8;
+  int64_t blocks = (rows + warps_per_block - 1) / warps_per_block;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  dim3 grid((unsigned)blocks), block(256);
+  uint8_t* p = (uint8_t*)packed;
+  __half* s = (__half*)scale;
+  if (in_dtype == HQ_BF16)
+    quant_pack_int4_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                                  packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
+  else if (in_dtype == HQ_F16)
+    quant_pack_int4_kernel<__half><<<grid, block, 0, st>>>((const __half*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                           packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
+  else if (in_dtype == HQ_F32)
+    quant_pack_int4_kernel<float><<<grid, block, 0, st>>>((const float*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                          packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
+  else
+    HQ_REQUIRE(false, HQ_ERR_UNSUPPORTED, "hq_quant_pack_int4: unknown dtype %d", in_dtype);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}

@@ -1,0 +1,356 @@
+"""Four-segment KV cache for decode — host-side mirror of the reference module
+``src/ops/d_stage_kv_cache.py`` (``DStageLayerCache`` / ``DStageKVCache``: same
+constructor, methods, attributes and Hugging Face ``Cache`` surface).
+
+Layout in HBM, all at KV-head granularity (BH = B * H_KV):
+  k/v_quant_packed  int8 [BH, cap, 64]   INT4 prefix, 2 codes per byte, pre-allocated capacity
+  k/v_scale         fp16 [BH, cap]       per-token scales
+  k/v_topk          bf16 [BH, T, 128]    frozen vertical-line tokens (descending score)
+  k/v_window        bf16 [BH, W, 128]    last-W prefill tokens
+  _staging_buf_k/v  bf16 [BH, 128, 128]  decode tokens waiting to be quantised
+
+Differences from the reference by design: the prefix lives in capacity buffers
+that the staging flush appends to in place (no O(N) ``torch.cat`` per flush), the
+prefill->decode transition runs as three kernels (scores, top-k, fused
+gather/compact/quantise) and decode attention is one kernel launch.  The public
+attributes (``k_quant_packed`` ...) are views of the live part of those buffers.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any, Callable, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import HyQuantError
+from .decode_d_stage import GROUP_SIZE, SCALE_MODE, DecodePlan, quantize_per_token_into
+from .patch._common import topk_indices, vertical_scores, vertical_topk_count
+
+try:
+    from transformers.cache_utils import Cache as _HF_Cache
+except Exception:  # transformers not available
+    _HF_Cache = object
+
+
+def _check_decode_kernel_env():
+    choice = os.environ.get("HYBRID_ATTN_DECODE_KERNEL", "sm100").lower()
+    if choice not in ("sm100", "splitk_mma"):
+        raise HyQuantError(
+            f"HYBRID_ATTN_DECODE_KERNEL={choice!r}: this build has one decode kernel (sm100) and no "
+            "PyTorch/Triton fallback")
+
+
+class DStageLayerCache:
+    """Per-layer KV cache with the prefill -> decode phase transition."""
+
+    def __init__(self, layer_idx: int, k_bits: int = 4, v_bits: int = 4, window_size: int = 256,
+                 top_ratio: float = 0.05, use_vert: bool = True):
+        self.layer_idx = layer_idx
+        self.k_bits = k_bits
+        self.v_bits = v_bits
+        self.window_size = window_size
+        self.top_ratio = top_ratio
+        self.use_vert = use_vert
+        self.phase: str = "prefill"
+        self._seq_len: int = 0
+        self._keys: Optional[torch.Tensor] = None        # [B, H_KV, N, D]
+        self._values: Optional[torch.Tensor] = None
+        self._query_tail: Optional[torch.Tensor] = None   # [B, H_Q, W, D]
+        self._kq: Optional[torch.Tensor] = None           # capacity buffers
+        self._vq: Optional[torch.Tensor] = None
+        self._ks: Optional[torch.Tensor] = None
+        self._vs: Optional[torch.Tensor] = None
+        self._n_quant: int = 0
+        self.k_topk: Optional[torch.Tensor] = None
+        self.v_topk: Optional[torch.Tensor] = None
+        self._staging_buf_k: Optional[torch.Tensor] = None
+        self._staging_buf_v: Optional[torch.Tensor] = None
+        self._staging_ptr: int = 0
+        self.k_window: Optional[torch.Tensor] = None
+        self.v_window: Optional[torch.Tensor] = None
+        self._B = self._H_KV = self._D = 0
+        self._plan: Optional[DecodePlan] = None
+        self.vertical_indices: Optional[torch.Tensor] = None   # [B, H_KV, T] chosen at freeze
+
+    # ---- views of the live prefix (reference attribute names) -----------------
+    @property
+    def k_quant_packed(self):
+        return None if self._kq is None else self._kq[:, :self._n_quant]
+
+    @property
+    def v_quant_packed(self):
+        return None if self._vq is None else self._vq[:, :self._n_quant]
+
+    @property
+    def k_scale(self):
+        return None if self._ks is None else self._ks[:, :self._n_quant]
+
+    @property
+    def v_scale(self):
+        return None if self._vs is None else self._vs[:, :self._n_quant]
+
+    # ---- prefill --------------------------------------------------------------
+    def update_prefill(self, key_states: torch.Tensor, value_states: torch.Tensor):
+        """Accumulate BF16 K/V during prefill (reference :82-95)."""
+        if self._keys is None:
+            self._keys, self._values = key_states, value_states
+        else:
+            self._keys = torch.cat([self._keys, key_states], dim=2)
+            self._values = torch.cat([self._values, value_states], dim=2)
+        self._seq_len = self._keys.shape[2]
+        return self._keys, self._values
+
+    def save_query_tail(self, query_states: torch.Tensor):
+        """Keep the last W queries of the prefill for freeze (reference :97-100)."""
+        W = min(self.window_size, query_states.shape[2])
+        self._query_tail = query_states[:, :, -W:, :].detach()
+
+    # ---- prefill -> decode ----------------------------------------------------
+    def _alloc_prefix(self, BH: int, n: int, device):
+        cap = n + max(8 * GROUP_SIZE, n // 8)
+        cap = (cap + GROUP_SIZE - 1) // GROUP_SIZE * GROUP_SIZE
+        self._kq = torch.empty(BH, cap, self._D // 2, dtype=torch.int8, device=device)
+        self._vq = torch.empty(BH, cap, self._D // 2, dtype=torch.int8, device=device)
+        self._ks = torch.empty(BH, cap, dtype=torch.float16, device=device)
+        self._vs = torch.empty(BH, cap, dtype=torch.float16, device=device)
+
+    def _grow_prefix(self, need: int):
+        BH, cap = self._kq.shape[0], self._kq.shape[1]
+        if need <= cap:
+            return
+        old = (self._kq, self._vq, self._ks, self._vs)
+        self._alloc_prefix(BH, max(need, cap + cap // 2), self._kq.device)
+        n = self._n_quant
+        self._kq[:, :n].copy_(old[0][:, :n]); self._vq[:, :n].copy_(old[1][:, :n])
+        self._ks[:, :n].copy_(old[2][:, :n]); self._vs[:, :n].copy_(old[3][:, :n])
+
+    def freeze(self, kv_repeat: int = 1, *, vertical_indices: Optional[torch.Tensor] = None):
+        """Quantise the prefix, keep window + vertical-line tokens in BF16, release
+        the BF16 K/V (reference :106-189, including its candidate range: the
+        selection helper subtracts the window from the already-sliced prefix, so
+        vertical lines are chosen among positions [0, N - 2W)).
+
+        ``vertical_indices`` (int64 [B, H_KV, T], distinct prefix positions per
+        head, an extension of the reference signature) skips the selection and
+        freezes exactly those rows in BF16, in the given order."""
+        assert self.phase == "prefill" and self._keys is not None
+        if self.k_bits != 4 or self.v_bits != 4:
+            raise HyQuantError(f"K{self.k_bits}/V{self.v_bits} is not built (K4/V4 only)")
+        _lib.require_cuda(self._keys, "keys")
+        B, H_KV, N, D = self._keys.shape
+        if D != 128:
+            raise HyQuantError(f"head_dim {D} is not built (128 only)")
+        self._B, self._H_KV, self._D = B, H_KV, D
+        BH = B * H_KV
+        W = min(self.window_size, N)
+        prefix_len = N - W
+        device = self._keys.device
+        dtype = self._keys.dtype
+        keys = self._keys if self._keys.dtype == torch.bfloat16 else self._keys.to(torch.bfloat16)
+        values = self._values if self._values.dtype == torch.bfloat16 else self._values.to(torch.bfloat16)
+        keys = keys.reshape(BH, N, D) if keys.is_contiguous() else keys.contiguous().reshape(BH, N, D)
+        values = values.reshape(BH, N, D) if values.is_contiguous() else values.contiguous().reshape(BH, N, D)
+
+        T = 0
+        vidx = vasc = None
+        if vertical_indices is not None and prefix_len > 0 and vertical_indices.shape[-1] > 0:
+            vidx = vertical_indices.to(device=device, dtype=torch.int64).reshape(B, H_KV, -1).contiguous()
+            T = int(vidx.shape[-1])
+            vasc = vidx.sort(dim=-1).values.to(torch.int32).contiguous()
+        elif vertical_indices is None and prefix_len > 0 and self.use_vert and self._query_tail is not None \
+                and kv_repeat >= 1:
+            cand = max(0, prefix_len - self.window_size)
+            if cand > 0:
+                # group mean of the saved queries, in the input dtype like the reference (:131-133)
+                q_kv = self._query_tail.reshape(B, H_KV, kv_repeat, -1, D).mean(dim=2)
+                scores = vertical_scores(q_kv.to(keys.dtype), keys.reshape(B, H_KV, N, D)[:, :, :prefix_len],
+                                         self.window_size, 1)
+                T = vertical_topk_count(cand, self.top_ratio)
+                vidx, vasc = topk_indices(scores, T, want_ascending=True)       # [B, H_KV, T]
+        self.vertical_indices = vidx
+        n_quant = prefix_len - T
+        self._alloc_prefix(BH, n_quant, device)
+        self.k_topk = torch.empty(BH, T, D, dtype=torch.bfloat16, device=device)
+        self.v_topk = torch.empty(BH, T, D, dtype=torch.bfloat16, device=device)
+        self.k_window = torch.empty(BH, W, D, dtype=torch.bfloat16, device=device)
+        self.v_window = torch.empty(BH, W, D, dtype=torch.bfloat16, device=device)
+        rc = _lib.lib().hq_cache_reorganize(
+            keys.data_ptr(), values.data_ptr(), keys.stride(0), BH, N, W, T,
+            vidx.data_ptr() if T else None, vasc.data_ptr() if T else None,
+            self.k_topk.data_ptr(), self.v_topk.data_ptr(), self.k_window.data_ptr(), self.v_window.data_ptr(),
+            self._kq.data_ptr(), self._vq.data_ptr(), self._kq.stride(0),
+            self._ks.data_ptr(), self._vs.data_ptr(), self._ks.stride(0),
+            SCALE_MODE, _lib.stream_ptr(device))
+        _lib.check(rc, "hq_cache_reorganize")
+        self._n_quant = n_quant
+        if dtype != torch.bfloat16:   # keep the reference's attribute dtype for non-bf16 models
+            self.k_topk, self.v_topk = self.k_topk.to(dtype), self.v_topk.to(dtype)
+            self.k_window, self.v_window = self.k_window.to(dtype), self.v_window.to(dtype)
+        self._staging_buf_k = torch.zeros(BH, GROUP_SIZE, D, device=device, dtype=dtype)
+        self._staging_buf_v = torch.zeros(BH, GROUP_SIZE, D, device=device, dtype=dtype)
+        self._staging_ptr = 0
+        self._keys = self._values = self._query_tail = None
+        self._plan = None
+        self.phase = "decode"
+
+    # ---- decode ---------------------------------------------------------------
+    def append_staging(self, key_states: torch.Tensor, value_states: torch.Tensor):
+        """Append new decode token(s) to the staging ring (reference :195-207)."""
+        B, H_KV, S, D = key_states.shape
+        BH = B * H_KV
+        k = key_states.reshape(BH, S, D)
+        v = value_states.reshape(BH, S, D)
+        for i in range(S):
+            self._staging_buf_k[:, self._staging_ptr, :] = k[:, i, :]
+            self._staging_buf_v[:, self._staging_ptr, :] = v[:, i, :]
+            self._staging_ptr += 1
+            if self._staging_ptr >= GROUP_SIZE:
+                self._flush_staging_buffer()
+        self._seq_len += S
+
+    def _flush_staging_buffer(self):
+        """Quantise the full staging buffer and append it to the prefix in place
+        (reference :209-217)."""
+        n = self._n_quant
+        if n + GROUP_SIZE > self._kq.shape[1]:
+            self._grow_prefix(n + GROUP_SIZE)
+            self._plan = None
+        quantize_per_token_into(self._staging_buf_k, self._kq, self._ks, n)
+        quantize_per_token_into(self._staging_buf_v, self._vq, self._vs, n)
+        self._n_quant = n + GROUP_SIZE
+        self._staging_ptr = 0
+
+    def _decode_plan(self, q2d: torch.Tensor, kv_repeat: int) -> DecodePlan:
+        if self._staging_buf_k.dtype != torch.bfloat16:
+            # non-bf16 models: segments are cast on the way in (as the reference kernel
+            # does on load), so nothing can be cached across steps
+            return DecodePlan(q2d, self.k_quant_packed, self.v_quant_packed, self.k_scale, self.v_scale,
+                              self.k_topk, self.v_topk, self._staging_buf_k[:, :self._staging_ptr],
+                              self._staging_buf_v[:, :self._staging_ptr], self.k_window, self.v_window,
+                              kv_repeat, None)
+        p = self._plan
+        if p is None or p.kv_repeat != kv_repeat:
+            p = DecodePlan(q2d, self._kq, self._vq, self._ks, self._vs, self.k_topk, self.v_topk,
+                           self._staging_buf_k, self._staging_buf_v, self.k_window, self.v_window,
+                           kv_repeat, None)
+            self._plan = p
+        p.args.n_quant = self._n_quant
+        p.args.n_staging = self._staging_ptr
+        return p
+
+    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, *, partial=None) -> torch.Tensor:
+        """Attention of one new token over the four segments (reference :219-303).
+
+        query_states [B, H_Q, 1, D] -> [B, H_Q, 1, D] in the query dtype.
+        ``partial=(m, l, acc)`` requests the un-normalised softmax state instead
+        (sequence-sharded decode)."""
+        _check_decode_kernel_env()
+        if self.k_bits != 4 or self.v_bits != 4:
+            raise HyQuantError(f"K{self.k_bits}/V{self.v_bits} is not built (K4/V4 only)")
+        B_, H_Q_, _, D_ = query_states.shape
+        q2d = query_states.reshape(B_ * H_Q_, D_)
+        plan = self._decode_plan(q2d, kv_repeat)
+        out = plan.run(q2d, partial=partial)
+        return None if partial is not None else out.reshape(B_, H_Q_, 1, D_)
+
+    def get_seq_length(self) -> int:
+        return self._seq_len
+
+
+class DStageKVCache(_HF_Cache):
+    """HF-compatible KV cache with D-stage quantisation (reference :360-494)."""
+
+    is_compileable = False
+
+    def __init__(self, num_layers: int = 32, k_bits: int | Callable[[int], int] = 4,
+                 v_bits_fn: Callable[[int], int] = lambda i: 4 if i == 0 else 2,
+                 window_size: int = 256, top_ratio: float = 0.05, use_vert: bool = True):
+        try:
+            super().__init__()
+        except (TypeError, ValueError):
+            # newer transformers require layer arguments this cache does not use;
+            # provide the attributes their Cache helpers look at
+            self.layers = []
+            self.layer_class_to_replicate = None
+            self.offloading = False
+        self.num_layers = num_layers
+        self.window_size = window_size
+        self.top_ratio = top_ratio
+        self.use_vert = use_vert
+        k_bits_fn = k_bits if callable(k_bits) else (lambda i, _kb=k_bits: _kb)
+        self._layers = [
+            DStageLayerCache(layer_idx=i, k_bits=k_bits_fn(i), v_bits=v_bits_fn(i), window_size=window_size,
+                             top_ratio=top_ratio, use_vert=use_vert)
+            for i in range(num_layers)
+        ]
+        self._seen_tokens: int = 0
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs: Optional[dict[str, Any]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        layer = self._layers[layer_idx]
+        if layer.phase == "prefill":
+            result = layer.update_prefill(key_states, value_states)
+            if layer_idx == 0:
+                self._seen_tokens = layer.get_seq_length()
+            return result
+        layer.append_staging(key_states, value_states)
+        if layer_idx == 0:
+            self._seen_tokens = layer.get_seq_length()
+        return key_states, value_states
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        if layer_idx < len(self._layers):
+            return self._layers[layer_idx].get_seq_length()
+        return 0
+
+    def get_max_cache_shape(self) -> int:
+        return -1
+
+    def reset(self):
+        for layer in self._layers:
+            layer.__init__(layer.layer_idx, layer.k_bits, layer.v_bits, layer.window_size, layer.top_ratio,
+                           layer.use_vert)
+        self._seen_tokens = 0
+
+    def get_mask_sizes(self, query_length: int, layer_idx: int = 0) -> Tuple[int, int]:
+        kv_length = self.get_seq_length(layer_idx)
+        if kv_length == 0:
+            return query_length, 0
+        return kv_length, max(0, kv_length - query_length)
+
+    def get_layer(self, layer_idx: int) -> DStageLayerCache:
+        return self._layers[layer_idx]
+
+    @property
+    def seen_tokens(self) -> int:
+        return self._seen_tokens
+
+    def batch_repeat_interleave(self, repeats: int):
+        raise NotImplementedError("DStageKVCache does not support beam search yet.")
+
+    def batch_select_indices(self, indices: torch.Tensor):
+        raise NotImplementedError("DStageKVCache does not support beam search yet.")
+
+    def crop(self, max_length: int):
+        pass
+
+    def __len__(self) -> int:
+        return self.num_layers
+
+    def __getitem__(self, idx: int):
+        layer = self._layers[idx]
+        if layer.phase == "prefill" and layer._keys is not None:
+            return (layer._keys, layer._values)
+        return (None, None)
+
+    def __iter__(self):
+        for i in range(len(self._layers)):
+            yield self[i]
+
+    def __bool__(self) -> bool:
+        return True
+
+
+QuantizedKVCache = DStageKVCache

@@ -1,0 +1,190 @@
+/*
+ * hyquant_b200 — C ABI of the B200 (sm_100a) hybrid-precision attention path.
+ *
+ * The reference (jerrysfls/HyQuant) exposes this path only as Python
+ * functions (src/ops, src/patch) that launch Triton kernels; it has no C
+ * interface of its own.  Each entry point below names the reference function
+ * (file:line inside the reference project) whose device work it replaces.  The
+ * Python package `hyquant_b200` binds these with ctypes and keeps the
+ * reference's Python signatures on top.
+ *
+ * Conventions
+ *  - every pointer is a borrowed DEVICE pointer unless the name says `host`;
+ *  - `stream` is a cudaStream_t (pass 0 for the legacy default stream); all
+ *    work is stream-ordered and no entry point synchronises the device;
+ *  - no entry point allocates or frees device memory: scratch is passed in as
+ *    `workspace` (size from the matching *_workspace_bytes call);
+ *  - return value: HQ_OK (0) or a negative HQ_ERR_* code; hq_last_error()
+ *    returns a thread-local message for the last failure on this thread;
+ *  - dtype codes: HQ_BF16 / HQ_F16 / HQ_F32.
+ */
+#ifndef HYQUANT_B200_H_
+#define HYQUANT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HQ_OK                 0
+#define HQ_ERR_INVALID       -1   /* bad argument (null pointer, negative size, ...) */
+#define HQ_ERR_UNSUPPORTED   -2   /* shape / dtype / bit-width outside what is built */
+#define HQ_ERR_ALIGNMENT     -3   /* a pointer or stride breaks a 16-byte rule        */
+#define HQ_ERR_WORKSPACE     -4   /* workspace missing or too small                   */
+#define HQ_ERR_CUDA          -5   /* a CUDA runtime call failed (see hq_last_error)   */
+#define HQ_ERR_TIMEOUT       -6   /* a bounded device-side wait expired               */
+
+#define HQ_BF16 0
+#define HQ_F16  1
+#define HQ_F32  2
+
+#define HQ_GROUP_SIZE 128         /* staging flush threshold, decode_d_stage.py:19 */
+
+/* Library identification and error text. */
+const char* hq_version(void);
+const char* hq_last_error(void);
+
+/* --------------------------------------------------------------------------
+ * Per-token symmetric INT4 quantise + nibble pack, appended in place.
+ * Replaces quantize_per_token(x, 4) + _pack_int4 (src/ops/decode_d_stage.py:50-77,
+ * 104-111) as used by DStageLayerCache._flush_staging_buffer and freeze
+ * (src/ops/d_stage_kv_cache.py:209-217, 168-169), and removes the torch.cat
+ * growth of the prefix (:213-216): rows are written at token `dst_token_offset`
+ * of pre-allocated capacity buffers.
+ *
+ *   x        [BH, n, 128] in_dtype, row stride x_stride_n, head stride x_stride_bh (elements)
+ *   packed   int8  [BH, cap, 64], head stride packed_stride_bh (bytes)
+ *   scale    fp16  [BH, cap],     head stride scale_stride_bh (elements)
+ *   scale_mode 0: scale = half(max(|x|,1e-5) / 7)            (IEEE divide; CPU-eager PyTorch)
+ *              1: scale = half(max(|x|,1e-5) * (1.0f/7.0f))  (CUDA-eager PyTorch)
+ * Codes: q = clamp(rint(x / float(scale)), -8, 7); byte = (q[2i] & 15) | (q[2i+1] << 4).
+ */
+int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
+                       int BH, int n,
+                       void* packed, int64_t packed_stride_bh,
+                       void* scale, int64_t scale_stride_bh,
+                       int64_t dst_token_offset, int scale_mode, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Split-K decode attention over the four-segment cache, one launch.
+ * Replaces fused_d_stage_decode / fused_d_stage_decode_splitk and the kernels
+ * _fused_d_stage_decode_kernel, _splitk_partial_kernel, _splitk_reduce_kernel
+ * (src/ops/decode_d_stage.py:916-1005, 823-913, 270-469, 481-743, 746-782),
+ * i.e. the device work of DStageLayerCache.decode_attention
+ * (src/ops/d_stage_kv_cache.py:219-303), without the torch.cat of the BF16
+ * segments (:848-849).
+ *
+ * Strides are in ELEMENTS of the tensor's dtype except where noted.  The
+ * innermost (channel) dimension must be contiguous; packed rows must be 64
+ * bytes apart and BF16 rows 128 elements apart; every base pointer and head
+ * stride must keep rows 16-byte aligned (HQ_ERR_ALIGNMENT otherwise).
+ */
+typedef struct hq_decode_args {
+  int32_t struct_bytes;        /* sizeof(hq_decode_args), checked */
+  int32_t BH_KV;               /* batch * kv heads */
+  int32_t kv_repeat;           /* query heads per kv head (1..16) */
+  int32_t head_dim;            /* 128 */
+  int32_t n_quant;             /* INT4 prefix tokens */
+  int32_t n_topk;              /* frozen BF16 vertical-line tokens */
+  int32_t n_staging;           /* live tokens in the staging buffer (0..128) */
+  int32_t n_window;            /* BF16 window tokens */
+  int32_t out_dtype;           /* HQ_BF16 / HQ_F16 / HQ_F32 */
+  int32_t num_splits;          /* 0 = choose automatically */
+  float   sm_scale;            /* softmax scale, e.g. head_dim^-0.5 */
+  int32_t reserved0;
+  const void* q;               /* bf16 [BH_KV*kv_repeat, 128] */
+  int64_t q_stride;            /* elements between query rows */
+  const void* k_packed;        /* int8 [BH_KV, n_quant, 64] */
+  const void* v_packed;
+  int64_t kp_stride_bh;        /* BYTES between heads */
+  int64_t vp_stride_bh;
+  const void* k_scale;         /* fp16 [BH_KV, n_quant] */
+  const void* v_scale;
+  int64_t ks_stride_bh;
+  int64_t vs_stride_bh;
+  const void* k_topk;          /* bf16 [BH_KV, n_topk, 128] */
+  const void* v_topk;
+  int64_t kt_stride_bh;
+  int64_t vt_stride_bh;
+  const void* k_staging;       /* bf16 [BH_KV, n_staging, 128] */
+  const void* v_staging;
+  int64_t kg_stride_bh;
+  int64_t vg_stride_bh;
+  const void* k_window;        /* bf16 [BH_KV, n_window, 128] */
+  const void* v_window;
+  int64_t kw_stride_bh;
+  int64_t vw_stride_bh;
+  void*   out;                 /* out_dtype [BH_KV*kv_repeat, 128]; may be NULL in partial mode */
+  int64_t out_stride;
+  /* Partial mode (sequence-sharded decode): when partial_acc != NULL the
+   * un-normalised base-2 softmax state of this shard is written instead of
+   * `out`: partial_m/partial_l fp32 [BH_Q], partial_acc fp32 [BH_Q, 128]. */
+  float*  partial_m;
+  float*  partial_l;
+  float*  partial_acc;
+  void*   workspace;           /* hq_decode_workspace_bytes(); zero-filled once by the caller */
+  int64_t workspace_bytes;
+} hq_decode_args;
+
+int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);
+int hq_decode_splitk(const hq_decode_args* args, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Log-sum-exp merge of G shards' partials (the algebra of _splitk_reduce_kernel,
+ * src/ops/decode_d_stage.py:764-781, applied across GPUs after an all-gather).
+ *   m, l  fp32 [G, rows];  acc fp32 [G, rows, 128];  out out_dtype [rows, 128]
+ */
+int hq_lse_merge(const float* m, const float* l, const float* acc, int G, int rows,
+                 void* out, int out_dtype, int64_t out_stride, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Vertical-line scores: mean of the last `tail_len` queries, dotted with every
+ * candidate key.  Replaces the mean/matmul/einsum of compute_vertical_indices
+ * (src/patch/_common.py:161-185).
+ *   q       io_dtype [B, H_Q, n_q, 128] (strides in elements)
+ *   k       io_dtype [B, H_KV, *, 128]; candidates are rows [0, n_cand)
+ *   pooled  fp32 [B, H_Q, 128]  (out: the pooled query; also the kernel's scratch)
+ *   scores  fp32 [B, H_Q, n_cand]
+ * kv_repeat = H_Q / H_KV.  round_mean != 0 rounds the pooled query to io_dtype
+ * first (what the reference's in-dtype mean does); round_scores != 0 rounds the
+ * scores to io_dtype as the reference's in-dtype matmul does.
+ */
+int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                       int B, int H_Q, int n_q, int tail_len,
+                       const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                       int H_KV, int n_cand, int round_mean, int round_scores,
+                       float* pooled, float* scores, void* stream);
+
+/* Top-k of each row of `scores` ([rows, n] fp32, row stride `scores_stride`),
+ * descending, ties towards the lower index.  Replaces torch.topk(..., sorted=True)
+ * in compute_vertical_indices (src/patch/_common.py:187-190).  idx_desc int64
+ * [rows, k]; idx_asc int32 [rows, k] (the same set in ascending position, may be
+ * NULL).  1 <= k <= min(n, 16384).  Uses no global scratch. */
+int hq_topk(const float* scores, int64_t scores_stride, int rows, int n, int k,
+            int64_t* idx_desc, int32_t* idx_asc, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Prefill -> decode cache reorganisation.  Replaces the gather / scatter / sort
+ * / gather / quantise chain of DStageLayerCache.freeze
+ * (src/ops/d_stage_kv_cache.py:119-169).
+ *   keys/values io_dtype(bf16) [BH, N, 128] (head stride kv_stride_bh, row stride 128)
+ *   prefix_len  = N - W; window rows [prefix_len, N) are copied to k/v_window
+ *   vidx_desc   int64 [BH, T] rows to keep in BF16, in output order
+ *   vidx_asc    int32 [BH, T] the same rows in ascending position
+ *   k/v_topk    bf16 [BH, T, 128]
+ *   packed/scale as in hq_quant_pack_int4, written from token 0; n_quant = prefix_len - T
+ */
+int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_bh,
+                        int BH, int N, int window, int T,
+                        const int64_t* vidx_desc, const int32_t* vidx_asc,
+                        void* k_topk, void* v_topk,
+                        void* k_window, void* v_window,
+                        void* k_packed, void* v_packed, int64_t packed_stride_bh,
+                        void* k_scale, void* v_scale, int64_t scale_stride_bh,
+                        int scale_mode, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* HYQUANT_B200_H_ */

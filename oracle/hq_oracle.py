@@ -48,10 +48,14 @@ E4M3_MAX = 448.0
 def bf16_round(x: np.ndarray) -> np.ndarray:
     """Round fp32 to the nearest bf16 (ties to even); result stays float32."""
     x = np.ascontiguousarray(x, dtype=np.float32)
-    u = x.view(np.uint32).astype(np.uint64)
-    r = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    out = r.astype(np.uint32).view(np.float32)
-    return np.where(np.isnan(x), x, out).astype(np.float32)
+    u = x.view(np.uint32)
+    bias = ((u >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF)
+    r = (u + bias) & np.uint32(0xFFFF0000)           # wraps only for NaN payloads, restored below
+    out = r.view(np.float32)
+    nan = np.isnan(x)
+    if nan.any():
+        out = np.where(nan, x, out).astype(np.float32)
+    return out
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

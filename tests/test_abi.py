@@ -1,0 +1,85 @@
+"""CPU checks of the boundary: the shared library builds, loads and exports every
+symbol the public header declares; host-side argument checks fail loudly."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+import hyquant_b200 as hq
+from hyquant_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "hyquant_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.lib()
+    syms = header_symbols()
+    assert syms, "no declarations found in the header"
+    for s in syms:
+        assert hasattr(lib, s), f"{s} declared in include/hyquant_b200.h but not exported"
+    assert sorted(_lib.EXPORTS) == syms
+    assert b"sm_100a" in lib.hq_version()
+
+
+def test_decode_args_struct_matches_header_size():
+    # the C side checks struct_bytes; a mismatch must come back as HQ_ERR_INVALID, not a crash
+    a = _lib.DecodeArgs()
+    a.struct_bytes = C.sizeof(_lib.DecodeArgs) - 8
+    rc = _lib.lib().hq_decode_splitk(C.byref(a), None)
+    assert rc == -1
+    assert b"struct_bytes" in _lib.lib().hq_last_error()
+
+
+def test_argument_validation_without_gpu():
+    lib = _lib.lib()
+    n = C.c_int64(0)
+    assert lib.hq_decode_workspace_bytes(8, 4, C.byref(n)) == 0 and n.value > 0
+    assert lib.hq_decode_workspace_bytes(8, 17, C.byref(n)) == -1
+    assert lib.hq_topk(None, 0, 1, 10, 20, None, None, None) == -1          # k > n
+    assert lib.hq_quant_pack_int4(None, 0, 0, 0, 2, 2, None, 0, None, 0, 0, 0, None) == -1
+    assert lib.hq_lse_merge(None, None, None, 0, 4, None, 0, 0, None) == -1
+
+
+def test_product_path_has_no_cpu_fallback():
+    x = torch.zeros(1, 4, 128)
+    with pytest.raises(hq.HyQuantError):
+        hq.quantize_per_token(x, 4)
+    with pytest.raises(hq.HyQuantError):
+        hq.compute_vertical_indices(torch.zeros(1, 2, 8, 128), torch.zeros(1, 2, 300, 128), 64, 0.05)
+    with pytest.raises(hq.HyQuantError):
+        hq.fused_d_stage_decode(torch.zeros(4, 128), *[torch.zeros(1, 0, 64)] * 10, 4, 4, kv_repeat=4)
+    with pytest.raises(hq.HyQuantError):
+        hq.fused_d_stage_decode(torch.zeros(4, 128), *[torch.zeros(1, 0, 64)] * 10, 8, 8, kv_repeat=4)
+    with pytest.raises(ValueError):
+        hq.quantize_per_token(x, 3)
+
+
+def test_reference_interface_names():
+    hq.install_as_src()
+    import src.ops as ops
+    from src.ops.d_stage_kv_cache import DStageKVCache, DStageLayerCache
+    from src.ops.decode_d_stage import GROUP_SIZE, fused_d_stage_decode, quantize_per_token
+    from src.patch._common import D_STAGE_MODES, compute_vertical_indices, handle_d_stage_cache, validate_patch_args
+    assert GROUP_SIZE == 128 and "hybrid_full" in D_STAGE_MODES
+    cache = ops.create_cache_for_mode("hybrid_full", num_layers=2, window_size=128, top_ratio=0.05)
+    assert isinstance(cache, DStageKVCache) and len(cache) == 2 and cache.get_seq_length() == 0
+    assert cache.get_layer(1).k_bits == 4 and cache.get_layer(1).use_vert
+    assert ops.create_cache_for_mode("dense", 2) is None
+    assert cache.get_mask_sizes(5) == (5, 0) and cache.get_max_cache_shape() == -1 and bool(cache)
+    with pytest.raises(NotImplementedError):
+        cache.batch_repeat_interleave(2)
+    with pytest.raises(ValueError):
+        validate_patch_args("nope", 128, 0.05)
+    with pytest.raises(ValueError):
+        validate_patch_args("d_k4v4", -1, 0.05)
+    with pytest.raises(ValueError):
+        validate_patch_args("d_k4v4", 1, 0.0)

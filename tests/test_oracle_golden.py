@@ -97,3 +97,15 @@ def test_hybrid_prefill_restatement_close_to_dense():
     ref = orc.dense_causal_attention(q, k, v)
     assert max_abs(out, ref) < 2e-2
     assert orc.rel_mse(out, ref) < 1e-4
+
+
+def test_torch_cpu_baseline_matches_fixture():
+    """The torch-CPU restatement that bench.py times agrees with the reference's outputs."""
+    import torch
+    from oracle import hq_oracle_torch as ot
+    cc = CacheCase("cache_cfg0_f32")
+    c = cc.oracle_freeze()
+    for step in range(1, cc.n_append + 1):
+        orc.append_staging(c, cc.new_k[step - 1], cc.new_v[step - 1])
+    out = ot.decode_attention_fallback(torch.from_numpy(cc.new_q[cc.n_append - 1]), *ot.from_numpy_cache(c), cc.B, cc.H_KV, cc.R)
+    assert max_abs(out.numpy(), cc.g[f"out_step{cc.n_append}"]) < 2e-5
