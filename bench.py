@@ -139,7 +139,7 @@ def layer_bytes(layer, h_q_total):
     return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16)
 
 
-def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None):
+def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True):
     """K steps of (one decode launch per layer), device-timed; returns ms total, launches.
     ``flush``: a buffer larger than L2 that is rewritten before every step (outside the
     timed events) when the step's own caches do not exceed L2."""
@@ -157,12 +157,25 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None):
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
+    def launch_all():
+        for (p, q2), o in zip(plans, outs):
+            p.run(q2, out=o)
+
+    step_fn = launch_all
+    if graph:
+        # one token's launches captured once and replayed: the host cost of 32 Python
+        # calls per step is not part of the kernel-side number
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            launch_all()
+        step_fn = g.replay
+        step_fn()
+        torch.cuda.synchronize()
     if flush is None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            for (p, q2), o in zip(plans, outs):
-                p.run(q2, out=o)
+            step_fn()
         e1.record()
         torch.cuda.synchronize()
         total = e0.elapsed_time(e1)
@@ -172,8 +185,7 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None):
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for (p, q2), o in zip(plans, outs):
-                p.run(q2, out=o)
+            step_fn()
             e1.record()
             evs.append((e0, e1))
         torch.cuda.synchronize()
@@ -307,7 +319,7 @@ def run_ours(args):
         dist_.init_process_group("nccl", device_id=dev)
         dist = dist_
     layers, qs = [], []
-    for li in range(LAYERS):
+    for li in range(args.layers):
         layer, qd = build_layer(hq, torch, 1015 + 100 * rank + li, N_PREFIX, dev)
         layers.append(layer); qs.append(qd)
     call_bytes = layer_bytes(layers[0], B * H_Q)
@@ -315,9 +327,12 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist)
+    ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph)
     clocks = sampler.stop()
-    e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, args.warmup, 99 + rank, dist)
+    if args.no_e2e:
+        e2e_ms, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, args.warmup, 99 + rank, dist)
     e2e_bytes = sum(layer_bytes(l, B * H_Q) for l in layers)     # staging has grown by then; close enough per step
 
     if dist is not None:
@@ -325,7 +340,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
     ms_per_step = ms / args.steps
-    us_per_call = ms_per_step * 1e3 / LAYERS
+    us_per_call = ms_per_step * 1e3 / args.layers
     gbs_one = call_bytes / (us_per_call * 1e-6) / 1e9
     value = gbs_one * world
     e2e_val = e2e_bytes / (e2e_ms / args.steps * 1e-3) / 1e9 * world
@@ -337,7 +352,7 @@ def run_ours(args):
         for n in (1024, 2048, 4096, 8192, 16384, 32768):
             ncache = 16
             ls, qq = zip(*[build_layer(hq, torch, 5000 + n + i, n, dev) for i in range(ncache)])
-            m, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush)
+            m, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=not args.no_graph)
             us = m * 1e3 / cnt
             bts = layer_bytes(ls[0], B * H_Q)
             sweep.append({"prefix": n, "us_per_call": round(us, 3), "gbps": round(bts / us / 1e3, 1),
@@ -361,7 +376,7 @@ def run_ours(args):
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
                     "path": "DStageLayerCache.append_staging + decode_attention per layer, q/k/v from pinned host, out to host"},
-            "gpu_launches": launches,
+            "gpu_launches": launches, "launch_mode": "python" if args.no_graph else "cuda graph replay of one token (32 launches)",
             "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src,
                          "kernel": "hq::decode_splitk_kernel<1>", "algorithmic_bytes_per_launch": call_bytes},
@@ -385,6 +400,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

@@ -129,7 +129,7 @@ vertical_scores_kernel(const uint16_t* __restrict__ k, int64_t ksb, int64_t ksh,
 
 // ------------------------------------------------------------------- top-k
 __device__ __forceinline__ uint32_t orderable(float f) {
-  uint32_t u = __float_as_uint(f);
+  uint32_t u = (f == 0.0f) ? 0u : __float_as_uint(f);   // -0.0 and +0.0 compare equal, as in torch.topk
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
