@@ -17,9 +17,15 @@
 // Math.  Scores are computed transposed, S^T = K Q^T, with tokens on the MMA M
 // axis and the kv-group's query heads on the N axis (N = 8 per tile, so GQA
 // ratios 4 and 8 fit one tile and 16 two tiles).  INT4 codes are expanded to
-// fp16 in registers with the 0x6400 magic-number trick (exact for -8..7) and
-// fed to mma.sync.m16n8k16.f16; the per-token K scale multiplies the fp32 score
-// afterwards, the per-token V scale is folded into P before the PV product.
+// fp16 in registers with the 0x6400 magic-number trick and fed to
+// mma.sync.m16n8k16.f16.  For K the magic offset is NOT subtracted per element:
+// the MMA sees 1032 + code (low nibbles) or 1152 + 16 code (high nibbles, with
+// q/16 on the other operand) and the per-head constant 1032 sum(q_even) +
+// 1152 sum(q_odd/16) is subtracted from the fp32 score, which removes half of
+// the conversion instructions.  V is converted exactly (offset subtracted per
+// element) because its products accumulate over the whole sequence.  The
+// per-token K scale multiplies the fp32 score, the per-token V scale is folded
+// into P before the PV product.
 // BF16 segments use mma.sync bf16.  All segments share one online softmax in
 // base 2 with a lazily updated reference maximum.  O^T = V^T P^T accumulates in
 // fp32 registers.  Warps merge through shared memory, CTAs through a fp32
@@ -32,7 +38,7 @@ namespace hq {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kSlots = 3;
-constexpr int kSlotBytes = 4096;          // K 2048 | V 2048
+constexpr int kSlotBytes = 4224;          // K 2048 | V 2048 | k_scale 64 | v_scale 64
 constexpr int kUnitQ = 32;                // INT4 tokens per unit
 constexpr int kUnitB = 8;                 // BF16 tokens per unit
 constexpr float kLazyRescale = 4.0f;      // rescale only if the max grows by > 2^4
@@ -54,6 +60,7 @@ struct DecodeParams {
   float sml;                              // sm_scale * log2(e)
   void* out; int64_t out_stride;
   float* pm; float* pl; float* pacc;      // partial mode outputs (or null)
+  int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
   int* status; int* counters;             // workspace
   float* ws_m; float* ws_l; float* ws_acc;
 };
@@ -98,6 +105,16 @@ __device__ __forceinline__ void cvt_nibbles_f16(uint32_t w, uint32_t (&h)[4]) {
   h[1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_xor(w, 0x00F000F0u, 0x64806480u)), c16th, cm72));
   h[2] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_xor(w8, 0x000F000Fu, 0x64086408u)), c1032));
   h[3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_xor(w8, 0x00F000F0u, 0x64806480u)), c16th, cm72));
+}
+
+// Same lanes, without removing the magic offset: result k holds 1032 + code for
+// k = 0, 2 (low nibbles) and 1152 + 16 code for k = 1, 3 (high nibbles).
+__device__ __forceinline__ void cvt_nibbles_biased(uint32_t w, uint32_t (&h)[4]) {
+  const uint32_t w8 = w >> 8;
+  h[0] = lop3_and_xor(w, 0x000F000Fu, 0x64086408u);
+  h[1] = lop3_and_xor(w, 0x00F000F0u, 0x64806480u);
+  h[2] = lop3_and_xor(w8, 0x000F000Fu, 0x64086408u);
+  h[3] = lop3_and_xor(w8, 0x00F000F0u, 0x64806480u);
 }
 
 __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -170,15 +187,18 @@ __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m
 
 // ---- the kernel -------------------------------------------------------------
 
-template <int NT>
+template <int NT, bool kScaleTma>
 __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1)
 decode_splitk_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: ring [kWarps][kSlots][4096] | fragH [NT*1024 u32 = NT*4 KB]... see offsets below
+  // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same | qs [NT*8][128] bf16 |
+  //         headC [NT*8] f32 | mbarriers [kWarps][kSlots]
   uint8_t* ring = smem;
-  uint32_t* fragH = reinterpret_cast<uint32_t*>(smem + kWarps * kSlots * kSlotBytes);   // [NT][8][2][32]
-  uint32_t* fragB = fragH + NT * 512;                                                    // [NT][8][2][32]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(fragB + NT * 512);                        // [kWarps][kSlots]
+  uint32_t* fragH = reinterpret_cast<uint32_t*>(smem + kWarps * kSlots * kSlotBytes);
+  uint32_t* fragB = fragH + NT * 512;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(fragB + NT * 512);
+  float* headC = reinterpret_cast<float*>(qs + NT * 8 * 128);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(headC + NT * 8);
   __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -191,6 +211,18 @@ decode_splitk_kernel(const DecodeParams p) {
   uint8_t* my_ring = ring + warp * (kSlots * kSlotBytes);
   uint64_t* my_bar = bars + warp * kSlots;
 
+  // ---- 1. the query rows first: these small loads must be in the memory system
+  // before the bulk copies below, or they queue behind megabytes of KV traffic.
+  uint2 qraw[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int hd = nt * 8 + warp;
+    qraw[nt] = make_uint2(0u, 0u);
+    if (hd < p.R)
+      qraw[nt] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
+  }
+
+  // ---- 2. barriers and the first bulk copies
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) mbar_init(&my_bar[s], 1);
@@ -201,40 +233,63 @@ decode_splitk_kernel(const DecodeParams p) {
   auto issue = [&](int i) {   // lane 0 only
     const Unit un = unit_of(p, head, u_begin + warp + kWarps * i);
     const int slot = i % kSlots;
-    const uint32_t bytes = un.kind == 0 ? (uint32_t)un.ntok * 64u : (uint32_t)un.ntok * 256u;
     uint8_t* dst = my_ring + slot * kSlotBytes;
-    mbar_expect_tx(&my_bar[slot], 2 * bytes);
-    bulk_g2s(dst, un.k, bytes, &my_bar[slot]);
-    bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
+    if (un.kind == 0) {
+      const uint32_t bytes = (uint32_t)un.ntok * 64u;
+      if (kScaleTma) {
+        const uint32_t sbytes = (uint32_t)((un.ntok + 7) & ~7) * 2u;
+        mbar_expect_tx(&my_bar[slot], 2 * bytes + 2 * sbytes);
+        bulk_g2s(dst + 4096, p.k_scale + head * p.ks_stride_bh + un.tok0, sbytes, &my_bar[slot]);
+        bulk_g2s(dst + 4160, p.v_scale + head * p.vs_stride_bh + un.tok0, sbytes, &my_bar[slot]);
+      } else {
+        mbar_expect_tx(&my_bar[slot], 2 * bytes);
+      }
+      bulk_g2s(dst, un.k, bytes, &my_bar[slot]);
+      bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
+    } else {
+      const uint32_t bytes = (uint32_t)un.ntok * 256u;
+      mbar_expect_tx(&my_bar[slot], 2 * bytes);
+      bulk_g2s(dst, un.k, bytes, &my_bar[slot]);
+      bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
+    }
   };
   if (lane == 0) {
     for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
   }
 
-  // ---- query fragments: B operands of S^T = K Q^T, permuted along the channel
+  // ---- 3. query rows -> shared memory, per-head offset constant of the biased K codes
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int hd = nt * 8 + warp;
+    reinterpret_cast<uint2*>(qs + hd * 128)[lane] = qraw[nt];
+    const float q0 = __uint_as_float(qraw[nt].x << 16), q1 = __uint_as_float(qraw[nt].x & 0xFFFF0000u);
+    const float q2 = __uint_as_float(qraw[nt].y << 16), q3 = __uint_as_float(qraw[nt].y & 0xFFFF0000u);
+    // even channels meet 1032 + code, odd channels (pre-divided by 16) meet 1152 + 16 code
+    float c = 1032.f * (__half2float(__float2half_rn(q0)) + __half2float(__float2half_rn(q2))) +
+              1152.f * (__half2float(__float2half_rn(q1 * 0.0625f)) + __half2float(__float2half_rn(q3 * 0.0625f)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) headC[hd] = c;
+  }
+  __syncthreads();
+
+  // ---- 4. query fragments: B operands of S^T = K Q^T, permuted along the channel
   // axis to match the order in which channels fall out of the K loads.
-  {
-    const int heads = NT * 8;
-    for (int e = tid; e < NT * 512; e += kThreads) {
-      const int l = e & 31, r = (e >> 5) & 1, c = (e >> 6) & 7, nt = e >> 9;
-      const int gg = l >> 2, tt = l & 3, i = c >> 1, odd = c & 1;
-      const int hd = nt * 8 + gg;
-      // INT4 path: word i of thread tt covers channels 32 tt + 8 i + m (nibble m);
-      // register r of MMA chunk c pairs nibbles (2*odd + r, 2*odd + r + 4).
-      const int chA = 32 * tt + 8 * i + 2 * odd + r, chB = chA + 4;
-      // BF16 path: 16-byte chunk j = 4 i + tt covers channels 8 j .. 8 j + 7.
-      const int cbA = 8 * (4 * i + tt) + 4 * odd + 2 * r, cbB = cbA + 1;
-      float qa = 0.f, qb = 0.f, ra = 0.f, rb = 0.f;
-      if (hd < p.R) {
-        const __nv_bfloat16* qrow = p.q + (int64_t)(head * p.R + hd) * p.q_stride;
-        qa = __bfloat162float(qrow[chA]); qb = __bfloat162float(qrow[chB]);
-        ra = __bfloat162float(qrow[cbA]); rb = __bfloat162float(qrow[cbB]);
-      }
-      qa = fminf(fmaxf(qa, -65504.f), 65504.f); qb = fminf(fmaxf(qb, -65504.f), 65504.f);
-      fragH[e] = pack_f16x2(qa, qb);
-      fragB[e] = pack_bf16x2(ra, rb);
-      (void)heads;
-    }
+  for (int e = tid; e < NT * 512; e += kThreads) {
+    const int l = e & 31, r = (e >> 5) & 1, c = (e >> 6) & 7, nt = e >> 9;
+    const int gg = l >> 2, tt = l & 3, i = c >> 1, odd = c & 1;
+    const __nv_bfloat16* qrow = qs + (nt * 8 + gg) * 128;
+    // INT4 path: word i of thread tt covers channels 32 tt + 8 i + m (nibble m);
+    // register r of MMA chunk c pairs nibbles (2*odd + r, 2*odd + r + 4).  r = 1 are
+    // high nibbles: the query value is pre-divided by 16 (see cvt_nibbles_biased).
+    const int chA = 32 * tt + 8 * i + 2 * odd + r, chB = chA + 4;
+    const float sc = r ? 0.0625f : 1.0f;
+    const float qa = fminf(fmaxf(__bfloat162float(qrow[chA]) * sc, -65504.f), 65504.f);
+    const float qb = fminf(fmaxf(__bfloat162float(qrow[chB]) * sc, -65504.f), 65504.f);
+    fragH[e] = pack_f16x2(qa, qb);
+    // BF16 path: 16-byte chunk j = 4 i + tt covers channels 8 j .. 8 j + 7.
+    const int cbA = 8 * (4 * i + tt) + 4 * odd + 2 * r;
+    fragB[e] = *reinterpret_cast<const uint32_t*>(qrow + cbA);
   }
   __syncthreads();
 
@@ -256,16 +311,20 @@ decode_splitk_kernel(const DecodeParams p) {
   // ======================= INT4 units =======================================
   {
     uint32_t Qh[NT][8][2];
+    float hc[NT][2];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
       for (int c = 0; c < 8; ++c)
 #pragma unroll
         for (int r = 0; r < 2; ++r) Qh[nt][c][r] = fragH[((nt * 8 + c) * 2 + r) * 32 + lane];
+      hc[nt][0] = headC[nt * 8 + 2 * t];
+      hc[nt][1] = headC[nt * 8 + 2 * t + 1];
+    }
 
-    // per-lane packed (k_scale, v_scale) of token `lane` of the upcoming unit
+    // direct-load path only: per-lane packed (k_scale, v_scale) of token `lane` of a unit
     auto load_scales = [&](int ii) -> uint32_t {
-      if (ii >= n_my) return 0u;
+      if (kScaleTma || ii >= n_my) return 0u;
       const int u = u_begin + warp + kWarps * ii;
       if (u >= p.uq) return 0u;
       const int tok = u * kUnitQ + lane;
@@ -285,44 +344,63 @@ decode_splitk_kernel(const DecodeParams p) {
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
       const uint8_t* Ks = my_ring + slot * kSlotBytes;
       const uint8_t* Vs = Ks + 2048;
+      const __half* kss = reinterpret_cast<const __half*>(Ks + 4096);
+      const __half* vss = reinterpret_cast<const __half*>(Ks + 4160);
 
-      float s[2][NT][4];
-      float vsc[2][2];
+      // K words of both 16-token chunks: tokens g, g+8, 16+g, 24+g
+      uint4 kw[2][2];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
-        const int tokA = 16 * ch + g, tokB = tokA + 8;
-        const uint4 ka = *reinterpret_cast<const uint4*>(Ks + tokA * 64 + t * 16);
-        const uint4 kb = *reinterpret_cast<const uint4*>(Ks + tokB * 64 + t * 16);
-        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w};
-        const uint32_t wb[4] = {kb.x, kb.y, kb.z, kb.w};
+        kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
+        kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
+      }
+      float s[2][NT][4];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int x = 0; x < 4; ++x) s[ch][nt][x] = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          const uint32_t wa = w == 0 ? kw[ch][0].x : w == 1 ? kw[ch][0].y : w == 2 ? kw[ch][0].z : kw[ch][0].w;
+          const uint32_t wb = w == 0 ? kw[ch][1].x : w == 1 ? kw[ch][1].y : w == 2 ? kw[ch][1].z : kw[ch][1].w;
           uint32_t ha[4], hb[4];
-          cvt_nibbles_f16(wa[w], ha);
-          cvt_nibbles_f16(wb[w], hb);
+          cvt_nibbles_biased(wa, ha);
+          cvt_nibbles_biased(wb, hb);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
             mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
           }
         }
-        const uint32_t scA = __shfl_sync(0xffffffffu, sc_cur, tokA);
-        const uint32_t scB = __shfl_sync(0xffffffffu, sc_cur, tokB);
-        const float ksA = __half2float(__ushort_as_half((uint16_t)(scA & 0xFFFFu))) * p.sml;
-        const float ksB = __half2float(__ushort_as_half((uint16_t)(scB & 0xFFFFu))) * p.sml;
-        vsc[ch][0] = __half2float(__ushort_as_half((uint16_t)(scA >> 16)));
-        vsc[ch][1] = __half2float(__ushort_as_half((uint16_t)(scB >> 16)));
+      }
+      float vsc[2][2];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int tokA = 16 * ch + g, tokB = tokA + 8;
         const bool okA = tokA < ntok, okB = tokB < ntok;
+        float ksA, ksB;
+        if (kScaleTma) {
+          ksA = __half2float(kss[tokA]) * p.sml; ksB = __half2float(kss[tokB]) * p.sml;
+          vsc[ch][0] = okA ? __half2float(vss[tokA]) : 0.f;
+          vsc[ch][1] = okB ? __half2float(vss[tokB]) : 0.f;
+        } else {
+          const uint32_t scA = __shfl_sync(0xffffffffu, sc_cur, tokA);
+          const uint32_t scB = __shfl_sync(0xffffffffu, sc_cur, tokB);
+          ksA = __half2float(__ushort_as_half((uint16_t)(scA & 0xFFFFu))) * p.sml;
+          ksB = __half2float(__ushort_as_half((uint16_t)(scB & 0xFFFFu))) * p.sml;
+          vsc[ch][0] = __half2float(__ushort_as_half((uint16_t)(scA >> 16)));
+          vsc[ch][1] = __half2float(__ushort_as_half((uint16_t)(scB >> 16)));
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          s[ch][nt][0] = okA ? s[ch][nt][0] * ksA : -INFINITY;
-          s[ch][nt][1] = okA ? s[ch][nt][1] * ksA : -INFINITY;
-          s[ch][nt][2] = okB ? s[ch][nt][2] * ksB : -INFINITY;
-          s[ch][nt][3] = okB ? s[ch][nt][3] * ksB : -INFINITY;
+          s[ch][nt][0] = okA ? (s[ch][nt][0] - hc[nt][0]) * ksA : -INFINITY;
+          s[ch][nt][1] = okA ? (s[ch][nt][1] - hc[nt][1]) * ksA : -INFINITY;
+          s[ch][nt][2] = okB ? (s[ch][nt][2] - hc[nt][0]) * ksB : -INFINITY;
+          s[ch][nt][3] = okB ? (s[ch][nt][3] - hc[nt][1]) * ksB : -INFINITY;
         }
       }
       // one online-softmax step for the 32 tokens
@@ -376,7 +454,7 @@ decode_splitk_kernel(const DecodeParams p) {
       }
       sc_cur = sc_next;
       __syncwarp();
-      if (lane == 0 && i + kSlots < n_my) { fence_proxy_async_smem(); issue(i + kSlots); }
+      if (lane == 0 && i + kSlots < n_my) issue(i + kSlots);
     }
   }
 
@@ -396,7 +474,8 @@ decode_splitk_kernel(const DecodeParams p) {
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
       uint8_t* Ks = my_ring + slot * kSlotBytes;
       uint8_t* Vs = Ks + 2048;
-      if (un.ntok < kUnitB) {   // stale bytes past the copied rows must not reach the MMA as NaN/Inf
+      const bool patched = un.ntok < kUnitB;
+      if (patched) {   // stale bytes past the copied rows must not reach the MMA as NaN/Inf
         const int n16 = (kUnitB - un.ntok) * 16;
         for (int x = lane; x < n16; x += 32) {
           reinterpret_cast<uint4*>(Ks + un.ntok * 256)[x] = make_uint4(0, 0, 0, 0);
@@ -453,7 +532,10 @@ decode_splitk_kernel(const DecodeParams p) {
         for (int nt = 0; nt < NT; ++nt) mma_bf16_1688(O[nt][mt], r0, r1, pb[nt]);
       }
       __syncwarp();
-      if (lane == 0 && i + kSlots < n_my) { fence_proxy_async_smem(); issue(i + kSlots); }
+      if (lane == 0 && i + kSlots < n_my) {
+        if (patched) fence_proxy_async_smem();   // generic-proxy writes above precede the next async write
+        issue(i + kSlots);
+      }
     }
   }
   if (failed && lane == 0) atomicOr(p.status, 1);
@@ -470,10 +552,12 @@ decode_splitk_kernel(const DecodeParams p) {
       const int hd = nt * 8 + 2 * t + j;
       const float lsum = group_sum(l_part[nt][j]);
       if (g == 0) { mrg_m[warp * NT * 8 + hd] = m_ref[nt][j]; mrg_l[warp * NT * 8 + hd] = lsum; }
-      float* orow = mrg_o + ((size_t)(warp * NT * 8 + hd)) * 128 + 16 * g;
+      if (hd < p.R) {
+        float* orow = mrg_o + ((size_t)(warp * NT * 8 + hd)) * 128 + 16 * g;
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt)
-        *reinterpret_cast<float2*>(orow + 2 * mt) = make_float2(O[nt][mt][j], O[nt][mt][2 + j]);
+        for (int mt = 0; mt < 8; ++mt)
+          *reinterpret_cast<float2*>(orow + 2 * mt) = make_float2(O[nt][mt][j], O[nt][mt][2 + j]);
+      }
     }
   __syncthreads();
 
@@ -517,29 +601,52 @@ decode_splitk_kernel(const DecodeParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  float* sm_m = reinterpret_cast<float*>(smem);            // [nsplit * R]
-  float* sm_l = sm_m + p.nsplit * p.R;
+  // weights: sm_w[s*R + h] = 2^(m_s - M_h) ; sm_L[h] = sum_s w l
+  float* sm_w = reinterpret_cast<float*>(smem);             // [nsplit * R]
+  float* sm_l = sm_w + p.nsplit * p.R;                      // [nsplit * R]
+  float* sm_M = sm_l + p.nsplit * p.R;                      // [R]
+  float* sm_L = sm_M + 16;                                  // [R]
+  float* red = sm_w + ((2 * p.nsplit * p.R + 32 + 3) & ~3); // [kWarps][R][128], 16-byte aligned
   const int64_t base = (int64_t)head * p.nsplit * p.R;
   for (int x = tid; x < p.nsplit * p.R; x += kThreads) {
-    sm_m[x] = __ldcg(p.ws_m + base + x);
+    sm_w[x] = __ldcg(p.ws_m + base + x);
     sm_l[x] = __ldcg(p.ws_l + base + x);
   }
   __syncthreads();
-  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+  if (tid < p.R) {
     float M = -INFINITY;
-    for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, sm_m[s2 * p.R + hd]);
-    float acc = 0.f, l = 0.f;
-#pragma unroll 4
+    for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, sm_w[s2 * p.R + tid]);
+    float L = 0.f;
     for (int s2 = 0; s2 < p.nsplit; ++s2) {
-      const float ms = sm_m[s2 * p.R + hd];
+      const float ms = sm_w[s2 * p.R + tid];
       const float wt = (ms == -INFINITY) ? 0.f : ex2f(ms - M);
-      acc += wt * __ldcg(p.ws_acc + (base + (int64_t)s2 * p.R + hd) * 128 + d);
-      l += wt * sm_l[s2 * p.R + hd];
+      sm_w[s2 * p.R + tid] = wt;
+      L += wt * sm_l[s2 * p.R + tid];
     }
+    sm_M[tid] = M;
+    sm_L[tid] = L;
+  }
+  __syncthreads();
+  // warp w sums splits w, w+8, ... ; lane covers channels 4*lane .. 4*lane+3 ; all loads independent
+  for (int hd = 0; hd < p.R; ++hd) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = warp; s2 < p.nsplit; s2 += kWarps) {
+      const float wt = sm_w[s2 * p.R + hd];
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd) * 128) + lane);
+      a.x += wt * v.x; a.y += wt * v.y; a.z += wt * v.z; a.w += wt * v.w;
+    }
+    reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = a;
+  }
+  __syncthreads();
+  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + d];
+    const float l = sm_L[hd];
     const int64_t qrow = (int64_t)head * p.R + hd;
     if (p.pacc) {
       p.pacc[qrow * 128 + d] = acc;
-      if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
+      if (d == 0) { p.pm[qrow] = sm_M[hd]; p.pl[qrow] = l; }
     } else {
       store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
     }
@@ -547,10 +654,27 @@ decode_splitk_kernel(const DecodeParams p) {
   if (tid == 0) p.counters[head] = 0;   // ready for the next launch on this workspace
 }
 
+
 // ---- host side ---------------------------------------------------------------
 
 static size_t decode_smem_bytes(int NT) {
-  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)kWarps * kSlots * 8;
+  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 128 * 2 + (size_t)NT * 8 * 4 +
+         (size_t)kWarps * kSlots * 8;
+}
+
+template <int NT, bool kScaleTma>
+static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  const size_t smem = decode_smem_bytes(NT);
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  HQ_CUDA(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_dev = dev;
+  }
+  decode_splitk_kernel<NT, kScaleTma><<<grid, dim3(kThreads), smem, st>>>(p);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
 }
 
 static int max_ctas() { return 4 * sm_count(); }
@@ -586,6 +710,8 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   HQ_REQUIRE(a->out_dtype == HQ_BF16 || a->out_dtype == HQ_F16 || a->out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,
              "hq_decode_splitk: out_dtype %d", a->out_dtype);
 
+  HQ_REQUIRE(((uintptr_t)a->q & 7) == 0 && a->q_stride % 4 == 0, HQ_ERR_ALIGNMENT,
+             "hq_decode_splitk: q rows must be 8-byte aligned");
   DecodeParams p{};
   p.q = (const __nv_bfloat16*)a->q; p.q_stride = a->q_stride;
   p.n_quant = a->n_quant;
@@ -652,29 +778,17 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.ws_acc = (float*)(((uintptr_t)p.ws_acc + 15) & ~(uintptr_t)15);
 
   const int NT = a->kv_repeat <= 8 ? 1 : 2;
-  const size_t smem = decode_smem_bytes(NT);
-  // the split-merge staging (2 * nsplit * R floats) reuses the ring
-  HQ_REQUIRE((size_t)2 * nsplit * a->kv_repeat * 4 <= (size_t)kWarps * kSlots * kSlotBytes, HQ_ERR_UNSUPPORTED,
-             "hq_decode_splitk: too many splits (%d)", nsplit);
+  // the split-merge staging reuses the ring: weights + l (2 nsplit R) + 32 + warp partial sums (8 R 128) floats
+  HQ_REQUIRE(((size_t)2 * nsplit * a->kv_repeat + 36 + (size_t)kWarps * a->kv_repeat * 128) * 4 <=
+                 (size_t)kWarps * kSlots * kSlotBytes,
+             HQ_ERR_UNSUPPORTED, "hq_decode_splitk: too many splits (%d)", nsplit);
+  // scales can ride in the bulk copies when every 32-token group of a row starts on a
+  // 16-byte boundary and a row has room for the round-up of its tail to 8 tokens
+  const int64_t nq8 = ((int64_t)a->n_quant + 7) & ~(int64_t)7;
+  p.scale_tma = a->n_quant > 0 && aligned16(a->k_scale) && aligned16(a->v_scale) && a->ks_stride_bh % 8 == 0 &&
+                a->vs_stride_bh % 8 == 0 && a->ks_stride_bh >= nq8 && a->vs_stride_bh >= nq8;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid((unsigned)(a->BH_KV * nsplit)), block(kThreads);
-  if (NT == 1) {
-    static thread_local int attr_dev1 = -1;
-    int dev = 0; HQ_CUDA(cudaGetDevice(&dev));
-    if (attr_dev1 != dev) {
-      HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_dev1 = dev;
-    }
-    decode_splitk_kernel<1><<<grid, block, smem, st>>>(p);
-  } else {
-    static thread_local int attr_dev2 = -1;
-    int dev = 0; HQ_CUDA(cudaGetDevice(&dev));
-    if (attr_dev2 != dev) {
-      HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_dev2 = dev;
-    }
-    decode_splitk_kernel<2><<<grid, block, smem, st>>>(p);
-  }
-  HQ_CUDA(cudaGetLastError());
-  return HQ_OK;
+  dim3 grid((unsigned)(a->BH_KV * nsplit));
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true>(p, grid, st) : launch_decode<1, false>(p, grid, st);
+  return p.scale_tma ? launch_decode<2, true>(p, grid, st) : launch_decode<2, false>(p, grid, st);
 }
