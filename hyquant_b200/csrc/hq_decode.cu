@@ -191,13 +191,12 @@ template <int NT, bool kScaleTma>
 __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1)
 decode_splitk_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same | qs [NT*8][128] bf16 |
+  // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same |
   //         headC [NT*8] f32 | mbarriers [kWarps][kSlots]
   uint8_t* ring = smem;
   uint32_t* fragH = reinterpret_cast<uint32_t*>(smem + kWarps * kSlots * kSlotBytes);
   uint32_t* fragB = fragH + NT * 512;
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(fragB + NT * 512);
-  float* headC = reinterpret_cast<float*>(qs + NT * 8 * 128);
+  float* headC = reinterpret_cast<float*>(fragB + NT * 512);
   uint64_t* bars = reinterpret_cast<uint64_t*>(headC + NT * 8);
   __shared__ int s_last;
 
@@ -257,39 +256,42 @@ decode_splitk_kernel(const DecodeParams p) {
     for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
   }
 
-  // ---- 3. query rows -> shared memory, per-head offset constant of the biased K codes
+  // ---- 3. query fragments (B operands of S^T = K Q^T) scattered straight into fragment
+  // order, permuted along the channel axis to match the order in which channels fall out
+  // of the K loads; plus the per-head offset constant of the biased K codes.
+  // This thread holds channels 4*lane + x (x = 0..3) of head nt*8 + warp.
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int hd = nt * 8 + warp;
-    reinterpret_cast<uint2*>(qs + hd * 128)[lane] = qraw[nt];
-    const float q0 = __uint_as_float(qraw[nt].x << 16), q1 = __uint_as_float(qraw[nt].x & 0xFFFF0000u);
-    const float q2 = __uint_as_float(qraw[nt].y << 16), q3 = __uint_as_float(qraw[nt].y & 0xFFFF0000u);
-    // even channels meet 1032 + code, odd channels (pre-divided by 16) meet 1152 + 16 code
-    float c = 1032.f * (__half2float(__float2half_rn(q0)) + __half2float(__float2half_rn(q2))) +
-              1152.f * (__half2float(__float2half_rn(q1 * 0.0625f)) + __half2float(__float2half_rn(q3 * 0.0625f)));
+    const float qv[4] = {__uint_as_float(qraw[nt].x << 16), __uint_as_float(qraw[nt].x & 0xFFFF0000u),
+                         __uint_as_float(qraw[nt].y << 16), __uint_as_float(qraw[nt].y & 0xFFFF0000u)};
+    // INT4 path: word i of thread tt of a token row covers channels 32 tt + 8 i + m (nibble m);
+    // register r of MMA chunk c = 2 i + odd pairs nibbles (2 odd + r, 2 odd + r + 4).  Odd
+    // nibbles (r = 1) are high nibbles: the query value is pre-divided by 16.
+    {
+      const int tt = lane >> 3, i = (lane >> 1) & 3, isB = lane & 1;
+      __half* fh = reinterpret_cast<__half*>(fragH);
+      float c = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if (lane == 0) headC[hd] = c;
-  }
-  __syncthreads();
-
-  // ---- 4. query fragments: B operands of S^T = K Q^T, permuted along the channel
-  // axis to match the order in which channels fall out of the K loads.
-  for (int e = tid; e < NT * 512; e += kThreads) {
-    const int l = e & 31, r = (e >> 5) & 1, c = (e >> 6) & 7, nt = e >> 9;
-    const int gg = l >> 2, tt = l & 3, i = c >> 1, odd = c & 1;
-    const __nv_bfloat16* qrow = qs + (nt * 8 + gg) * 128;
-    // INT4 path: word i of thread tt covers channels 32 tt + 8 i + m (nibble m);
-    // register r of MMA chunk c pairs nibbles (2*odd + r, 2*odd + r + 4).  r = 1 are
-    // high nibbles: the query value is pre-divided by 16 (see cvt_nibbles_biased).
-    const int chA = 32 * tt + 8 * i + 2 * odd + r, chB = chA + 4;
-    const float sc = r ? 0.0625f : 1.0f;
-    const float qa = fminf(fmaxf(__bfloat162float(qrow[chA]) * sc, -65504.f), 65504.f);
-    const float qb = fminf(fmaxf(__bfloat162float(qrow[chB]) * sc, -65504.f), 65504.f);
-    fragH[e] = pack_f16x2(qa, qb);
-    // BF16 path: 16-byte chunk j = 4 i + tt covers channels 8 j .. 8 j + 7.
-    const int cbA = 8 * (4 * i + tt) + 4 * odd + 2 * r;
-    fragB[e] = *reinterpret_cast<const uint32_t*>(qrow + cbA);
+      for (int x = 0; x < 4; ++x) {
+        const int odd = x >> 1, r = x & 1;
+        const float v = fminf(fmaxf(qv[x] * (r ? 0.0625f : 1.0f), -65504.f), 65504.f);
+        const __half hv = __float2half_rn(v);
+        fh[((((nt * 8 + 2 * i + odd) * 2 + r) * 32) + 4 * warp + tt) * 2 + isB] = hv;
+        // even channels meet 1032 + code, odd channels meet 1152 + 16 code
+        c += (r ? 1152.f : 1032.f) * __half2float(hv);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+      if (lane == 0) headC[hd] = c;
+    }
+    // BF16 path: 16-byte chunk j = 4 i + tt of a token row covers channels 8 j .. 8 j + 7;
+    // chunk c = 2 i + odd takes channels 4 odd + (0,1 | 2,3) of it.
+    {
+      const int j = lane >> 1, tt = j & 3, i = j >> 2, odd = lane & 1;
+      fragB[((nt * 8 + 2 * i + odd) * 2 + 0) * 32 + 4 * warp + tt] = qraw[nt].x;
+      fragB[((nt * 8 + 2 * i + odd) * 2 + 1) * 32 + 4 * warp + tt] = qraw[nt].y;
+    }
   }
   __syncthreads();
 
@@ -592,20 +594,20 @@ decode_splitk_kernel(const DecodeParams p) {
   if (single) return;
 
   // ======================= merge the splits (last CTA of the head) ===========
-  __threadfence();
+  // Ticket: the CTA barrier orders every thread's partial stores before thread 0's
+  // release-add; the last arriver's acquire-add + barrier orders them before its loads.
   __syncthreads();
   if (tid == 0) {
-    const int ticket = atomicAdd(&p.counters[head], 1);
-    s_last = (ticket == p.nsplit - 1);
+    unsigned ticket;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + head) : "memory");
+    s_last = (ticket == (unsigned)(p.nsplit - 1));
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
-  // weights: sm_w[s*R + h] = 2^(m_s - M_h) ; sm_L[h] = sum_s w l
-  float* sm_w = reinterpret_cast<float*>(smem);             // [nsplit * R]
+  float* sm_w = reinterpret_cast<float*>(smem);             // [nsplit * R]  m, then weights 2^(m - M)
   float* sm_l = sm_w + p.nsplit * p.R;                      // [nsplit * R]
-  float* sm_M = sm_l + p.nsplit * p.R;                      // [R]
-  float* sm_L = sm_M + 16;                                  // [R]
+  float* sm_M = sm_l + p.nsplit * p.R;                      // [16]
+  float* sm_L = sm_M + 16;                                  // [16]
   float* red = sm_w + ((2 * p.nsplit * p.R + 32 + 3) & ~3); // [kWarps][R][128], 16-byte aligned
   const int64_t base = (int64_t)head * p.nsplit * p.R;
   for (int x = tid; x < p.nsplit * p.R; x += kThreads) {
@@ -613,29 +615,57 @@ decode_splitk_kernel(const DecodeParams p) {
     sm_l[x] = __ldcg(p.ws_l + base + x);
   }
   __syncthreads();
-  if (tid < p.R) {
+  // weights: warp `hd` (mod 8) reduces over the splits of head hd
+  for (int hd = warp; hd < p.R; hd += kWarps) {
     float M = -INFINITY;
-    for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, sm_w[s2 * p.R + tid]);
+    for (int s2 = lane; s2 < p.nsplit; s2 += 32) M = fmaxf(M, sm_w[s2 * p.R + hd]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     float L = 0.f;
-    for (int s2 = 0; s2 < p.nsplit; ++s2) {
-      const float ms = sm_w[s2 * p.R + tid];
+    for (int s2 = lane; s2 < p.nsplit; s2 += 32) {
+      const float ms = sm_w[s2 * p.R + hd];
       const float wt = (ms == -INFINITY) ? 0.f : ex2f(ms - M);
-      sm_w[s2 * p.R + tid] = wt;
-      L += wt * sm_l[s2 * p.R + tid];
+      sm_w[s2 * p.R + hd] = wt;
+      L += wt * sm_l[s2 * p.R + hd];
     }
-    sm_M[tid] = M;
-    sm_L[tid] = L;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) { sm_M[hd] = M; sm_L[hd] = L; }
   }
   __syncthreads();
-  // warp w sums splits w, w+8, ... ; lane covers channels 4*lane .. 4*lane+3 ; all loads independent
-  for (int hd = 0; hd < p.R; ++hd) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s2 = warp; s2 < p.nsplit; s2 += kWarps) {
-      const float wt = sm_w[s2 * p.R + hd];
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd) * 128) + lane);
-      a.x += wt * v.x; a.y += wt * v.y; a.z += wt * v.z; a.w += wt * v.w;
+  // warp w sums splits w, w+8, ... of every head; lane covers channels 4*lane .. 4*lane+3.
+  // Loads are issued in groups of 16 independent 16-byte reads (two heads x 8 splits).
+  for (int s0 = warp; s0 < p.nsplit; s0 += 8 * kWarps) {
+    for (int hd = 0; hd < p.R; hd += 2) {
+      float4 v[2][8];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int s2 = s0 + j * kWarps;
+          v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (s2 < p.nsplit && hd + hh < p.R)
+            v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
+        }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        if (hd + hh >= p.R) break;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int s2 = s0 + j * kWarps;
+          const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
+          a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
+        }
+        float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
+        if (s0 >= 8 * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
+        *dst = a;
+      }
     }
-    reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = a;
+  }
+  if (warp >= p.nsplit) {   // a warp without splits still owns a slot of `red`
+    for (int hd = 0; hd < p.R; ++hd)
+      reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   __syncthreads();
   for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
@@ -658,7 +688,7 @@ decode_splitk_kernel(const DecodeParams p) {
 // ---- host side ---------------------------------------------------------------
 
 static size_t decode_smem_bytes(int NT) {
-  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 128 * 2 + (size_t)NT * 8 * 4 +
+  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 +
          (size_t)kWarps * kSlots * 8;
 }
 
