@@ -610,7 +610,22 @@ decode_splitk_kernel(const DecodeParams p) {
   float* sm_L = sm_M + 16;                                  // [16]
   float* red = sm_w + ((2 * p.nsplit * p.R + 32 + 3) & ~3); // [kWarps][R][128], 16-byte aligned
   const int64_t base = (int64_t)head * p.nsplit * p.R;
-  for (int x = tid; x < p.nsplit * p.R; x += kThreads) {
+  const int nitems = p.nsplit * p.R;            // partial rows of this head: row k = split * R + head
+  // When R divides the warp count, warp w only ever meets head w % R (rows w, w+8, ...), so one
+  // accumulator per warp suffices and every partial row can be requested up front, in the same
+  // round trip to L2 as the maxima and sums.
+  const bool fast = (kWarps % p.R) == 0;
+  constexpr int kPre = 20;
+  float4 pre[kPre];
+  if (fast) {
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int k = warp + j * kWarps;
+      pre[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < nitems) pre[j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + k) * 128) + lane);
+    }
+  }
+  for (int x = tid; x < nitems; x += kThreads) {
     sm_w[x] = __ldcg(p.ws_m + base + x);
     sm_l[x] = __ldcg(p.ws_l + base + x);
   }
@@ -633,45 +648,64 @@ decode_splitk_kernel(const DecodeParams p) {
     if (lane == 0) { sm_M[hd] = M; sm_L[hd] = L; }
   }
   __syncthreads();
-  // warp w sums splits w, w+8, ... of every head; lane covers channels 4*lane .. 4*lane+3.
-  // Loads are issued in groups of 16 independent 16-byte reads (two heads x 8 splits).
-  for (int s0 = warp; s0 < p.nsplit; s0 += 8 * kWarps) {
-    for (int hd = 0; hd < p.R; hd += 2) {
-      float4 v[2][8];
+  if (fast) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh)
+    for (int j = 0; j < kPre; ++j) {
+      const int k = warp + j * kWarps;
+      const float wt = k < nitems ? sm_w[k] : 0.f;
+      a.x += wt * pre[j].x; a.y += wt * pre[j].y; a.z += wt * pre[j].z; a.w += wt * pre[j].w;
+    }
+    for (int k = warp + kPre * kWarps; k < nitems; k += kWarps) {
+      const float wt = sm_w[k];
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + k) * 128) + lane);
+      a.x += wt * v.x; a.y += wt * v.y; a.z += wt * v.z; a.w += wt * v.w;
+    }
+    reinterpret_cast<float4*>(red + (size_t)warp * 128)[lane] = a;     // partial of head warp % R
+  } else {
+    // generic GQA ratio: warp w sums splits w, w+8, ... of every head, 16 independent reads at a time
+    for (int s0 = warp; s0 < p.nsplit; s0 += 8 * kWarps) {
+      for (int hd = 0; hd < p.R; hd += 2) {
+        float4 v[2][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int s2 = s0 + j * kWarps;
-          v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (s2 < p.nsplit && hd + hh < p.R)
-            v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int s2 = s0 + j * kWarps;
+            v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s2 < p.nsplit && hd + hh < p.R)
+              v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
+          }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          if (hd + hh >= p.R) break;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int s2 = s0 + j * kWarps;
+            const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
+            a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
+          }
+          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
+          if (s0 >= 8 * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
+          *dst = a;
         }
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        if (hd + hh >= p.R) break;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int s2 = s0 + j * kWarps;
-          const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
-          a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
-        }
-        float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
-        if (s0 >= 8 * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
-        *dst = a;
       }
     }
-  }
-  if (warp >= p.nsplit) {   // a warp without splits still owns a slot of `red`
-    for (int hd = 0; hd < p.R; ++hd)
-      reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (warp >= p.nsplit) {   // a warp without splits still owns a slot of `red`
+      for (int hd = 0; hd < p.R; ++hd)
+        reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   __syncthreads();
   for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
     float acc = 0.f;
+    if (fast) {
+      for (int w = hd; w < kWarps; w += p.R) acc += red[(size_t)w * 128 + d];
+    } else {
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + d];
+      for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + d];
+    }
     const float l = sm_L[hd];
     const int64_t qrow = (int64_t)head * p.R + hd;
     if (p.pacc) {
