@@ -24,6 +24,9 @@ from .decode_d_stage import (  # noqa: F401
     quantize_per_token, quantize_per_token_into,
 )
 from .d_stage_kv_cache import DStageKVCache, DStageLayerCache, QuantizedKVCache  # noqa: F401
+from .sage_unified import (  # noqa: F401
+    full_attention_fp16_triton, hybrid_prefill, sage_fp8_attention, sage_unified_attention, sage_vertical_attention_v2,
+)
 from .patch._common import (  # noqa: F401
     D_STAGE_MODES, compute_vertical_indices, handle_d_stage_cache, is_d_stage_mode, topk_indices,
     validate_patch_args, vertical_scores,
@@ -32,6 +35,7 @@ from .patch._common import (  # noqa: F401
 __all__ = [
     "fused_d_stage_decode", "DStageKVCache", "DStageLayerCache", "create_cache_for_mode",
     "compute_vertical_indices", "quantize_per_token", "dequantize_per_token", "lse_merge",
+    "sage_vertical_attention_v2", "sage_unified_attention", "sage_fp8_attention", "full_attention_fp16_triton",
     "install_as_src", "HyQuantError",
 ]
 
@@ -58,13 +62,18 @@ def install_as_src() -> None:
     from .patch import _common
     src = types.ModuleType("src")
     ops = types.ModuleType("src.ops")
-    for name in ("fused_d_stage_decode", "DStageKVCache", "create_cache_for_mode"):
+    names = ["sage_unified_attention", "sage_vertical_attention_v2", "sage_fp8_attention",
+             "full_attention_fp16_triton", "fused_d_stage_decode", "DStageKVCache", "create_cache_for_mode"]
+    for name in names:
         setattr(ops, name, globals()[name])
-    ops.__all__ = ["fused_d_stage_decode", "DStageKVCache", "create_cache_for_mode"]
+    ops.__all__ = names
+    from . import sage_unified
+    ops.sage_unified = sage_unified
     ops.decode_d_stage = decode_d_stage
     ops.d_stage_kv_cache = d_stage_kv_cache
     src.ops, src.patch = ops, patch_pkg
     sys.modules.update({
         "src": src, "src.ops": ops, "src.ops.decode_d_stage": decode_d_stage,
-        "src.ops.d_stage_kv_cache": d_stage_kv_cache, "src.patch": patch_pkg, "src.patch._common": _common,
+        "src.ops.d_stage_kv_cache": d_stage_kv_cache, "src.ops.sage_unified": sage_unified,
+        "src.patch": patch_pkg, "src.patch._common": _common,
     })

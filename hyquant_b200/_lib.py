@@ -27,6 +27,7 @@ EXPORTS = [
     "hq_vertical_scores",
     "hq_topk",
     "hq_cache_reorganize",
+    "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_hybrid",
 ]
 
 
@@ -52,6 +53,20 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class PrefillArgs(C.Structure):
+    """Mirror of ``hq_prefill_args``."""
+    _fields_ = [
+        ("struct_bytes", C.c_int32), ("B", C.c_int32), ("H_Q", C.c_int32), ("H_KV", C.c_int32), ("N", C.c_int32),
+        ("head_dim", C.c_int32), ("window", C.c_int32), ("T", C.c_int32), ("out_dtype", C.c_int32),
+        ("reserved0", C.c_int32),
+        ("q_i8", C.c_void_p), ("q_bf", C.c_void_p), ("q_scale", C.c_void_p),
+        ("k_i8", C.c_void_p), ("k_bf", C.c_void_p), ("k_scale", C.c_void_p),
+        ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_sn", C.c_int64),
+        ("vert_k", C.c_void_p), ("vert_v", C.c_void_p), ("vmask", C.c_void_p), ("nv_valid", C.c_void_p),
+        ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sn", C.c_int64),
+    ]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -69,6 +84,12 @@ def _declare(lib):
     lib.hq_topk.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp]
     lib.hq_cache_reorganize.argtypes = [vp, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
                                         vp, vp, i64, vp, vp, i64, i32, vp]
+    lib.hq_prefill_quant_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
+    lib.hq_prefill_quant.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, i32,
+                                     vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    lib.hq_prefill_vertical_prepare.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, i64, i64,
+                                                vp, vp, vp, vp, vp]
+    lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
     for name in EXPORTS:
         if name not in ("hq_version", "hq_last_error"):
             getattr(lib, name).restype = C.c_int

@@ -1,0 +1,153 @@
+// Operand preparation for the hybrid prefill kernel (one pass over Q and K):
+//   * K smoothing: k_sm = k - mean_n(k) per (batch, kv-head, channel), formed in bf16
+//     like the reference (src/ops/sage_unified.py:565-568);
+//   * per-64-key-block INT8 of k_sm and per-128-query-block INT8 of q * sm_scale * log2(e)
+//     with scale = max|x| / 127 and round-half-away-from-zero
+//     (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101);
+//   * the pre-scaled BF16 query used by the BF16 tiles.
+// HBM-bound: reads Q and K once, writes the INT8 and BF16 copies.
+#include "hq_common.cuh"
+
+namespace hq {
+
+constexpr int kMeanChunks = 32;
+
+// partial[bh][chunk][128] = sum over the chunk's rows
+__global__ void __launch_bounds__(256)
+kmean_partial_kernel(const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sh, int64_t sn, int H, int N,
+                     float* __restrict__ partial) {
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, chunk = blockIdx.x;
+  const int d = threadIdx.x & 127, half = threadIdx.x >> 7;
+  const int rows_per = (N + kMeanChunks - 1) / kMeanChunks;
+  const int r0 = chunk * rows_per, r1 = min(N, r0 + rows_per);
+  const __nv_bfloat16* base = k + b * sb + h * sh + d;
+  float acc = 0.f;
+  for (int r = r0 + half; r < r1; r += 2) acc += __bfloat162float(base[(int64_t)r * sn]);
+  __shared__ float s[256];
+  s[threadIdx.x] = acc;
+  __syncthreads();
+  if (half == 0) partial[((int64_t)bh * kMeanChunks + chunk) * 128 + d] = s[d] + s[128 + d];
+}
+
+__global__ void kmean_final_kernel(const float* __restrict__ partial, int N, int smooth, __nv_bfloat16* __restrict__ mean) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  float acc = 0.f;
+  for (int c = 0; c < kMeanChunks; ++c) acc += partial[((int64_t)bh * kMeanChunks + c) * 128 + d];
+  mean[(int64_t)bh * 128 + d] = __float2bfloat16_rn(smooth ? acc / (float)N : 0.f);
+}
+
+__device__ __forceinline__ int8_t q_half_away(float x, float scale) {
+  float y = x / scale;
+  y += y >= 0.f ? 0.5f : -0.5f;
+  y = fminf(fmaxf(truncf(y), -128.f), 127.f);
+  return (int8_t)(int)y;
+}
+
+// One CTA per block of BLK rows (BLK = 64 for K, 128 for Q) of one head: 256 threads.
+// kIsK: subtract the bf16 mean (rounding the difference to bf16) and write it as the BF16 copy;
+// else multiply by `mul` in fp32, INT8 from the fp32 product and BF16 copy of the product.
+template <int BLK, bool kIsK>
+__global__ void __launch_bounds__(256)
+block_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
+                   const __nv_bfloat16* __restrict__ mean, float mul,
+                   int8_t* __restrict__ xi8, __nv_bfloat16* __restrict__ xbf, float* __restrict__ scale, int nblk) {
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, blk = blockIdx.x;
+  const int tid = threadIdx.x;
+  constexpr int kPer = BLK * 128 / 256;        // elements per thread, 8 at a time
+  const int row0 = blk * BLK;
+  float v[kPer];
+  float amax = 0.f;
+#pragma unroll
+  for (int it = 0; it < kPer / 8; ++it) {
+    const int e = (it * 256 + tid) * 8;          // element index inside the block
+    const int r = e >> 7, c = e & 127;
+    const int row = row0 + r;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (row < N) raw = __ldg(reinterpret_cast<const uint4*>(x + b * sb + h * sh + (int64_t)row * sn + c));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint4 outbf;
+    uint32_t* ob = reinterpret_cast<uint32_t*>(&outbf);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
+      if (kIsK) {
+        const float m0 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j]);
+        const float m1 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j + 1]);
+        f0 = __bfloat162float(__float2bfloat16_rn(f0 - m0));
+        f1 = __bfloat162float(__float2bfloat16_rn(f1 - m1));
+      } else {
+        f0 *= mul; f1 *= mul;
+      }
+      if (row >= N) { f0 = 0.f; f1 = 0.f; }
+      v[it * 8 + 2 * j] = f0; v[it * 8 + 2 * j + 1] = f1;
+      amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+      __nv_bfloat162 pk = __floats2bfloat162_rn(f0, f1);
+      ob[j] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    if (row < N) *reinterpret_cast<uint4*>(xbf + ((int64_t)bh * N + row) * 128 + c) = outbf;
+  }
+  // block-wide absmax
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  __shared__ float s_max[8];
+  if ((tid & 31) == 0) s_max[tid >> 5] = amax;
+  __syncthreads();
+  amax = s_max[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_max[i]);
+  const float sc = fmaxf(amax, 1e-30f) / 127.f;     // an all-zero block keeps codes 0 instead of NaN
+  if (tid == 0) scale[(int64_t)bh * nblk + blk] = sc;
+#pragma unroll
+  for (int it = 0; it < kPer / 8; ++it) {
+    const int e = (it * 256 + tid) * 8;
+    const int r = e >> 7, c = e & 127;
+    const int row = row0 + r;
+    if (row >= N) continue;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= ((uint32_t)(uint8_t)q_half_away(v[it * 8 + j], sc)) << (8 * j);
+      hi |= ((uint32_t)(uint8_t)q_half_away(v[it * 8 + 4 + j], sc)) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(xi8 + ((int64_t)bh * N + row) * 128 + c) = make_uint2(lo, hi);
+  }
+}
+
+}  // namespace hq
+
+extern "C" int hq_prefill_quant_workspace_bytes(int B, int H_KV, int64_t* bytes) {
+  using namespace hq;
+  HQ_REQUIRE(bytes && B > 0 && H_KV > 0, HQ_ERR_INVALID, "hq_prefill_quant_workspace_bytes: bad sizes");
+  *bytes = (int64_t)B * H_KV * kMeanChunks * 128 * 4;
+  return HQ_OK;
+}
+
+extern "C" int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
+                                const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn,
+                                int B, int H_Q, int H_KV, int N, float sm_scale, int smooth_k,
+                                void* q_i8, void* q_bf, float* q_scale,
+                                void* k_i8, void* k_bf, float* k_scale, void* k_mean,
+                                void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(B > 0 && H_Q > 0 && H_KV > 0 && N > 0, HQ_ERR_INVALID, "hq_prefill_quant: bad sizes");
+  HQ_REQUIRE(q && k && q_i8 && q_bf && q_scale && k_i8 && k_bf && k_scale && k_mean && workspace, HQ_ERR_INVALID,
+             "hq_prefill_quant: null pointer");
+  int64_t need = 0;
+  hq_prefill_quant_workspace_bytes(B, H_KV, &need);
+  HQ_REQUIRE(workspace_bytes >= need, HQ_ERR_WORKSPACE, "hq_prefill_quant: workspace of %lld bytes needed", (long long)need);
+  HQ_REQUIRE(aligned16(q) && aligned16(k) && q_sb % 8 == 0 && q_sh % 8 == 0 && q_sn % 8 == 0 && k_sb % 8 == 0 &&
+                 k_sh % 8 == 0 && k_sn % 8 == 0,
+             HQ_ERR_ALIGNMENT, "hq_prefill_quant: q/k rows must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const __nv_bfloat16* kk = (const __nv_bfloat16*)k;
+  kmean_partial_kernel<<<dim3(kMeanChunks, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (float*)workspace);
+  kmean_final_kernel<<<B * H_KV, 128, 0, st>>>((const float*)workspace, N, smooth_k, (__nv_bfloat16*)k_mean);
+  const int nkb = (N + 63) / 64, nqb = (N + 127) / 128;
+  block_quant_kernel<64, true><<<dim3(nkb, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (const __nv_bfloat16*)k_mean,
+                                                                   1.0f, (int8_t*)k_i8, (__nv_bfloat16*)k_bf, k_scale, nkb);
+  block_quant_kernel<128, false><<<dim3(nqb, B * H_Q), 256, 0, st>>>((const __nv_bfloat16*)q, q_sb, q_sh, q_sn, H_Q, N, nullptr,
+                                                                    sm_scale * 1.44269504f, (int8_t*)q_i8,
+                                                                    (__nv_bfloat16*)q_bf, q_scale, nqb);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}

@@ -1,0 +1,143 @@
+"""Hybrid-precision prefill attention — host-side mirror of the reference module
+``src/ops/sage_unified.py`` (``sage_vertical_attention_v2``, ``sage_unified_attention``)
+plus ``full_attention_fp16_triton`` (``src/ops/v_sageattention.py``) and
+``sage_fp8_attention`` (``src/ops/sage_fp8_attention.py``), all served by one sm_100a
+kernel (``hq_prefill_hybrid``) after one operand-preparation pass (``hq_prefill_quant``).
+
+By design nothing is expanded to query heads and nothing is physically reordered:
+K/V stay at kv-head granularity, the vertical lines of a query head are removed from
+its INT8 pass by a bit mask and served from a small gathered BF16 copy.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import HyQuantError, PrefillArgs
+
+_LOG2_E = 1.44269504
+
+
+def _prep_inputs(q, k, v):
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _lib.require_cuda(t, name)
+    B, H_q, N, D = q.shape
+    if D != 128:
+        raise HyQuantError(f"head_dim {D} is not built (128 only)")
+    H_kv = k.shape[1]
+    if H_q % H_kv != 0 or k.shape[2] != N or v.shape[2] != N:
+        raise HyQuantError("q/k/v shapes do not agree")
+    def bf(t):
+        t = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+        ok = t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+    return bf(q), bf(k), bf(v), B, H_q, H_kv, N
+
+
+def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smooth_k: bool):
+    """Operand preparation (``hq_prefill_quant``): returns q_i8, q_bf, q_scale, k_i8, k_bf, k_scale, k_mean."""
+    B, H_q, N, _ = qb.shape
+    H_kv = kb.shape[1]
+    dev = qb.device
+    lib = _lib.lib()
+    nqb, nkb = (N + 127) // 128, (N + 63) // 64
+    q_i8 = torch.empty(B, H_q, N, 128, dtype=torch.int8, device=dev)
+    q_bf = torch.empty(B, H_q, N, 128, dtype=torch.bfloat16, device=dev)
+    q_sc = torch.empty(B, H_q, nqb, dtype=torch.float32, device=dev)
+    k_i8 = torch.empty(B, H_kv, N, 128, dtype=torch.int8, device=dev)
+    k_bf = torch.empty(B, H_kv, N, 128, dtype=torch.bfloat16, device=dev)
+    k_sc = torch.empty(B, H_kv, nkb, dtype=torch.float32, device=dev)
+    k_mean = torch.empty(B, H_kv, 128, dtype=torch.bfloat16, device=dev)
+    nb = C.c_int64(0)
+    _lib.check(lib.hq_prefill_quant_workspace_bytes(B, H_kv, C.byref(nb)), "hq_prefill_quant_workspace_bytes")
+    ws = torch.empty(int(nb.value), dtype=torch.uint8, device=dev)
+    rc = lib.hq_prefill_quant(qb.data_ptr(), qb.stride(0), qb.stride(1), qb.stride(2),
+                              kb.data_ptr(), kb.stride(0), kb.stride(1), kb.stride(2),
+                              B, H_q, H_kv, N, float(sm_scale), 1 if smooth_k else 0,
+                              q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr(),
+                              k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr(), k_mean.data_ptr(),
+                              ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "hq_prefill_quant")
+    return q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean
+
+
+def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
+                   window_size: int, sm_scale: Optional[float], smooth_k: bool) -> torch.Tensor:
+    """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
+    vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
+    dtype = q.dtype
+    qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
+    dev = q.device
+    lib = _lib.lib()
+    st = _lib.stream_ptr(dev)
+    if sm_scale is None:
+        sm_scale = 128 ** -0.5
+    nqb, nkb = (N + 127) // 128, (N + 63) // 64
+    q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
+    T = 0
+    vert_k = vert_v = vmask = nvv = None
+    prefix_len = max(0, N - window_size)
+    if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
+        if tuple(vertical_indices.shape[:2]) != (B, H_q):
+            raise HyQuantError("vertical_indices must be [B, H_q, T]")
+        vid = vertical_indices.to(device=dev, dtype=torch.int64).clamp(0, prefix_len - 1)   # reference :510
+        vasc = vid.sort(dim=-1).values.to(torch.int32).contiguous()
+        T = int(vasc.shape[-1])
+        vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+        vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+        vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
+        nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
+        rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
+                                             vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
+                                             vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
+        _lib.check(rc, "hq_prefill_vertical_prepare")
+    out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)
+    a = PrefillArgs()
+    a.struct_bytes = C.sizeof(PrefillArgs)
+    a.B, a.H_Q, a.H_KV, a.N, a.head_dim, a.window, a.T = B, H_q, H_kv, N, 128, int(window_size), T
+    a.out_dtype = _lib.dtype_code(dtype)
+    a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
+    a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
+    a.v, a.v_sb, a.v_sh, a.v_sn = vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2)
+    if T:
+        a.vert_k, a.vert_v, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
+    a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    _lib.check(lib.hq_prefill_hybrid(C.byref(a), st), "hq_prefill_hybrid")
+    return out
+
+
+def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,
+                               window_size: int = 256, sm_scale: Optional[float] = None,
+                               smooth_k: bool = True) -> torch.Tensor:
+    """int8 QK for the rest, 16-bit QK for vertical lines + window (reference sage_unified.py:550-622).
+    q [B,H_q,N,D], k/v [B,H_kv,N,D], vertical_indices [B,H_q,T] int64; returns q's dtype."""
+    return hybrid_prefill(q, k, v, vertical_indices, window_size, sm_scale, smooth_k)
+
+
+def sage_unified_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, window_size: int = 0,
+                           sm_scale: Optional[float] = None, smooth_k: bool = True) -> torch.Tensor:
+    """int8 QK prefix + 16-bit window (reference sage_unified.py:234-313); window_size=0 keeps only the
+    diagonal query block in 16 bit."""
+    return hybrid_prefill(q, k, v, None, window_size, sm_scale, smooth_k)
+
+
+def full_attention_fp16_triton(q, k, v, tensor_layout: str = "HND", is_causal: bool = True,
+                               sm_scale: Optional[float] = None, **kwargs):
+    """16-bit causal attention without quantisation (reference v_sageattention.py:14-51)."""
+    del kwargs
+    if tensor_layout == "NHD":
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    out = hybrid_prefill(q, k, v, None, int(q.shape[2]), sm_scale, False)
+    return out.transpose(1, 2) if tensor_layout == "NHD" else out
+
+
+def sage_fp8_attention(q, k, v, *, is_causal: bool = True, sm_scale: Optional[float] = None, smooth_k: bool = True):
+    """INT8 QK causal attention without vertical lines or window (reference sage_fp8_attention.py:15-45).
+    The P V product of this build runs in BF16."""
+    if not is_causal:
+        raise HyQuantError("only causal attention is built")
+    return hybrid_prefill(q, k, v, None, 0, sm_scale, smooth_k)

@@ -184,6 +184,56 @@ int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_
                         void* k_scale, void* v_scale, int64_t scale_stride_bh,
                         int scale_mode, void* stream);
 
+/* --------------------------------------------------------------------------
+ * Hybrid prefill, step 1: operand preparation.  Replaces per_block_int8 and the
+ * K-smoothing / query pre-scaling of sage_vertical_attention_v2
+ * (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101,
+ *  src/ops/sage_unified.py:565-576).
+ *   q [B,H_Q,N,128] bf16, k [B,H_KV,N,128] bf16 (strides in elements)
+ *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (q * sm_scale * log2 e), q_scale fp32 [B,H_Q,ceil(N/128)]
+ *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,ceil(N/64)], k_mean bf16 [B,H_KV,128]
+ * smooth_k == 0 leaves K unshifted.
+ */
+int hq_prefill_quant_workspace_bytes(int B, int H_KV, int64_t* bytes);
+int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
+                     const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn,
+                     int B, int H_Q, int H_KV, int N, float sm_scale, int smooth_k,
+                     void* q_i8, void* q_bf, float* q_scale,
+                     void* k_i8, void* k_bf, float* k_scale, void* k_mean,
+                     void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Step 2: vertical-line bookkeeping.  Replaces reorder_kv_for_vertical
+ * (src/ops/sage_unified.py:499-547) without expanding K/V to query heads:
+ *   vidx_asc int32 [B,H_Q,T] ascending distinct positions
+ *   vert_k/vert_v bf16 [B,H_Q,T,128] gathered rows (k from k_bf), vmask u64 [B,H_Q,ceil(N/64)],
+ *   nv_valid int32 [B,H_Q,ceil(N/128)] = number of vertical lines below the window start of a query block.
+ */
+int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int window, int T,
+                                const void* k_bf, const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
+                                void* vert_k, void* vert_v, uint64_t* vmask, int32_t* nv_valid, void* stream);
+
+/* Step 3: the attention kernel.  Replaces _attn_fwd_vertical_v2 / _attn_fwd_unified
+ * (src/ops/sage_unified.py:398-496, 112-231): causal, GQA-native, INT8 QK^T for the
+ * non-vertical prefix, BF16 QK^T for vertical lines and for the window; one online softmax.
+ * window == N gives plain BF16 causal attention (full_attention_fp16_triton,
+ * src/ops/v_sageattention.py:14-51); T == 0 gives sage_unified_attention.
+ */
+typedef struct hq_prefill_args {
+  int32_t struct_bytes;
+  int32_t B, H_Q, H_KV, N, head_dim;
+  int32_t window;              /* W; keys within W-1 of a query block's start (64-aligned) are BF16 */
+  int32_t T;                   /* vertical lines per query head (0 = none) */
+  int32_t out_dtype;
+  int32_t reserved0;
+  const void* q_i8; const void* q_bf; const float* q_scale;
+  const void* k_i8; const void* k_bf; const float* k_scale;
+  const void* v; int64_t v_sb, v_sh, v_sn;     /* bf16 [B,H_KV,N,128], strides in elements */
+  const void* vert_k; const void* vert_v;
+  const uint64_t* vmask; const int32_t* nv_valid;
+  void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements */
+} hq_prefill_args;
+int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
