@@ -1,7 +1,7 @@
 // Hybrid-precision causal prefill attention, GQA-native.
 //
 // For the 128-query block starting at s of query head h (kv head h / R):
-//   keys j <  wla(s)          : INT8 QK^T (per-128 Q block / per-64 K block scales, smoothed K)
+//   keys j <  wla(s)          : INT8 QK^T (one scale per query row and per key row, smoothed K)
 //                               unless j is a vertical line of head h -> masked here and taken
 //                               from the gathered BF16 vertical tiles instead;
 //   vertical lines < wla(s)   : BF16 QK^T on the gathered rows (ascending position);
@@ -22,8 +22,8 @@
 namespace hq {
 
 struct PrefillParams {
-  const int8_t* q_i8; const __nv_bfloat16* q_bf; const float* q_scale;        // [B,H_Q,N,128], [B,H_Q,nqb]
-  const int8_t* k_i8; const __nv_bfloat16* k_bf; const float* k_scale;        // [B,H_KV,N,128], [B,H_KV,nkb]
+  const int8_t* q_i8; const __nv_bfloat16* q_bf; const float* q_scale;        // [B,H_Q,N,128], [B,H_Q,N]
+  const int8_t* k_i8; const __nv_bfloat16* k_bf; const float* k_scale;        // [B,H_KV,N,128], [B,H_KV,N]
   const __nv_bfloat16* v; int64_t v_sb, v_sh, v_sn;                            // [B,H_KV,N,128] strided
   const __nv_bfloat16* vert_k; const __nv_bfloat16* vert_v;                    // [B,H_Q,T,128] ascending position
   const unsigned long long* vmask;                                             // [B,H_Q,nkb]
@@ -130,8 +130,15 @@ prefill_hybrid_kernel(const PrefillParams p) {
   auto issue_tile = [&](int i) {
     const PfTile tl = tile_of(i);
     uint8_t* st = sT + (i & 1) * kStageBytes;
-    if (tl.kind == 0) load_tile(st, tl.k, 128, kBN, tl.valid, 128, tid);
-    else load_tile(st, tl.k, 256, kBN, tl.valid, 256, tid);
+    if (tl.kind == 0) {
+      load_tile(st, tl.k, 128, kBN, tl.valid, 128, tid);
+      if (tid < 64) {   // the 64 key scales of the tile ride behind the 8 KB of codes
+        const uint32_t d = smem_u32(st + 8192 + tid * 4);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(p.k_scale + bhk * p.N + tl.key0 + tid) : "memory");
+      }
+    } else {
+      load_tile(st, tl.k, 256, kBN, tl.valid, 256, tid);
+    }
     load_tile(st + 16384, tl.v, tl.v_stride, kBN, tl.valid, 256, tid);
   };
 
@@ -143,7 +150,12 @@ prefill_hybrid_kernel(const PrefillParams p) {
     if (n_tiles > 0) issue_tile(0);
     cp_async_commit();
   }
-  const float qsc = p.q_scale[bhq * p.nqb + qb];
+  float qsc[2];       // INT8 scales of this thread's accumulator rows g and g + 8
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = s0 + warp * 16 + g + 8 * r;
+    qsc[r] = row < p.N ? p.q_scale[bhq * p.N + row] : 0.f;
+  }
 
   float O[16][4];
 #pragma unroll
@@ -178,15 +190,17 @@ prefill_hybrid_kernel(const PrefillParams p) {
           mma_s8(Si[2 * np + 1], a, bq[2], bq[3]);
         }
       }
-      const float sc = qsc * p.k_scale[bhk * p.nkb + tl.kblk];
+      const float* ksc = reinterpret_cast<const float*>(sK + 8192);
       const unsigned long long vm = p.T > 0 ? p.vmask[bhq * p.nkb + tl.kblk] : 0ull;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
+      for (int j = 0; j < 8; ++j) {
+        const float2 kc = *reinterpret_cast<const float2*>(ksc + 8 * j + 2 * t);
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           const int col = 8 * j + 2 * t + (x & 1);
-          S[j][x] = ((vm >> col) & 1ull) ? -INFINITY : (float)Si[j][x] * sc;
+          S[j][x] = ((vm >> col) & 1ull) ? -INFINITY : (float)Si[j][x] * (qsc[x >> 1] * ((x & 1) ? kc.y : kc.x));
         }
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) S[j][0] = S[j][1] = S[j][2] = S[j][3] = 0.f;

@@ -1,9 +1,11 @@
 // Operand preparation for the hybrid prefill kernel (one pass over Q and K):
 //   * K smoothing: k_sm = k - mean_n(k) per (batch, kv-head, channel), formed in bf16
 //     like the reference (src/ops/sage_unified.py:565-568);
-//   * per-64-key-block INT8 of k_sm and per-128-query-block INT8 of q * sm_scale * log2(e)
-//     with scale = max|x| / 127 and round-half-away-from-zero
-//     (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101);
+//   * INT8 of k_sm and of q * sm_scale * log2(e) with scale = max|x| / 127 and
+//     round-half-away-from-zero — the arithmetic of the reference's block quantiser
+//     (src/ops/vendor/sageattention/triton/quant_per_block.py:21-47) applied with one scale
+//     per token row instead of one per 64-key / 128-query block: an outlier row then costs
+//     no precision in its neighbours, and the scales are applied to the fp32 score for free;
 //   * the pre-scaled BF16 query used by the BF16 tiles.
 // HBM-bound: reads Q and K once, writes the INT8 and BF16 copies.
 #include "hq_common.cuh"
@@ -43,74 +45,55 @@ __device__ __forceinline__ int8_t q_half_away(float x, float scale) {
   return (int8_t)(int)y;
 }
 
-// One CTA per block of BLK rows (BLK = 64 for K, 128 for Q) of one head: 256 threads.
+// 16 rows per CTA (256 threads, 16 threads per 128-channel row, 8 channels each).
 // kIsK: subtract the bf16 mean (rounding the difference to bf16) and write it as the BF16 copy;
 // else multiply by `mul` in fp32, INT8 from the fp32 product and BF16 copy of the product.
-template <int BLK, bool kIsK>
+// One INT8 scale per ROW (token): scale = max|x| / 127.
+template <bool kIsK>
 __global__ void __launch_bounds__(256)
-block_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
-                   const __nv_bfloat16* __restrict__ mean, float mul,
-                   int8_t* __restrict__ xi8, __nv_bfloat16* __restrict__ xbf, float* __restrict__ scale, int nblk) {
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, blk = blockIdx.x;
+row_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
+                 const __nv_bfloat16* __restrict__ mean, float mul,
+                 int8_t* __restrict__ xi8, __nv_bfloat16* __restrict__ xbf, float* __restrict__ scale) {
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
   const int tid = threadIdx.x;
-  constexpr int kPer = BLK * 128 / 256;        // elements per thread, 8 at a time
-  const int row0 = blk * BLK;
-  float v[kPer];
+  const int row = blockIdx.x * 16 + (tid >> 4), c = (tid & 15) * 8;
+  const bool ok = row < N;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (ok) raw = __ldg(reinterpret_cast<const uint4*>(x + b * sb + h * sh + (int64_t)row * sn + c));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float v[8];
   float amax = 0.f;
+  uint4 outbf;
+  uint32_t* ob = reinterpret_cast<uint32_t*>(&outbf);
 #pragma unroll
-  for (int it = 0; it < kPer / 8; ++it) {
-    const int e = (it * 256 + tid) * 8;          // element index inside the block
-    const int r = e >> 7, c = e & 127;
-    const int row = row0 + r;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (row < N) raw = __ldg(reinterpret_cast<const uint4*>(x + b * sb + h * sh + (int64_t)row * sn + c));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    uint4 outbf;
-    uint32_t* ob = reinterpret_cast<uint32_t*>(&outbf);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
-      if (kIsK) {
-        const float m0 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j]);
-        const float m1 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j + 1]);
-        f0 = __bfloat162float(__float2bfloat16_rn(f0 - m0));
-        f1 = __bfloat162float(__float2bfloat16_rn(f1 - m1));
-      } else {
-        f0 *= mul; f1 *= mul;
-      }
-      if (row >= N) { f0 = 0.f; f1 = 0.f; }
-      v[it * 8 + 2 * j] = f0; v[it * 8 + 2 * j + 1] = f1;
-      amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
-      __nv_bfloat162 pk = __floats2bfloat162_rn(f0, f1);
-      ob[j] = *reinterpret_cast<uint32_t*>(&pk);
+  for (int j = 0; j < 4; ++j) {
+    float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
+    if (kIsK) {
+      const float m0 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j]);
+      const float m1 = __bfloat162float(mean[(int64_t)bh * 128 + c + 2 * j + 1]);
+      f0 = __bfloat162float(__float2bfloat16_rn(f0 - m0));
+      f1 = __bfloat162float(__float2bfloat16_rn(f1 - m1));
+    } else {
+      f0 *= mul; f1 *= mul;
     }
-    if (row < N) *reinterpret_cast<uint4*>(xbf + ((int64_t)bh * N + row) * 128 + c) = outbf;
+    v[2 * j] = f0; v[2 * j + 1] = f1;
+    amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+    __nv_bfloat162 pk = __floats2bfloat162_rn(f0, f1);
+    ob[j] = *reinterpret_cast<uint32_t*>(&pk);
   }
-  // block-wide absmax
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  __shared__ float s_max[8];
-  if ((tid & 31) == 0) s_max[tid >> 5] = amax;
-  __syncthreads();
-  amax = s_max[0];
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!ok) return;
+  *reinterpret_cast<uint4*>(xbf + ((int64_t)bh * N + row) * 128 + c) = outbf;
+  const float sc = fmaxf(amax, 1e-30f) / 127.f;     // an all-zero row keeps codes 0 instead of NaN
+  if ((tid & 15) == 0) scale[(int64_t)bh * N + row] = sc;
+  uint32_t lo = 0, hi = 0;
 #pragma unroll
-  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_max[i]);
-  const float sc = fmaxf(amax, 1e-30f) / 127.f;     // an all-zero block keeps codes 0 instead of NaN
-  if (tid == 0) scale[(int64_t)bh * nblk + blk] = sc;
-#pragma unroll
-  for (int it = 0; it < kPer / 8; ++it) {
-    const int e = (it * 256 + tid) * 8;
-    const int r = e >> 7, c = e & 127;
-    const int row = row0 + r;
-    if (row >= N) continue;
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      lo |= ((uint32_t)(uint8_t)q_half_away(v[it * 8 + j], sc)) << (8 * j);
-      hi |= ((uint32_t)(uint8_t)q_half_away(v[it * 8 + 4 + j], sc)) << (8 * j);
-    }
-    *reinterpret_cast<uint2*>(xi8 + ((int64_t)bh * N + row) * 128 + c) = make_uint2(lo, hi);
+  for (int j = 0; j < 4; ++j) {
+    lo |= ((uint32_t)(uint8_t)q_half_away(v[j], sc)) << (8 * j);
+    hi |= ((uint32_t)(uint8_t)q_half_away(v[4 + j], sc)) << (8 * j);
   }
+  *reinterpret_cast<uint2*>(xi8 + ((int64_t)bh * N + row) * 128 + c) = make_uint2(lo, hi);
 }
 
 }  // namespace hq
@@ -142,12 +125,12 @@ extern "C" int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64
   const __nv_bfloat16* kk = (const __nv_bfloat16*)k;
   kmean_partial_kernel<<<dim3(kMeanChunks, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (float*)workspace);
   kmean_final_kernel<<<B * H_KV, 128, 0, st>>>((const float*)workspace, N, smooth_k, (__nv_bfloat16*)k_mean);
-  const int nkb = (N + 63) / 64, nqb = (N + 127) / 128;
-  block_quant_kernel<64, true><<<dim3(nkb, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (const __nv_bfloat16*)k_mean,
-                                                                   1.0f, (int8_t*)k_i8, (__nv_bfloat16*)k_bf, k_scale, nkb);
-  block_quant_kernel<128, false><<<dim3(nqb, B * H_Q), 256, 0, st>>>((const __nv_bfloat16*)q, q_sb, q_sh, q_sn, H_Q, N, nullptr,
-                                                                    sm_scale * 1.44269504f, (int8_t*)q_i8,
-                                                                    (__nv_bfloat16*)q_bf, q_scale, nqb);
+  const int nrb = (N + 15) / 16;
+  row_quant_kernel<true><<<dim3(nrb, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (const __nv_bfloat16*)k_mean, 1.0f,
+                                                             (int8_t*)k_i8, (__nv_bfloat16*)k_bf, k_scale);
+  row_quant_kernel<false><<<dim3(nrb, B * H_Q), 256, 0, st>>>((const __nv_bfloat16*)q, q_sb, q_sh, q_sn, H_Q, N, nullptr,
+                                                             sm_scale * 1.44269504f, (int8_t*)q_i8, (__nv_bfloat16*)q_bf,
+                                                             q_scale);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

@@ -136,6 +136,8 @@ def vertical_scores(query_states: torch.Tensor, key_states: torch.Tensor, window
     if k.stride(3) != 1 or (k.stride(2) % 8) or (k.stride(1) % 8) or (k.stride(0) % 8) or k.data_ptr() % 16:
         k = k.contiguous()
     tail_len = min(window_size, n_q)
+    if tail_len == 0:          # the reference's slice [-0:] keeps every query
+        tail_len = n_q
     pooled = torch.empty(B, H_Q, D, dtype=torch.float32, device=q.device)
     scores = torch.empty(B, H_Q, P, dtype=torch.float32, device=q.device)
     rl = 1 if round_like_reference else 0

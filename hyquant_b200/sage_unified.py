@@ -47,10 +47,10 @@ def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smoot
     nqb, nkb = (N + 127) // 128, (N + 63) // 64
     q_i8 = torch.empty(B, H_q, N, 128, dtype=torch.int8, device=dev)
     q_bf = torch.empty(B, H_q, N, 128, dtype=torch.bfloat16, device=dev)
-    q_sc = torch.empty(B, H_q, nqb, dtype=torch.float32, device=dev)
+    q_sc = torch.empty(B, H_q, N, dtype=torch.float32, device=dev)
     k_i8 = torch.empty(B, H_kv, N, 128, dtype=torch.int8, device=dev)
     k_bf = torch.empty(B, H_kv, N, 128, dtype=torch.bfloat16, device=dev)
-    k_sc = torch.empty(B, H_kv, nkb, dtype=torch.float32, device=dev)
+    k_sc = torch.empty(B, H_kv, N, dtype=torch.float32, device=dev)
     k_mean = torch.empty(B, H_kv, 128, dtype=torch.bfloat16, device=dev)
     nb = C.c_int64(0)
     _lib.check(lib.hq_prefill_quant_workspace_bytes(B, H_kv, C.byref(nb)), "hq_prefill_quant_workspace_bytes")

@@ -1,0 +1,89 @@
+"""Multi-GPU decode: one process per GPU, ``torch.distributed`` for the plumbing.
+
+Two ways the path shards (the reference itself has neither; results equal the
+single-GPU result):
+
+* KV-head groups — every (batch, kv-head) is independent in decode, flush, freeze and
+  prefill, so rank r owns kv-heads ``kv_head_range(H_KV, world, r)`` and their query
+  heads.  No collective on the data path; outputs stay per rank.
+* Sequence shards (very long prefixes) — contiguous 128-token-aligned ranges of the INT4
+  prefix and contiguous ranges of the BF16 vertical-line segment per rank; window and
+  staging live on the last rank, which also receives the staging flushes.  Each rank runs
+  the decode kernel in partial mode, the un-normalised softmax states ``(m, l, acc)`` are
+  all-gathered (NCCL over NVLink; 66.5 KB per rank at B=4, 32 query heads) and merged by
+  ``hq_lse_merge`` on every rank.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+
+
+def kv_head_range(h_kv: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous kv-head range of ``rank``; requires ``h_kv % world == 0``."""
+    if h_kv % world != 0:
+        raise ValueError(f"{h_kv} kv heads do not divide over {world} ranks")
+    per = h_kv // world
+    return rank * per, (rank + 1) * per
+
+
+def sequence_shard_plan(n_quant: int, n_topk: int, world: int, align: int = 128) -> List[Tuple[int, int, int, int]]:
+    """Per rank ``(q0, q1, t0, t1)``: INT4 prefix tokens [q0, q1) (starts aligned to ``align``)
+    and vertical-line tokens [t0, t1).  Ranges are contiguous, disjoint and cover everything;
+    a rank may get an empty range."""
+    plan = []
+    for r in range(world):
+        q0 = (r * n_quant // world) // align * align
+        q1 = n_quant if r == world - 1 else ((r + 1) * n_quant // world) // align * align
+        t0, t1 = r * n_topk // world, (r + 1) * n_topk // world
+        plan.append((q0, max(q0, q1), t0, t1))
+    return plan
+
+
+def gather_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, group=None):
+    """All-gather one rank's ``(m [rows], l [rows], acc [rows, D])`` into ``[G, rows]``,
+    ``[G, rows]``, ``[G, rows, D]``.  One collective: the three are packed into a single
+    ``[rows, D + 2]`` message."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rows, d = acc.shape
+    msg = torch.empty(rows, d + 2, dtype=torch.float32, device=acc.device)
+    msg[:, :d] = acc
+    msg[:, d] = m
+    msg[:, d + 1] = l
+    out = torch.empty(world, rows, d + 2, dtype=torch.float32, device=acc.device)
+    dist.all_gather_into_tensor(out.view(world * rows, d + 2), msg, group=group)
+    return out[:, :, d].contiguous(), out[:, :, d + 1].contiguous(), out[:, :, :d].contiguous()
+
+
+class SequenceShardedLayer:
+    """One rank's shard of a frozen layer cache plus the merge step.
+
+    ``layer`` is a ``DStageLayerCache`` in decode phase that holds only this rank's
+    ranges (empty window/staging on every rank but the last).  ``decode_attention``
+    returns the full result on every rank."""
+
+    def __init__(self, layer, group=None):
+        self.layer = layer
+        self.group = group
+        self._bufs = None
+
+    def append_staging(self, key_states, value_states, is_tail_rank: bool):
+        if is_tail_rank:
+            self.layer.append_staging(key_states, value_states)
+
+    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int) -> torch.Tensor:
+        from .decode_d_stage import lse_merge
+        B, H_Q, _, D = query_states.shape
+        rows = B * H_Q
+        if self._bufs is None or self._bufs[2].shape[0] != rows:
+            dev = query_states.device
+            self._bufs = (torch.empty(rows, dtype=torch.float32, device=dev),
+                          torch.empty(rows, dtype=torch.float32, device=dev),
+                          torch.empty(rows, D, dtype=torch.float32, device=dev))
+        m, l, acc = self._bufs
+        self.layer.decode_attention(query_states, kv_repeat, partial=(m, l, acc))
+        gm, gl, gacc = gather_partials(m, l, acc, self.group)
+        return lse_merge(gm, gl, gacc, out_dtype=query_states.dtype).reshape(B, H_Q, 1, D)

@@ -190,8 +190,8 @@ int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_
  * (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101,
  *  src/ops/sage_unified.py:565-576).
  *   q [B,H_Q,N,128] bf16, k [B,H_KV,N,128] bf16 (strides in elements)
- *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (q * sm_scale * log2 e), q_scale fp32 [B,H_Q,ceil(N/128)]
- *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,ceil(N/64)], k_mean bf16 [B,H_KV,128]
+ *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (q * sm_scale * log2 e), q_scale fp32 [B,H_Q,N]   (one per row)
+ *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,N], k_mean bf16 [B,H_KV,128]
  * smooth_k == 0 leaves K unshifted.
  */
 int hq_prefill_quant_workspace_bytes(int B, int H_KV, int64_t* bytes);

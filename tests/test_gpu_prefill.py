@@ -1,6 +1,6 @@
 """GPU parity tests of the hybrid prefill path (operand preparation + attention kernel).
 
-Tolerances: INT8 codes and block scales bit-exact against the oracle's per-block quantiser;
+Tolerances: INT8 codes and scales bit-exact against the oracle's block quantiser (block = 1 row);
 attention outputs max-abs <= 2e-2 and rel-MSE <= 1e-4 against float64 dense causal attention
 on the same BF16 inputs."""
 
@@ -46,10 +46,10 @@ def test_operand_preparation_bit_exact(N, smooth):
         assert np.abs(km).max() == 0
     ksm = orc.bf16_round(k - km)
     assert np.array_equal(to_np(k_bf), ksm)
-    ki, ks = orc.quant_per_block_int8(ksm, 64, 1.0)
+    ki, ks = orc.quant_per_block_int8(ksm, 1, 1.0)           # the block quantiser's arithmetic, one row per block
     assert np.array_equal(k_sc.cpu().numpy(), ks)
     assert np.array_equal(k_i8.cpu().numpy(), ki)
-    qi, qs = orc.quant_per_block_int8(q, 128, sm * orc.LOG2E)
+    qi, qs = orc.quant_per_block_int8(q, 1, sm * orc.LOG2E)
     assert np.allclose(q_sc.cpu().numpy(), qs, rtol=1e-6)
     assert (np.abs(q_i8.cpu().numpy().astype(int) - qi.astype(int)) <= 1).all()      # fp32 product order of sm * log2e
     assert (q_i8.cpu().numpy() != qi).mean() < 1e-3
