@@ -359,6 +359,38 @@ def run_ours(args):
                           "bytes": bts, "caches": len(ls), "l2": "flushed before each pass over the caches"})
             del ls, qq
         del flush
+    prefill = []
+    if rank == 0 and not args.no_prefill:
+        from hyquant_b200.synth import gen_torch
+        from hyquant_b200.sage_unified import PrefillPlan
+        bf16_peak = None
+        try:
+            bf16_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+        except Exception:
+            pass
+        for n in (8192, 32768):
+            t = gen_torch(1, H_Q, H_KV, n, D, W, RHO, 2000 + n.bit_length(), n_qry=n, device=dev)
+            t0 = time.perf_counter()
+            vidx = hq.compute_vertical_indices(t["q"][:, :, -256:].mean(dim=2, keepdim=True), t["k"], W, RHO, kv_repeat=H_Q // H_KV)
+            plan = PrefillPlan(t["q"], t["k"], t["v"], vidx, W, None, True)
+            torch.cuda.synchronize()
+            prep_ms = (time.perf_counter() - t0) * 1e3
+            for _ in range(2):
+                plan.run()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 5 if n <= 8192 else 3
+            e0.record()
+            for _ in range(reps):
+                plan.run()
+            e1.record()
+            torch.cuda.synchronize()
+            ms_ = e0.elapsed_time(e1) / reps
+            prefill.append({"seq": n, "ms": round(ms_, 3), "tflops": round(plan.flops / ms_ / 1e9, 1),
+                            "frac_of_measured_bf16_sustained": None if not bf16_peak else round(plan.flops / ms_ / 1e9 / bf16_peak, 3),
+                            "prepare_ms_first_call": round(prep_ms, 2),
+                            "kernel": "hq::prefill_hybrid_kernel (INT8 QK^T + BF16 tiles, BF16 PV, mma.sync)"})
+            del plan, t
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -382,6 +414,7 @@ def run_ours(args):
                          "kernel": "hq::decode_splitk_kernel<1>", "algorithmic_bytes_per_launch": call_bytes},
             "cpu_baseline": cpu,
             "sweep": sweep,
+            "prefill": prefill,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -401,6 +434,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -58,7 +58,7 @@ class PrefillArgs(C.Structure):
     _fields_ = [
         ("struct_bytes", C.c_int32), ("B", C.c_int32), ("H_Q", C.c_int32), ("H_KV", C.c_int32), ("N", C.c_int32),
         ("head_dim", C.c_int32), ("window", C.c_int32), ("T", C.c_int32), ("out_dtype", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("sm_scale", C.c_float),
         ("q_i8", C.c_void_p), ("q_bf", C.c_void_p), ("q_scale", C.c_void_p),
         ("k_i8", C.c_void_p), ("k_bf", C.c_void_p), ("k_scale", C.c_void_p),
         ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_sn", C.c_int64),

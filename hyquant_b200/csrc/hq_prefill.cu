@@ -8,7 +8,7 @@
 //   keys in [wla(s), s + 128) : BF16 QK^T with the causal mask (local window + diagonal);
 // with wla(s) = floor(max(0, s - (W - 1)) / 64) * 64 — the block rule of the reference kernel
 // (src/ops/sage_unified.py:483-485, 538-544).  All tiles share one online softmax in base 2
-// (the query is pre-scaled by sm_scale * log2 e) and one fp32 accumulator; P V runs in BF16.
+// (sm_scale * log2 e is folded into the INT8 query scale and applied to the fp32 score of BF16 tiles) and one fp32 accumulator; P V runs in BF16.
 // Unlike the reference nothing is expanded to query heads or physically reordered: K / V stay
 // at kv-head granularity and a 64-bit mask word per (query head, 64-key block) removes the
 // vertical columns from the INT8 pass.
@@ -30,6 +30,7 @@ struct PrefillParams {
   const int* nv_valid;                                                         // [B,H_Q,nqb]
   void* out; int out_dtype; int64_t o_sb, o_sh, o_sn;
   int B, H_Q, H_KV, N, W, T, nqb, nkb;
+  float sml;      // sm_scale * log2(e), applied to the fp32 score of BF16 tiles
 };
 
 constexpr int kPfWarps = 8;
@@ -216,6 +217,10 @@ prefill_hybrid_kernel(const PrefillParams p) {
           mma_bf(S[2 * np + 1], a, bq[2], bq[3]);
         }
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) S[j][x] *= p.sml;
       if (tl.kind == 1) {
         if (tl.valid < kBN) {
 #pragma unroll
@@ -410,6 +415,7 @@ extern "C" int hq_prefill_hybrid(const hq_prefill_args* a, void* stream) {
   p.out = a->out; p.out_dtype = a->out_dtype; p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_sn = a->o_sn;
   p.B = a->B; p.H_Q = a->H_Q; p.H_KV = a->H_KV; p.N = a->N; p.W = a->window; p.T = a->T;
   p.nqb = (a->N + 127) / 128; p.nkb = (a->N + 63) / 64;
+  p.sml = a->sm_scale * 1.44269504f;
   const size_t smem = 16384 + 32768 + 2 * kStageBytes;
   static thread_local int attr_dev = -1;
   int dev = 0;

@@ -6,7 +6,8 @@
 //     (src/ops/vendor/sageattention/triton/quant_per_block.py:21-47) applied with one scale
 //     per token row instead of one per 64-key / 128-query block: an outlier row then costs
 //     no precision in its neighbours, and the scales are applied to the fp32 score for free;
-//   * the pre-scaled BF16 query used by the BF16 tiles.
+//   * a contiguous BF16 copy of the query for the BF16 tiles (unscaled: the kernel applies
+//     sm_scale * log2(e) to the fp32 score, so no rounding is added to the query).
 // HBM-bound: reads Q and K once, writes the INT8 and BF16 copies.
 #include "hq_common.cuh"
 
@@ -79,7 +80,7 @@ row_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, in
     v[2 * j] = f0; v[2 * j + 1] = f1;
     amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
     __nv_bfloat162 pk = __floats2bfloat162_rn(f0, f1);
-    ob[j] = *reinterpret_cast<uint32_t*>(&pk);
+    ob[j] = kIsK ? *reinterpret_cast<uint32_t*>(&pk) : w[j];     // the BF16 query copy stays unscaled (exact)
   }
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));

@@ -65,49 +65,64 @@ def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smoot
     return q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean
 
 
+class PrefillPlan:
+    """Prepared operands of one hybrid prefill call (INT8 / BF16 copies, vertical bookkeeping)
+    plus the filled ``hq_prefill_args``; ``run()`` launches only the attention kernel."""
+
+    def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
+                 window_size: int, sm_scale: Optional[float], smooth_k: bool):
+        dtype = q.dtype
+        qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
+        dev = q.device
+        lib = _lib.lib()
+        st = _lib.stream_ptr(dev)
+        if sm_scale is None:
+            sm_scale = 128 ** -0.5
+        nqb, nkb = (N + 127) // 128, (N + 63) // 64
+        q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
+        T = 0
+        vert_k = vert_v = vmask = nvv = None
+        prefix_len = max(0, N - window_size)
+        if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
+            if tuple(vertical_indices.shape[:2]) != (B, H_q):
+                raise HyQuantError("vertical_indices must be [B, H_q, T]")
+            vid = vertical_indices.to(device=dev, dtype=torch.int64).clamp(0, prefix_len - 1)   # reference :510
+            vasc = vid.sort(dim=-1).values.to(torch.int32).contiguous()
+            T = int(vasc.shape[-1])
+            vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+            vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+            vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
+            nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
+            rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
+                                                 vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
+                                                 vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
+            _lib.check(rc, "hq_prefill_vertical_prepare")
+        out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)
+        a = PrefillArgs()
+        a.struct_bytes = C.sizeof(PrefillArgs)
+        a.B, a.H_Q, a.H_KV, a.N, a.head_dim, a.window, a.T = B, H_q, H_kv, N, 128, int(window_size), T
+        a.out_dtype = _lib.dtype_code(dtype)
+        a.sm_scale = float(sm_scale)
+        a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
+        a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
+        a.v, a.v_sb, a.v_sh, a.v_sn = vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2)
+        if T:
+            a.vert_k, a.vert_v, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
+        a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+        self.args, self.out, self.device = a, out, dev
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_v, vmask, nvv)
+        self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
+
+    def run(self) -> torch.Tensor:
+        _lib.check(_lib.lib().hq_prefill_hybrid(C.byref(self.args), _lib.stream_ptr(self.device)), "hq_prefill_hybrid")
+        return self.out
+
+
 def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
                    window_size: int, sm_scale: Optional[float], smooth_k: bool) -> torch.Tensor:
     """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
     vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
-    dtype = q.dtype
-    qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
-    dev = q.device
-    lib = _lib.lib()
-    st = _lib.stream_ptr(dev)
-    if sm_scale is None:
-        sm_scale = 128 ** -0.5
-    nqb, nkb = (N + 127) // 128, (N + 63) // 64
-    q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
-    T = 0
-    vert_k = vert_v = vmask = nvv = None
-    prefix_len = max(0, N - window_size)
-    if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
-        if tuple(vertical_indices.shape[:2]) != (B, H_q):
-            raise HyQuantError("vertical_indices must be [B, H_q, T]")
-        vid = vertical_indices.to(device=dev, dtype=torch.int64).clamp(0, prefix_len - 1)   # reference :510
-        vasc = vid.sort(dim=-1).values.to(torch.int32).contiguous()
-        T = int(vasc.shape[-1])
-        vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
-        vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
-        vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
-        nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
-        rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
-                                             vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
-                                             vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
-        _lib.check(rc, "hq_prefill_vertical_prepare")
-    out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)
-    a = PrefillArgs()
-    a.struct_bytes = C.sizeof(PrefillArgs)
-    a.B, a.H_Q, a.H_KV, a.N, a.head_dim, a.window, a.T = B, H_q, H_kv, N, 128, int(window_size), T
-    a.out_dtype = _lib.dtype_code(dtype)
-    a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
-    a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
-    a.v, a.v_sb, a.v_sh, a.v_sn = vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2)
-    if T:
-        a.vert_k, a.vert_v, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
-    a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
-    _lib.check(lib.hq_prefill_hybrid(C.byref(a), st), "hq_prefill_hybrid")
-    return out
+    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k).run()
 
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,

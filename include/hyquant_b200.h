@@ -190,7 +190,7 @@ int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_
  * (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101,
  *  src/ops/sage_unified.py:565-576).
  *   q [B,H_Q,N,128] bf16, k [B,H_KV,N,128] bf16 (strides in elements)
- *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (q * sm_scale * log2 e), q_scale fp32 [B,H_Q,N]   (one per row)
+ *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (contiguous copy of q), q_scale fp32 [B,H_Q,N]   (one per row)
  *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,N], k_mean bf16 [B,H_KV,128]
  * smooth_k == 0 leaves K unshifted.
  */
@@ -224,7 +224,7 @@ typedef struct hq_prefill_args {
   int32_t window;              /* W; keys within W-1 of a query block's start (64-aligned) are BF16 */
   int32_t T;                   /* vertical lines per query head (0 = none) */
   int32_t out_dtype;
-  int32_t reserved0;
+  float   sm_scale;            /* same value as given to hq_prefill_quant */
   const void* q_i8; const void* q_bf; const float* q_scale;
   const void* k_i8; const void* k_bf; const float* k_scale;
   const void* v; int64_t v_sb, v_sh, v_sn;     /* bf16 [B,H_KV,N,128], strides in elements */

@@ -53,7 +53,7 @@ def test_operand_preparation_bit_exact(N, smooth):
     assert np.allclose(q_sc.cpu().numpy(), qs, rtol=1e-6)
     assert (np.abs(q_i8.cpu().numpy().astype(int) - qi.astype(int)) <= 1).all()      # fp32 product order of sm * log2e
     assert (q_i8.cpu().numpy() != qi).mean() < 1e-3
-    assert max_abs(to_np(q_bf), q * np.float32(sm * orc.LOG2E)) <= 1e-2
+    assert np.array_equal(to_np(q_bf), q)
 
 
 def check(out, ref):
