@@ -856,3 +856,50 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   if (NT == 1) return p.scale_tma ? launch_decode<1, true>(p, grid, st) : launch_decode<1, false>(p, grid, st);
   return p.scale_tma ? launch_decode<2, true>(p, grid, st) : launch_decode<2, false>(p, grid, st);
 }
+
+// ---- decode without caller-provided scratch -----------------------------------------------
+namespace hq {
+constexpr int64_t kStaticScratchBytes = 4 << 20;     // 4 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+}  // namespace hq
+
+// Same computation as hq_decode_splitk, for callers that cannot hand over device memory of
+// their own (a plugin host that forbids cudaMalloc in its callbacks, a process whose memory
+// pool is owned by another runtime): the split-K partials and tickets live in a fixed 4 MiB
+// array inside the library image.  `workspace` / `workspace_bytes` of the argument block are
+// ignored.  The first call on each device looks up the array's device address (with that
+// device current); make that first call outside any stream capture.  Every call shares the one
+// array, so two calls that may overlap on the GPU (different streams, or different host threads
+// without ordering between their streams) race; keep them in one stream.  The ticket and status
+// words are cleared in-stream before each launch.  A shape whose scratch need exceeds 4 MiB is
+// rejected with HQ_ERR_WORKSPACE.  No cudaMalloc / cudaFree or allocating library call is made.
+extern "C" int hq_decode_splitk_static(const hq_decode_args* a, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(a != nullptr, HQ_ERR_INVALID, "hq_decode_splitk_static: null args");
+  HQ_REQUIRE(a->struct_bytes == (int32_t)sizeof(hq_decode_args), HQ_ERR_INVALID,
+             "hq_decode_splitk_static: struct_bytes %d != %d", a->struct_bytes, (int)sizeof(hq_decode_args));
+  if (a->BH_KV == 0) return HQ_OK;
+  int64_t need = 0;
+  const int rc = hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
+  if (rc != HQ_OK) return rc;
+  HQ_REQUIRE(need <= kStaticScratchBytes, HQ_ERR_WORKSPACE,
+             "hq_decode_splitk_static: this shape needs %lld bytes of scratch, the built-in array holds %lld; "
+             "use hq_decode_splitk with a caller workspace", (long long)need, (long long)kStaticScratchBytes);
+  constexpr int kMaxDev = 64;
+  static void* dev_ptr[kMaxDev] = {nullptr};
+  int dev = 0;
+  HQ_CUDA(cudaGetDevice(&dev));
+  HQ_REQUIRE(dev >= 0 && dev < kMaxDev, HQ_ERR_UNSUPPORTED, "hq_decode_splitk_static: device index %d", dev);
+  if (dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    HQ_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));   // the host-side name is not a device address
+    HQ_REQUIRE(p != nullptr, HQ_ERR_CUDA, "hq_decode_splitk_static: no device address for the scratch array");
+    dev_ptr[dev] = p;
+  }
+  const int64_t head = kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256);
+  HQ_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, (size_t)head, (cudaStream_t)stream));
+  hq_decode_args b = *a;
+  b.workspace = dev_ptr[dev];
+  b.workspace_bytes = kStaticScratchBytes;
+  return hq_decode_splitk(&b, stream);
+}

@@ -130,6 +130,17 @@ typedef struct hq_decode_args {
 int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);
 int hq_decode_splitk(const hq_decode_args* args, void* stream);
 
+/* The same decode call for callers that cannot supply device scratch: hosts that forbid
+ * cudaMalloc inside their callbacks, or processes whose GPU memory belongs to another
+ * allocator.  It has no counterpart in the reference.  The split-K partials and tickets
+ * live in a 4 MiB array that is part of the library image (each GPU that loads the library
+ * holds it until exit); `workspace` / `workspace_bytes` in `args` are ignored.  Shapes that
+ * need more than 4 MiB of scratch (see hq_decode_workspace_bytes) fail with HQ_ERR_WORKSPACE.
+ * The first call on a device resolves the array's device address: make it before any stream
+ * capture.  All calls share the array, so calls that can overlap on the GPU race — issue them
+ * in one stream.  Allocates nothing. */
+int hq_decode_splitk_static(const hq_decode_args* args, void* stream);
+
 /* --------------------------------------------------------------------------
  * Log-sum-exp merge of G shards' partials (the algebra of _splitk_reduce_kernel,
  * src/ops/decode_d_stage.py:764-781, applied across GPUs after an all-gather).
