@@ -27,7 +27,8 @@ EXPORTS = [
     "hq_vertical_scores",
     "hq_topk",
     "hq_cache_reorganize",
-    "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_hybrid",
+    "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
+    "hq_prefill_hybrid",
 ]
 
 
@@ -64,6 +65,8 @@ class PrefillArgs(C.Structure):
         ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_sn", C.c_int64),
         ("vert_k", C.c_void_p), ("vert_v", C.c_void_p), ("vmask", C.c_void_p), ("nv_valid", C.c_void_p),
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sn", C.c_int64),
+        ("v_t", C.c_void_p), ("vert_vt", C.c_void_p), ("status", C.c_void_p), ("impl", C.c_int32),
+        ("reserved1", C.c_int32),
     ]
 
 
@@ -89,7 +92,8 @@ def _declare(lib):
     lib.hq_prefill_quant.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, i32,
                                      vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
     lib.hq_prefill_vertical_prepare.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, i64, i64,
-                                                vp, vp, vp, vp, vp]
+                                                vp, vp, vp, vp, vp, vp]
+    lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
     for name in EXPORTS:
         if name not in ("hq_version", "hq_last_error"):

@@ -29,7 +29,7 @@ struct PrefillParams {
   const unsigned long long* vmask;                                             // [B,H_Q,nkb]
   const int* nv_valid;                                                         // [B,H_Q,nqb]
   void* out; int out_dtype; int64_t o_sb, o_sh, o_sn;
-  int B, H_Q, H_KV, N, W, T, nqb, nkb;
+  int B, H_Q, H_KV, N, Npad, W, T, nqb, nkb;
   float sml;      // sm_scale * log2(e), applied to the fp32 score of BF16 tiles
 };
 
@@ -135,7 +135,7 @@ prefill_hybrid_kernel(const PrefillParams p) {
       load_tile(st, tl.k, 128, kBN, tl.valid, 128, tid);
       if (tid < 64) {   // the 64 key scales of the tile ride behind the 8 KB of codes
         const uint32_t d = smem_u32(st + 8192 + tid * 4);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(p.k_scale + bhk * p.N + tl.key0 + tid) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(p.k_scale + bhk * p.Npad + tl.key0 + tid) : "memory");
       }
     } else {
       load_tile(st, tl.k, 256, kBN, tl.valid, 256, tid);
@@ -155,7 +155,7 @@ prefill_hybrid_kernel(const PrefillParams p) {
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = s0 + warp * 16 + g + 8 * r;
-    qsc[r] = row < p.N ? p.q_scale[bhq * p.N + row] : 0.f;
+    qsc[r] = row < p.N ? p.q_scale[bhq * p.Npad + row] : 0.f;
   }
 
   float O[16][4];
@@ -368,20 +368,39 @@ __global__ void vertical_gather_kernel(const int* __restrict__ vasc, int T, int 
 
 }  // namespace hq
 
+namespace hq {
+int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st);
+int prefill_tc_prepare_v(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t, cudaStream_t st);
+int prefill_tc_prepare_vertical(const int32_t* vasc, int B, int H_Q, int H_KV, int N, int T, const void* k_bf, const void* v,
+                                int64_t v_sb, int64_t v_sh, int64_t v_sn, void* xk, void* xvt, cudaStream_t st);
+}
+
+extern "C" int hq_prefill_transpose_v(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
+                                      void* v_t, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(v && v_t && B > 0 && H_KV > 0 && N > 0, HQ_ERR_INVALID, "hq_prefill_transpose_v: bad arguments");
+  HQ_REQUIRE(aligned16(v) && aligned16(v_t) && v_sb % 8 == 0 && v_sh % 8 == 0 && v_sn % 8 == 0, HQ_ERR_ALIGNMENT,
+             "hq_prefill_transpose_v: rows must be 16-byte aligned");
+  return prefill_tc_prepare_v(v, v_sb, v_sh, v_sn, B, H_KV, N, v_t, (cudaStream_t)stream);
+}
+
 extern "C" int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int window, int T,
                                            const void* k_bf, const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
-                                           void* vert_k, void* vert_v, uint64_t* vmask, int32_t* nv_valid, void* stream) {
+                                           void* vert_k, void* vert_v, void* vert_vt, uint64_t* vmask, int32_t* nv_valid,
+                                           void* stream) {
   using namespace hq;
   HQ_REQUIRE(B > 0 && H_Q > 0 && H_KV > 0 && N > 0 && T >= 0 && window >= 0 && H_Q % H_KV == 0, HQ_ERR_INVALID,
              "hq_prefill_vertical_prepare: bad sizes");
   if (T == 0) return HQ_OK;
-  HQ_REQUIRE(vidx_asc && k_bf && v && vert_k && vert_v && vmask && nv_valid, HQ_ERR_INVALID,
+  HQ_REQUIRE(vidx_asc && k_bf && v && vert_k && (vert_v || vert_vt) && vmask && nv_valid, HQ_ERR_INVALID,
              "hq_prefill_vertical_prepare: null pointer");
-  HQ_REQUIRE(aligned16(v) && aligned16(k_bf) && aligned16(vert_k) && aligned16(vert_v) && v_sb % 8 == 0 && v_sh % 8 == 0 &&
-                 v_sn % 8 == 0, HQ_ERR_ALIGNMENT, "hq_prefill_vertical_prepare: rows must be 16-byte aligned");
+  HQ_REQUIRE(aligned16(v) && aligned16(k_bf) && aligned16(vert_k) && aligned16(vert_v) && aligned16(vert_vt) && v_sb % 8 == 0 &&
+                 v_sh % 8 == 0 && v_sn % 8 == 0, HQ_ERR_ALIGNMENT, "hq_prefill_vertical_prepare: rows must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   const int nkb = (N + 63) / 64, nqb = (N + 127) / 128;
   vertical_meta_kernel<<<B * H_Q, 256, 0, st>>>(vidx_asc, T, N, window, nkb, nqb, (unsigned long long*)vmask, nv_valid);
+  if (vert_vt != nullptr)     // layout of the tensor-memory kernel: rows padded to 64, V rows transposed
+    return prefill_tc_prepare_vertical(vidx_asc, B, H_Q, H_KV, N, T, k_bf, v, v_sb, v_sh, v_sn, vert_k, vert_vt, st);
   vertical_gather_kernel<<<dim3((T + 7) / 8, B * H_Q), 256, 0, st>>>(vidx_asc, T, N, H_Q, H_KV, (const __nv_bfloat16*)k_bf,
                                                                     (const __nv_bfloat16*)v, v_sb, v_sh, v_sn,
                                                                     (__nv_bfloat16*)vert_k, (__nv_bfloat16*)vert_v);
@@ -397,15 +416,17 @@ extern "C" int hq_prefill_hybrid(const hq_prefill_args* a, void* stream) {
   HQ_REQUIRE(a->head_dim == 128, HQ_ERR_UNSUPPORTED, "hq_prefill_hybrid: head_dim %d (only 128 is built)", a->head_dim);
   HQ_REQUIRE(a->B > 0 && a->H_Q > 0 && a->H_KV > 0 && a->N > 0 && a->H_Q % a->H_KV == 0 && a->window >= 0 && a->T >= 0,
              HQ_ERR_INVALID, "hq_prefill_hybrid: bad sizes");
-  HQ_REQUIRE(a->q_i8 && a->q_bf && a->q_scale && a->k_i8 && a->k_bf && a->k_scale && a->v && a->out, HQ_ERR_INVALID,
+  HQ_REQUIRE(a->q_i8 && a->q_bf && a->q_scale && a->k_i8 && a->k_bf && a->k_scale && a->out, HQ_ERR_INVALID,
              "hq_prefill_hybrid: null pointer");
-  HQ_REQUIRE(a->T == 0 || (a->vert_k && a->vert_v && a->vmask && a->nv_valid), HQ_ERR_INVALID,
+  HQ_REQUIRE(a->T == 0 || (a->vert_k && a->vmask && a->nv_valid), HQ_ERR_INVALID,
              "hq_prefill_hybrid: vertical arguments missing");
+  HQ_REQUIRE(a->impl == 0 || (a->v && (a->T == 0 || a->vert_v)), HQ_ERR_INVALID, "hq_prefill_hybrid: v / vert_v missing");
   HQ_REQUIRE(aligned16(a->q_i8) && aligned16(a->q_bf) && aligned16(a->k_i8) && aligned16(a->k_bf) && aligned16(a->v) &&
                  a->v_sb % 8 == 0 && a->v_sh % 8 == 0 && a->v_sn % 8 == 0 && a->o_sn % 2 == 0 && a->o_sh % 2 == 0 && a->o_sb % 2 == 0,
              HQ_ERR_ALIGNMENT, "hq_prefill_hybrid: operand rows must be 16-byte aligned");
   HQ_REQUIRE(a->out_dtype == HQ_BF16 || a->out_dtype == HQ_F16 || a->out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,
              "hq_prefill_hybrid: out_dtype %d", a->out_dtype);
+  if (a->impl == 0) return prefill_tc_launch(a, (cudaStream_t)stream);
   PrefillParams p{};
   p.q_i8 = (const int8_t*)a->q_i8; p.q_bf = (const __nv_bfloat16*)a->q_bf; p.q_scale = a->q_scale;
   p.k_i8 = (const int8_t*)a->k_i8; p.k_bf = (const __nv_bfloat16*)a->k_bf; p.k_scale = a->k_scale;
@@ -414,7 +435,7 @@ extern "C" int hq_prefill_hybrid(const hq_prefill_args* a, void* stream) {
   p.vmask = (const unsigned long long*)a->vmask; p.nv_valid = a->nv_valid;
   p.out = a->out; p.out_dtype = a->out_dtype; p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_sn = a->o_sn;
   p.B = a->B; p.H_Q = a->H_Q; p.H_KV = a->H_KV; p.N = a->N; p.W = a->window; p.T = a->T;
-  p.nqb = (a->N + 127) / 128; p.nkb = (a->N + 63) / 64;
+  p.nqb = (a->N + 127) / 128; p.nkb = (a->N + 63) / 64; p.Npad = p.nkb * 64;
   p.sml = a->sm_scale * 1.44269504f;
   const size_t smem = 16384 + 32768 + 2 * kStageBytes;
   static thread_local int attr_dev = -1;

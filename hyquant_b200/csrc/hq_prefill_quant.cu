@@ -54,7 +54,7 @@ template <bool kIsK>
 __global__ void __launch_bounds__(256)
 row_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
                  const __nv_bfloat16* __restrict__ mean, float mul,
-                 int8_t* __restrict__ xi8, __nv_bfloat16* __restrict__ xbf, float* __restrict__ scale) {
+                 int8_t* __restrict__ xi8, __nv_bfloat16* __restrict__ xbf, float* __restrict__ scale, int scale_pitch) {
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
   const int tid = threadIdx.x;
   const int row = blockIdx.x * 16 + (tid >> 4), c = (tid & 15) * 8;
@@ -87,7 +87,7 @@ row_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, in
   if (!ok) return;
   *reinterpret_cast<uint4*>(xbf + ((int64_t)bh * N + row) * 128 + c) = outbf;
   const float sc = fmaxf(amax, 1e-30f) / 127.f;     // an all-zero row keeps codes 0 instead of NaN
-  if ((tid & 15) == 0) scale[(int64_t)bh * N + row] = sc;
+  if ((tid & 15) == 0) scale[(int64_t)bh * scale_pitch + row] = sc;
   uint32_t lo = 0, hi = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -128,10 +128,10 @@ extern "C" int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64
   kmean_final_kernel<<<B * H_KV, 128, 0, st>>>((const float*)workspace, N, smooth_k, (__nv_bfloat16*)k_mean);
   const int nrb = (N + 15) / 16;
   row_quant_kernel<true><<<dim3(nrb, B * H_KV), 256, 0, st>>>(kk, k_sb, k_sh, k_sn, H_KV, N, (const __nv_bfloat16*)k_mean, 1.0f,
-                                                             (int8_t*)k_i8, (__nv_bfloat16*)k_bf, k_scale);
+                                                             (int8_t*)k_i8, (__nv_bfloat16*)k_bf, k_scale, (N + 63) / 64 * 64);
   row_quant_kernel<false><<<dim3(nrb, B * H_Q), 256, 0, st>>>((const __nv_bfloat16*)q, q_sb, q_sh, q_sn, H_Q, N, nullptr,
                                                              sm_scale * 1.44269504f, (int8_t*)q_i8, (__nv_bfloat16*)q_bf,
-                                                             q_scale);
+                                                             q_scale, (N + 63) / 64 * 64);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

@@ -20,6 +20,7 @@ from . import _lib
 from ._lib import HyQuantError, PrefillArgs
 
 _LOG2_E = 1.44269504
+PREFILL_IMPL = 0       # 0 = tcgen05 / tensor-memory kernel, 1 = mma.sync kernel
 
 
 def _prep_inputs(q, k, v):
@@ -47,10 +48,10 @@ def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smoot
     nqb, nkb = (N + 127) // 128, (N + 63) // 64
     q_i8 = torch.empty(B, H_q, N, 128, dtype=torch.int8, device=dev)
     q_bf = torch.empty(B, H_q, N, 128, dtype=torch.bfloat16, device=dev)
-    q_sc = torch.empty(B, H_q, N, dtype=torch.float32, device=dev)
+    q_sc = torch.zeros(B, H_q, (N + 63) // 64 * 64, dtype=torch.float32, device=dev)
     k_i8 = torch.empty(B, H_kv, N, 128, dtype=torch.int8, device=dev)
     k_bf = torch.empty(B, H_kv, N, 128, dtype=torch.bfloat16, device=dev)
-    k_sc = torch.empty(B, H_kv, N, dtype=torch.float32, device=dev)
+    k_sc = torch.zeros(B, H_kv, (N + 63) // 64 * 64, dtype=torch.float32, device=dev)
     k_mean = torch.empty(B, H_kv, 128, dtype=torch.bfloat16, device=dev)
     nb = C.c_int64(0)
     _lib.check(lib.hq_prefill_quant_workspace_bytes(B, H_kv, C.byref(nb)), "hq_prefill_quant_workspace_bytes")
@@ -70,7 +71,8 @@ class PrefillPlan:
     plus the filled ``hq_prefill_args``; ``run()`` launches only the attention kernel."""
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                 window_size: int, sm_scale: Optional[float], smooth_k: bool):
+                 window_size: int, sm_scale: Optional[float], smooth_k: bool, impl: Optional[int] = None):
+        impl = PREFILL_IMPL if impl is None else impl
         dtype = q.dtype
         qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
         dev = q.device
@@ -81,7 +83,12 @@ class PrefillPlan:
         nqb, nkb = (N + 127) // 128, (N + 63) // 64
         q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
         T = 0
-        vert_k = vert_v = vmask = nvv = None
+        vert_k = vert_v = vert_vt = vmask = nvv = v_t = None
+        Npad = (N + 63) // 64 * 64
+        if impl == 0:
+            v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
+            _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
+                                                  v_t.data_ptr(), st), "hq_prefill_transpose_v")
         prefix_len = max(0, N - window_size)
         if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
             if tuple(vertical_indices.shape[:2]) != (B, H_q):
@@ -89,13 +96,20 @@ class PrefillPlan:
             vid = vertical_indices.to(device=dev, dtype=torch.int64).clamp(0, prefix_len - 1)   # reference :510
             vasc = vid.sort(dim=-1).values.to(torch.int32).contiguous()
             T = int(vasc.shape[-1])
-            vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
-            vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+            Tpad = (T + 63) // 64 * 64
+            if impl == 0:
+                vert_k = torch.empty(B, H_q, Tpad, 128, dtype=torch.bfloat16, device=dev)
+                vert_vt = torch.empty(B, H_q, 128, Tpad, dtype=torch.bfloat16, device=dev)
+            else:
+                vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+                vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
             vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
             nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
             rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
                                                  vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
-                                                 vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
+                                                 vert_k.data_ptr(), vert_v.data_ptr() if vert_v is not None else None,
+                                                 vert_vt.data_ptr() if vert_vt is not None else None,
+                                                 vmask.data_ptr(), nvv.data_ptr(), st)
             _lib.check(rc, "hq_prefill_vertical_prepare")
         out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)
         a = PrefillArgs()
@@ -107,10 +121,15 @@ class PrefillPlan:
         a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
         a.v, a.v_sb, a.v_sh, a.v_sn = vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2)
         if T:
-            a.vert_k, a.vert_v, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_v.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
+            a.vert_k, a.vmask, a.nv_valid = vert_k.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
+            a.vert_v = vert_v.data_ptr() if vert_v is not None else None
+            a.vert_vt = vert_vt.data_ptr() if vert_vt is not None else None
         a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        a.v_t = v_t.data_ptr() if v_t is not None else None
+        a.status, a.impl = self.status.data_ptr(), impl
         self.args, self.out, self.device = a, out, dev
-        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_v, vmask, nvv)
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_v, vert_vt, vmask, nvv, v_t)
         self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
 
     def run(self) -> torch.Tensor:
@@ -119,10 +138,10 @@ class PrefillPlan:
 
 
 def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                   window_size: int, sm_scale: Optional[float], smooth_k: bool) -> torch.Tensor:
+                   window_size: int, sm_scale: Optional[float], smooth_k: bool, impl: Optional[int] = None) -> torch.Tensor:
     """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
     vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
-    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k).run()
+    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, impl).run()
 
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,

@@ -201,8 +201,8 @@ int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_
  * (src/ops/vendor/sageattention/triton/quant_per_block.py:21-101,
  *  src/ops/sage_unified.py:565-576).
  *   q [B,H_Q,N,128] bf16, k [B,H_KV,N,128] bf16 (strides in elements)
- *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (contiguous copy of q), q_scale fp32 [B,H_Q,N]   (one per row)
- *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,N], k_mean bf16 [B,H_KV,128]
+ *   q_i8 int8 [B,H_Q,N,128], q_bf bf16 (contiguous copy of q), q_scale fp32 [B,H_Q,Npad] (one per row; Npad = N rounded up to 64)
+ *   k_i8 int8 [B,H_KV,N,128], k_bf bf16 (k - mean), k_scale fp32 [B,H_KV,Npad], k_mean bf16 [B,H_KV,128]
  * smooth_k == 0 leaves K unshifted.
  */
 int hq_prefill_quant_workspace_bytes(int B, int H_KV, int64_t* bytes);
@@ -216,12 +216,21 @@ int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
 /* Step 2: vertical-line bookkeeping.  Replaces reorder_kv_for_vertical
  * (src/ops/sage_unified.py:499-547) without expanding K/V to query heads:
  *   vidx_asc int32 [B,H_Q,T] ascending distinct positions
- *   vert_k/vert_v bf16 [B,H_Q,T,128] gathered rows (k from k_bf), vmask u64 [B,H_Q,ceil(N/64)],
+ *   vert_k bf16 [B,H_Q,Tpad,128] gathered rows of k_bf (Tpad = T rounded up to 64, tail rows zero) and
+ *   vert_vt bf16 [B,H_Q,128,Tpad] the gathered rows of v, transposed — or, when vert_vt is NULL,
+ *   vert_k / vert_v bf16 [B,H_Q,T,128] untransposed; vmask u64 [B,H_Q,ceil(N/64)],
  *   nv_valid int32 [B,H_Q,ceil(N/128)] = number of vertical lines below the window start of a query block.
  */
 int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int window, int T,
                                 const void* k_bf, const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
-                                void* vert_k, void* vert_v, uint64_t* vmask, int32_t* nv_valid, void* stream);
+                                void* vert_k, void* vert_v, void* vert_vt, uint64_t* vmask, int32_t* nv_valid,
+                                void* stream);
+
+/* V transposed for the K-major operands of the tensor-memory kernel (the job of the reference's
+ * TransposePadPermuteKernel, vendor/sageattention/csrc/fused/fused.cu:264-315, without the fragment
+ * permutation): v bf16 [B,H_KV,N,128] -> v_t bf16 [B,H_KV,128,Npad], columns >= N zero. */
+int hq_prefill_transpose_v(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
+                           void* v_t, void* stream);
 
 /* Step 3: the attention kernel.  Replaces _attn_fwd_vertical_v2 / _attn_fwd_unified
  * (src/ops/sage_unified.py:398-496, 112-231): causal, GQA-native, INT8 QK^T for the
@@ -242,6 +251,11 @@ typedef struct hq_prefill_args {
   const void* vert_k; const void* vert_v;
   const uint64_t* vmask; const int32_t* nv_valid;
   void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements */
+  const void* v_t;             /* bf16 [B,H_KV,128,Npad] from hq_prefill_transpose_v */
+  const void* vert_vt;         /* bf16 [B,H_Q,128,Tpad] */
+  int32_t* status;             /* device word, zeroed by the caller; bit 1 = a bounded wait expired */
+  int32_t impl;                /* 0 = tcgen05 / tensor-memory kernel, 1 = mma.sync kernel */
+  int32_t reserved1;
 } hq_prefill_args;
 int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
 
