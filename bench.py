@@ -319,6 +319,8 @@ def run_ours(args):
         dist_.init_process_group("nccl", device_id=dev)
         dist = dist_
     layers, qs = [], []
+    if args.no_decode:
+        args.layers, args.no_e2e, args.no_sweep, args.no_cpu_baseline = 1, True, True, True
     for li in range(args.layers):
         layer, qd = build_layer(hq, torch, 1015 + 100 * rank + li, N_PREFIX, dev)
         layers.append(layer); qs.append(qd)
@@ -368,7 +370,7 @@ def run_ours(args):
             bf16_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
         except Exception:
             pass
-        for n in (8192, 32768):
+        for n in [int(x) for x in args.prefill_seq.split(",")]:
             t = gen_torch(1, H_Q, H_KV, n, D, W, RHO, 2000 + n.bit_length(), n_qry=n, device=dev)
             t0 = time.perf_counter()
             vidx = hq.compute_vertical_indices(t["q"][:, :, -256:].mean(dim=2, keepdim=True), t["k"], W, RHO, kv_repeat=H_Q // H_KV)
@@ -389,7 +391,7 @@ def run_ours(args):
             prefill.append({"seq": n, "ms": round(ms_, 3), "tflops": round(plan.flops / ms_ / 1e9, 1),
                             "frac_of_measured_bf16_sustained": None if not bf16_peak else round(plan.flops / ms_ / 1e9 / bf16_peak, 3),
                             "prepare_ms_first_call": round(prep_ms, 2),
-                            "kernel": "hq::prefill_hybrid_kernel (INT8 QK^T + BF16 tiles, BF16 PV, mma.sync)"})
+                            "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
     if rank == 0:
         cpu = None
@@ -435,6 +437,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="profiling: minimal decode leg, prefill only")
+    ap.add_argument("--prefill-seq", default="8192,32768", help="comma-separated prefill sequence lengths")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

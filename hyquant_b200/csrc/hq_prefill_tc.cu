@@ -6,7 +6,7 @@
 //
 // Structure of one CTA (128 queries of one head, 6 warps):
 //   warp 4 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of Q once and of a K tile
-//                      + a transposed V tile per step into a two-slot ring;
+//                      + a transposed V tile per step into a four-slot ring;
 //   warp 5 (one lane)  issues tcgen05.mma: S = Q K^T (kind::i8 with s32 accumulators or kind::f16 on
 //                      bf16) into one of two S buffers in tensor memory, and O += P V (kind::f16) into
 //                      the O accumulator in tensor memory; completion is signalled with tcgen05.commit;
@@ -34,14 +34,15 @@ constexpr int kTcThreads = 192;
 constexpr uint32_t kTmemCols = 256;        // S0 [0,64) | S1 [64,128) | O [128,256)
 constexpr float kTcLazy = 8.0f;
 
+constexpr int kKvStages = 4;   // K / V^T ring depth: tile loads run this many tiles ahead of the MMAs
 struct TcSmem {              // offsets from a 1024-aligned base
-  static constexpr int Qi = 0;                 // 16 KB  [128 rows][128 B] int8
-  static constexpr int Qb = 16384;             // 32 KB  2 x [128 rows][128 B] bf16
-  static constexpr int K = 49152;              // 2 x 16 KB
-  static constexpr int V = 81920;              // 2 x 16 KB  [128 d rows][128 B]
-  static constexpr int P = 114688;             // 16 KB  [128 rows][128 B] bf16
-  static constexpr int Bar = 131072;           // barriers + scratch
-  static constexpr int Total = 131072 + 256;
+  static constexpr int Qi = 0;                             // 16 KB  [128 rows][128 B] int8
+  static constexpr int Qb = 16384;                         // 32 KB  2 x [128 rows][128 B] bf16
+  static constexpr int K = 49152;                          // kKvStages x 16 KB
+  static constexpr int V = K + kKvStages * 16384;          // kKvStages x 16 KB  [128 d rows][128 B]
+  static constexpr int P = V + kKvStages * 16384;          // 2 x 16 KB  [128 rows][128 B] bf16
+  static constexpr int Bar = P + 32768;                    // barriers + scratch
+  static constexpr int Total = Bar + 256;
 };
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -53,14 +54,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::Bar);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;      // [2]
-  uint64_t* kv_empty = bars + 3;     // [2]
-  uint64_t* s_full = bars + 5;       // [2]
-  uint64_t* s_free = bars + 7;       // [2]
-  uint64_t* p_ready = bars + 9;
-  uint64_t* pv_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+  uint64_t* s_full = bars + 1;       // [2]
+  uint64_t* s_free = bars + 3;       // [2]
+  uint64_t* p_ready = bars + 5;      // [2]
+  uint64_t* pv_done = bars + 7;      // [2]
+  uint64_t* kv_full = bars + 9;                  // [kKvStages]
+  uint64_t* kv_empty = bars + 9 + kKvStages;     // [kKvStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9 + 2 * kKvStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 10 + 2 * kKvStages);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   __shared__ int s_skip;
@@ -81,9 +82,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
 
   if (tid == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); mbar_init(s_full + i, 1); mbar_init(s_free + i, 128); }
-    mbar_init(p_ready, 128);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < kKvStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_free + i, 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(p_ready + i, 128); mbar_init(pv_done + i, 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -103,8 +104,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       tc::tma_load_2d(smem + TcSmem::Qb, &mQb, 0, (int)(bhq * p.N + s0), q_full);
       tc::tma_load_2d(smem + TcSmem::Qb + 16384, &mQb, 64, (int)(bhq * p.N + s0), q_full);
       for (int i = 0; i < n_tiles; ++i) {
-        const int slot = i & 1;
-        if (!tc::mbar_wait_abortable(kv_empty + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag)) break;
+        const int slot = i % kKvStages;
+        if (!tc::mbar_wait_abortable(kv_empty + slot, (uint32_t)(((i / kKvStages) & 1) ^ 1), abort_flag, 200)) break;
         uint8_t* sK = smem + TcSmem::K + slot * 16384;
         uint8_t* sV = smem + TcSmem::V + slot * 16384;
         if (i < n_rest) {
@@ -133,16 +134,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       constexpr uint32_t idesc_i8 = tc::make_idesc(2, tc::kFmtS8, tc::kFmtS8, 128, 64);
       constexpr uint32_t idesc_qk = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 64);
       constexpr uint32_t idesc_pv = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 128);
-      bool ok = tc::mbar_wait_abortable(q_full, 0, abort_flag);
+      bool ok = tc::mbar_wait_abortable(q_full, 0, abort_flag, 100);
       for (int i = 0; ok && i <= n_tiles; ++i) {
         if (i < n_tiles) {
-          const int slot = i & 1;
-          ok = tc::mbar_wait_abortable(kv_full + slot, (uint32_t)((i >> 1) & 1), abort_flag) &&
-               tc::mbar_wait_abortable(s_free + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag);
+          const int slot = i & 1, kvs = i % kKvStages;
+          ok = tc::mbar_wait_abortable(kv_full + kvs, (uint32_t)((i / kKvStages) & 1), abort_flag, 40) &&
+               tc::mbar_wait_abortable(s_free + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, 40);
           if (!ok) break;
           tc::fence_after_sync();
           const uint32_t dS = tmem_base + (uint32_t)slot * 64;
-          const uint8_t* sK = smem + TcSmem::K + slot * 16384;
+          const uint8_t* sK = smem + TcSmem::K + kvs * 16384;
           if (i < n_rest) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
@@ -157,17 +158,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         }
         if (i > 0) {
           const int j = i - 1, slot = j & 1;
-          ok = tc::mbar_wait_abortable(p_ready, (uint32_t)(j & 1), abort_flag);
+          ok = tc::mbar_wait_abortable(p_ready + slot, (uint32_t)((j >> 1) & 1), abort_flag, 40);
           if (!ok) break;
           tc::fence_after_sync();
           const uint32_t dO = tmem_base + 128;
-          const uint8_t* sV = smem + TcSmem::V + slot * 16384;
+          const uint8_t* sV = smem + TcSmem::V + (j % kKvStages) * 16384;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc::mma_bf16_ss(dO, tc::smem_desc_k128(smem + TcSmem::P, k * 32), tc::smem_desc_k128(sV, k * 32), idesc_pv,
+            tc::mma_bf16_ss(dO, tc::smem_desc_k128(smem + TcSmem::P + slot * 16384, k * 32), tc::smem_desc_k128(sV, k * 32), idesc_pv,
                             (j > 0 || k > 0) ? 1u : 0u);
-          tc::mma_commit(pv_done);
-          tc::mma_commit(kv_empty + slot);
+          tc::mma_commit(pv_done + slot);
+          tc::mma_commit(kv_empty + (j % kKvStages));
         }
       }
     }
@@ -191,12 +192,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       tc::fence_before_sync();
       tc::mbar_arrive(s_free + slot);
 
-      float s[64];
-      float mx = -INFINITY;
+      // scores in the exponent's units: t[c] * esc - mu, with esc folded into one FFMA per element
+      float t[64];
+      float mx = -INFINITY, esc;
       if (i < n_rest) {
         const int key0 = i * 64;
         const float4* ks4 = reinterpret_cast<const float4*>(p.k_scale + bhk * p.Npad + key0);
         const unsigned long long vm = p.T > 0 ? p.vmask[bhq * p.nkb + i] : 0ull;
+        esc = qs;
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 kk = __ldg(ks4 + c4);
@@ -204,38 +207,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const int c = 4 * c4 + x;
-            const float v = (float)(int)sr[c >> 5][c & 31] * (qs * kv[x]);
-            s[c] = ((vm >> c) & 1ull) ? -INFINITY : v;
-            mx = fmaxf(mx, s[c]);
+            // int32 -> float without the conversion unit: |score| < 2^22
+            const float f = __int_as_float((int)sr[c >> 5][c & 31] + 0x4B400000) - 12582912.0f;
+            t[c] = f * kv[x];
           }
         }
-      } else if (i < n_rest + n_vert) {
-        const int valid = min(64, nv - (i - n_rest) * 64);
+        if (vm != 0ull) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          s[c] = c < valid ? __uint_as_float(sr[c >> 5][c & 31]) * p.sml : -INFINITY;
-          mx = fmaxf(mx, s[c]);
+          for (int c = 0; c < 64; ++c) if ((vm >> c) & 1ull) t[c] = -INFINITY;
         }
       } else {
-        const int key0 = wla + (i - n_rest - n_vert) * 64;
-        const int lim = min(row, p.N - 1) - key0;       // columns c <= lim are visible
+        esc = p.sml;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          s[c] = c <= lim ? __uint_as_float(sr[c >> 5][c & 31]) * p.sml : -INFINITY;
-          mx = fmaxf(mx, s[c]);
+        for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(sr[c >> 5][c & 31]);
+        int lim = 63;                                        // columns c <= lim are visible
+        if (i < n_rest + n_vert) lim = min(64, nv - (i - n_rest) * 64) - 1;
+        else lim = min(row, p.N - 1) - (wla + (i - n_rest - n_vert) * 64);
+        if (__any_sync(0xffffffffu, lim < 63)) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) if (c > lim) t[c] = -INFINITY;
         }
       }
-      // P of the previous tile must have been consumed (and O must be quiescent) before we go on
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done, (uint32_t)((i - 1) & 1), abort_flag));
-        if (!ok) break;
-        tc::fence_after_sync();
+      {   // 8 independent chains instead of one 64-long dependent one
+        float m8[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) m8[x] = t[x];
+#pragma unroll
+        for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], t[c]);
+        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       }
-      const bool grow = mx > m_ref + kTcLazy;            // also true for the first finite maximum
+      mx *= esc;                                             // esc >= 0
+      if (esc == 0.f) mx = -INFINITY;                        // rows past N
+      const bool grow = mx > m_ref + kTcLazy;                // also true for the first finite maximum
       if (__any_sync(0xffffffffu, grow)) {
         const float nm = grow ? mx : m_ref;
         const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - nm);
-        if (i > 0) {                                      // rescale this warp's 32 rows of O in tensor memory
+        if (i > 0) {     // O must be quiescent: every P V issued so far has to be complete
+          ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + ((i - 1) & 1), (uint32_t)(((i - 1) >> 1) & 1), abort_flag));
+          if (!ok) break;
+          tc::fence_after_sync();
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             uint32_t o[32];
@@ -246,31 +256,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
             tc::tmem_st32(lane_base + 128 + ch * 32, o);
           }
           tc::tmem_wait_st();
+          tc::fence_before_sync();
         }
         if (grow) { l *= alpha; m_ref = nm; }
       }
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
       uint32_t pk[32];
-      float rs = 0.f;
+      float rs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2f(s[c] - mu), p1 = ex2f(s[c + 1] - mu);
-        rs += p0 + p1;
+        const float p0 = ex2f(fmaf(t[c], esc, -mu)), p1 = ex2f(fmaf(t[c + 1], esc, -mu));
+        rs[c & 7] += p0; rs[(c & 7) + 1] += p1;
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l += rs;
-      uint8_t* prow = smem + TcSmem::P + r * 128;
+      l += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
+      // the P buffer of this parity was last read by the P V of tile i - 2
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag));
+      if (!ok) break;
+      uint8_t* prow = smem + TcSmem::P + slot * 16384 + r * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
       fence_proxy_async_smem();
       tc::fence_before_sync();
-      tc::mbar_arrive(p_ready);
+      tc::mbar_arrive(p_ready + slot);
     }
     // ---- epilogue
     if (ok && n_tiles > 0)
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done, (uint32_t)((n_tiles - 1) & 1), abort_flag));
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag));
     if (ok) {
       tc::fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;

@@ -54,10 +54,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // Wait with a poll limit and an abort flag shared by the CTA: once any wait of the CTA has given up,
 // every other wait returns at once, so a broken pipeline drains in bounded time.
+// `backoff_ns` > 0 makes a single-thread role sleep between polls so that it does not take issue slots
+// from the compute warps that share its scheduler.
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                    uint32_t limit = 400000u) {
+                                                    uint32_t backoff_ns = 0, uint32_t limit = 400000u) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
