@@ -1,16 +1,16 @@
 // Hybrid-precision causal prefill attention on the Blackwell tensor path.
 //
-// Same tile semantics as the rest of this path (see hq_prefill.cu's header): for the 128-query
+// Tile semantics as stated in hq_prefill.cu's header: for the 128-query
 // block at s of query head h, keys below wla(s) are INT8 unless they are vertical lines of h
 // (masked here, served from gathered BF16 tiles), keys in [wla(s), s + 128) are BF16 + causal mask.
 //
-// Structure of one CTA (128 queries of one head, 6 warps):
-//   warp 4 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of Q once and of a K tile
+// Structure of one CTA (128 queries of one head, 10 warps):
+//   warp 8 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of Q once and of a K tile
 //                      + a transposed V tile per step into a four-slot ring;
-//   warp 5 (one lane)  issues tcgen05.mma: S = Q K^T (kind::i8 with s32 accumulators or kind::f16 on
+//   warp 9 (one lane)  issues tcgen05.mma: S = Q K^T (kind::i8 with s32 accumulators or kind::f16 on
 //                      bf16) into one of two S buffers in tensor memory, and O += P V (kind::f16) into
 //                      the O accumulator in tensor memory; completion is signalled with tcgen05.commit;
-//   warps 0-3          one thread per query row: tcgen05.ld of the S row, scales / masks, online
+//   warps 0-7          two threads per query row (half of the columns each): tcgen05.ld of the S row, scales / masks, online
 //                      softmax in base 2 with a lazily updated maximum (the O accumulator is rescaled
 //                      in tensor memory only when the maximum grows by more than 2^8), P to shared
 //                      memory as the A operand of the next P V, final O / l from tensor memory.
@@ -30,7 +30,7 @@ struct PrefillTcParams {
   int* status;
 };
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;        // 8 softmax warps + producer warp + MMA warp
 constexpr uint32_t kTmemCols = 256;        // S0 [0,64) | S1 [64,128) | O [128,256)
 constexpr float kTcLazy = 8.0f;
 
@@ -42,14 +42,16 @@ struct TcSmem {              // offsets from a 1024-aligned base
   static constexpr int V = K + kKvStages * 16384;          // kKvStages x 16 KB  [128 d rows][128 B]
   static constexpr int P = V + kKvStages * 16384;          // 2 x 16 KB  [128 rows][128 B] bf16
   static constexpr int Bar = P + 32768;                    // barriers + scratch
-  static constexpr int Total = Bar + 256;
+  static constexpr int Xch = Bar + 256;                    // 3 x [2][128] floats: row maxima (two parities), row sums
+  static constexpr int Total = Xch + 3072;
 };
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant__ CUtensorMap mQb,
                   const __grid_constant__ CUtensorMap mKi, const __grid_constant__ CUtensorMap mKb,
                   const __grid_constant__ CUtensorMap mVt, const __grid_constant__ CUtensorMap mXk,
-                  const __grid_constant__ CUtensorMap mXv, const PrefillTcParams p) {
+                  const __grid_constant__ CUtensorMap mXv, const __grid_constant__ CUtensorMap mKs,
+                  const PrefillTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::Bar);
@@ -60,8 +62,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   uint64_t* pv_done = bars + 7;      // [2]
   uint64_t* kv_full = bars + 9;                  // [kKvStages]
   uint64_t* kv_empty = bars + 9 + kKvStages;     // [kKvStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9 + 2 * kKvStages);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 10 + 2 * kKvStages);
+  uint64_t* x_bar = bars + 9 + 2 * kKvStages;    // [3] row-maximum exchange (two parities) and row-sum exchange
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + 2 * kKvStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13 + 2 * kKvStages);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   __shared__ int s_skip;
@@ -83,18 +86,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   if (tid == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < kKvStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_free + i, 128); }
-    for (int i = 0; i < 2; ++i) { mbar_init(p_ready + i, 128); mbar_init(pv_done + i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_free + i, 256); }
+    for (int i = 0; i < 2; ++i) { mbar_init(p_ready + i, 256); mbar_init(pv_done + i, 1); mbar_init(x_bar + i, 256); }
+    mbar_init(x_bar + 2, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 4) tc::tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == 8) tc::tmem_alloc(tmem_slot, kTmemCols);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tc::tma_prefetch_desc(&mQi); tc::tma_prefetch_desc(&mQb); tc::tma_prefetch_desc(&mKi);
@@ -110,8 +114,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         uint8_t* sV = smem + TcSmem::V + slot * 16384;
         if (i < n_rest) {
           const int key0 = i * 64;
-          mbar_expect_tx(kv_full + slot, 8192 + 16384);
+          mbar_expect_tx(kv_full + slot, 8192 + 256 + 16384);
           tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + key0), kv_full + slot);
+          tc::tma_load_2d(sK + 8192, &mKs, key0, (int)bhk, kv_full + slot);      // the tile's 64 key scales
           tc::tma_load_2d(sV, &mVt, key0, (int)(bhk * 128), kv_full + slot);
         } else if (i < n_rest + n_vert) {
           const int j0 = (i - n_rest) * 64;
@@ -128,7 +133,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_i8 = tc::make_idesc(2, tc::kFmtS8, tc::kFmtS8, 128, 64);
@@ -173,71 +178,87 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax: thread = query row
-    const int r = tid;                       // 0..127 = tensor-memory lane
+    // ------------------------------------------------------------ softmax: two threads per query row
+    // Warps w and w + 4 share the tensor-memory lanes 32 (w % 4) .. + 31 (the hardware ties a warp to the
+    // lane quarter warp % 4) and split the row's 64 score columns / 128 output columns in halves, so every
+    // scheduler has two softmax warps to interleave.  Row maxima meet through shared memory once per tile.
+    const int half = warp >> 2, wq = warp & 3;
+    const int r = wq * 32 + lane;            // query row inside the block = tensor-memory lane
     const int row = s0 + r;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
+    float* xmax = reinterpret_cast<float*>(smem + TcSmem::Xch);        // [2 parities][2 halves][128]
+    float* xsum = xmax + 512;                                          // [2 halves][128]
     const float qs = row < p.N ? p.q_scale[bhq * p.Npad + row] : 0.f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    // the vertical-mask word of a tile is a fresh cache line every step: fetch it one step ahead
+    const unsigned long long* vmrow = p.vmask + bhq * p.nkb;
+    unsigned long long vm_next = (p.T > 0 && n_rest > 0) ? __ldg(vmrow) : 0ull;
     for (int i = 0; i < n_tiles; ++i) {
       const int slot = i & 1;
+      const unsigned long long vm64 = vm_next;
+      if (p.T > 0 && i + 1 < n_rest) vm_next = __ldg(vmrow + i + 1);
       ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(s_full + slot, (uint32_t)((i >> 1) & 1), abort_flag));
       if (!ok) break;
       tc::fence_after_sync();
-      uint32_t sr[2][32];
-      tc::tmem_ld32(lane_base + slot * 64, sr[0]);
-      tc::tmem_ld32(lane_base + slot * 64 + 32, sr[1]);
+      uint32_t sr[32];
+      tc::tmem_ld32(lane_base + slot * 64 + half * 32, sr);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       tc::mbar_arrive(s_free + slot);
 
       // scores in the exponent's units: t[c] * esc - mu, with esc folded into one FFMA per element
-      float t[64];
-      float mx = -INFINITY, esc;
+      float t[32];
+      float esc;
       if (i < n_rest) {
-        const int key0 = i * 64;
-        const float4* ks4 = reinterpret_cast<const float4*>(p.k_scale + bhk * p.Npad + key0);
-        const unsigned long long vm = p.T > 0 ? p.vmask[bhq * p.nkb + i] : 0ull;
+        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::K + (i % kKvStages) * 16384 + 8192) + half * 8;
+        const uint32_t vm = (uint32_t)(vm64 >> (32 * half));
         esc = qs;
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 kk = __ldg(ks4 + c4);
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 kk = ks4[c4];
           const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const int c = 4 * c4 + x;
             // int32 -> float without the conversion unit: |score| < 2^22
-            const float f = __int_as_float((int)sr[c >> 5][c & 31] + 0x4B400000) - 12582912.0f;
-            t[c] = f * kv[x];
+            t[c] = (__int_as_float((int)sr[c] + 0x4B400000) - 12582912.0f) * kv[x];
           }
         }
-        if (vm != 0ull) {
+        if (vm != 0u) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) if ((vm >> c) & 1ull) t[c] = -INFINITY;
+          for (int c = 0; c < 32; ++c) if ((vm >> c) & 1u) t[c] = -INFINITY;
         }
       } else {
         esc = p.sml;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(sr[c >> 5][c & 31]);
-        int lim = 63;                                        // columns c <= lim are visible
+        for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(sr[c]);
+        int lim;                                             // columns (of the full tile) <= lim are visible
         if (i < n_rest + n_vert) lim = min(64, nv - (i - n_rest) * 64) - 1;
         else lim = min(row, p.N - 1) - (wla + (i - n_rest - n_vert) * 64);
-        if (__any_sync(0xffffffffu, lim < 63)) {
+        lim -= 32 * half;
+        if (__any_sync(0xffffffffu, lim < 31)) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) if (c > lim) t[c] = -INFINITY;
+          for (int c = 0; c < 32; ++c) if (c > lim) t[c] = -INFINITY;
         }
       }
-      {   // 8 independent chains instead of one 64-long dependent one
+      float mx;
+      {
         float m8[8];
 #pragma unroll
         for (int x = 0; x < 8; ++x) m8[x] = t[x];
 #pragma unroll
-        for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], t[c]);
+        for (int c = 8; c < 32; ++c) m8[c & 7] = fmaxf(m8[c & 7], t[c]);
         mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       }
       mx *= esc;                                             // esc >= 0
       if (esc == 0.f) mx = -INFINITY;                        // rows past N
+      // exchange the half-row maxima
+      xmax[(slot * 2 + half) * 128 + r] = mx;
+      tc::mbar_arrive(x_bar + slot);
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(x_bar + slot, (uint32_t)((i >> 1) & 1), abort_flag));
+      if (!ok) break;
+      mx = fmaxf(mx, xmax[(slot * 2 + (half ^ 1)) * 128 + r]);
       const bool grow = mx > m_ref + kTcLazy;                // also true for the first finite maximum
       if (__any_sync(0xffffffffu, grow)) {
         const float nm = grow ? mx : m_ref;
@@ -247,13 +268,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
           if (!ok) break;
           tc::fence_after_sync();
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
+          for (int ch = 0; ch < 2; ++ch) {
             uint32_t o[32];
-            tc::tmem_ld32(lane_base + 128 + ch * 32, o);
+            tc::tmem_ld32(lane_base + 128 + half * 64 + ch * 32, o);
             tc::tmem_wait_ld();
 #pragma unroll
             for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * (grow ? alpha : 1.f));
-            tc::tmem_st32(lane_base + 128 + ch * 32, o);
+            tc::tmem_st32(lane_base + 128 + half * 64 + ch * 32, o);
           }
           tc::tmem_wait_st();
           tc::fence_before_sync();
@@ -261,38 +282,46 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         if (grow) { l *= alpha; m_ref = nm; }
       }
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-      uint32_t pk[32];
-      float rs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[16];
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < 32; c += 2) {
         const float p0 = ex2f(fmaf(t[c], esc, -mu)), p1 = ex2f(fmaf(t[c + 1], esc, -mu));
-        rs[c & 7] += p0; rs[(c & 7) + 1] += p1;
+        rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
+      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
       // the P buffer of this parity was last read by the P V of tile i - 2
       ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag));
       if (!ok) break;
       uint8_t* prow = smem + TcSmem::P + slot * 16384 + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      for (int x = 0; x < 4; ++x) {
+        const int ch = 4 * half + x;
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+      }
       fence_proxy_async_smem();
       tc::fence_before_sync();
       tc::mbar_arrive(p_ready + slot);
     }
-    // ---- epilogue
+    // ---- epilogue: O / l, each half of the row's threads stores 64 output columns
+    if (ok) {
+      xsum[half * 128 + r] = l;
+      tc::mbar_arrive(x_bar + 2);
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(x_bar + 2, 0, abort_flag));
+    }
     if (ok && n_tiles > 0)
       ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag));
     if (ok) {
       tc::fence_after_sync();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int64_t base = b * p.o_sb + hq * p.o_sh + (int64_t)row * p.o_sn;
+      const float lt = xsum[r] + xsum[128 + r];
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      const int64_t base = b * p.o_sb + hq * p.o_sh + (int64_t)row * p.o_sn + half * 64;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t o[32];
-        tc::tmem_ld32(lane_base + 128 + ch * 32, o);
+        tc::tmem_ld32(lane_base + 128 + half * 64 + ch * 32, o);
         tc::tmem_wait_ld();
         if (row < p.N) {
           if (p.out_dtype == HQ_BF16) {
@@ -316,7 +345,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   tc::fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicOr(p.status, 2);
-  if (warp == 4) tc::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 8) tc::tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ---- preparation for the tensor-memory kernel: transposed V tiles ---------------------------
@@ -379,9 +408,7 @@ vertical_gather_t_kernel(const int* __restrict__ vasc, int T, int Tpad, int N, i
 
 int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   const int N = a->N, Npad = (N + 63) / 64 * 64, T = a->T, Tpad = (T + 63) / 64 * 64;
-  HQ_REQUIRE(a->v_t && a->status, HQ_ERR_INVALID, "hq_prefill_hybrid: v_t / status missing");
-  HQ_REQUIRE(T == 0 || (a->vert_k && a->vert_vt), HQ_ERR_INVALID, "hq_prefill_hybrid: vertical tiles missing");
-  CUtensorMap mQi, mQb, mKi, mKb, mVt, mXk, mXv;
+  CUtensorMap mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs;
   const uint64_t qrows = (uint64_t)a->B * a->H_Q * N, krows = (uint64_t)a->B * a->H_KV * N;
   int rc;
   if ((rc = tc::make_map_2d(&mQi, a->q_i8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, qrows, 128, 128, 128))) return rc;
@@ -390,6 +417,8 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   if ((rc = tc::make_map_2d(&mKb, a->k_bf, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, krows, 256, 64, 64))) return rc;
   if ((rc = tc::make_map_2d(&mVt, a->v_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Npad, (uint64_t)a->B * a->H_KV * 128,
                             (uint64_t)Npad * 2, 64, 128))) return rc;
+  if ((rc = tc::make_map_2d(&mKs, a->k_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)Npad, (uint64_t)a->B * a->H_KV,
+                            (uint64_t)Npad * 4, 64, 1, false))) return rc;
   if (T > 0) {
     if ((rc = tc::make_map_2d(&mXk, a->vert_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, (uint64_t)a->B * a->H_Q * Tpad, 256, 64, 64))) return rc;
     if ((rc = tc::make_map_2d(&mXv, a->vert_vt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Tpad, (uint64_t)a->B * a->H_Q * 128,
@@ -414,7 +443,7 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
     attr_dev = dev;
   }
   dim3 grid((unsigned)p.nqb, (unsigned)a->H_Q, (unsigned)a->B);
-  prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, p);
+  prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, p);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

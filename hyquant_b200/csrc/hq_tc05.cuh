@@ -27,9 +27,9 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major tensor [rows][cols] of `esz`-byte elements, row pitch `pitch_bytes`;
-// box = [box_cols][box_rows]; 128-byte swizzle (box_cols * esz must be 128).
+// box = [box_cols][box_rows]; 128-byte swizzle (box_cols * esz must be 128) or none.
 inline int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esz, uint64_t cols, uint64_t rows,
-                       uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+                       uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return HQ_ERR_CUDA; }
   const cuuint64_t dims[2] = {cols, rows};
@@ -37,7 +37,8 @@ inline int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt,
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with %d (cols=%llu rows=%llu pitch=%llu box=%ux%u esz=%d)", (int)r,
               (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)pitch_bytes, box_cols, box_rows, esz);

@@ -2,7 +2,7 @@
 ``src/ops/sage_unified.py`` (``sage_vertical_attention_v2``, ``sage_unified_attention``)
 plus ``full_attention_fp16_triton`` (``src/ops/v_sageattention.py``) and
 ``sage_fp8_attention`` (``src/ops/sage_fp8_attention.py``), all served by one sm_100a
-kernel (``hq_prefill_hybrid``) after one operand-preparation pass (``hq_prefill_quant``).
+tcgen05 / tensor-memory kernel (``hq_prefill_hybrid``) after one operand-preparation pass (``hq_prefill_quant``).
 
 By design nothing is expanded to query heads and nothing is physically reordered:
 K/V stay at kv-head granularity, the vertical lines of a query head are removed from
@@ -20,7 +20,6 @@ from . import _lib
 from ._lib import HyQuantError, PrefillArgs
 
 _LOG2_E = 1.44269504
-PREFILL_IMPL = 0       # 0 = tcgen05 / tensor-memory kernel, 1 = mma.sync kernel
 
 
 def _prep_inputs(q, k, v):
@@ -71,8 +70,7 @@ class PrefillPlan:
     plus the filled ``hq_prefill_args``; ``run()`` launches only the attention kernel."""
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                 window_size: int, sm_scale: Optional[float], smooth_k: bool, impl: Optional[int] = None):
-        impl = PREFILL_IMPL if impl is None else impl
+                 window_size: int, sm_scale: Optional[float], smooth_k: bool):
         dtype = q.dtype
         qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
         dev = q.device
@@ -83,12 +81,11 @@ class PrefillPlan:
         nqb, nkb = (N + 127) // 128, (N + 63) // 64
         q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
         T = 0
-        vert_k = vert_v = vert_vt = vmask = nvv = v_t = None
+        vert_k = vert_vt = vmask = nvv = None
         Npad = (N + 63) // 64 * 64
-        if impl == 0:
-            v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
-            _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
-                                                  v_t.data_ptr(), st), "hq_prefill_transpose_v")
+        v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
+                                              v_t.data_ptr(), st), "hq_prefill_transpose_v")
         prefix_len = max(0, N - window_size)
         if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
             if tuple(vertical_indices.shape[:2]) != (B, H_q):
@@ -97,21 +94,15 @@ class PrefillPlan:
             vasc = vid.sort(dim=-1).values.to(torch.int32).contiguous()
             T = int(vasc.shape[-1])
             Tpad = (T + 63) // 64 * 64
-            if impl == 0:
-                vert_k = torch.empty(B, H_q, Tpad, 128, dtype=torch.bfloat16, device=dev)
-                vert_vt = torch.empty(B, H_q, 128, Tpad, dtype=torch.bfloat16, device=dev)
-            else:
-                vert_k = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
-                vert_v = torch.empty(B, H_q, T, 128, dtype=torch.bfloat16, device=dev)
+            vert_k = torch.empty(B, H_q, Tpad, 128, dtype=torch.bfloat16, device=dev)
+            vert_vt = torch.empty(B, H_q, 128, Tpad, dtype=torch.bfloat16, device=dev)
             vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
             nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
             rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
                                                  vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
-                                                 vert_k.data_ptr(), vert_v.data_ptr() if vert_v is not None else None,
-                                                 vert_vt.data_ptr() if vert_vt is not None else None,
-                                                 vmask.data_ptr(), nvv.data_ptr(), st)
+                                                 vert_k.data_ptr(), vert_vt.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
             _lib.check(rc, "hq_prefill_vertical_prepare")
-        out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)
+        out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)      # contiguous: rows 16-byte aligned
         a = PrefillArgs()
         a.struct_bytes = C.sizeof(PrefillArgs)
         a.B, a.H_Q, a.H_KV, a.N, a.head_dim, a.window, a.T = B, H_q, H_kv, N, 128, int(window_size), T
@@ -119,29 +110,32 @@ class PrefillPlan:
         a.sm_scale = float(sm_scale)
         a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
         a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
-        a.v, a.v_sb, a.v_sh, a.v_sn = vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2)
+        a.v_t = v_t.data_ptr()
         if T:
-            a.vert_k, a.vmask, a.nv_valid = vert_k.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
-            a.vert_v = vert_v.data_ptr() if vert_v is not None else None
-            a.vert_vt = vert_vt.data_ptr() if vert_vt is not None else None
+            a.vert_k, a.vert_vt, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_vt.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
         a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        a.v_t = v_t.data_ptr() if v_t is not None else None
-        a.status, a.impl = self.status.data_ptr(), impl
+        a.status = self.status.data_ptr()
         self.args, self.out, self.device = a, out, dev
-        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_v, vert_vt, vmask, nvv, v_t)
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, vmask, nvv, v_t)
         self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
 
     def run(self) -> torch.Tensor:
         _lib.check(_lib.lib().hq_prefill_hybrid(C.byref(self.args), _lib.stream_ptr(self.device)), "hq_prefill_hybrid")
         return self.out
 
+    def check_status(self) -> None:
+        """Synchronising check of the kernel's status word (bit 1: a bounded device wait expired)."""
+        st = int(self.status.item())
+        if st != 0:
+            raise HyQuantError(f"hq_prefill_hybrid reported device status {st} (a bounded wait expired)")
+
 
 def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                   window_size: int, sm_scale: Optional[float], smooth_k: bool, impl: Optional[int] = None) -> torch.Tensor:
+                   window_size: int, sm_scale: Optional[float], smooth_k: bool) -> torch.Tensor:
     """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
     vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
-    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, impl).run()
+    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k).run()
 
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,
@@ -171,7 +165,7 @@ def full_attention_fp16_triton(q, k, v, tensor_layout: str = "HND", is_causal: b
 
 def sage_fp8_attention(q, k, v, *, is_causal: bool = True, sm_scale: Optional[float] = None, smooth_k: bool = True):
     """INT8 QK causal attention without vertical lines or window (reference sage_fp8_attention.py:15-45).
-    The P V product of this build runs in BF16."""
+    The P V product of this build runs in BF16 on the tcgen05 path."""
     if not is_causal:
         raise HyQuantError("only causal attention is built")
     return hybrid_prefill(q, k, v, None, 0, sm_scale, smooth_k)

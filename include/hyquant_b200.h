@@ -216,15 +216,13 @@ int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
 /* Step 2: vertical-line bookkeeping.  Replaces reorder_kv_for_vertical
  * (src/ops/sage_unified.py:499-547) without expanding K/V to query heads:
  *   vidx_asc int32 [B,H_Q,T] ascending distinct positions
- *   vert_k bf16 [B,H_Q,Tpad,128] gathered rows of k_bf (Tpad = T rounded up to 64, tail rows zero) and
- *   vert_vt bf16 [B,H_Q,128,Tpad] the gathered rows of v, transposed — or, when vert_vt is NULL,
- *   vert_k / vert_v bf16 [B,H_Q,T,128] untransposed; vmask u64 [B,H_Q,ceil(N/64)],
+ *   vert_k bf16 [B,H_Q,Tpad,128] gathered rows of k_bf (Tpad = T rounded up to 64, tail rows zero),
+ *   vert_vt bf16 [B,H_Q,128,Tpad] the gathered rows of v, transposed; vmask u64 [B,H_Q,ceil(N/64)],
  *   nv_valid int32 [B,H_Q,ceil(N/128)] = number of vertical lines below the window start of a query block.
  */
 int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int window, int T,
                                 const void* k_bf, const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
-                                void* vert_k, void* vert_v, void* vert_vt, uint64_t* vmask, int32_t* nv_valid,
-                                void* stream);
+                                void* vert_k, void* vert_vt, uint64_t* vmask, int32_t* nv_valid, void* stream);
 
 /* V transposed for the K-major operands of the tensor-memory kernel (the job of the reference's
  * TransposePadPermuteKernel, vendor/sageattention/csrc/fused/fused.cu:264-315, without the fragment
@@ -232,7 +230,8 @@ int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_K
 int hq_prefill_transpose_v(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
                            void* v_t, void* stream);
 
-/* Step 3: the attention kernel.  Replaces _attn_fwd_vertical_v2 / _attn_fwd_unified
+/* Step 3: the attention kernel (tcgen05.mma kind::i8 / kind::f16 with tensor-memory accumulators,
+ * TMA tensor-map tile loads).  Replaces _attn_fwd_vertical_v2 / _attn_fwd_unified
  * (src/ops/sage_unified.py:398-496, 112-231): causal, GQA-native, INT8 QK^T for the
  * non-vertical prefix, BF16 QK^T for vertical lines and for the window; one online softmax.
  * window == N gives plain BF16 causal attention (full_attention_fp16_triton,
@@ -245,17 +244,14 @@ typedef struct hq_prefill_args {
   int32_t T;                   /* vertical lines per query head (0 = none) */
   int32_t out_dtype;
   float   sm_scale;            /* same value as given to hq_prefill_quant */
-  const void* q_i8; const void* q_bf; const float* q_scale;
+  const void* q_i8; const void* q_bf; const float* q_scale;     /* from hq_prefill_quant */
   const void* k_i8; const void* k_bf; const float* k_scale;
-  const void* v; int64_t v_sb, v_sh, v_sn;     /* bf16 [B,H_KV,N,128], strides in elements */
-  const void* vert_k; const void* vert_v;
-  const uint64_t* vmask; const int32_t* nv_valid;
-  void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements */
   const void* v_t;             /* bf16 [B,H_KV,128,Npad] from hq_prefill_transpose_v */
-  const void* vert_vt;         /* bf16 [B,H_Q,128,Tpad] */
+  const void* vert_k;          /* from hq_prefill_vertical_prepare (T > 0) */
+  const void* vert_vt;
+  const uint64_t* vmask; const int32_t* nv_valid;
+  void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements (multiples of 8) */
   int32_t* status;             /* device word, zeroed by the caller; bit 1 = a bounded wait expired */
-  int32_t impl;                /* 0 = tcgen05 / tensor-memory kernel, 1 = mma.sync kernel */
-  int32_t reserved1;
 } hq_prefill_args;
 int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
 

@@ -78,6 +78,17 @@ def test_vertical_attention_vs_dense(B, H_Q, H_KV, N, W):
         assert max_abs(to_np(out), rr) <= MAX_ABS
 
 
+def test_plan_reuse_and_status_word():
+    q, k, v = make(1, 8, 2, 900, 128, 17)
+    vidx = hq.compute_vertical_indices(t_bf16(q), t_bf16(k), 128, 0.05, kv_repeat=4)
+    plan = su.PrefillPlan(t_bf16(q), t_bf16(k), t_bf16(v), vidx, 128, None, True)
+    a = to_np(plan.run()).copy()
+    b = to_np(plan.run())
+    plan.check_status()                      # no bounded wait expired on the device
+    assert np.array_equal(a, b)              # deterministic
+    check(a, orc.dense_causal_attention(q, k, v))
+
+
 def test_window_only_full_and_int8_only_variants():
     q, k, v = make(1, 8, 2, 700, 128, 5)
     ref = orc.dense_causal_attention(q, k, v)
