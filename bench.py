@@ -202,17 +202,18 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
     n = len(layers)
     g = torch.Generator(); g.manual_seed(seed)
     tot = steps + warmup
-    hq_ = torch.randn(tot, n, B, H_Q, 1, D, generator=g).to(torch.bfloat16).pin_memory()
-    hk_ = torch.randn(tot, n, B, H_KV, 1, D, generator=g).to(torch.bfloat16).pin_memory()
-    hv_ = torch.randn(tot, n, B, H_KV, 1, D, generator=g).to(torch.bfloat16).pin_memory()
+    rows = B * (H_Q + 2 * H_KV)
+    # one pinned message per (step, layer): the new token's q | k | v rows
+    hin = torch.randn(tot, n, rows, D, generator=g).to(torch.bfloat16).pin_memory()
     hout = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16).pin_memory()
     dev = layers[0].k_window.device
 
     def one_step(s):
         for li, layer in enumerate(layers):
-            q = hq_[s, li].to(dev, non_blocking=True)
-            k = hk_[s, li].to(dev, non_blocking=True)
-            v = hv_[s, li].to(dev, non_blocking=True)
+            x = hin[s, li].to(dev, non_blocking=True)
+            q = x[:B * H_Q].view(B, H_Q, 1, D)
+            k = x[B * H_Q:B * (H_Q + H_KV)].view(B, H_KV, 1, D)
+            v = x[B * (H_Q + H_KV):].view(B, H_KV, 1, D)
             layer.append_staging(k, v)
             o = layer.decode_attention(q, r)
             hout[li].copy_(o, non_blocking=True)

@@ -21,7 +21,7 @@ ERR_NAMES = {-1: "HQ_ERR_INVALID", -2: "HQ_ERR_UNSUPPORTED", -3: "HQ_ERR_ALIGNME
 # every symbol include/hyquant_b200.h declares
 EXPORTS = [
     "hq_version", "hq_last_error",
-    "hq_quant_pack_int4",
+    "hq_quant_pack_int4", "hq_staging_append",
     "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static",
     "hq_lse_merge",
     "hq_vertical_scores",
@@ -78,6 +78,7 @@ def _declare(lib):
     lib.hq_version.restype = C.c_char_p
     lib.hq_last_error.restype = C.c_char_p
     lib.hq_quant_pack_int4.argtypes = [vp, i32, i64, i64, i32, i32, vp, i64, vp, i64, i64, i32, vp]
+    lib.hq_staging_append.argtypes = [vp, vp, i64, i64, vp, vp, i32, i32, vp]
     lib.hq_decode_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_decode_splitk.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.hq_decode_splitk_static.argtypes = [C.POINTER(DecodeArgs), vp]

@@ -32,7 +32,36 @@ quant_pack_int4_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_s
   }
 }
 
+// One new token per head into slot `slot` of the staging buffers: k_new/v_new [BH, 128] (row stride
+// given) -> staging_k/v [BH, 128 slots, 128].  64 threads per head: 32 move K, 32 move V, 8 bytes each.
+__global__ void __launch_bounds__(256)
+staging_append_kernel(const uint2* __restrict__ k_new, const uint2* __restrict__ v_new, int64_t k_stride8, int64_t v_stride8,
+                      uint2* __restrict__ staging_k, uint2* __restrict__ staging_v, int BH, int slot) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int bh = idx >> 6, part = idx & 63;
+  if (bh >= BH) return;
+  const int64_t dst = ((int64_t)bh * HQ_GROUP_SIZE + slot) * 32 + (part & 31);
+  if (part < 32) staging_k[dst] = __ldg(k_new + bh * k_stride8 + part);
+  else staging_v[dst] = __ldg(v_new + bh * v_stride8 + (part - 32));
+}
+
 }  // namespace hq
+
+extern "C" int hq_staging_append(const void* k_new, const void* v_new, int64_t k_stride, int64_t v_stride,
+                                 void* staging_k, void* staging_v, int BH, int slot, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(BH >= 0 && slot >= 0 && slot < HQ_GROUP_SIZE, HQ_ERR_INVALID, "hq_staging_append: slot %d outside 0..127", slot);
+  if (BH == 0) return HQ_OK;
+  HQ_REQUIRE(k_new && v_new && staging_k && staging_v, HQ_ERR_INVALID, "hq_staging_append: null pointer");
+  HQ_REQUIRE(((uintptr_t)k_new % 8) == 0 && ((uintptr_t)v_new % 8) == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 &&
+                 ((uintptr_t)staging_k % 8) == 0 && ((uintptr_t)staging_v % 8) == 0,
+             HQ_ERR_ALIGNMENT, "hq_staging_append: rows must be 8-byte aligned");
+  const int threads = BH * 64;
+  staging_append_kernel<<<(threads + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      (const uint2*)k_new, (const uint2*)v_new, k_stride / 4, v_stride / 4, (uint2*)staging_k, (uint2*)staging_v, BH, slot);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}
 
 extern "C" int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
                                   int BH, int n, void* packed, int64_t packed_stride_bh,

@@ -72,6 +72,7 @@ class DStageLayerCache:
         self.v_window: Optional[torch.Tensor] = None
         self._B = self._H_KV = self._D = 0
         self._plan: Optional[DecodePlan] = None
+        self._lib = None
         self.vertical_indices: Optional[torch.Tensor] = None   # [B, H_KV, T] chosen at freeze
 
     # ---- views of the live prefix (reference attribute names) -----------------
@@ -193,6 +194,7 @@ class DStageLayerCache:
         self._staging_ptr = 0
         self._keys = self._values = self._query_tail = None
         self._plan = None
+        self._lib = _lib.lib()
         self.phase = "decode"
 
     # ---- decode ---------------------------------------------------------------
@@ -200,6 +202,20 @@ class DStageLayerCache:
         """Append new decode token(s) to the staging ring (reference :195-207)."""
         B, H_KV, S, D = key_states.shape
         BH = B * H_KV
+        if (S == 1 and key_states.dtype == torch.bfloat16 and self._staging_buf_k.dtype == torch.bfloat16
+                and key_states.stride(3) == 1 and value_states.stride(3) == 1):
+            # one token: a single small kernel instead of two strided tensor copies
+            k2, v2 = key_states.reshape(BH, D), value_states.reshape(BH, D)
+            rc = self._lib.hq_staging_append(k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0),
+                                             self._staging_buf_k.data_ptr(), self._staging_buf_v.data_ptr(), BH,
+                                             self._staging_ptr, torch.cuda.current_stream(k2.device).cuda_stream)
+            if rc != 0:
+                _lib.check(rc, "hq_staging_append")
+            self._staging_ptr += 1
+            if self._staging_ptr >= GROUP_SIZE:
+                self._flush_staging_buffer()
+            self._seq_len += 1
+            return
         k = key_states.reshape(BH, S, D)
         v = value_states.reshape(BH, S, D)
         for i in range(S):

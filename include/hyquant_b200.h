@@ -66,6 +66,12 @@ int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t
                        void* scale, int64_t scale_stride_bh,
                        int64_t dst_token_offset, int scale_mode, void* stream);
 
+/* One decode token per head into slot `slot` (0..127) of the staging buffers — the device work of
+ * DStageLayerCache.append_staging (src/ops/d_stage_kv_cache.py:195-207) for a single new token.
+ *   k_new/v_new bf16 [BH, 128] with row strides in elements; staging_k/v bf16 [BH, 128, 128]. */
+int hq_staging_append(const void* k_new, const void* v_new, int64_t k_stride, int64_t v_stride,
+                      void* staging_k, void* staging_v, int BH, int slot, void* stream);
+
 /* --------------------------------------------------------------------------
  * Split-K decode attention over the four-segment cache, one launch.
  * Replaces fused_d_stage_decode / fused_d_stage_decode_splitk and the kernels
