@@ -425,8 +425,8 @@ def run_ours(args):
 
 
 # DRAM bytes per launch of the decode kernel from an ncu capture of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# (dram__bytes_read.sum + dram__bytes_write.sum, profiles/decode_splitk_cfg1_32k.md)
+TRAFFIC_BYTES_PER_LAUNCH = 40289792
 
 
 def main():
