@@ -77,3 +77,12 @@ def install_as_src() -> None:
         "src.ops.d_stage_kv_cache": d_stage_kv_cache, "src.ops.sage_unified": sage_unified,
         "src.patch": patch_pkg, "src.patch._common": _common,
     })
+    # the reference keeps one module per model family; here they are views of one builder
+    from .patch import forwards
+    for mod, fn in (("patch_llama", "patch_llama3_attention_forward_model"),
+                    ("patch_qwen", "patch_qwen3_attention_forward_model"),
+                    ("patch_glm", "patch_glm4_attention_forward_model")):
+        m = types.ModuleType(f"src.patch.{mod}")
+        setattr(m, fn, getattr(forwards, fn))
+        setattr(patch_pkg, mod, m)
+        sys.modules[f"src.patch.{mod}"] = m

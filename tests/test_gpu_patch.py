@@ -1,0 +1,87 @@
+"""Patched Hugging Face models on the GPU: a random-init Llama / Qwen3 / GLM-4 of two layers runs a prompt
+and a few decode steps through the patched attention (hybrid prefill kernel, cache freeze, four-segment
+decode kernel behind DStageKVCache) and is compared with the same weights under the stock attention.
+
+The comparison is on the logits.  Quantised attention is not bit-equal to 16-bit attention, so the bound is
+a relative mean-square error; the values measured on a B200 are written beside each bound."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+transformers = pytest.importorskip("transformers")
+
+PROMPT, STEPS, WINDOW, RATIO = 1024, 4, 128, 0.05
+
+
+def tiny(family):
+    from transformers import (Glm4Config, Glm4ForCausalLM, LlamaConfig, LlamaForCausalLM, Qwen3Config,
+                              Qwen3ForCausalLM)
+    cfg_cls, model_cls = {"llama": (LlamaConfig, LlamaForCausalLM), "qwen": (Qwen3Config, Qwen3ForCausalLM),
+                          "glm4": (Glm4Config, Glm4ForCausalLM)}[family]
+    cfg = cfg_cls(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=128, vocab_size=256, max_position_embeddings=8192, pad_token_id=0)
+    torch.manual_seed(1)
+    return model_cls(cfg).eval().to(device="cuda", dtype=torch.bfloat16)
+
+
+def rel_mse(got, want):
+    got, want = got.float(), want.float()
+    return float(((got - want) ** 2).sum() / (want ** 2).sum())
+
+
+def run(model, ids, steps_ids, cache):
+    logits = []
+    with torch.no_grad():
+        out = model(ids, past_key_values=cache, use_cache=True)
+        logits.append(out.logits[:, -1])
+        for t in range(steps_ids.shape[1]):
+            out = model(steps_ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+            logits.append(out.logits[:, -1])
+    return torch.stack(logits, 1)
+
+
+CASES = [
+    # family, mode, bound on rel-MSE of the prompt's last logits and of the decode logits
+    ("llama", "hybrid_full", 2e-3),
+    ("llama", "d_k4v4_vert", 2e-3),
+    ("llama", "d_k4v4", 2e-3),
+    ("qwen", "hybrid_full", 2e-3),
+    ("llama", "sage_w", 1e-3),
+    ("llama", "sage_w0", 1e-3),
+    ("llama", "vquant_vert", 1e-3),
+    ("llama", "full_attention", 1e-4),
+    ("qwen", "vquant_vert", 1e-3),
+    ("glm4", "sage_w", 1e-3),
+    ("glm4", "vquant_vert", 1e-3),
+]
+
+
+@pytest.mark.parametrize("family,mode,bound", CASES)
+def test_patched_model_matches_stock_attention(family, mode, bound):
+    from transformers import DynamicCache
+
+    from hyquant_b200 import create_cache_for_mode
+    from hyquant_b200.patch import D_STAGE_MODES, patch_attention_forward_model
+
+    model = tiny(family)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    ids = torch.randint(1, 256, (1, PROMPT), generator=g).cuda()
+    steps_ids = torch.randint(1, 256, (1, STEPS), generator=g).cuda()
+    want = run(model, ids, steps_ids, DynamicCache(config=model.config))
+
+    patch_attention_forward_model(model, mode=mode, window_size=WINDOW, top_ratio=RATIO)
+    if mode in D_STAGE_MODES:
+        cache = create_cache_for_mode(mode, num_layers=2, window_size=WINDOW, top_ratio=RATIO)
+    else:
+        cache = DynamicCache(config=model.config)
+    got = run(model, ids, steps_ids, cache)
+    torch.cuda.synchronize()
+    assert torch.isfinite(got).all()
+    err_prefill, err_decode = rel_mse(got[:, 0], want[:, 0]), rel_mse(got[:, 1:], want[:, 1:])
+    print(f"{family}/{mode}: rel-MSE prefill {err_prefill:.3e} decode {err_decode:.3e}")
+    assert err_prefill < bound and err_decode < bound
+    if mode in D_STAGE_MODES:
+        layer = cache.get_layer(0)
+        assert layer.phase == "decode" and cache.get_seq_length() == PROMPT + STEPS
