@@ -139,11 +139,11 @@ def layer_bytes(layer, h_q_total):
     return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16)
 
 
-def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True):
+def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None):
     """K steps of (one decode launch per layer), device-timed; returns ms total, launches.
     ``flush``: a buffer larger than L2 that is rewritten before every step (outside the
     timed events) when the step's own caches do not exceed L2."""
-    r = H_Q // H_KV
+    r = H_Q // H_KV if kv_repeat is None else kv_repeat
     plans = []
     outs = []
     for layer, q in zip(layers, qs):
@@ -240,6 +240,90 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
 # CPU baseline (oracle port of the reference's PyTorch fallback)
 # ---------------------------------------------------------------------------
 
+def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
+    """Batched decode at Qwen3-32B attention shapes (batch 16, 64 query / 8 KV heads, prefix 32K): the KV heads
+    are split over the ranks, each rank decodes its heads, nothing is exchanged.  Total work is fixed."""
+    b, h_q, h_kv, n = 16, 64, 8, 32768
+    if h_kv % world:
+        return None
+    hq_l, hkv_l = h_q // world, h_kv // world
+    caches = 4
+    ls, qq = zip(*[build_layer(hq, torch, 7000 + 10 * i + rank, n, dev, b=b, h_q=hq_l, h_kv=hkv_l) for i in range(caches)])
+    bts = layer_bytes(ls[0], b * hq_l)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if caches * bts < (256 << 20) else None
+    ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, dist, flush=flush, graph=graph, kv_repeat=h_q // h_kv)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    us = ms * 1e3 / cnt
+    return {"workload": "batch 16, 64q/8kv, d=128, prefix 32768, W=128, rho=5%, K4V4, 64 staging tokens",
+            "sharding": f"kv heads over {world} rank(s), {hkv_l} per rank, no collective", "scaling": "strong",
+            "us_per_call": round(us, 2), "bytes_per_call_per_rank": bts,
+            "gbps_all_ranks": round(bts * world / us / 1e3, 1), "caches_per_rank": caches,
+            "l2": "caches exceed L2" if flush is None else "flushed before each pass"}
+
+
+def bench_long_context_decode(torch, hq, dev, rank, world, dist):
+    """Long-context decode at GLM-4-9B attention shapes (batch 4, 32 query / 2 KV heads, prefix 128K): each step
+    appends one token per layer (a staging flush every 128 tokens) and decodes.  With more than one rank the prefix
+    is sequence-sharded: partial softmax states are all-gathered with NCCL and merged on every rank."""
+    from hyquant_b200 import sharded
+    b, h_q, h_kv, n = 4, 32, 2, 131072
+    nl, steps, warm = 4, 136, 8
+    r = h_q // h_kv
+    layers, qs = [], []
+    for i in range(nl):
+        full, qd = build_layer(hq, torch, 9000 + i, n, dev, b=b, h_q=h_q, h_kv=h_kv)     # same seed on every rank
+        if world > 1:
+            shard = sharded.shard_layer_sequence(full, world, rank)
+            del full
+            layers.append(sharded.SequenceShardedLayer(shard))
+        else:
+            layers.append(full)
+        qs.append(qd)
+    torch.cuda.empty_cache()
+    g = torch.Generator(device=dev); g.manual_seed(4242)
+    kn = torch.randn(steps + warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    vn = torch.randn(steps + warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    tail = rank == world - 1
+
+    def one(s):
+        for layer, q in zip(layers, qs):
+            if world > 1:
+                layer.append_staging(kn[s], vn[s], tail)
+                layer.decode_attention(q, r)
+            else:
+                layer.append_staging(kn[s], vn[s])
+                layer.decode_attention(q, r)
+    for s in range(warm):
+        one(s)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(warm, warm + steps):
+        one(s)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    us = ms * 1e3 / (steps * nl)
+    full_bytes = algorithmic_bytes(b * h_kv, b * h_q, n - W - int((n - W) * RHO), int((n - W) * RHO) + W + 64)
+    return {"workload": "batch 4, 32q/2kv, d=128, prefix 131072, W=128, rho=5%, K4V4; per step and layer: append one "
+                        "token (flush at 128) + decode", "layers": nl, "steps": steps,
+            "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks, NCCL all-gather of (m, l, acc) + merge",
+            "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
+            "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
+            "launch_mode": "python (host-driven: append + decode" + (" + all-gather + merge)" if world > 1 else ")"),
+            "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
+
+
 def build_cpu_layer(seed=1015, n_prefix=N_PREFIX):
     from hyquant_b200.synth import gen_numpy, n_vertical
     from oracle import hq_oracle as orc
@@ -321,7 +405,7 @@ def run_ours(args):
         dist = dist_
     layers, qs = [], []
     if args.no_decode:
-        args.layers, args.no_e2e, args.no_sweep, args.no_cpu_baseline = 1, True, True, True
+        args.layers, args.no_e2e, args.no_sweep, args.no_cpu_baseline, args.no_extra = 1, True, True, True, True
     for li in range(args.layers):
         layer, qd = build_layer(hq, torch, 1015 + 100 * rank + li, N_PREFIX, dev)
         layers.append(layer); qs.append(qd)
@@ -394,6 +478,12 @@ def run_ours(args):
                             "prepare_ms_first_call": round(prep_ms, 2),
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
+    batched = long_ctx = None
+    if not args.no_extra:
+        batched = bench_batched_decode(torch, hq, dev, rank, world, dist, not args.no_graph)
+        torch.cuda.empty_cache()
+        long_ctx = bench_long_context_decode(torch, hq, dev, rank, world, dist)
+        torch.cuda.empty_cache()
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -418,6 +508,8 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "sweep": sweep,
             "prefill": prefill,
+            "batched_decode": batched,
+            "long_context_decode": long_ctx,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -443,6 +535,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the batched (64q/8kv x 16) and 128K long-context decode legs")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

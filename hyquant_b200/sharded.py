@@ -58,6 +58,36 @@ def gather_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, group=N
     return out[:, :, d].contiguous(), out[:, :, d + 1].contiguous(), out[:, :, :d].contiguous()
 
 
+def shard_layer_sequence(layer, world: int, rank: int):
+    """This rank's sequence shard of a frozen ``DStageLayerCache`` that holds the whole cache:
+    a new layer cache owning copies of its INT4-prefix and vertical-line ranges; window and live
+    staging tokens go to the last rank only, which is also the rank whose prefix grows at a flush."""
+    from .d_stage_kv_cache import GROUP_SIZE, DStageLayerCache
+    if layer.phase != "decode":
+        raise ValueError("shard_layer_sequence needs a frozen cache")
+    q0, q1, t0, t1 = sequence_shard_plan(layer._n_quant, layer.k_topk.shape[1], world)[rank]
+    tail = rank == world - 1
+    s = DStageLayerCache(layer.layer_idx, layer.k_bits, layer.v_bits, layer.window_size, layer.top_ratio, layer.use_vert)
+    s._B, s._H_KV, s._D = layer._B, layer._H_KV, layer._D
+    BH, dev = layer._kq.shape[0], layer._kq.device
+    n = q1 - q0
+    s._alloc_prefix(BH, n, dev)
+    for dst, src in ((s._kq, layer._kq), (s._vq, layer._vq), (s._ks, layer._ks), (s._vs, layer._vs)):
+        dst[:, :n].copy_(src[:, q0:q1])
+    s._n_quant = n
+    s.k_topk, s.v_topk = layer.k_topk[:, t0:t1].contiguous(), layer.v_topk[:, t0:t1].contiguous()
+    w = layer.k_window.shape[1] if tail else 0
+    s.k_window, s.v_window = layer.k_window[:, :w].contiguous(), layer.v_window[:, :w].contiguous()
+    s._staging_buf_k = layer._staging_buf_k.clone() if tail else torch.zeros_like(layer._staging_buf_k)
+    s._staging_buf_v = layer._staging_buf_v.clone() if tail else torch.zeros_like(layer._staging_buf_v)
+    s._staging_ptr = layer._staging_ptr if tail else 0
+    assert s._staging_buf_k.shape[1] == GROUP_SIZE
+    s._seq_len = n + (t1 - t0) + w + s._staging_ptr
+    s._lib = layer._lib
+    s.phase = "decode"
+    return s
+
+
 class SequenceShardedLayer:
     """One rank's shard of a frozen layer cache plus the merge step.
 

@@ -321,3 +321,50 @@ def test_full_size_split_and_shard_invariance():
     merged = hq.lse_merge(torch.stack(ms), torch.stack(ls), torch.stack(accs), out_dtype=torch.float32)
     assert (merged - ref).abs().max().item() <= MAX_ABS
     assert (merged - full).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_sequence_shards_of_a_layer_merge_to_the_full_result(world):
+    """`shard_layer_sequence` splits a frozen layer cache into per-rank caches; decoding every shard in
+    partial mode (all on this one GPU, one after the other) and merging equals the unsharded decode,
+    before and after a staging flush on the tail rank."""
+    import hyquant_b200 as hq
+    from hyquant_b200 import sharded
+    from hyquant_b200.decode_d_stage import lse_merge
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV, N, W = 2, 8, 2, 4096 + 77, 128
+    R = H_Q // H_KV
+    t = gen_torch(B, H_Q, H_KV, N, 128, W, 0.05, 321, n_qry=W, device="cuda")
+    full = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=0.05, use_vert=True)
+    full.update_prefill(t["k"], t["v"])
+    full.save_query_tail(t["q"])
+    full.freeze(kv_repeat=R)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    new = [(torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16(),
+            torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()) for _ in range(140)]
+    for kn, vn in new[:9]:
+        full.append_staging(kn, vn)
+    shards = [sharded.shard_layer_sequence(full, world, r) for r in range(world)]
+    plan = sharded.sequence_shard_plan(full._n_quant, full.k_topk.shape[1], world)
+    assert sum(s._n_quant for s in shards) == full._n_quant and plan[0][0] == 0
+    assert sum(s.k_topk.shape[1] for s in shards) == full.k_topk.shape[1]
+    q = t["q_decode"]
+    rows = B * H_Q
+
+    def sharded_decode():
+        m = torch.empty(world, rows, device="cuda"); l = torch.empty_like(m)
+        acc = torch.empty(world, rows, 128, device="cuda")
+        for r, s in enumerate(shards):
+            s.decode_attention(q, R, partial=(m[r], l[r], acc[r]))
+        return lse_merge(m, l, acc, out_dtype=q.dtype).reshape(B, H_Q, 1, 128)
+
+    want = full.decode_attention(q, R)
+    got = sharded_decode()
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2 * 0.25
+    for kn, vn in new[9:]:                      # crosses one flush of 128 tokens
+        full.append_staging(kn, vn)
+        shards[-1].append_staging(kn, vn)
+    assert shards[-1]._n_quant == plan[-1][1] - plan[-1][0] + 128 and shards[-1]._staging_ptr == full._staging_ptr
+    want = full.decode_attention(q, R)
+    got = sharded_decode()
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2 * 0.25
