@@ -139,7 +139,7 @@ def layer_bytes(layer, h_q_total):
     return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16)
 
 
-def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None):
+def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None, overlap=True):
     """K steps of (one decode launch per layer), device-timed; returns ms total, launches.
     ``flush``: a buffer larger than L2 that is rewritten before every step (outside the
     timed events) when the step's own caches do not exceed L2."""
@@ -148,7 +148,12 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, g
     outs = []
     for layer, q in zip(layers, qs):
         q2 = q.reshape(-1, D)
-        plans.append((layer._decode_plan(q2, r), q2))
+        plan = layer._decode_plan(q2, r)
+        # consecutive calls work on different caches and only write their own output and the shared
+        # workspace, so each may be launched to overlap the end of the call before it
+        plan.args.flags = 1 if overlap else 0
+        layer._plan_fresh = not overlap
+        plans.append((plan, q2))
         outs.append(torch.empty_like(q2))
     for _ in range(warmup):
         for (p, q2), o in zip(plans, outs):
@@ -414,8 +419,12 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph)
+    ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph,
+                                     overlap=not args.no_overlap)
     clocks = sampler.stop()
+    ms_plain = None
+    if not args.no_overlap and not args.no_decode:
+        ms_plain, _ = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph, overlap=False)
     if args.no_e2e:
         e2e_ms, h2d, d2h = float("nan"), 0, 0
     else:
@@ -496,12 +505,16 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": CONFIG,
             "us_per_call": us_per_call, "us_per_token_32_layers": ms_per_step * 1e3,
+            "us_per_call_without_overlap": None if ms_plain is None else ms_plain / args.steps * 1e3 / args.layers,
             "bytes_per_call": call_bytes, "frac_of_8TBps": gbs_one / 8000.0,
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
                     "path": "DStageLayerCache.append_staging + decode_attention per layer, q/k/v from pinned host, out to host"},
-            "gpu_launches": launches, "launch_mode": "python" if args.no_graph else "cuda graph replay of one token (32 launches)",
+            "gpu_launches": launches,
+            "launch_mode": ("python" if args.no_graph else "cuda graph replay of one token (32 launches)") +
+                           ("" if args.no_overlap else "; programmatic dependent launch: a call's blocks start and fetch their first "
+                            "cache units while the call before it merges its splits; q, staging, output and workspace wait for it"),
             "roofline": {"bound": "hbm", "achieved": gbs_one, "peak": peak, "unit": "GB/s", "frac": gbs_one / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peak_src,
                          "kernel": "hq::decode_splitk_kernel<1>", "algorithmic_bytes_per_launch": call_bytes},
@@ -535,6 +548,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="launch every decode call plainly (no programmatic dependent launch)")
     ap.add_argument("--no-extra", action="store_true", help="skip the batched (64q/8kv x 16) and 128K long-context decode legs")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

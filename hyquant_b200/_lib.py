@@ -14,6 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libhyquant_b200.so")
 
 HQ_BF16, HQ_F16, HQ_F32 = 0, 1, 2
+HQ_DECODE_OVERLAP_PREVIOUS = 1
 HQ_OK = 0
 ERR_NAMES = {-1: "HQ_ERR_INVALID", -2: "HQ_ERR_UNSUPPORTED", -3: "HQ_ERR_ALIGNMENT",
              -4: "HQ_ERR_WORKSPACE", -5: "HQ_ERR_CUDA", -6: "HQ_ERR_TIMEOUT"}
@@ -41,7 +42,7 @@ class DecodeArgs(C.Structure):
     _fields_ = [
         ("struct_bytes", C.c_int32), ("BH_KV", C.c_int32), ("kv_repeat", C.c_int32), ("head_dim", C.c_int32),
         ("n_quant", C.c_int32), ("n_topk", C.c_int32), ("n_staging", C.c_int32), ("n_window", C.c_int32),
-        ("out_dtype", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float), ("reserved0", C.c_int32),
+        ("out_dtype", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float), ("flags", C.c_int32),
         ("q", C.c_void_p), ("q_stride", C.c_int64),
         ("k_packed", C.c_void_p), ("v_packed", C.c_void_p), ("kp_stride_bh", C.c_int64), ("vp_stride_bh", C.c_int64),
         ("k_scale", C.c_void_p), ("v_scale", C.c_void_p), ("ks_stride_bh", C.c_int64), ("vs_stride_bh", C.c_int64),

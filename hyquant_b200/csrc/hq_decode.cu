@@ -61,6 +61,8 @@ struct DecodeParams {
   void* out; int64_t out_stride;
   float* pm; float* pl; float* pacc;      // partial mode outputs (or null)
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
+  int overlap;                            // launched with programmatic stream serialisation
+  int uq_stable;                          // INT4 units [0, uq_stable) cannot have been written by the previous kernel
   int* status; int* counters;             // workspace
   float* ws_m; float* ws_l; float* ws_acc;
 };
@@ -210,18 +212,7 @@ decode_splitk_kernel(const DecodeParams p) {
   uint8_t* my_ring = ring + warp * (kSlots * kSlotBytes);
   uint64_t* my_bar = bars + warp * kSlots;
 
-  // ---- 1. the query rows first: these small loads must be in the memory system
-  // before the bulk copies below, or they queue behind megabytes of KV traffic.
-  uint2 qraw[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int hd = nt * 8 + warp;
-    qraw[nt] = make_uint2(0u, 0u);
-    if (hd < p.R)
-      qraw[nt] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
-  }
-
-  // ---- 2. barriers and the first bulk copies
+  // ---- 1. barriers
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) mbar_init(&my_bar[s], 1);
@@ -252,8 +243,46 @@ decode_splitk_kernel(const DecodeParams p) {
       bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
     }
   };
-  if (lane == 0) {
-    for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
+  // A unit is stable when the kernel running just before this one cannot have written it:
+  // INT4 tokens older than the newest 128, vertical-line tokens, window tokens.
+  auto stable = [&](int i) -> bool {
+    const int u = u_begin + warp + kWarps * i;
+    if (u < p.uq) return u < p.uq_stable;
+    const int ub = u - p.uq;
+    return ub < p.useg[0] || ub >= p.useg[0] + p.useg[1];
+  };
+
+  // ---- 2. the query rows and the first bulk copies.
+  // Plain launch: the small query loads go first, or they queue behind megabytes of cache
+  // traffic.  Overlapped launch: the previous kernel may still be running, so only stable
+  // units are requested; then this grid waits for the previous one to complete (its q,
+  // staging and workspace writes are visible after that) and requests the rest.
+  uint2 qraw[NT];
+  auto load_q = [&]() {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int hd = nt * 8 + warp;
+      qraw[nt] = make_uint2(0u, 0u);
+      if (hd < p.R)
+        qraw[nt] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
+    }
+  };
+  if (!p.overlap) {
+    load_q();
+    if (lane == 0) {
+      for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
+    }
+  } else {
+    int early = 0;
+    if (lane == 0) {
+      while (early < kSlots && early < n_my && stable(early)) { issue(early); ++early; }
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    load_q();
+    if (lane == 0) {
+      for (int i = early; i < kSlots && i < n_my; ++i) issue(i);
+    }
   }
 
   // ---- 3. query fragments (B operands of S^T = K Q^T) scattered straight into fragment
@@ -736,8 +765,17 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
     HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_dev = dev;
   }
-  decode_splitk_kernel<NT, kScaleTma><<<grid, dim3(kThreads), smem, st>>>(p);
-  HQ_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.overlap ? 1 : 0;
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma>, p));
   return HQ_OK;
 }
 
@@ -807,6 +845,9 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
                  "hq_decode_splitk: BF16 segment %d must be 16-byte aligned with head strides multiple of 8", s);
     }
   }
+  HQ_REQUIRE((a->flags & ~HQ_DECODE_OVERLAP_PREVIOUS) == 0, HQ_ERR_INVALID, "hq_decode_splitk: unknown flags 0x%x", a->flags);
+  p.overlap = (a->flags & HQ_DECODE_OVERLAP_PREVIOUS) ? 1 : 0;
+  p.uq_stable = a->n_quant > 128 ? (a->n_quant - 128) / kUnitQ : 0;
   p.R = a->kv_repeat;
   p.out_dtype = a->out_dtype;
   p.sml = a->sm_scale * 1.44269504f;
@@ -899,6 +940,7 @@ extern "C" int hq_decode_splitk_static(const hq_decode_args* a, void* stream) {
   const int64_t head = kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256);
   HQ_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, (size_t)head, (cudaStream_t)stream));
   hq_decode_args b = *a;
+  b.flags = 0;                       // the kernel's predecessor in the stream is the memset above
   b.workspace = dev_ptr[dev];
   b.workspace_bytes = kStaticScratchBytes;
   return hq_decode_splitk(&b, stream);

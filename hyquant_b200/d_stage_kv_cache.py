@@ -74,6 +74,8 @@ class DStageLayerCache:
         self._plan: Optional[DecodePlan] = None
         self._lib = None
         self.vertical_indices: Optional[torch.Tensor] = None   # [B, H_KV, T] chosen at freeze
+        self.overlap_previous: bool = True     # decode launches may overlap the end of the previous kernel
+        self._plan_fresh: bool = False
 
     # ---- views of the live prefix (reference attribute names) -----------------
     @property
@@ -248,10 +250,20 @@ class DStageLayerCache:
                               kv_repeat, None)
         p = self._plan
         if p is None or p.kv_repeat != kv_repeat:
+            # After freeze this cache's segments are written only by its own staging append and
+            # flush kernels (staging buffer, newest 128 prefix tokens), so the decode kernel may
+            # start fetching older units while whatever runs just before it finishes.  The
+            # first decode after a freeze or a prefix growth is launched plainly: the kernel
+            # before it may be the one that wrote the whole prefix.
             p = DecodePlan(q2d, self._kq, self._vq, self._ks, self._vs, self.k_topk, self.v_topk,
                            self._staging_buf_k, self._staging_buf_v, self.k_window, self.v_window,
-                           kv_repeat, None)
+                           kv_repeat, None, overlap_previous=self.overlap_previous)
+            p.args.flags = 0
             self._plan = p
+            self._plan_fresh = True
+        elif self.overlap_previous and self._plan_fresh:
+            self._plan_fresh = False
+            p.args.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS
         p.args.n_quant = self._n_quant
         p.args.n_staging = self._staging_ptr
         return p

@@ -147,7 +147,11 @@ class DecodePlan:
 
     def __init__(self, q, k_quant_packed, v_quant_packed, k_scale, v_scale,
                  k_topk, v_topk, k_staging, v_staging, k_window, v_window,
-                 kv_repeat: int, sm_scale: Optional[float], num_splits: int = 0):
+                 kv_repeat: int, sm_scale: Optional[float], num_splits: int = 0, overlap_previous: bool = False):
+        """``overlap_previous``: launch with ``HQ_DECODE_OVERLAP_PREVIOUS`` — the kernel's blocks may
+        start, and fetch cache units that are older than the newest 128 prefix tokens or lie in the
+        vertical-line / window segments, while the kernel launched just before it on the stream is
+        finishing.  Only for callers that know that kernel writes none of those."""
         _lib.require_cuda(q, "q")
         BH_Q, D = q.shape
         if D != 128:
@@ -164,6 +168,7 @@ class DecodePlan:
         a.BH_KV, a.kv_repeat, a.head_dim = self.BH_KV, kv_repeat, D
         a.sm_scale = float(D ** -0.5 if sm_scale is None else sm_scale)
         a.num_splits = num_splits
+        a.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS if overlap_previous else 0
         keep = []
         n_quant = 0 if k_quant_packed is None else int(k_quant_packed.shape[1])
         a.n_quant = n_quant

@@ -86,6 +86,16 @@ int hq_staging_append(const void* k_new, const void* v_new, int64_t k_stride, in
  * bytes apart and BF16 rows 128 elements apart; every base pointer and head
  * stride must keep rows 16-byte aligned (HQ_ERR_ALIGNMENT otherwise).
  */
+/* hq_decode_args.flags.  HQ_DECODE_OVERLAP_PREVIOUS launches the kernel with programmatic
+ * stream serialisation: its blocks may become resident while the kernel launched just before
+ * it on the same stream is still finishing, and they fetch their first cache units in that
+ * time.  q, the staging buffers, the newest 128 tokens of the INT4 prefix (codes and scales),
+ * the output and the workspace are touched only after the previous kernel has completed, so
+ * the previous kernel may write any of those (a staging append, a staging flush, the producer
+ * of q, the previous decode call).  The caller promises that it writes nothing else of this
+ * call's cache: not the older prefix, nor the vertical-line and window segments. */
+#define HQ_DECODE_OVERLAP_PREVIOUS 1
+
 typedef struct hq_decode_args {
   int32_t struct_bytes;        /* sizeof(hq_decode_args), checked */
   int32_t BH_KV;               /* batch * kv heads */
@@ -98,7 +108,7 @@ typedef struct hq_decode_args {
   int32_t out_dtype;           /* HQ_BF16 / HQ_F16 / HQ_F32 */
   int32_t num_splits;          /* 0 = choose automatically */
   float   sm_scale;            /* softmax scale, e.g. head_dim^-0.5 */
-  int32_t reserved0;
+  int32_t flags;               /* 0, or HQ_DECODE_OVERLAP_PREVIOUS */
   const void* q;               /* bf16 [BH_KV*kv_repeat, 128] */
   int64_t q_stride;            /* elements between query rows */
   const void* k_packed;        /* int8 [BH_KV, n_quant, 64] */

@@ -368,3 +368,83 @@ def test_sequence_shards_of_a_layer_merge_to_the_full_result(world):
     want = full.decode_attention(q, R)
     got = sharded_decode()
     assert float((got.float() - want.float()).abs().max()) <= 2e-2 * 0.25
+
+
+def test_overlapped_launch_equals_plain_launch():
+    """HQ_DECODE_OVERLAP_PREVIOUS changes when a call's blocks start, not what they compute.  Two identical
+    layer caches take the same 300 appended tokens (two staging flushes); one decodes with plain launches,
+    the other with launches that may overlap the kernel before them (the staging append or the flush)."""
+    import hyquant_b200 as hq
+    from hyquant_b200.decode_d_stage import decode_status
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV, N, W = 1, 32, 8, 8192 + 5, 128
+    R = H_Q // H_KV
+    t = gen_torch(B, H_Q, H_KV, N, 128, W, 0.05, 99, n_qry=W, device="cuda")
+    layers = []
+    for overlap in (False, True):
+        layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=0.05, use_vert=True)
+        layer.overlap_previous = overlap
+        layer.update_prefill(t["k"], t["v"])
+        layer.save_query_tail(t["q"])
+        layer.freeze(kv_repeat=R)
+        layers.append(layer)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for step in range(300):
+        kn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        vn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        qn = torch.randn(B, H_Q, 1, 128, generator=g, device="cuda").bfloat16()
+        outs = []
+        for layer in layers:
+            layer.append_staging(kn, vn)
+            outs.append(layer.decode_attention(qn, R).clone())
+        assert torch.equal(outs[0], outs[1]), f"step {step}"
+    assert layers[1]._plan.args.flags == 1 and layers[0]._plan.args.flags == 0
+    assert decode_status(layers[1]._plan.ws) == 0
+
+
+def test_overlapped_launches_back_to_back_in_a_graph():
+    """A captured sequence of overlapped decode launches over different caches (the bench's launch pattern)
+    replays to the same outputs as plain launches."""
+    import hyquant_b200 as hq
+    from hyquant_b200.decode_d_stage import decode_status
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV, W = 1, 32, 8, 128
+    R = H_Q // H_KV
+    plans, qs, want = [], [], []
+    for i, n in enumerate((1024, 4096 + 33, 16384, 700, 32768)):
+        t = gen_torch(B, H_Q, H_KV, n, 128, W, 0.05, 500 + i, n_qry=W, device="cuda")
+        layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=0.05, use_vert=True)
+        layer.update_prefill(t["k"], t["v"])
+        layer.save_query_tail(t["q"])
+        layer.freeze(kv_repeat=R)
+        for j in range(3 + i):
+            layer.append_staging(t["k"][:, :, j:j + 1].contiguous(), t["v"][:, :, j:j + 1].contiguous())
+        q2 = t["q_decode"].reshape(-1, 128)
+        plan = layer._decode_plan(q2, R)
+        plan.args.flags = 0
+        want.append(plan.run(q2).clone())
+        plans.append((layer, plan)); qs.append(q2)
+    torch.cuda.synchronize()
+    outs = [torch.zeros_like(w) for w in want]
+    for _, plan in plans:
+        plan.args.flags = 1
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            for (_, plan), q2, o in zip(plans, qs, outs):
+                plan.run(q2, out=o)
+    s.synchronize()
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    for o in outs:
+        o.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for (_, plan), q2, o in zip(plans, qs, outs):
+            plan.run(q2, out=o)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    assert decode_status(plans[0][1].ws) == 0

@@ -44,10 +44,10 @@ def run(model, ids, steps_ids, cache):
 
 CASES = [
     # family, mode, bound on rel-MSE of the prompt's last logits and of the decode logits
-    ("llama", "hybrid_full", 2e-3),
-    ("llama", "d_k4v4_vert", 2e-3),
-    ("llama", "d_k4v4", 2e-3),
-    ("qwen", "hybrid_full", 2e-3),
+    ("llama", "hybrid_full", 2e-2),
+    ("llama", "d_k4v4_vert", 2e-2),
+    ("llama", "d_k4v4", 2e-2),
+    ("qwen", "hybrid_full", 2e-2),
     ("llama", "sage_w", 1e-3),
     ("llama", "sage_w0", 1e-3),
     ("llama", "vquant_vert", 1e-3),
