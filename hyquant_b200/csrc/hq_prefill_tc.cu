@@ -4,18 +4,25 @@
 // block at s of query head h, keys below wla(s) are INT8 unless they are vertical lines of h
 // (masked here, served from gathered BF16 tiles), keys in [wla(s), s + 128) are BF16 + causal mask.
 //
-// Structure of one CTA (128 queries of one head, 10 warps):
-//   warp 8 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of Q once and of a K tile
-//                      + a transposed V tile per step into a four-slot ring;
-//   warp 9 (one lane)  issues tcgen05.mma: S = Q K^T (kind::i8 with s32 accumulators or kind::f16 on
-//                      bf16) into one of two S buffers in tensor memory, and O += P V (kind::f16) into
-//                      the O accumulator in tensor memory; completion is signalled with tcgen05.commit;
-//   warps 0-7          two threads per query row (half of the columns each): tcgen05.ld of the S row, scales / masks, online
-//                      softmax in base 2 with a lazily updated maximum (the O accumulator is rescaled
-//                      in tensor memory only when the maximum grows by more than 2^8), P to shared
-//                      memory as the A operand of the next P V, final O / l from tensor memory.
-// S is double-buffered so that Q K^T of tile i+1 runs while the softmax of tile i is in flight.
-// All operands are K-major: V is transposed once per call by the preparation pass.
+// One CTA works on the same 128 queries of TWO query heads of one KV group (A and B), so every INT8 and
+// window K / V tile that reaches shared memory feeds two score tiles, and the two heads' softmax chains
+// interleave on the SM: while one head's threads are in their exponentials the tensor core runs the other
+// head's products.  10 warps:
+//   warp 8 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of both heads' Q once and of one
+//                      item (a K tile + a transposed V tile) per step into a four-slot ring.  INT8 and
+//                      window items serve both heads; the gathered vertical-line tiles are per head.
+//   warp 9 (one lane)  issues tcgen05.mma in a fixed order of (head, tile) operations: S = Q K^T
+//                      (kind::i8 with s32 accumulators, or kind::f16 on bf16) into one of the head's two
+//                      S buffers in tensor memory, two operations ahead of O += P V (kind::f16, P read
+//                      from tensor memory, V^T from shared memory); completion is signalled with
+//                      tcgen05.commit.
+//   warps 0-3 / 4-7    softmax of head A / B, one thread per query row: tcgen05.ld of the 64 scores,
+//                      scales / masks, online softmax in base 2 with a lazily updated maximum (the O
+//                      accumulator is rescaled in tensor memory only when the maximum grows by more than
+//                      2^8), P as bf16 pairs written back over the first 32 columns of the same S buffer,
+//                      final O / l from tensor memory.
+// Tensor memory (512 columns): S_A0 | S_A1 | S_B0 | S_B1 (64 each) | O_A | O_B (128 each).
+// All shared-memory operands are K-major: V is transposed once per call by the preparation pass.
 // Every wait is bounded and abortable; a failed wait raises bit 1 of the status word.
 #include "hq_tc05.cuh"
 
@@ -30,20 +37,59 @@ struct PrefillTcParams {
   int* status;
 };
 
-constexpr int kTcThreads = 320;        // 8 softmax warps + producer warp + MMA warp
-constexpr uint32_t kTmemCols = 256;        // S0 [0,64) | S1 [64,128) | O [128,256)
+constexpr int kTcThreads = 320;            // 2 x 4 softmax warps + producer warp + MMA warp
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 256; // S buffer of head h, parity s: kColS + 128 h + 64 s; O of head h: kColO + 128 h
 constexpr float kTcLazy = 8.0f;
 
-constexpr int kKvStages = 4;   // K / V^T ring depth: tile loads run this many tiles ahead of the MMAs
+constexpr int kKvStages = 4;   // item ring depth: loads run this many items ahead of the MMAs
 struct TcSmem {              // offsets from a 1024-aligned base
-  static constexpr int Qi = 0;                             // 16 KB  [128 rows][128 B] int8
-  static constexpr int Qb = 16384;                         // 32 KB  2 x [128 rows][128 B] bf16
-  static constexpr int K = 49152;                          // kKvStages x 16 KB
-  static constexpr int V = K + kKvStages * 16384;          // kKvStages x 16 KB  [128 d rows][128 B]
-  static constexpr int P = V + kKvStages * 16384;          // 2 x 16 KB  [128 rows][128 B] bf16
-  static constexpr int Bar = P + 32768;                    // barriers + scratch
-  static constexpr int Xch = Bar + 256;                    // 3 x [2][128] floats: row maxima (two parities), row sums
-  static constexpr int Total = Xch + 3072;
+  static constexpr int Qi = 0;                             // 2 x 16 KB  [head][128 rows][128 B] int8
+  static constexpr int Qb = 32768;                         // 2 x 32 KB  [head][2 halves][128 rows][128 B] bf16
+  static constexpr int KV = 98304;                         // kKvStages x 32 KB: K 16 KB (int8 tile + scales at 8192,
+                                                           // or two bf16 halves) | V^T 16 KB [128 d rows][128 B]
+  static constexpr int Bar = KV + kKvStages * 32768;       // barriers + scratch
+  static constexpr int Total = Bar + 512;
+};
+
+// One (head, tile) operation of the MMA issuer's fixed order.
+struct TcOp {
+  int h;        // head 0 / 1
+  int item;     // ring item that holds its K / V
+  int t;        // tile index within the head's own sequence
+  int kind;     // 0 INT8, 1 vertical, 2 window
+  bool first;   // first operation that uses the item (waits for the load)
+  bool last;    // last operation that uses the item (frees the slot)
+};
+
+struct TcPlan {
+  int n_rest, n_win, nvert[2], nheads;
+  __device__ __forceinline__ int n_ops() const { return nheads * (n_rest + n_win) + nvert[0] + nvert[1]; }
+  __device__ __forceinline__ int n_tiles(int h) const { return h < nheads ? n_rest + nvert[h] + n_win : 0; }
+  __device__ __forceinline__ TcOp op(int n) const {
+    TcOp o;
+    const int a = nheads * n_rest;
+    if (n < a) {
+      o.kind = 0; o.item = n / nheads; o.h = n - o.item * nheads; o.t = o.item;
+      o.first = o.h == 0; o.last = o.h == nheads - 1;
+      return o;
+    }
+    n -= a;
+    const int nvs = nvert[0] + nvert[1];
+    if (n < nvs) {
+      const int mn = min(nvert[0], nvert[1]);
+      int j;
+      if (n < 2 * mn) { j = n >> 1; o.h = n & 1; }
+      else { j = mn + (n - 2 * mn); o.h = nvert[0] > nvert[1] ? 0 : 1; }
+      o.kind = 1; o.item = n_rest + n; o.t = n_rest + j; o.first = true; o.last = true;
+      return o;
+    }
+    n -= nvs;
+    const int w = n / nheads;
+    o.kind = 2; o.h = n - w * nheads; o.item = n_rest + nvs + w; o.t = n_rest + nvert[o.h] + w;
+    o.first = o.h == 0; o.last = o.h == nheads - 1;
+    return o;
+  }
 };
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -56,39 +102,42 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::Bar);
   uint64_t* q_full = bars + 0;
-  uint64_t* s_full = bars + 1;       // [2]
-  uint64_t* s_free = bars + 3;       // [2]
-  uint64_t* p_ready = bars + 5;      // [2]
-  uint64_t* pv_done = bars + 7;      // [2]
-  uint64_t* kv_full = bars + 9;                  // [kKvStages]
-  uint64_t* kv_empty = bars + 9 + kKvStages;     // [kKvStages]
-  uint64_t* x_bar = bars + 9 + 2 * kKvStages;    // [3] row-maximum exchange (two parities) and row-sum exchange
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + 2 * kKvStages);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13 + 2 * kKvStages);
+  uint64_t* kv_full = bars + 1;                  // [kKvStages]
+  uint64_t* kv_empty = kv_full + kKvStages;      // [kKvStages]
+  uint64_t* s_full = kv_empty + kKvStages;       // [head][2]
+  uint64_t* p_ready = s_full + 4;                // [head][2]
+  uint64_t* pv_done = p_ready + 4;               // [head][2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(pv_done + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   __shared__ int s_skip;
   if (tid == 0) s_skip = *reinterpret_cast<volatile int*>(p.status) & 2;
   __syncthreads();
   if (s_skip) return;                         // an earlier CTA gave up: drain the grid quickly
+  const int R = p.H_Q / p.H_KV, pairs = (R + 1) / 2;
   const int qb = p.nqb - 1 - blockIdx.x;     // heavy blocks first
-  const int hq = blockIdx.y, b = blockIdx.z, hkv = hq / (p.H_Q / p.H_KV);
+  const int hkv = blockIdx.y / pairs, pr = blockIdx.y - hkv * pairs, b = blockIdx.z;
   const int s0 = qb * 128;
-  const int64_t bhq = (int64_t)b * p.H_Q + hq, bhk = (int64_t)b * p.H_KV + hkv;
+  TcPlan plan;
+  plan.nheads = (2 * pr + 1 < R) ? 2 : 1;
+  const int64_t bhk = (int64_t)b * p.H_KV + hkv;
+  const int64_t bhq0 = (int64_t)b * p.H_Q + hkv * R + 2 * pr;
   const int wla = p.W > 0 ? (max(0, s0 - (p.W - 1)) / 64) * 64 : s0;
-  const int n_rest = wla / 64;
-  const int nv = p.T > 0 ? p.nv_valid[bhq * p.nqb + qb] : 0;
-  const int n_vert = (nv + 63) / 64;
+  plan.n_rest = wla / 64;
   const int win_end = min(p.N, s0 + 128);
-  const int n_win = (win_end - wla + 63) / 64;
-  const int n_tiles = n_rest + n_vert + n_win;
+  plan.n_win = (win_end - wla + 63) / 64;
+  int nv[2] = {0, 0};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (p.T > 0 && h < plan.nheads) nv[h] = p.nv_valid[(bhq0 + h) * p.nqb + qb];
+    plan.nvert[h] = (nv[h] + 63) / 64;
+  }
 
   if (tid == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < kKvStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_free + i, 256); }
-    for (int i = 0; i < 2; ++i) { mbar_init(p_ready + i, 256); mbar_init(pv_done + i, 1); mbar_init(x_bar + i, 256); }
-    mbar_init(x_bar + 2, 256);
+    for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(p_ready + i, 128); mbar_init(pv_done + i, 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -102,35 +151,57 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tc::tma_prefetch_desc(&mQi); tc::tma_prefetch_desc(&mQb); tc::tma_prefetch_desc(&mKi);
-      tc::tma_prefetch_desc(&mKb); tc::tma_prefetch_desc(&mVt);
-      mbar_expect_tx(q_full, 16384 + 32768);
-      tc::tma_load_2d(smem + TcSmem::Qi, &mQi, 0, (int)(bhq * p.N + s0), q_full);
-      tc::tma_load_2d(smem + TcSmem::Qb, &mQb, 0, (int)(bhq * p.N + s0), q_full);
-      tc::tma_load_2d(smem + TcSmem::Qb + 16384, &mQb, 64, (int)(bhq * p.N + s0), q_full);
-      for (int i = 0; i < n_tiles; ++i) {
-        const int slot = i % kKvStages;
-        if (!tc::mbar_wait_abortable(kv_empty + slot, (uint32_t)(((i / kKvStages) & 1) ^ 1), abort_flag, 200)) break;
-        uint8_t* sK = smem + TcSmem::K + slot * 16384;
-        uint8_t* sV = smem + TcSmem::V + slot * 16384;
-        if (i < n_rest) {
-          const int key0 = i * 64;
-          mbar_expect_tx(kv_full + slot, 8192 + 256 + 16384);
-          tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + key0), kv_full + slot);
-          tc::tma_load_2d(sK + 8192, &mKs, key0, (int)bhk, kv_full + slot);      // the tile's 64 key scales
-          tc::tma_load_2d(sV, &mVt, key0, (int)(bhk * 128), kv_full + slot);
-        } else if (i < n_rest + n_vert) {
-          const int j0 = (i - n_rest) * 64;
-          mbar_expect_tx(kv_full + slot, 16384 + 16384);
-          tc::tma_load_2d(sK, &mXk, 0, (int)(bhq * p.Tpad + j0), kv_full + slot);
-          tc::tma_load_2d(sK + 8192, &mXk, 64, (int)(bhq * p.Tpad + j0), kv_full + slot);
-          tc::tma_load_2d(sV, &mXv, j0, (int)(bhq * 128), kv_full + slot);
-        } else {
-          const int key0 = wla + (i - n_rest - n_vert) * 64;
-          mbar_expect_tx(kv_full + slot, 16384 + 16384);
-          tc::tma_load_2d(sK, &mKb, 0, (int)(bhk * p.N + key0), kv_full + slot);
-          tc::tma_load_2d(sK + 8192, &mKb, 64, (int)(bhk * p.N + key0), kv_full + slot);
-          tc::tma_load_2d(sV, &mVt, key0, (int)(bhk * 128), kv_full + slot);
+      tc::tma_prefetch_desc(&mKb); tc::tma_prefetch_desc(&mVt); tc::tma_prefetch_desc(&mKs);
+      mbar_expect_tx(q_full, (uint32_t)plan.nheads * (16384 + 32768));
+      for (int h = 0; h < plan.nheads; ++h) {
+        const int qrow = (int)((bhq0 + h) * p.N + s0);
+        tc::tma_load_2d(smem + TcSmem::Qi + h * 16384, &mQi, 0, qrow, q_full);
+        tc::tma_load_2d(smem + TcSmem::Qb + h * 32768, &mQb, 0, qrow, q_full);
+        tc::tma_load_2d(smem + TcSmem::Qb + h * 32768 + 16384, &mQb, 64, qrow, q_full);
+      }
+      int it = 0;
+      bool ok = true;
+      auto acquire = [&]() -> uint8_t* {
+        const int slot = it % kKvStages;
+        ok = tc::mbar_wait_abortable(kv_empty + slot, (uint32_t)(((it / kKvStages) & 1) ^ 1), abort_flag, 200);
+        return smem + TcSmem::KV + slot * 32768;
+      };
+      for (int i = 0; ok && i < plan.n_rest; ++i) {
+        uint8_t* sK = acquire();
+        if (!ok) break;
+        uint64_t* full = kv_full + it % kKvStages;
+        const int key0 = i * 64;
+        mbar_expect_tx(full, 8192 + 256 + 16384);
+        tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + key0), full);
+        tc::tma_load_2d(sK + 8192, &mKs, key0, (int)bhk, full);          // the tile's 64 key scales
+        tc::tma_load_2d(sK + 16384, &mVt, key0, (int)(bhk * 128), full);
+        ++it;
+      }
+      const int nvmax = max(plan.nvert[0], plan.nvert[1]);
+      for (int j = 0; ok && j < nvmax; ++j) {
+        for (int h = 0; ok && h < 2; ++h) {
+          if (j >= plan.nvert[h]) continue;
+          uint8_t* sK = acquire();
+          if (!ok) break;
+          uint64_t* full = kv_full + it % kKvStages;
+          const int j0 = j * 64;
+          mbar_expect_tx(full, 16384 + 16384);
+          tc::tma_load_2d(sK, &mXk, 0, (int)((bhq0 + h) * p.Tpad + j0), full);
+          tc::tma_load_2d(sK + 8192, &mXk, 64, (int)((bhq0 + h) * p.Tpad + j0), full);
+          tc::tma_load_2d(sK + 16384, &mXv, j0, (int)((bhq0 + h) * 128), full);
+          ++it;
         }
+      }
+      for (int w = 0; ok && w < plan.n_win; ++w) {
+        uint8_t* sK = acquire();
+        if (!ok) break;
+        uint64_t* full = kv_full + it % kKvStages;
+        const int key0 = wla + w * 64;
+        mbar_expect_tx(full, 16384 + 16384);
+        tc::tma_load_2d(sK, &mKb, 0, (int)(bhk * p.N + key0), full);
+        tc::tma_load_2d(sK + 8192, &mKb, 64, (int)(bhk * p.N + key0), full);
+        tc::tma_load_2d(sK + 16384, &mVt, key0, (int)(bhk * 128), full);
+        ++it;
       }
     }
   } else if (warp == 9) {
@@ -140,196 +211,188 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       constexpr uint32_t idesc_qk = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 64);
       constexpr uint32_t idesc_pv = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 128);
       bool ok = tc::mbar_wait_abortable(q_full, 0, abort_flag, 100);
-      for (int i = 0; ok && i <= n_tiles; ++i) {
-        if (i < n_tiles) {
-          const int slot = i & 1, kvs = i % kKvStages;
-          ok = tc::mbar_wait_abortable(kv_full + kvs, (uint32_t)((i / kKvStages) & 1), abort_flag, 40) &&
-               tc::mbar_wait_abortable(s_free + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag, 40);
-          if (!ok) break;
-          tc::fence_after_sync();
-          const uint32_t dS = tmem_base + (uint32_t)slot * 64;
-          const uint8_t* sK = smem + TcSmem::K + kvs * 16384;
-          if (i < n_rest) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc::mma_s8_ss(dS, tc::smem_desc_k128(smem + TcSmem::Qi, k * 32), tc::smem_desc_k128(sK, k * 32), idesc_i8, k > 0);
-          } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              tc::mma_bf16_ss(dS, tc::smem_desc_k128(smem + TcSmem::Qb + (k >> 2) * 16384, (k & 3) * 32),
-                              tc::smem_desc_k128(sK + (k >> 2) * 8192, (k & 3) * 32), idesc_qk, k > 0);
-          }
-          tc::mma_commit(s_full + slot);
+      const int n_ops = plan.n_ops();
+      auto issue_qk = [&](int n) {
+        const TcOp o = plan.op(n);
+        const int kvs = o.item % kKvStages;
+        if (o.first) {
+          ok = tc::mbar_wait_abortable(kv_full + kvs, (uint32_t)((o.item / kKvStages) & 1), abort_flag, 40);
+          if (!ok) return;
         }
-        if (i > 0) {
-          const int j = i - 1, slot = j & 1;
-          ok = tc::mbar_wait_abortable(p_ready + slot, (uint32_t)((j >> 1) & 1), abort_flag, 40);
-          if (!ok) break;
-          tc::fence_after_sync();
-          const uint32_t dO = tmem_base + 128;
-          const uint8_t* sV = smem + TcSmem::V + (j % kKvStages) * 16384;
+        tc::fence_after_sync();
+        const uint32_t dS = tmem_base + kColS + (uint32_t)(128 * o.h + 64 * (o.t & 1));
+        const uint8_t* sK = smem + TcSmem::KV + kvs * 32768;
+        if (o.kind == 0) {
+          const uint8_t* sQ = smem + TcSmem::Qi + o.h * 16384;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc::mma_bf16_ss(dO, tc::smem_desc_k128(smem + TcSmem::P + slot * 16384, k * 32), tc::smem_desc_k128(sV, k * 32), idesc_pv,
-                            (j > 0 || k > 0) ? 1u : 0u);
-          tc::mma_commit(pv_done + slot);
-          tc::mma_commit(kv_empty + (j % kKvStages));
+            tc::mma_s8_ss(dS, tc::smem_desc_k128(sQ, k * 32), tc::smem_desc_k128(sK, k * 32), idesc_i8, k > 0);
+        } else {
+          const uint8_t* sQ = smem + TcSmem::Qb + o.h * 32768;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            tc::mma_bf16_ss(dS, tc::smem_desc_k128(sQ + (k >> 2) * 16384, (k & 3) * 32),
+                            tc::smem_desc_k128(sK + (k >> 2) * 8192, (k & 3) * 32), idesc_qk, k > 0);
         }
+        tc::mma_commit(s_full + 2 * o.h + (o.t & 1));
+      };
+      auto issue_pv = [&](int n) {
+        const TcOp o = plan.op(n);
+        const int kvs = o.item % kKvStages, sl = 2 * o.h + (o.t & 1);
+        ok = tc::mbar_wait_abortable(p_ready + sl, (uint32_t)((o.t >> 1) & 1), abort_flag, 40);
+        if (!ok) return;
+        tc::fence_after_sync();
+        const uint32_t dO = tmem_base + kColO + (uint32_t)(128 * o.h);
+        const uint32_t aP = tmem_base + kColS + (uint32_t)(128 * o.h + 64 * (o.t & 1));
+        const uint8_t* sV = smem + TcSmem::KV + kvs * 32768 + 16384;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc::mma_bf16_ts(dO, aP + 8 * k, tc::smem_desc_k128(sV, k * 32), idesc_pv, (o.t > 0 || k > 0) ? 1u : 0u);
+        tc::mma_commit(pv_done + sl);
+        if (o.last) tc::mma_commit(kv_empty + kvs);
+      };
+      if (ok && n_ops > 0) issue_qk(0);
+      if (ok && n_ops > 1) issue_qk(1);
+      for (int n = 0; ok && n < n_ops; ++n) {
+        issue_pv(n);
+        if (ok && n + 2 < n_ops) issue_qk(n + 2);
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax: two threads per query row
-    // Warps w and w + 4 share the tensor-memory lanes 32 (w % 4) .. + 31 (the hardware ties a warp to the
-    // lane quarter warp % 4) and split the row's 64 score columns / 128 output columns in halves, so every
-    // scheduler has two softmax warps to interleave.  Row maxima meet through shared memory once per tile.
-    const int half = warp >> 2, wq = warp & 3;
+    // ------------------------------------------------------------ softmax: one thread per query row and head
+    // Warps 0-3 serve head A, warps 4-7 head B; warp w reaches the tensor-memory lanes 32 (w % 4) .. + 31.
+    const int h = warp >> 2, wq = warp & 3;
+    const int n_tiles = plan.n_tiles(h);
     const int r = wq * 32 + lane;            // query row inside the block = tensor-memory lane
     const int row = s0 + r;
+    const int64_t bhq = bhq0 + (h < plan.nheads ? h : 0);
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
-    float* xmax = reinterpret_cast<float*>(smem + TcSmem::Xch);        // [2 parities][2 halves][128]
-    float* xsum = xmax + 512;                                          // [2 halves][128]
-    const float qs = row < p.N ? p.q_scale[bhq * p.Npad + row] : 0.f;
+    const uint32_t colS = kColS + 128 * h, colO = kColO + 128 * h;
+    const int n_rest = plan.n_rest, n_vert = plan.nvert[h], nvh = nv[h];
+    const float qs = (row < p.N && n_tiles > 0) ? p.q_scale[bhq * p.Npad + row] : 0.f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     // the vertical-mask word of a tile is a fresh cache line every step: fetch it one step ahead
     const unsigned long long* vmrow = p.vmask + bhq * p.nkb;
-    unsigned long long vm_next = (p.T > 0 && n_rest > 0) ? __ldg(vmrow) : 0ull;
-    for (int i = 0; i < n_tiles; ++i) {
-      const int slot = i & 1;
+    unsigned long long vm_next = (p.T > 0 && n_rest > 0 && n_tiles > 0) ? __ldg(vmrow) : 0ull;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int slot = t & 1, sl = 2 * h + slot;
       const unsigned long long vm64 = vm_next;
-      if (p.T > 0 && i + 1 < n_rest) vm_next = __ldg(vmrow + i + 1);
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(s_full + slot, (uint32_t)((i >> 1) & 1), abort_flag));
+      if (p.T > 0 && t + 1 < n_rest) vm_next = __ldg(vmrow + t + 1);
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(s_full + sl, (uint32_t)((t >> 1) & 1), abort_flag));
       if (!ok) break;
       tc::fence_after_sync();
-      uint32_t sr[32];
-      tc::tmem_ld32(lane_base + slot * 64 + half * 32, sr);
+      uint32_t sr[64];
+      tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+      tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
       tc::tmem_wait_ld();
-      tc::fence_before_sync();
-      tc::mbar_arrive(s_free + slot);
 
-      // scores in the exponent's units: t[c] * esc - mu, with esc folded into one FFMA per element
-      float t[32];
+      // scores in the exponent's units: v[c] * esc - mu, with esc folded into one FFMA per element
+      float v[64];
       float esc;
-      if (i < n_rest) {
-        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::K + (i % kKvStages) * 16384 + 8192) + half * 8;
-        const uint32_t vm = (uint32_t)(vm64 >> (32 * half));
+      if (t < n_rest) {
+        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::KV + (t % kKvStages) * 32768 + 8192);
         esc = qs;
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
+        for (int c4 = 0; c4 < 16; ++c4) {
           const float4 kk = ks4[c4];
           const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const int c = 4 * c4 + x;
             // int32 -> float without the conversion unit: |score| < 2^22
-            t[c] = (__int_as_float((int)sr[c] + 0x4B400000) - 12582912.0f) * kv[x];
+            v[c] = (__int_as_float((int)sr[c] + 0x4B400000) - 12582912.0f) * kv[x];
           }
         }
-        if (vm != 0u) {
+        if (vm64 != 0ull) {
+          const uint32_t lo = (uint32_t)vm64, hi = (uint32_t)(vm64 >> 32);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) if ((vm >> c) & 1u) t[c] = -INFINITY;
+          for (int c = 0; c < 32; ++c) {
+            if ((lo >> c) & 1u) v[c] = -INFINITY;
+            if ((hi >> c) & 1u) v[32 + c] = -INFINITY;
+          }
         }
       } else {
         esc = p.sml;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(sr[c]);
-        int lim;                                             // columns (of the full tile) <= lim are visible
-        if (i < n_rest + n_vert) lim = min(64, nv - (i - n_rest) * 64) - 1;
-        else lim = min(row, p.N - 1) - (wla + (i - n_rest - n_vert) * 64);
-        lim -= 32 * half;
-        if (__any_sync(0xffffffffu, lim < 31)) {
+        for (int c = 0; c < 64; ++c) v[c] = __uint_as_float(sr[c]);
+        int lim;                                             // columns <= lim are visible
+        if (t < n_rest + n_vert) lim = min(64, nvh - (t - n_rest) * 64) - 1;
+        else lim = min(row, p.N - 1) - (wla + (t - n_rest - n_vert) * 64);
+        if (__any_sync(0xffffffffu, lim < 63)) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) if (c > lim) t[c] = -INFINITY;
+          for (int c = 0; c < 64; ++c) if (c > lim) v[c] = -INFINITY;
         }
       }
       float mx;
       {
         float m8[8];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) m8[x] = t[x];
+        for (int x = 0; x < 8; ++x) m8[x] = v[x];
 #pragma unroll
-        for (int c = 8; c < 32; ++c) m8[c & 7] = fmaxf(m8[c & 7], t[c]);
+        for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], v[c]);
         mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       }
       mx *= esc;                                             // esc >= 0
       if (esc == 0.f) mx = -INFINITY;                        // rows past N
-      // exchange the half-row maxima
-      xmax[(slot * 2 + half) * 128 + r] = mx;
-      tc::mbar_arrive(x_bar + slot);
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(x_bar + slot, (uint32_t)((i >> 1) & 1), abort_flag));
-      if (!ok) break;
-      mx = fmaxf(mx, xmax[(slot * 2 + (half ^ 1)) * 128 + r]);
       const bool grow = mx > m_ref + kTcLazy;                // also true for the first finite maximum
       if (__any_sync(0xffffffffu, grow)) {
         const float nm = grow ? mx : m_ref;
         const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - nm);
-        if (i > 0) {     // O must be quiescent: every P V issued so far has to be complete
-          ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + ((i - 1) & 1), (uint32_t)(((i - 1) >> 1) & 1), abort_flag));
+        if (t > 0) {     // O must be quiescent: every P V of this head issued so far has to be complete
+          ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + 2 * h + ((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1), abort_flag));
           if (!ok) break;
           tc::fence_after_sync();
 #pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
+          for (int ch = 0; ch < 4; ++ch) {
             uint32_t o[32];
-            tc::tmem_ld32(lane_base + 128 + half * 64 + ch * 32, o);
+            tc::tmem_ld32(lane_base + colO + ch * 32, o);
             tc::tmem_wait_ld();
 #pragma unroll
             for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * (grow ? alpha : 1.f));
-            tc::tmem_st32(lane_base + 128 + half * 64 + ch * 32, o);
+            tc::tmem_st32(lane_base + colO + ch * 32, o);
           }
           tc::tmem_wait_st();
-          tc::fence_before_sync();
         }
         if (grow) { l *= alpha; m_ref = nm; }
       }
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-      uint32_t pk[16];
+      uint32_t pk[32];
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float p0 = ex2f(fmaf(t[c], esc, -mu)), p1 = ex2f(fmaf(t[c + 1], esc, -mu));
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2f(fmaf(v[c], esc, -mu)), p1 = ex2f(fmaf(v[c + 1], esc, -mu));
         rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-        pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);   // low half = even column
+        pk[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
       }
       l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
-      // the P buffer of this parity was last read by the P V of tile i - 2
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + slot, (uint32_t)(((i >> 1) & 1) ^ 1), abort_flag));
-      if (!ok) break;
-      uint8_t* prow = smem + TcSmem::P + slot * 16384 + r * 128;
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int ch = 4 * half + x;
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
-      }
-      fence_proxy_async_smem();
+      // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
+      tc::tmem_st32(lane_base + colS + slot * 64, pk);
+      tc::tmem_wait_st();
       tc::fence_before_sync();
-      tc::mbar_arrive(p_ready + slot);
+      tc::mbar_arrive(p_ready + sl);
     }
-    // ---- epilogue: O / l, each half of the row's threads stores 64 output columns
-    if (ok) {
-      xsum[half * 128 + r] = l;
-      tc::mbar_arrive(x_bar + 2);
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(x_bar + 2, 0, abort_flag));
-    }
+    // ---- epilogue: O / l
     if (ok && n_tiles > 0)
-      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag));
-    if (ok) {
+      ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + 2 * h + ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag));
+    if (ok && n_tiles > 0) {
       tc::fence_after_sync();
-      const float lt = xsum[r] + xsum[128 + r];
-      const float inv = lt > 0.f ? 1.f / lt : 0.f;
-      const int64_t base = b * p.o_sb + hq * p.o_sh + (int64_t)row * p.o_sn + half * 64;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int hq = (int)(bhq - (int64_t)b * p.H_Q);
+      const int64_t base = b * p.o_sb + hq * p.o_sh + (int64_t)row * p.o_sn;
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      for (int ch = 0; ch < 4; ++ch) {
         uint32_t o[32];
-        tc::tmem_ld32(lane_base + 128 + half * 64 + ch * 32, o);
+        tc::tmem_ld32(lane_base + colO + ch * 32, o);
         tc::tmem_wait_ld();
         if (row < p.N) {
           if (p.out_dtype == HQ_BF16) {
             uint32_t w[16];
 #pragma unroll
             for (int x = 0; x < 16; ++x) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
-              w[x] = *reinterpret_cast<uint32_t*>(&h);
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
+              w[x] = *reinterpret_cast<uint32_t*>(&hh);
             }
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base + ch * 32);
 #pragma unroll
@@ -442,7 +505,8 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
     HQ_CUDA(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_dev = dev;
   }
-  dim3 grid((unsigned)p.nqb, (unsigned)a->H_Q, (unsigned)a->B);
+  const int R = a->H_Q / a->H_KV;
+  dim3 grid((unsigned)p.nqb, (unsigned)(a->H_KV * ((R + 1) / 2)), (unsigned)a->B);   // two query heads of a KV group per CTA
   prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, p);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
