@@ -7,15 +7,15 @@
 // One CTA works on the same 128 queries of TWO query heads of one KV group (A and B), so every INT8 and
 // window K / V tile that reaches shared memory feeds two score tiles, and the two heads' softmax chains
 // interleave on the SM: while one head's threads are in their exponentials the tensor core runs the other
-// head's products.  10 warps:
-//   warp 8 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of both heads' Q once and of one
-//                      item (a K tile + a transposed V tile) per step into a four-slot ring.  INT8 and
-//                      window items serve both heads; the gathered vertical-line tiles are per head.
-//   warp 9 (one lane)  issues tcgen05.mma in a fixed order of (head, tile) operations: S = Q K^T
-//                      (kind::i8 with s32 accumulators, or kind::f16 on bf16) into one of the head's two
-//                      S buffers in tensor memory, two operations ahead of O += P V (kind::f16, P read
-//                      from tensor memory, V^T from shared memory); completion is signalled with
-//                      tcgen05.commit.
+// head's products.  11 warps:
+//   warp 8 (one lane)  producer: TMA tensor-map loads (128-byte swizzle) of both heads' Q once, then K tiles
+//                      and transposed V tiles into two four-slot rings (a K slot is free again after the
+//                      heads' Q K^T, a V slot after their P V).  INT8 and window items serve both heads;
+//                      the gathered vertical-line tiles are per head.
+//   warps 9, 10        (one lane each) issue tcgen05.mma for head A / B: S = Q K^T (kind::i8 with s32
+//                      accumulators, or kind::f16 on bf16) into one of the head's two S buffers in tensor
+//                      memory, two tiles ahead of O += P V (kind::f16, P read from tensor memory, V^T from
+//                      shared memory); completion is signalled with tcgen05.commit.
 //   warps 0-3 / 4-7    softmax of head A / B, one thread per query row: tcgen05.ld of the 64 scores,
 //                      scales / masks, online softmax in base 2 with a lazily updated maximum (the O
 //                      accumulator is rescaled in tensor memory only when the maximum grows by more than
@@ -37,59 +37,59 @@ struct PrefillTcParams {
   int* status;
 };
 
-constexpr int kTcThreads = 320;            // 2 x 4 softmax warps + producer warp + MMA warp
+constexpr int kTcThreads = 352;            // 2 x 4 softmax warps + producer warp + one MMA warp per head
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256; // S buffer of head h, parity s: kColS + 128 h + 64 s; O of head h: kColO + 128 h
 constexpr float kTcLazy = 8.0f;
 
-constexpr int kKvStages = 4;   // item ring depth: loads run this many items ahead of the MMAs
+constexpr int kKvStages = 4;   // depth of the K ring and of the V ring
+constexpr int kKsSlots = 6;    // ring of key-scale rows: a row is dead once P V of its item + 2 has been issued
 struct TcSmem {              // offsets from a 1024-aligned base
   static constexpr int Qi = 0;                             // 2 x 16 KB  [head][128 rows][128 B] int8
   static constexpr int Qb = 32768;                         // 2 x 32 KB  [head][2 halves][128 rows][128 B] bf16
-  static constexpr int KV = 98304;                         // kKvStages x 32 KB: K 16 KB (int8 tile + scales at 8192,
-                                                           // or two bf16 halves) | V^T 16 KB [128 d rows][128 B]
-  static constexpr int Bar = KV + kKvStages * 32768;       // barriers + scratch
-  static constexpr int Total = Bar + 512;
-};
-
-// One (head, tile) operation of the MMA issuer's fixed order.
-struct TcOp {
-  int h;        // head 0 / 1
-  int item;     // ring item that holds its K / V
-  int t;        // tile index within the head's own sequence
-  int kind;     // 0 INT8, 1 vertical, 2 window
-  bool first;   // first operation that uses the item (waits for the load)
-  bool last;    // last operation that uses the item (frees the slot)
+  static constexpr int K = 98304;                          // kKvStages x 16 KB: int8 tile, or two bf16 halves
+  static constexpr int V = K + kKvStages * 16384;          // kKvStages x 16 KB: V^T [128 d rows][128 B]
+  static constexpr int Ks = V + kKvStages * 16384;         // kKsSlots x 256 B: the 64 key scales of an INT8 item
+  static constexpr int Bar = Ks + kKsSlots * 256;          // barriers + scratch
+  static constexpr int Total = Bar + 256;
 };
 
 struct TcPlan {
-  int n_rest, n_win, nvert[2], nheads;
-  __device__ __forceinline__ int n_ops() const { return nheads * (n_rest + n_win) + nvert[0] + nvert[1]; }
-  __device__ __forceinline__ int n_tiles(int h) const { return h < nheads ? n_rest + nvert[h] + n_win : 0; }
-  __device__ __forceinline__ TcOp op(int n) const {
-    TcOp o;
-    const int a = nheads * n_rest;
-    if (n < a) {
-      o.kind = 0; o.item = n / nheads; o.h = n - o.item * nheads; o.t = o.item;
-      o.first = o.h == 0; o.last = o.h == nheads - 1;
-      return o;
-    }
-    n -= a;
-    const int nvs = nvert[0] + nvert[1];
-    if (n < nvs) {
-      const int mn = min(nvert[0], nvert[1]);
-      int j;
-      if (n < 2 * mn) { j = n >> 1; o.h = n & 1; }
-      else { j = mn + (n - 2 * mn); o.h = nvert[0] > nvert[1] ? 0 : 1; }
-      o.kind = 1; o.item = n_rest + n; o.t = n_rest + j; o.first = true; o.last = true;
-      return o;
-    }
-    n -= nvs;
-    const int w = n / nheads;
-    o.kind = 2; o.h = n - w * nheads; o.item = n_rest + nvs + w; o.t = n_rest + nvert[o.h] + w;
-    o.first = o.h == 0; o.last = o.h == nheads - 1;
-    return o;
+  int n_rest, n_win, nvert0, nvert1, nheads;
+  __device__ __forceinline__ int nvert(int h) const { return h ? nvert1 : nvert0; }
+  __device__ __forceinline__ int n_ops() const { return nheads * (n_rest + n_win) + nvert0 + nvert1; }
+  __device__ __forceinline__ int n_tiles(int h) const { return h < nheads ? n_rest + nvert(h) + n_win : 0; }
+  __device__ __forceinline__ int n_items() const { return n_rest + nvert0 + nvert1 + n_win; }
+};
+
+// The ring items of a CTA in load order, walked with counters only (the threads that walk it are single
+// lanes whose instruction latency paces the pipeline): the INT8 tiles, then the vertical-line tiles of the
+// two heads interleaved (A's j-th, B's j-th, ...), then the window tiles.  INT8 and window items feed both
+// heads, a vertical item only its own head.
+struct TcItemIter {
+  int kind;     // 0 INT8, 1 vertical, 2 window, 3 = past the end
+  int j;        // index within the kind
+  int hh;       // owning head of a vertical item
+  int stage;    // ring slot
+  uint32_t par; // phase parity of the slot's "full" barrier for this item
+  __device__ __forceinline__ bool valid(const TcPlan& pl) const {
+    return kind == 0 ? j < pl.n_rest : kind == 1 ? j < pl.nvert(hh) : j < pl.n_win;
   }
+  __device__ __forceinline__ void step(const TcPlan& pl) {
+    if (kind == 1) { if (++hh == 2) { hh = 0; ++j; } } else ++j;
+    const int lim = kind == 0 ? pl.n_rest : kind == 1 ? max(pl.nvert0, pl.nvert1) : pl.n_win;
+    if (j >= lim) { ++kind; j = 0; hh = 0; }
+  }
+  __device__ __forceinline__ void begin(const TcPlan& pl) {
+    kind = 0; j = 0; hh = 0; stage = 0; par = 0u;
+    while (kind < 3 && !valid(pl)) step(pl);
+  }
+  __device__ __forceinline__ void next(const TcPlan& pl) {
+    do step(pl); while (kind < 3 && !valid(pl));
+    if (++stage == kKvStages) { stage = 0; par ^= 1u; }
+  }
+  __device__ __forceinline__ bool done() const { return kind >= 3; }
+  __device__ __forceinline__ bool feeds(int h) const { return kind != 1 || hh == h; }
 };
 
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -102,9 +102,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::Bar);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;                  // [kKvStages]
-  uint64_t* kv_empty = kv_full + kKvStages;      // [kKvStages]
-  uint64_t* s_full = kv_empty + kKvStages;       // [head][2]
+  uint64_t* k_full = bars + 1;                   // [kKvStages]
+  uint64_t* k_empty = k_full + kKvStages;        // [kKvStages]
+  uint64_t* v_full = k_empty + kKvStages;        // [kKvStages]
+  uint64_t* v_empty = v_full + kKvStages;        // [kKvStages]
+  uint64_t* s_full = v_empty + kKvStages;        // [head][2]
   uint64_t* p_ready = s_full + 4;                // [head][2]
   uint64_t* pv_done = p_ready + 4;               // [head][2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 4);
@@ -127,16 +129,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
   plan.n_rest = wla / 64;
   const int win_end = min(p.N, s0 + 128);
   plan.n_win = (win_end - wla + 63) / 64;
-  int nv[2] = {0, 0};
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if (p.T > 0 && h < plan.nheads) nv[h] = p.nv_valid[(bhq0 + h) * p.nqb + qb];
-    plan.nvert[h] = (nv[h] + 63) / 64;
-  }
+  const int nv0 = p.T > 0 ? p.nv_valid[bhq0 * p.nqb + qb] : 0;
+  const int nv1 = (p.T > 0 && plan.nheads == 2) ? p.nv_valid[(bhq0 + 1) * p.nqb + qb] : 0;
+  plan.nvert0 = (nv0 + 63) / 64;
+  plan.nvert1 = (nv1 + 63) / 64;
 
   if (tid == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kKvStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < kKvStages; ++i) {     // a slot comes back when every head has arrived
+      mbar_init(k_full + i, 1); mbar_init(k_empty + i, plan.nheads); mbar_init(v_full + i, 1); mbar_init(v_empty + i, plan.nheads);
+    }
     for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(p_ready + i, 128); mbar_init(pv_done + i, 1); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -159,103 +161,124 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         tc::tma_load_2d(smem + TcSmem::Qb + h * 32768, &mQb, 0, qrow, q_full);
         tc::tma_load_2d(smem + TcSmem::Qb + h * 32768 + 16384, &mQb, 64, qrow, q_full);
       }
-      int it = 0;
-      bool ok = true;
-      auto acquire = [&]() -> uint8_t* {
-        const int slot = it % kKvStages;
-        ok = tc::mbar_wait_abortable(kv_empty + slot, (uint32_t)(((it / kKvStages) & 1) ^ 1), abort_flag, 200);
-        return smem + TcSmem::KV + slot * 32768;
-      };
-      for (int i = 0; ok && i < plan.n_rest; ++i) {
-        uint8_t* sK = acquire();
-        if (!ok) break;
-        uint64_t* full = kv_full + it % kKvStages;
-        const int key0 = i * 64;
-        mbar_expect_tx(full, 8192 + 256 + 16384);
-        tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + key0), full);
-        tc::tma_load_2d(sK + 8192, &mKs, key0, (int)bhk, full);          // the tile's 64 key scales
-        tc::tma_load_2d(sK + 16384, &mVt, key0, (int)(bhk * 128), full);
-        ++it;
-      }
-      const int nvmax = max(plan.nvert[0], plan.nvert[1]);
-      for (int j = 0; ok && j < nvmax; ++j) {
-        for (int h = 0; ok && h < 2; ++h) {
-          if (j >= plan.nvert[h]) continue;
-          uint8_t* sK = acquire();
-          if (!ok) break;
-          uint64_t* full = kv_full + it % kKvStages;
-          const int j0 = j * 64;
-          mbar_expect_tx(full, 16384 + 16384);
-          tc::tma_load_2d(sK, &mXk, 0, (int)((bhq0 + h) * p.Tpad + j0), full);
-          tc::tma_load_2d(sK + 8192, &mXk, 64, (int)((bhq0 + h) * p.Tpad + j0), full);
-          tc::tma_load_2d(sK + 16384, &mXv, j0, (int)((bhq0 + h) * 128), full);
-          ++it;
+      // K tiles and V tiles travel in rings of their own: a K slot comes back as soon as both heads' Q K^T
+      // of its item have run, a V slot only after their P V, so K runs further ahead than V.  One thread
+      // feeds both rings and never blocks on either.
+      TcItemIter ck, cv;
+      ck.begin(plan);
+      cv.begin(plan);
+      int ks_slot = 0;
+      uint32_t idle = 0;
+      while (!ck.done() || !cv.done()) {
+        bool progress = false;
+        if (!ck.done() && mbar_test_wait(k_empty + ck.stage, ck.par ^ 1u)) {
+          uint8_t* sK = smem + TcSmem::K + ck.stage * 16384;
+          uint64_t* full = k_full + ck.stage;
+          if (ck.kind == 0) {
+            mbar_expect_tx(full, 8192 + 256);
+            tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + ck.j * 64), full);
+            tc::tma_load_2d(smem + TcSmem::Ks + ks_slot * 256, &mKs, ck.j * 64, (int)bhk, full);
+            if (++ks_slot == kKsSlots) ks_slot = 0;
+          } else {
+            const CUtensorMap* m = ck.kind == 1 ? &mXk : &mKb;
+            const int krow = ck.kind == 1 ? (int)((bhq0 + ck.hh) * p.Tpad + ck.j * 64) : (int)(bhk * p.N + wla + ck.j * 64);
+            mbar_expect_tx(full, 16384);
+            tc::tma_load_2d(sK, m, 0, krow, full);
+            tc::tma_load_2d(sK + 8192, m, 64, krow, full);
+          }
+          ck.next(plan);
+          progress = true;
         }
-      }
-      for (int w = 0; ok && w < plan.n_win; ++w) {
-        uint8_t* sK = acquire();
-        if (!ok) break;
-        uint64_t* full = kv_full + it % kKvStages;
-        const int key0 = wla + w * 64;
-        mbar_expect_tx(full, 16384 + 16384);
-        tc::tma_load_2d(sK, &mKb, 0, (int)(bhk * p.N + key0), full);
-        tc::tma_load_2d(sK + 8192, &mKb, 64, (int)(bhk * p.N + key0), full);
-        tc::tma_load_2d(sK + 16384, &mVt, key0, (int)(bhk * 128), full);
-        ++it;
+        if (!cv.done() && mbar_test_wait(v_empty + cv.stage, cv.par ^ 1u)) {
+          uint8_t* sV = smem + TcSmem::V + cv.stage * 16384;
+          uint64_t* full = v_full + cv.stage;
+          mbar_expect_tx(full, 16384);
+          if (cv.kind == 1) tc::tma_load_2d(sV, &mXv, cv.j * 64, (int)((bhq0 + cv.hh) * 128), full);
+          else tc::tma_load_2d(sV, &mVt, (cv.kind == 0 ? 0 : wla) + cv.j * 64, (int)(bhk * 128), full);
+          cv.next(plan);
+          progress = true;
+        }
+        if (progress) { idle = 0; continue; }
+        __nanosleep(64);
+        if (*abort_flag) break;
+        if (++idle > 2000000u) { *abort_flag = 1; break; }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp >= 9) {
+    // ------------------------------------------------------------ MMA issuers: warp 9 for head A, warp 10 for head B
+    // One lane per head issues, in the head's own order, Q K^T of tiles 0 and 1, then for every tile t:
+    // P V of t, Q K^T of t + 2.  The S buffer that Q K^T of t + 2 overwrites held P of tile t, and the tensor
+    // core runs one thread's operations in issue order, so the scores of the next tile are ready while the
+    // head's softmax threads are still on the current one.  Ring slots come back when both heads are done
+    // with them: a head arrives by tcgen05.commit for an item it used and by a plain arrive for a
+    // vertical-line item of the other head, in ring order either way.
+    const int h = warp - 9;
+    if (lane == 0 && h < plan.nheads) {
       constexpr uint32_t idesc_i8 = tc::make_idesc(2, tc::kFmtS8, tc::kFmtS8, 128, 64);
       constexpr uint32_t idesc_qk = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 64);
       constexpr uint32_t idesc_pv = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 128);
       bool ok = tc::mbar_wait_abortable(q_full, 0, abort_flag, 100);
-      const int n_ops = plan.n_ops();
-      auto issue_qk = [&](int n) {
-        const TcOp o = plan.op(n);
-        const int kvs = o.item % kKvStages;
-        if (o.first) {
-          ok = tc::mbar_wait_abortable(kv_full + kvs, (uint32_t)((o.item / kKvStages) & 1), abort_flag, 40);
+      // operand descriptors differ only in their start-address field (16-byte units)
+      const uint64_t dQi = tc::smem_desc_k128(smem + TcSmem::Qi + h * 16384, 0);
+      const uint64_t dQb = tc::smem_desc_k128(smem + TcSmem::Qb + h * 32768, 0);
+      const uint64_t dK = tc::smem_desc_k128(smem + TcSmem::K, 0), dV = tc::smem_desc_k128(smem + TcSmem::V, 0);
+      const uint32_t tS = tmem_base + kColS + 128u * h, tO = tmem_base + kColO + 128u * h;
+      const int n_t = plan.n_tiles(h);
+      TcItemIter cq, cp;
+      cq.begin(plan);
+      cp.begin(plan);
+      int tq = 0;
+      auto qk_next = [&]() {
+        for (;;) {          // the next item that feeds this head; hand back the other head's on the way
+          ok = tc::mbar_wait_abortable(k_full + cq.stage, cq.par, abort_flag);
           if (!ok) return;
+          if (cq.feeds(h)) break;
+          tc::mbar_arrive(k_empty + cq.stage);
+          cq.next(plan);
         }
         tc::fence_after_sync();
-        const uint32_t dS = tmem_base + kColS + (uint32_t)(128 * o.h + 64 * (o.t & 1));
-        const uint8_t* sK = smem + TcSmem::KV + kvs * 32768;
-        if (o.kind == 0) {
-          const uint8_t* sQ = smem + TcSmem::Qi + o.h * 16384;
+        const uint32_t dS = tS + 64u * (tq & 1);
+        const uint64_t bK = dK + (uint64_t)(cq.stage * 1024);
+        if (cq.kind == 0) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc::mma_s8_ss(dS, tc::smem_desc_k128(sQ, k * 32), tc::smem_desc_k128(sK, k * 32), idesc_i8, k > 0);
+          for (int k = 0; k < 4; ++k) tc::mma_s8_ss(dS, dQi + 2 * k, bK + 2 * k, idesc_i8, k > 0);
         } else {
-          const uint8_t* sQ = smem + TcSmem::Qb + o.h * 32768;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            tc::mma_bf16_ss(dS, tc::smem_desc_k128(sQ + (k >> 2) * 16384, (k & 3) * 32),
-                            tc::smem_desc_k128(sK + (k >> 2) * 8192, (k & 3) * 32), idesc_qk, k > 0);
+            tc::mma_bf16_ss(dS, dQb + (k >> 2) * 1024 + 2 * (k & 3), bK + (k >> 2) * 512 + 2 * (k & 3), idesc_qk, k > 0);
         }
-        tc::mma_commit(s_full + 2 * o.h + (o.t & 1));
+        tc::mma_commit(s_full + 2 * h + (tq & 1));
+        tc::mma_commit(k_empty + cq.stage);
+        ++tq;
+        cq.next(plan);
       };
-      auto issue_pv = [&](int n) {
-        const TcOp o = plan.op(n);
-        const int kvs = o.item % kKvStages, sl = 2 * o.h + (o.t & 1);
-        ok = tc::mbar_wait_abortable(p_ready + sl, (uint32_t)((o.t >> 1) & 1), abort_flag, 40);
-        if (!ok) return;
+      if (ok && n_t > 0) qk_next();
+      if (ok && n_t > 1) qk_next();
+      for (int t = 0; ok && t < n_t; ++t) {
+        for (;;) {
+          ok = tc::mbar_wait_abortable(v_full + cp.stage, cp.par, abort_flag);
+          if (!ok || cp.feeds(h)) break;
+          tc::mbar_arrive(v_empty + cp.stage);
+          cp.next(plan);
+        }
+        if (!ok) break;
+        const int sl = 2 * h + (t & 1);
+        ok = tc::mbar_wait_abortable(p_ready + sl, (uint32_t)((t >> 1) & 1), abort_flag);
+        if (!ok) break;
         tc::fence_after_sync();
-        const uint32_t dO = tmem_base + kColO + (uint32_t)(128 * o.h);
-        const uint32_t aP = tmem_base + kColS + (uint32_t)(128 * o.h + 64 * (o.t & 1));
-        const uint8_t* sV = smem + TcSmem::KV + kvs * 32768 + 16384;
+        const uint32_t aP = tS + 64u * (t & 1);
+        const uint64_t bV = dV + (uint64_t)(cp.stage * 1024);
+        if (t > 0) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc::mma_bf16_ts(dO, aP + 8 * k, tc::smem_desc_k128(sV, k * 32), idesc_pv, (o.t > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) tc::mma_bf16_ts(tO, aP + 8 * k, bV + 2 * k, idesc_pv, 1u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc::mma_bf16_ts(tO, aP + 8 * k, bV + 2 * k, idesc_pv, k > 0);
+        }
         tc::mma_commit(pv_done + sl);
-        if (o.last) tc::mma_commit(kv_empty + kvs);
-      };
-      if (ok && n_ops > 0) issue_qk(0);
-      if (ok && n_ops > 1) issue_qk(1);
-      for (int n = 0; ok && n < n_ops; ++n) {
-        issue_pv(n);
-        if (ok && n + 2 < n_ops) issue_qk(n + 2);
+        tc::mma_commit(v_empty + cp.stage);
+        cp.next(plan);
+        if (t + 2 < n_t) qk_next();
       }
     }
   } else {
@@ -268,7 +291,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
     const int64_t bhq = bhq0 + (h < plan.nheads ? h : 0);
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t colS = kColS + 128 * h, colO = kColO + 128 * h;
-    const int n_rest = plan.n_rest, n_vert = plan.nvert[h], nvh = nv[h];
+    const int n_rest = plan.n_rest, n_vert = plan.nvert(h), nvh = h ? nv1 : nv0;
     const float qs = (row < p.N && n_tiles > 0) ? p.q_scale[bhq * p.Npad + row] : 0.f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -291,7 +314,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       float v[64];
       float esc;
       if (t < n_rest) {
-        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::KV + (t % kKvStages) * 32768 + 8192);
+        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::Ks + (t % kKsSlots) * 256);
         esc = qs;
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
