@@ -62,9 +62,9 @@ class PrefillArgs(C.Structure):
         ("head_dim", C.c_int32), ("window", C.c_int32), ("T", C.c_int32), ("out_dtype", C.c_int32),
         ("sm_scale", C.c_float),
         ("q_i8", C.c_void_p), ("q_bf", C.c_void_p), ("q_scale", C.c_void_p),
-        ("k_i8", C.c_void_p), ("k_bf", C.c_void_p), ("k_scale", C.c_void_p),
+        ("k_i8", C.c_void_p), ("k_bf", C.c_void_p), ("k_scale", C.c_void_p), ("k_bias", C.c_void_p),
         ("v_t", C.c_void_p), ("vert_k", C.c_void_p), ("vert_vt", C.c_void_p),
-        ("vmask", C.c_void_p), ("nv_valid", C.c_void_p),
+        ("nv_valid", C.c_void_p),
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sn", C.c_int64),
         ("status", C.c_void_p),
     ]
@@ -93,7 +93,7 @@ def _declare(lib):
     lib.hq_prefill_quant.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, i32,
                                      vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
     lib.hq_prefill_vertical_prepare.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, i64, i64,
-                                                vp, vp, vp, vp, vp]
+                                                vp, vp, vp, vp, vp, vp]
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
     for name in EXPORTS:

@@ -30,7 +30,7 @@ namespace hq {
 
 struct PrefillTcParams {
   const float* q_scale; const float* k_scale;      // [B,H_Q,Npad], [B,H_KV,Npad]
-  const unsigned long long* vmask; const int* nv_valid;
+  const int* nv_valid;
   void* out; int out_dtype; int64_t o_sb, o_sh, o_sn;
   int B, H_Q, H_KV, N, Npad, W, T, Tpad, nqb, nkb;
   float sml;
@@ -42,17 +42,34 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256; // S buffer of head h, parity s: kColS + 128 h + 64 s; O of head h: kColO + 128 h
 constexpr float kTcLazy = 8.0f;
 
-constexpr int kKvStages = 4;   // depth of the K ring and of the V ring
+constexpr int kKStages = 3;    // depth of the K ring: Q K^T runs two tiles ahead of P V and frees its slot at once
+constexpr int kVStages = 4;    // depth of the V ring
 constexpr int kKsSlots = 6;    // ring of key-scale rows: a row is dead once P V of its item + 2 has been issued
+constexpr int kKsBytes = 768;  // 64 key scales | 64 bias terms of head A | 64 bias terms of head B
 struct TcSmem {              // offsets from a 1024-aligned base
   static constexpr int Qi = 0;                             // 2 x 16 KB  [head][128 rows][128 B] int8
   static constexpr int Qb = 32768;                         // 2 x 32 KB  [head][2 halves][128 rows][128 B] bf16
-  static constexpr int K = 98304;                          // kKvStages x 16 KB: int8 tile, or two bf16 halves
-  static constexpr int V = K + kKvStages * 16384;          // kKvStages x 16 KB: V^T [128 d rows][128 B]
-  static constexpr int Ks = V + kKvStages * 16384;         // kKsSlots x 256 B: the 64 key scales of an INT8 item
-  static constexpr int Bar = Ks + kKsSlots * 256;          // barriers + scratch
+  static constexpr int K = 98304;                          // kKStages x 16 KB: int8 tile, or two bf16 halves
+  static constexpr int V = K + kKStages * 16384;           // kVStages x 16 KB: V^T [128 d rows][128 B]
+  static constexpr int Ks = V + kVStages * 16384;          // kKsSlots x kKsBytes
+  static constexpr int Bar = Ks + kKsSlots * kKsBytes;     // barriers + scratch
   static constexpr int Total = Bar + 256;
 };
+
+// two fp32 lanes per instruction (sm_100 packed forms)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
+}
 
 struct TcPlan {
   int n_rest, n_win, nvert0, nvert1, nheads;
@@ -71,6 +88,7 @@ struct TcItemIter {
   int j;        // index within the kind
   int hh;       // owning head of a vertical item
   int stage;    // ring slot
+  int depth;    // ring depth
   uint32_t par; // phase parity of the slot's "full" barrier for this item
   __device__ __forceinline__ bool valid(const TcPlan& pl) const {
     return kind == 0 ? j < pl.n_rest : kind == 1 ? j < pl.nvert(hh) : j < pl.n_win;
@@ -80,13 +98,13 @@ struct TcItemIter {
     const int lim = kind == 0 ? pl.n_rest : kind == 1 ? max(pl.nvert0, pl.nvert1) : pl.n_win;
     if (j >= lim) { ++kind; j = 0; hh = 0; }
   }
-  __device__ __forceinline__ void begin(const TcPlan& pl) {
-    kind = 0; j = 0; hh = 0; stage = 0; par = 0u;
+  __device__ __forceinline__ void begin(const TcPlan& pl, int ring_depth) {
+    kind = 0; j = 0; hh = 0; stage = 0; par = 0u; depth = ring_depth;
     while (kind < 3 && !valid(pl)) step(pl);
   }
   __device__ __forceinline__ void next(const TcPlan& pl) {
     do step(pl); while (kind < 3 && !valid(pl));
-    if (++stage == kKvStages) { stage = 0; par ^= 1u; }
+    if (++stage == depth) { stage = 0; par ^= 1u; }
   }
   __device__ __forceinline__ bool done() const { return kind >= 3; }
   __device__ __forceinline__ bool feeds(int h) const { return kind != 1 || hh == h; }
@@ -97,16 +115,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
                   const __grid_constant__ CUtensorMap mKi, const __grid_constant__ CUtensorMap mKb,
                   const __grid_constant__ CUtensorMap mVt, const __grid_constant__ CUtensorMap mXk,
                   const __grid_constant__ CUtensorMap mXv, const __grid_constant__ CUtensorMap mKs,
-                  const PrefillTcParams p) {
+                  const __grid_constant__ CUtensorMap mKbs, const PrefillTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::Bar);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;                   // [kKvStages]
-  uint64_t* k_empty = k_full + kKvStages;        // [kKvStages]
-  uint64_t* v_full = k_empty + kKvStages;        // [kKvStages]
-  uint64_t* v_empty = v_full + kKvStages;        // [kKvStages]
-  uint64_t* s_full = v_empty + kKvStages;        // [head][2]
+  uint64_t* k_full = bars + 1;                   // [kKStages]
+  uint64_t* k_empty = k_full + kKStages;         // [kKStages]
+  uint64_t* v_full = k_empty + kKStages;         // [kVStages]
+  uint64_t* v_empty = v_full + kVStages;         // [kVStages]
+  uint64_t* s_full = v_empty + kVStages;         // [head][2]
   uint64_t* p_ready = s_full + 4;                // [head][2]
   uint64_t* pv_done = p_ready + 4;               // [head][2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 4);
@@ -136,9 +154,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
 
   if (tid == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kKvStages; ++i) {     // a slot comes back when every head has arrived
-      mbar_init(k_full + i, 1); mbar_init(k_empty + i, plan.nheads); mbar_init(v_full + i, 1); mbar_init(v_empty + i, plan.nheads);
-    }
+    // a slot comes back when every head has arrived
+    for (int i = 0; i < kKStages; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, plan.nheads); }
+    for (int i = 0; i < kVStages; ++i) { mbar_init(v_full + i, 1); mbar_init(v_empty + i, plan.nheads); }
     for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(p_ready + i, 128); mbar_init(pv_done + i, 1); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -153,7 +171,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tc::tma_prefetch_desc(&mQi); tc::tma_prefetch_desc(&mQb); tc::tma_prefetch_desc(&mKi);
-      tc::tma_prefetch_desc(&mKb); tc::tma_prefetch_desc(&mVt); tc::tma_prefetch_desc(&mKs);
+      tc::tma_prefetch_desc(&mKb); tc::tma_prefetch_desc(&mVt); tc::tma_prefetch_desc(&mKs); tc::tma_prefetch_desc(&mKbs);
       mbar_expect_tx(q_full, (uint32_t)plan.nheads * (16384 + 32768));
       for (int h = 0; h < plan.nheads; ++h) {
         const int qrow = (int)((bhq0 + h) * p.N + s0);
@@ -165,8 +183,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       // of its item have run, a V slot only after their P V, so K runs further ahead than V.  One thread
       // feeds both rings and never blocks on either.
       TcItemIter ck, cv;
-      ck.begin(plan);
-      cv.begin(plan);
+      ck.begin(plan, kKStages);
+      cv.begin(plan, kVStages);
       int ks_slot = 0;
       uint32_t idle = 0;
       while (!ck.done() || !cv.done()) {
@@ -175,9 +193,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
           uint8_t* sK = smem + TcSmem::K + ck.stage * 16384;
           uint64_t* full = k_full + ck.stage;
           if (ck.kind == 0) {
-            mbar_expect_tx(full, 8192 + 256);
+            uint8_t* sS = smem + TcSmem::Ks + ks_slot * kKsBytes;
+            mbar_expect_tx(full, 8192 + 256 + 256 * (uint32_t)plan.nheads);
             tc::tma_load_2d(sK, &mKi, 0, (int)(bhk * p.N + ck.j * 64), full);
-            tc::tma_load_2d(smem + TcSmem::Ks + ks_slot * 256, &mKs, ck.j * 64, (int)bhk, full);
+            tc::tma_load_2d(sS, &mKs, ck.j * 64, (int)bhk, full);
+            for (int h = 0; h < plan.nheads; ++h) tc::tma_load_2d(sS + 256 + 256 * h, &mKbs, ck.j * 64, (int)(bhq0 + h), full);
             if (++ks_slot == kKsSlots) ks_slot = 0;
           } else {
             const CUtensorMap* m = ck.kind == 1 ? &mXk : &mKb;
@@ -225,8 +245,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       const uint32_t tS = tmem_base + kColS + 128u * h, tO = tmem_base + kColO + 128u * h;
       const int n_t = plan.n_tiles(h);
       TcItemIter cq, cp;
-      cq.begin(plan);
-      cp.begin(plan);
+      cq.begin(plan, kKStages);
+      cp.begin(plan, kVStages);
       int tq = 0;
       auto qk_next = [&]() {
         for (;;) {          // the next item that feeds this head; hand back the other head's on the way
@@ -292,104 +312,124 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t colS = kColS + 128 * h, colO = kColO + 128 * h;
     const int n_rest = plan.n_rest, n_vert = plan.nvert(h), nvh = h ? nv1 : nv0;
-    const float qs = (row < p.N && n_tiles > 0) ? p.q_scale[bhq * p.Npad + row] : 0.f;
-    float m_ref = -INFINITY, l = 0.f;
+    // rows past N compute on a token scale, so that a masked column (-inf) times the scale stays -inf
+    const float qs = (row < p.N && n_tiles > 0) ? p.q_scale[bhq * p.Npad + row] : 1e-30f;
+    float m_ref = row < p.N ? -INFINITY : 0.f, l = 0.f;
     bool ok = true;
-    // the vertical-mask word of a tile is a fresh cache line every step: fetch it one step ahead
-    const unsigned long long* vmrow = p.vmask + bhq * p.nkb;
-    unsigned long long vm_next = (p.T > 0 && n_rest > 0 && n_tiles > 0) ? __ldg(vmrow) : 0ull;
+    int ks_slot = 0;
     for (int t = 0; t < n_tiles; ++t) {
       const int slot = t & 1, sl = 2 * h + slot;
-      const unsigned long long vm64 = vm_next;
-      if (p.T > 0 && t + 1 < n_rest) vm_next = __ldg(vmrow + t + 1);
       ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(s_full + sl, (uint32_t)((t >> 1) & 1), abort_flag));
       if (!ok) break;
       tc::fence_after_sync();
-      uint32_t sr[64];
-      tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-      tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-      tc::tmem_wait_ld();
-
-      // scores in the exponent's units: v[c] * esc - mu, with esc folded into one FFMA per element
-      float v[64];
-      float esc;
-      if (t < n_rest) {
-        const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::Ks + (t % kKsSlots) * 256);
-        esc = qs;
-#pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 kk = ks4[c4];
-          const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int c = 4 * c4 + x;
-            // int32 -> float without the conversion unit: |score| < 2^22
-            v[c] = (__int_as_float((int)sr[c] + 0x4B400000) - 12582912.0f) * kv[x];
-          }
-        }
-        if (vm64 != 0ull) {
-          const uint32_t lo = (uint32_t)vm64, hi = (uint32_t)(vm64 >> 32);
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if ((lo >> c) & 1u) v[c] = -INFINITY;
-            if ((hi >> c) & 1u) v[32 + c] = -INFINITY;
-          }
-        }
-      } else {
-        esc = p.sml;
-#pragma unroll
-        for (int c = 0; c < 64; ++c) v[c] = __uint_as_float(sr[c]);
+      const bool is_i8 = t < n_rest;
+      const float esc = is_i8 ? qs : p.sml;                  // > 0
+      const float4* ks4 = reinterpret_cast<const float4*>(smem + TcSmem::Ks + ks_slot * kKsBytes);
+      const float4* kb4 = ks4 + 16 + 16 * h;
+      if (is_i8 && ++ks_slot == kKsSlots) ks_slot = 0;
+      uint32_t mlo = 0u, mhi = 0u;                           // BF16 tiles: bit c set = column c (of 64) is masked
+      if (!is_i8) {
         int lim;                                             // columns <= lim are visible
         if (t < n_rest + n_vert) lim = min(64, nvh - (t - n_rest) * 64) - 1;
         else lim = min(row, p.N - 1) - (wla + (t - n_rest - n_vert) * 64);
-        if (__any_sync(0xffffffffu, lim < 63)) {
-#pragma unroll
-          for (int c = 0; c < 64; ++c) if (c > lim) v[c] = -INFINITY;
-        }
+        mlo = lim >= 31 ? 0u : lim < 0 ? 0xFFFFFFFFu : (0xFFFFFFFFu << (lim + 1));
+        mhi = lim >= 63 ? 0u : lim < 32 ? 0xFFFFFFFFu : (0xFFFFFFFFu << (lim - 31));
       }
-      float mx;
-      {
-        float m8[8];
-#pragma unroll
-        for (int x = 0; x < 8; ++x) m8[x] = v[x];
-#pragma unroll
-        for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], v[c]);
-        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
-      }
-      mx *= esc;                                             // esc >= 0
-      if (esc == 0.f) mx = -INFINITY;                        // rows past N
-      const bool grow = mx > m_ref + kTcLazy;                // also true for the first finite maximum
-      if (__any_sync(0xffffffffu, grow)) {
-        const float nm = grow ? mx : m_ref;
-        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - nm);
-        if (t > 0) {     // O must be quiescent: every P V of this head issued so far has to be complete
-          ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + 2 * h + ((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1), abort_flag));
-          if (!ok) break;
-          tc::fence_after_sync();
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t o[32];
-            tc::tmem_ld32(lane_base + colO + ch * 32, o);
-            tc::tmem_wait_ld();
-#pragma unroll
-            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * (grow ? alpha : 1.f));
-            tc::tmem_st32(lane_base + colO + ch * 32, o);
-          }
-          tc::tmem_wait_st();
-        }
-        if (grow) { l *= alpha; m_ref = nm; }
-      }
-      const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+      // One fused pass per tile: score -> exponent units -> 2^(y - mu) against the reference maximum as it
+      // stands -> row sum and bf16 P, two columns per instruction where the hardware has packed fp32 forms.
+      // The row maximum is not computed: P values above 2^8 would show in the row sum of the tile, which
+      // is then > 2^8.  Only then (and for a row's first finite scores) the scores are read from tensor
+      // memory again, the maximum is taken, O is rescaled, the reference moves and the pass is repeated.
       uint32_t pk[32];
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      float lsum = 0.f;
+      bool redo = false;
+      for (;;) {
+        uint32_t sr[64];
+        tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+        tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+        tc::tmem_wait_ld();
+        const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+        const float2 esc2 = make_float2(esc, esc), nmu2 = make_float2(-mu, -mu);
+        float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
+        if (is_i8) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2f(fmaf(v[c], esc, -mu)), p1 = ex2f(fmaf(v[c + 1], esc, -mu));
-        rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
-        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);   // low half = even column
-        pk[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const float4 kk = ks4[c4], bb = kb4[c4];
+            // bits(i + 0x4B400000) = 12582912 + i for |i| < 2^22; the bias row carries -12582912 * scale (or -inf)
+            const float2 a01 = make_float2(__int_as_float((int)sr[4 * c4] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 1] + 0x4B400000));
+            const float2 a23 = make_float2(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 3] + 0x4B400000));
+            const float2 y01 = ffma2(ffma2(a01, make_float2(kk.x, kk.y), make_float2(bb.x, bb.y)), esc2, nmu2);
+            const float2 y23 = ffma2(ffma2(a23, make_float2(kk.z, kk.w), make_float2(bb.z, bb.w)), esc2, nmu2);
+            const float2 p01 = make_float2(ex2f(y01.x), ex2f(y01.y)), p23 = make_float2(ex2f(y23.x), ex2f(y23.y));
+            rsa = fadd2(rsa, p01);
+            rsb = fadd2(rsb, p23);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(p01.x, p01.y), h1 = __floats2bfloat162_rn(p23.x, p23.y);   // low half = even column
+            pk[2 * c4] = *reinterpret_cast<uint32_t*>(&h0);
+            pk[2 * c4 + 1] = *reinterpret_cast<uint32_t*>(&h1);
+          }
+        } else {
+#pragma unroll
+          for (int c2 = 0; c2 < 32; ++c2) {
+            const uint32_t mw = c2 < 16 ? mlo : mhi;
+            float2 y = ffma2(make_float2(__uint_as_float(sr[2 * c2]), __uint_as_float(sr[2 * c2 + 1])), esc2, nmu2);
+            if ((mw >> ((2 * c2) & 31)) & 1u) y.x = -INFINITY;
+            if ((mw >> ((2 * c2 + 1) & 31)) & 1u) y.y = -INFINITY;
+            const float2 pp = make_float2(ex2f(y.x), ex2f(y.y));
+            if (c2 & 1) rsb = fadd2(rsb, pp); else rsa = fadd2(rsa, pp);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(pp.x, pp.y);
+            pk[c2] = *reinterpret_cast<uint32_t*>(&h0);
+          }
+        }
+        lsum = (rsa.x + rsa.y) + (rsb.x + rsb.y);
+        if (redo) break;
+        const bool need = m_ref == -INFINITY || !(lsum <= 256.f);
+        if (!__any_sync(0xffffffffu, need)) break;
+        // ---- the tile's true row maximum, from the scores in tensor memory
+        tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+        tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+        tc::tmem_wait_ld();
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (is_i8) {
+#pragma unroll
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const float4 kk = ks4[c4], bb = kb4[c4];
+            m4[0] = fmaxf(m4[0], fmaf(__int_as_float((int)sr[4 * c4] + 0x4B400000), kk.x, bb.x));
+            m4[1] = fmaxf(m4[1], fmaf(__int_as_float((int)sr[4 * c4 + 1] + 0x4B400000), kk.y, bb.y));
+            m4[2] = fmaxf(m4[2], fmaf(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), kk.z, bb.z));
+            m4[3] = fmaxf(m4[3], fmaf(__int_as_float((int)sr[4 * c4 + 3] + 0x4B400000), kk.w, bb.w));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const uint32_t mw = c < 32 ? mlo : mhi;
+            if (!((mw >> (c & 31)) & 1u)) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sr[c]));
+          }
+        }
+        const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * esc;
+        const bool grow = mx > m_ref + kTcLazy;              // also true for the first finite maximum
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - mx);
+          if (t > 0) {     // O must be quiescent: every P V of this head issued so far has to be complete
+            ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + 2 * h + ((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1), abort_flag));
+            if (!ok) break;
+            tc::fence_after_sync();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint32_t o[32];
+              tc::tmem_ld32(lane_base + colO + ch * 32, o);
+              tc::tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (grow ? alpha : 1.f));
+              tc::tmem_st32(lane_base + colO + ch * 32, o);
+            }
+            tc::tmem_wait_st();
+          }
+          if (grow) { l *= alpha; m_ref = mx; }
+        }
+        redo = true;
       }
-      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      if (!ok) break;
+      l += lsum;
       // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
       tc::tmem_st32(lane_base + colS + slot * 64, pk);
       tc::tmem_wait_st();
@@ -494,7 +534,7 @@ vertical_gather_t_kernel(const int* __restrict__ vasc, int T, int Tpad, int N, i
 
 int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   const int N = a->N, Npad = (N + 63) / 64 * 64, T = a->T, Tpad = (T + 63) / 64 * 64;
-  CUtensorMap mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs;
+  CUtensorMap mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, mKbs;
   const uint64_t qrows = (uint64_t)a->B * a->H_Q * N, krows = (uint64_t)a->B * a->H_KV * N;
   int rc;
   if ((rc = tc::make_map_2d(&mQi, a->q_i8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, qrows, 128, 128, 128))) return rc;
@@ -505,6 +545,8 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
                             (uint64_t)Npad * 2, 64, 128))) return rc;
   if ((rc = tc::make_map_2d(&mKs, a->k_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)Npad, (uint64_t)a->B * a->H_KV,
                             (uint64_t)Npad * 4, 64, 1, false))) return rc;
+  if ((rc = tc::make_map_2d(&mKbs, a->k_bias, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)Npad, (uint64_t)a->B * a->H_Q,
+                            (uint64_t)Npad * 4, 64, 1, false))) return rc;
   if (T > 0) {
     if ((rc = tc::make_map_2d(&mXk, a->vert_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, (uint64_t)a->B * a->H_Q * Tpad, 256, 64, 64))) return rc;
     if ((rc = tc::make_map_2d(&mXv, a->vert_vt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Tpad, (uint64_t)a->B * a->H_Q * 128,
@@ -514,7 +556,7 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   }
   PrefillTcParams p{};
   p.q_scale = a->q_scale; p.k_scale = a->k_scale;
-  p.vmask = (const unsigned long long*)a->vmask; p.nv_valid = a->nv_valid;
+  p.nv_valid = a->nv_valid;
   p.out = a->out; p.out_dtype = a->out_dtype; p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_sn = a->o_sn;
   p.B = a->B; p.H_Q = a->H_Q; p.H_KV = a->H_KV; p.N = N; p.Npad = Npad; p.W = a->window; p.T = T; p.Tpad = Tpad;
   p.nqb = (N + 127) / 128; p.nkb = (N + 63) / 64;
@@ -530,7 +572,7 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   }
   const int R = a->H_Q / a->H_KV;
   dim3 grid((unsigned)p.nqb, (unsigned)(a->H_KV * ((R + 1) / 2)), (unsigned)a->B);   // two query heads of a KV group per CTA
-  prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, p);
+  prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, mKbs, p);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

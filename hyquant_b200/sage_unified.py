@@ -81,7 +81,7 @@ class PrefillPlan:
         nqb, nkb = (N + 127) // 128, (N + 63) // 64
         q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
         T = 0
-        vert_k = vert_vt = vmask = nvv = None
+        vert_k = vert_vt = nvv = vasc = None
         Npad = (N + 63) // 64 * 64
         v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
         _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
@@ -96,12 +96,14 @@ class PrefillPlan:
             Tpad = (T + 63) // 64 * 64
             vert_k = torch.empty(B, H_q, Tpad, 128, dtype=torch.bfloat16, device=dev)
             vert_vt = torch.empty(B, H_q, 128, Tpad, dtype=torch.bfloat16, device=dev)
-            vmask = torch.empty(B, H_q, nkb, dtype=torch.int64, device=dev)
             nvv = torch.empty(B, H_q, nqb, dtype=torch.int32, device=dev)
-            rc = lib.hq_prefill_vertical_prepare(vasc.data_ptr(), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
-                                                 vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2),
-                                                 vert_k.data_ptr(), vert_vt.data_ptr(), vmask.data_ptr(), nvv.data_ptr(), st)
-            _lib.check(rc, "hq_prefill_vertical_prepare")
+        # per (query head, key) term of the INT8 score conversion; -inf on the head's vertical lines
+        k_bias = torch.empty(B, H_q, Npad, dtype=torch.float32, device=dev)
+        ptr = lambda t: None if t is None else t.data_ptr()     # noqa: E731
+        rc = lib.hq_prefill_vertical_prepare(ptr(vasc), B, H_q, H_kv, N, window_size, T, k_bf.data_ptr(),
+                                             vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), k_sc.data_ptr(),
+                                             ptr(vert_k), ptr(vert_vt), k_bias.data_ptr(), ptr(nvv), st)
+        _lib.check(rc, "hq_prefill_vertical_prepare")
         out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)      # contiguous: rows 16-byte aligned
         a = PrefillArgs()
         a.struct_bytes = C.sizeof(PrefillArgs)
@@ -110,14 +112,15 @@ class PrefillPlan:
         a.sm_scale = float(sm_scale)
         a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
         a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
+        a.k_bias = k_bias.data_ptr()
         a.v_t = v_t.data_ptr()
         if T:
-            a.vert_k, a.vert_vt, a.vmask, a.nv_valid = vert_k.data_ptr(), vert_vt.data_ptr(), vmask.data_ptr(), nvv.data_ptr()
+            a.vert_k, a.vert_vt, a.nv_valid = vert_k.data_ptr(), vert_vt.data_ptr(), nvv.data_ptr()
         a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         a.status = self.status.data_ptr()
         self.args, self.out, self.device = a, out, dev
-        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, vmask, nvv, v_t)
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, k_bias, nvv, v_t)
         self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
 
     def run(self) -> torch.Tensor:

@@ -233,12 +233,17 @@ int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
  * (src/ops/sage_unified.py:499-547) without expanding K/V to query heads:
  *   vidx_asc int32 [B,H_Q,T] ascending distinct positions
  *   vert_k bf16 [B,H_Q,Tpad,128] gathered rows of k_bf (Tpad = T rounded up to 64, tail rows zero),
- *   vert_vt bf16 [B,H_Q,128,Tpad] the gathered rows of v, transposed; vmask u64 [B,H_Q,ceil(N/64)],
+ *   vert_vt bf16 [B,H_Q,128,Tpad] the gathered rows of v, transposed;
+ *   k_bias fp32 [B,H_Q,Npad]: the additive term of the INT8 score conversion for every key of every
+ *   query head, -12582912 * k_scale[key], or -inf where the key is a vertical line of the head (the
+ *   kernel serves those from vert_k);
  *   nv_valid int32 [B,H_Q,ceil(N/128)] = number of vertical lines below the window start of a query block.
+ * Call it for every prefill: with T == 0 it fills k_bias only and the vertical pointers may be null.
  */
 int hq_prefill_vertical_prepare(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int window, int T,
                                 const void* k_bf, const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
-                                void* vert_k, void* vert_vt, uint64_t* vmask, int32_t* nv_valid, void* stream);
+                                const float* k_scale, void* vert_k, void* vert_vt, float* k_bias, int32_t* nv_valid,
+                                void* stream);
 
 /* V transposed for the K-major operands of the tensor-memory kernel (the job of the reference's
  * TransposePadPermuteKernel, vendor/sageattention/csrc/fused/fused.cu:264-315, without the fragment
@@ -262,10 +267,11 @@ typedef struct hq_prefill_args {
   float   sm_scale;            /* same value as given to hq_prefill_quant */
   const void* q_i8; const void* q_bf; const float* q_scale;     /* from hq_prefill_quant */
   const void* k_i8; const void* k_bf; const float* k_scale;
+  const float* k_bias;         /* fp32 [B,H_Q,Npad] from hq_prefill_vertical_prepare (always) */
   const void* v_t;             /* bf16 [B,H_KV,128,Npad] from hq_prefill_transpose_v */
   const void* vert_k;          /* from hq_prefill_vertical_prepare (T > 0) */
   const void* vert_vt;
-  const uint64_t* vmask; const int32_t* nv_valid;
+  const int32_t* nv_valid;
   void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements (multiples of 8) */
   int32_t* status;             /* device word, zeroed by the caller; bit 1 = a bounded wait expired */
 } hq_prefill_args;
