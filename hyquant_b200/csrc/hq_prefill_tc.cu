@@ -40,7 +40,6 @@ struct PrefillTcParams {
 constexpr int kTcThreads = 352;            // 2 x 4 softmax warps + producer warp + one MMA warp per head
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256; // S buffer of head h, parity s: kColS + 128 h + 64 s; O of head h: kColO + 128 h
-constexpr float kTcLazy = 8.0f;
 
 constexpr int kKStages = 3;    // depth of the K ring: Q K^T runs two tiles ahead of P V and frees its slot at once
 constexpr int kVStages = 4;    // depth of the V ring
@@ -109,6 +108,80 @@ struct TcItemIter {
   __device__ __forceinline__ bool done() const { return kind >= 3; }
   __device__ __forceinline__ bool feeds(int h) const { return kind != 1 || hh == h; }
 };
+
+// The rare tile of a row whose P values against the current reference may be too large (or that has no
+// reference yet): take the true maximum of the tile from the scores in tensor memory, rescale O and the row sum
+// if the reference moves, and write the tile's P against the reference as it then stands.  Called by whole
+// warps; kept out of line so that the common path keeps its registers.
+struct TcSlowResult { float m_ref, l; bool ok; };
+__device__ __noinline__ TcSlowResult tc_slow_tile(uint32_t tS, uint32_t tO, const float4* ks4, const float4* kb4, bool is_i8,
+                                                  float esc, uint32_t mlo, uint32_t mhi, float m_ref, float l,
+                                                  uint64_t* pv_bar, uint32_t pv_parity, volatile int* abort_flag) {
+  TcSlowResult res;
+  res.ok = true;
+  uint32_t sr[64];
+  float x[64];
+  tc::tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+  tc::tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+  tc::tmem_wait_ld();
+  if (is_i8) {
+#pragma unroll
+    for (int c4 = 0; c4 < 16; ++c4) {
+      const float4 kk = ks4[c4], bb = kb4[c4];
+      x[4 * c4] = fmaf(__int_as_float((int)sr[4 * c4] + 0x4B400000), kk.x, bb.x);
+      x[4 * c4 + 1] = fmaf(__int_as_float((int)sr[4 * c4 + 1] + 0x4B400000), kk.y, bb.y);
+      x[4 * c4 + 2] = fmaf(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), kk.z, bb.z);
+      x[4 * c4 + 3] = fmaf(__int_as_float((int)sr[4 * c4 + 3] + 0x4B400000), kk.w, bb.w);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 64; ++c) {
+      const uint32_t mw = c < 32 ? mlo : mhi;
+      x[c] = ((mw >> (c & 31)) & 1u) ? -INFINITY : __uint_as_float(sr[c]);
+    }
+  }
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], x[c]);
+  const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * esc;      // esc > 0
+  // Once here, move the reference all the way up to the maximum seen: with the reference left below it,
+  // every later tile with a few scores near that maximum would bring the row back here.
+  const bool grow = mx > m_ref;                              // also true for the first finite maximum
+  if (__any_sync(0xffffffffu, grow)) {
+    const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - mx);
+    if (pv_bar != nullptr) {   // O must be quiescent: every P V of this head issued so far has to be complete
+      res.ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_bar, pv_parity, abort_flag));
+      if (!res.ok) { res.m_ref = m_ref; res.l = l; return res; }
+      tc::fence_after_sync();
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[32];
+        tc::tmem_ld32(tO + ch * 32, o);
+        tc::tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (grow ? alpha : 1.f));
+        tc::tmem_st32(tO + ch * 32, o);
+      }
+      tc::tmem_wait_st();
+    }
+    if (grow) { l *= alpha; m_ref = mx; }
+  }
+  const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+  uint32_t pk[32];
+  float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 64; c += 2) {
+    const float p0 = ex2f(fmaf(x[c], esc, -mu)), p1 = ex2f(fmaf(x[c + 1], esc, -mu));
+    rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
+    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);       // low half = even column
+    pk[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+  }
+  tc::tmem_st32(tS, pk);
+  tc::tmem_wait_st();
+  res.m_ref = m_ref;
+  res.l = l + (rs[0] + rs[1]) + (rs[2] + rs[3]);
+  return res;
+}
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant__ CUtensorMap mQb,
@@ -337,13 +410,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       }
       // One fused pass per tile: score -> exponent units -> 2^(y - mu) against the reference maximum as it
       // stands -> row sum and bf16 P, two columns per instruction where the hardware has packed fp32 forms.
-      // The row maximum is not computed: P values above 2^8 would show in the row sum of the tile, which
+      // The row maximum is not computed: a P value above 2^8 would show in the row sum of the tile, which
       // is then > 2^8.  Only then (and for a row's first finite scores) the scores are read from tensor
       // memory again, the maximum is taken, O is rescaled, the reference moves and the pass is repeated.
       uint32_t pk[32];
-      float lsum = 0.f;
-      bool redo = false;
-      for (;;) {
+      float lsum;
+      {
         uint32_t sr[64];
         tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
         tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
@@ -381,58 +453,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
           }
         }
         lsum = (rsa.x + rsa.y) + (rsb.x + rsb.y);
-        if (redo) break;
-        const bool need = m_ref == -INFINITY || !(lsum <= 256.f);
-        if (!__any_sync(0xffffffffu, need)) break;
-        // ---- the tile's true row maximum, from the scores in tensor memory
-        tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-        tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-        tc::tmem_wait_ld();
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (is_i8) {
-#pragma unroll
-          for (int c4 = 0; c4 < 16; ++c4) {
-            const float4 kk = ks4[c4], bb = kb4[c4];
-            m4[0] = fmaxf(m4[0], fmaf(__int_as_float((int)sr[4 * c4] + 0x4B400000), kk.x, bb.x));
-            m4[1] = fmaxf(m4[1], fmaf(__int_as_float((int)sr[4 * c4 + 1] + 0x4B400000), kk.y, bb.y));
-            m4[2] = fmaxf(m4[2], fmaf(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), kk.z, bb.z));
-            m4[3] = fmaxf(m4[3], fmaf(__int_as_float((int)sr[4 * c4 + 3] + 0x4B400000), kk.w, bb.w));
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            const uint32_t mw = c < 32 ? mlo : mhi;
-            if (!((mw >> (c & 31)) & 1u)) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sr[c]));
-          }
-        }
-        const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * esc;
-        const bool grow = mx > m_ref + kTcLazy;              // also true for the first finite maximum
-        if (__any_sync(0xffffffffu, grow)) {
-          const float alpha = (m_ref == -INFINITY) ? 0.f : ex2f(m_ref - mx);
-          if (t > 0) {     // O must be quiescent: every P V of this head issued so far has to be complete
-            ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(pv_done + 2 * h + ((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1), abort_flag));
-            if (!ok) break;
-            tc::fence_after_sync();
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              uint32_t o[32];
-              tc::tmem_ld32(lane_base + colO + ch * 32, o);
-              tc::tmem_wait_ld();
-#pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * (grow ? alpha : 1.f));
-              tc::tmem_st32(lane_base + colO + ch * 32, o);
-            }
-            tc::tmem_wait_st();
-          }
-          if (grow) { l *= alpha; m_ref = mx; }
-        }
-        redo = true;
       }
-      if (!ok) break;
-      l += lsum;
-      // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
-      tc::tmem_st32(lane_base + colS + slot * 64, pk);
-      tc::tmem_wait_st();
+      const bool need = m_ref == -INFINITY || !(lsum <= 256.f);
+      if (__any_sync(0xffffffffu, need)) {
+        // out of line: the maximum, the move of the reference and the tile's P against the new reference
+        const bool wait_pv = t > 0;
+        const TcSlowResult sr2 = tc_slow_tile(lane_base + colS + slot * 64, lane_base + colO, ks4, kb4, is_i8, esc, mlo, mhi, m_ref, l,
+                                              wait_pv ? pv_done + 2 * h + ((t - 1) & 1) : nullptr, (uint32_t)(((t - 1) >> 1) & 1),
+                                              abort_flag);
+        ok = sr2.ok;
+        if (!ok) break;
+        m_ref = sr2.m_ref;
+        l = sr2.l;
+      } else {
+        l += lsum;
+        // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
+        tc::tmem_st32(lane_base + colS + slot * 64, pk);
+        tc::tmem_wait_st();
+      }
       tc::fence_before_sync();
       tc::mbar_arrive(p_ready + sl);
     }
