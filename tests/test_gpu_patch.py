@@ -43,18 +43,21 @@ def run(model, ids, steps_ids, cache):
 
 
 CASES = [
-    # family, mode, bound on rel-MSE of the prompt's last logits and of the decode logits
+    # family, mode, bound on the rel-MSE of the logits (prompt's last position; decode steps).
+    # Measured on a B200: the 16-bit and INT8-QK prefill modes land at 4e-5 .. 8e-5 (the noise floor of two bf16
+    # attention implementations through two layers), their decode steps run the stock attention (2e-5).  The D-stage
+    # modes decode against the INT4 cache, which is lossy by design: 3.4e-3 .. 7.6e-3 on these random-init models.
     ("llama", "hybrid_full", 2e-2),
     ("llama", "d_k4v4_vert", 2e-2),
     ("llama", "d_k4v4", 2e-2),
     ("qwen", "hybrid_full", 2e-2),
-    ("llama", "sage_w", 1e-3),
-    ("llama", "sage_w0", 1e-3),
-    ("llama", "vquant_vert", 1e-3),
-    ("llama", "full_attention", 1e-4),
-    ("qwen", "vquant_vert", 1e-3),
-    ("glm4", "sage_w", 1e-3),
-    ("glm4", "vquant_vert", 1e-3),
+    ("llama", "sage_w", 3e-4),
+    ("llama", "sage_w0", 3e-4),
+    ("llama", "vquant_vert", 3e-4),
+    ("llama", "full_attention", 2e-4),
+    ("qwen", "vquant_vert", 3e-4),
+    ("glm4", "sage_w", 3e-4),
+    ("glm4", "vquant_vert", 3e-4),
 ]
 
 
@@ -81,7 +84,7 @@ def test_patched_model_matches_stock_attention(family, mode, bound):
     assert torch.isfinite(got).all()
     err_prefill, err_decode = rel_mse(got[:, 0], want[:, 0]), rel_mse(got[:, 1:], want[:, 1:])
     print(f"{family}/{mode}: rel-MSE prefill {err_prefill:.3e} decode {err_decode:.3e}")
-    assert err_prefill < bound and err_decode < bound
+    assert err_prefill < min(bound, 3e-4) and err_decode < bound
     if mode in D_STAGE_MODES:
         layer = cache.get_layer(0)
         assert layer.phase == "decode" and cache.get_seq_length() == PROMPT + STEPS
