@@ -1,0 +1,33 @@
+"""Why P·V stays in BF16: rounding P and V to FP8 (e4m3, the format of the reference's sm_90a FP8 path,
+src/ops/sage_fp8_attention.py:15-45) on the synthetic prefill data misses the accuracy bar of this path
+(max-abs 2e-2, rel-MSE 1e-4 against 16-bit attention) by an order of magnitude, while BF16 operands stay
+two orders inside it.  Pure torch on CPU."""
+
+import torch
+
+from hyquant_b200.synth import gen_torch
+
+
+def rel_mse(a, b):
+    return float(((a - b) ** 2).sum() / (b ** 2).sum())
+
+
+def test_fp8_pv_misses_the_tolerance_bf16_meets_it():
+    t = gen_torch(1, 4, 1, 1024, 128, 128, 0.05, 2013, device="cpu")
+    q, k, v = t["q"].float(), t["k"].float().repeat_interleave(4, 1), t["v"].float().repeat_interleave(4, 1)
+    s = torch.einsum("bhqd,bhkd->bhqk", q, k) * 128 ** -0.5
+    pos = torch.arange(s.shape[-1])
+    s = s.masked_fill(pos[None, None, None, :] > pos[None, None, :, None], float("-inf"))
+    p = torch.softmax(s, -1)
+    ref = p @ v
+
+    def r8(x):
+        return x.to(torch.float8_e4m3fn).float()
+
+    # the most favourable scaling: every row of P and every channel of V uses the full e4m3 range
+    pmax = p.amax(-1, keepdim=True)
+    vscale = v.abs().amax(dim=2, keepdim=True) / 448.0
+    out8 = (r8(p / pmax * 448.0) @ r8(v / vscale)) * vscale * pmax / 448.0
+    out16 = p.bfloat16().float() @ v.bfloat16().float()
+    assert rel_mse(out8, ref) > 5e-4 and float((out8 - ref).abs().max()) > 2e-2
+    assert rel_mse(out16, ref) < 1e-5
