@@ -201,27 +201,30 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, g
 
 
 def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
-    """Per layer and step: q/k/v of the new token from pinned host memory -> device,
-    append to staging (flush when full), decode attention, output back to the host."""
+    """Per step: q/k/v of the new token for every layer from pinned host memory -> device; per layer append
+    to staging (flush when full) and decode attention; every layer's output back to the host."""
     r = H_Q // H_KV
     n = len(layers)
     g = torch.Generator(); g.manual_seed(seed)
     tot = steps + warmup
     rows = B * (H_Q + 2 * H_KV)
-    # one pinned message per (step, layer): the new token's q | k | v rows
+    # one pinned message per step: the new token's q | k | v rows of every layer; one pinned result per step
     hin = torch.randn(tot, n, rows, D, generator=g).to(torch.bfloat16).pin_memory()
     hout = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16).pin_memory()
     dev = layers[0].k_window.device
+    xdev = torch.empty(n, rows, D, dtype=torch.bfloat16, device=dev)
+    odev = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16, device=dev)
+    qv = [xdev[li, :B * H_Q].view(B, H_Q, 1, D) for li in range(n)]
+    kv = [xdev[li, B * H_Q:B * (H_Q + H_KV)].view(B, H_KV, 1, D) for li in range(n)]
+    vv = [xdev[li, B * (H_Q + H_KV):].view(B, H_KV, 1, D) for li in range(n)]
+    ov = [odev[li] for li in range(n)]
 
     def one_step(s):
+        xdev.copy_(hin[s], non_blocking=True)
         for li, layer in enumerate(layers):
-            x = hin[s, li].to(dev, non_blocking=True)
-            q = x[:B * H_Q].view(B, H_Q, 1, D)
-            k = x[B * H_Q:B * (H_Q + H_KV)].view(B, H_KV, 1, D)
-            v = x[B * (H_Q + H_KV):].view(B, H_KV, 1, D)
-            layer.append_staging(k, v)
-            o = layer.decode_attention(q, r)
-            hout[li].copy_(o, non_blocking=True)
+            layer.append_staging(kv[li], vv[li])
+            layer.decode_attention(qv[li], r, out=ov[li])
+        hout.copy_(odev, non_blocking=True)
         torch.cuda.synchronize()      # the step's result is on the host
 
     for s in range(warmup):
@@ -510,7 +513,7 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "path": "DStageLayerCache.append_staging + decode_attention per layer, q/k/v from pinned host, out to host"},
+                    "path": "per step one pinned host message (q/k/v of every layer) to the device, DStageLayerCache.append_staging + decode_attention per layer, one message with every layer's output back to the host"},
             "gpu_launches": launches,
             "launch_mode": ("python" if args.no_graph else "cuda graph replay of one token (32 launches)") +
                            ("" if args.no_overlap else "; programmatic dependent launch: a call's blocks start and fetch their first "

@@ -242,6 +242,7 @@ class DStageLayerCache:
 
     def _decode_plan(self, q2d: torch.Tensor, kv_repeat: int) -> DecodePlan:
         if self._staging_buf_k.dtype != torch.bfloat16:
+            _check_decode_kernel_env()
             # non-bf16 models: segments are cast on the way in (as the reference kernel
             # does on load), so nothing can be cached across steps
             return DecodePlan(q2d, self.k_quant_packed, self.v_quant_packed, self.k_scale, self.v_scale,
@@ -250,6 +251,7 @@ class DStageLayerCache:
                               kv_repeat, None)
         p = self._plan
         if p is None or p.kv_repeat != kv_repeat:
+            _check_decode_kernel_env()
             # After freeze this cache's segments are written only by its own staging append and
             # flush kernels (staging buffer, newest 128 prefix tokens), so the decode kernel may
             # start fetching older units while whatever runs just before it finishes.  The
@@ -268,20 +270,23 @@ class DStageLayerCache:
         p.args.n_staging = self._staging_ptr
         return p
 
-    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, *, partial=None) -> torch.Tensor:
+    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, *, partial=None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of one new token over the four segments (reference :219-303).
 
         query_states [B, H_Q, 1, D] -> [B, H_Q, 1, D] in the query dtype.
         ``partial=(m, l, acc)`` requests the un-normalised softmax state instead
-        (sequence-sharded decode)."""
-        _check_decode_kernel_env()
+        (sequence-sharded decode).  ``out`` (not in the reference): a [B, H_Q, 1, D] tensor with
+        contiguous rows to write into instead of a new one."""
         if self.k_bits != 4 or self.v_bits != 4:
             raise HyQuantError(f"K{self.k_bits}/V{self.v_bits} is not built (K4/V4 only)")
         B_, H_Q_, _, D_ = query_states.shape
         q2d = query_states.reshape(B_ * H_Q_, D_)
         plan = self._decode_plan(q2d, kv_repeat)
-        out = plan.run(q2d, partial=partial)
-        return None if partial is not None else out.reshape(B_, H_Q_, 1, D_)
+        res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial)
+        if partial is not None:
+            return None
+        return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
     def get_seq_length(self) -> int:
         return self._seq_len
