@@ -24,7 +24,7 @@ EXPORTS = [
     "hq_version", "hq_last_error",
     "hq_quant_pack_int4", "hq_staging_append",
     "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static",
-    "hq_lse_merge",
+    "hq_lse_merge", "hq_lse_merge_strided",
     "hq_vertical_scores",
     "hq_topk",
     "hq_cache_reorganize",
@@ -84,6 +84,7 @@ def _declare(lib):
     lib.hq_decode_splitk.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.hq_decode_splitk_static.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.hq_lse_merge.argtypes = [vp, vp, vp, i32, i32, vp, i32, i64, vp]
+    lib.hq_lse_merge_strided.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp, i32, i64, vp]
     lib.hq_vertical_scores.argtypes = [vp, i32, i64, i64, i64, i32, i32, i32, i32,
                                        vp, i64, i64, i64, i32, i32, i32, i32, vp, vp, vp]
     lib.hq_topk.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp]
@@ -146,8 +147,19 @@ def dtype_code(dt) -> int:
     raise HyQuantError(f"unsupported dtype {dt}")
 
 
+_raw_stream = None
+
+
 def stream_ptr(device=None) -> int:
+    """cudaStream_t of torch's current stream on ``device`` (an int handle).  Uses torch's raw-stream
+    query, a fraction of the cost of building a ``torch.cuda.Stream`` object per call."""
+    global _raw_stream
     import torch
+    if _raw_stream is None:
+        _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", False)
+    if _raw_stream:
+        idx = None if device is None else getattr(device, "index", device)
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
 
 

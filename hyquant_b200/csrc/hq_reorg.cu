@@ -111,17 +111,18 @@ cache_reorg_kernel(const __nv_bfloat16* __restrict__ keys, const __nv_bfloat16* 
 
 // ------------------------------------------------------------ cross-shard merge
 __global__ void __launch_bounds__(128)
-lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l, const float* __restrict__ acc, int G, int rows,
-                 void* __restrict__ out, int out_dtype, int64_t out_stride) {
+lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l, const float* __restrict__ acc, int64_t m_stride,
+                 int64_t l_stride, int64_t acc_stride, int G, int rows, void* __restrict__ out, int out_dtype,
+                 int64_t out_stride) {
   const int r = blockIdx.x, d = threadIdx.x;
   float M = -INFINITY;
-  for (int gI = 0; gI < G; ++gI) M = fmaxf(M, m[(int64_t)gI * rows + r]);
+  for (int gI = 0; gI < G; ++gI) M = fmaxf(M, m[gI * m_stride + r]);
   float num = 0.f, den = 0.f;
   for (int gI = 0; gI < G; ++gI) {
-    const float mg = m[(int64_t)gI * rows + r];
+    const float mg = m[gI * m_stride + r];
     const float w = (mg == -INFINITY) ? 0.f : ex2f(mg - M);
-    num += w * acc[((int64_t)gI * rows + r) * 128 + d];
-    den += w * l[(int64_t)gI * rows + r];
+    num += w * acc[gI * acc_stride + (int64_t)r * 128 + d];
+    den += w * l[gI * l_stride + r];
   }
   store_out(out, (int64_t)r * out_stride + d, den > 0.f ? num / den : 0.f, out_dtype);
 }
@@ -165,15 +166,22 @@ extern "C" int hq_cache_reorganize(const void* keys, const void* values, int64_t
   return HQ_OK;
 }
 
-extern "C" int hq_lse_merge(const float* m, const float* l, const float* acc, int G, int rows,
-                            void* out, int out_dtype, int64_t out_stride, void* stream) {
+extern "C" int hq_lse_merge_strided(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
+                                    int64_t acc_stride, int G, int rows, void* out, int out_dtype, int64_t out_stride,
+                                    void* stream) {
   using namespace hq;
   HQ_REQUIRE(G >= 1 && rows >= 0, HQ_ERR_INVALID, "hq_lse_merge: G >= 1 and rows >= 0 required");
   if (rows == 0) return HQ_OK;
   HQ_REQUIRE(m && l && acc && out, HQ_ERR_INVALID, "hq_lse_merge: null pointer");
   HQ_REQUIRE(out_dtype == HQ_BF16 || out_dtype == HQ_F16 || out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,
              "hq_lse_merge: out_dtype %d", out_dtype);
-  lse_merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(m, l, acc, G, rows, out, out_dtype, out_stride);
+  lse_merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(m, l, acc, m_stride, l_stride, acc_stride, G, rows, out, out_dtype,
+                                                           out_stride);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
+}
+
+extern "C" int hq_lse_merge(const float* m, const float* l, const float* acc, int G, int rows,
+                            void* out, int out_dtype, int64_t out_stride, void* stream) {
+  return hq_lse_merge_strided(m, l, acc, rows, rows, (int64_t)rows * 128, G, rows, out, out_dtype, out_stride, stream);
 }

@@ -210,7 +210,7 @@ class DStageLayerCache:
             k2, v2 = key_states.reshape(BH, D), value_states.reshape(BH, D)
             rc = self._lib.hq_staging_append(k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0),
                                              self._staging_buf_k.data_ptr(), self._staging_buf_v.data_ptr(), BH,
-                                             self._staging_ptr, torch.cuda.current_stream(k2.device).cuda_stream)
+                                             self._staging_ptr, _lib.stream_ptr(k2.device))
             if rc != 0:
                 _lib.check(rc, "hq_staging_append")
             self._staging_ptr += 1

@@ -113,7 +113,7 @@ _ws_cache: dict = {}
 def decode_workspace(device: torch.device, BH_KV: int, kv_repeat: int) -> torch.Tensor:
     """Scratch for the split-K partials and tickets, zero-filled once, cached per
     (device, stream, shape) — calls on different streams never share one."""
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _lib.stream_ptr(device)
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream, BH_KV, kv_repeat)
     ws = _ws_cache.get(key)
     if ws is None:
@@ -221,7 +221,7 @@ class DecodePlan:
                 out = torch.empty(q.shape[0], 128, dtype=q.dtype, device=q.device)
             a.partial_m = a.partial_l = a.partial_acc = None
             a.out, a.out_stride, a.out_dtype = out.data_ptr(), out.stride(0), _lib.dtype_code(out.dtype)
-        rc = self._fn(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream)
+        rc = self._fn(C.byref(a), _lib.stream_ptr(self.device))
         if rc != 0:
             _lib.check(rc, "hq_decode_splitk")
         return out

@@ -105,15 +105,25 @@ class SequenceShardedLayer:
             self.layer.append_staging(key_states, value_states)
 
     def decode_attention(self, query_states: torch.Tensor, kv_repeat: int) -> torch.Tensor:
-        from .decode_d_stage import lse_merge
+        """Partial decode over this rank's shard, one all-gather of the per-rank message
+        ``m [rows] | l [rows] | acc [rows, D]`` (the kernel writes straight into it), merge on every rank."""
+        import torch.distributed as dist
+        from . import _lib
         B, H_Q, _, D = query_states.shape
         rows = B * H_Q
-        if self._bufs is None or self._bufs[2].shape[0] != rows:
+        world = dist.get_world_size(self.group)
+        if self._bufs is None or self._bufs[0].numel() != rows * (D + 2):
             dev = query_states.device
-            self._bufs = (torch.empty(rows, dtype=torch.float32, device=dev),
-                          torch.empty(rows, dtype=torch.float32, device=dev),
-                          torch.empty(rows, D, dtype=torch.float32, device=dev))
-        m, l, acc = self._bufs
+            msg = torch.empty(rows * (D + 2), dtype=torch.float32, device=dev)
+            self._bufs = (msg, torch.empty(world, rows * (D + 2), dtype=torch.float32, device=dev))
+        msg, gathered = self._bufs
+        m, l, acc = msg[:rows], msg[rows:2 * rows], msg[2 * rows:].view(rows, D)
         self.layer.decode_attention(query_states, kv_repeat, partial=(m, l, acc))
-        gm, gl, gacc = gather_partials(m, l, acc, self.group)
-        return lse_merge(gm, gl, gacc, out_dtype=query_states.dtype).reshape(B, H_Q, 1, D)
+        dist.all_gather_into_tensor(gathered, msg, group=self.group)
+        out = torch.empty(rows, D, dtype=query_states.dtype, device=query_states.device)
+        base, fl, stride = gathered.data_ptr(), 4, gathered.stride(0)
+        rc = _lib.lib().hq_lse_merge_strided(base, base + fl * rows, base + fl * 2 * rows, stride, stride, stride, world, rows,
+                                             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0),
+                                             _lib.stream_ptr(out.device))
+        _lib.check(rc, "hq_lse_merge_strided")
+        return out.reshape(B, H_Q, 1, D)

@@ -164,6 +164,10 @@ int hq_decode_splitk_static(const hq_decode_args* args, void* stream);
  */
 int hq_lse_merge(const float* m, const float* l, const float* acc, int G, int rows,
                  void* out, int out_dtype, int64_t out_stride, void* stream);
+/* The same with a stride (in floats) between consecutive shards of each array, for partials that arrive as one
+ * message per shard (m | l | acc back to back, all-gathered into [G][rows * 130]). */
+int hq_lse_merge_strided(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
+                         int64_t acc_stride, int G, int rows, void* out, int out_dtype, int64_t out_stride, void* stream);
 
 /* --------------------------------------------------------------------------
  * Vertical-line scores: mean of the last `tail_len` queries, dotted with every

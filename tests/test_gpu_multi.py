@@ -57,8 +57,27 @@ def _worker(rank, world, port, errs):
         part = hq.fused_d_stage_decode(q[h0 * R:h1 * R], c["kq"][sl], c["vq"][sl], c["ks"][sl], c["vs"][sl], c["kt"][sl],
                                        c["vt"][sl], c["kst"][sl], c["vst"][sl], c["kw"][sl], c["vw"][sl], 4, 4, kv_repeat=R).float()
         e2 = (part - full[h0 * R:h1 * R]).abs().max().item()
+        # --- the layer-level path: a frozen cache split by shard_layer_sequence, decoded through
+        # SequenceShardedLayer (kernel writes the per-rank message, one all-gather, strided merge),
+        # across a staging flush on the tail rank
+        from hyquant_b200.synth import gen_torch
+        t = gen_torch(2, 8, 2, 4096 + 77, 128, 128, 0.05, 321, n_qry=128, device=dev)     # same seed on every rank
+        lay = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=128, top_ratio=0.05, use_vert=True)
+        lay.update_prefill(t["k"], t["v"]); lay.save_query_tail(t["q"]); lay.freeze(kv_repeat=4)
+        sh = sharded.SequenceShardedLayer(sharded.shard_layer_sequence(lay, world, rank))
+        g2 = torch.Generator(device=dev); g2.manual_seed(11)
+        e3 = 0.0
+        for step in range(140):
+            kn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
+            vn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
+            lay.append_staging(kn, vn)
+            sh.append_staging(kn, vn, last)
+            if step % 23 == 0 or step >= 126:
+                want = lay.decode_attention(t["q_decode"], 4).float()
+                got = sh.decode_attention(t["q_decode"], 4).float()
+                e3 = max(e3, (got - want).abs().max().item())
         torch.cuda.synchronize()
-        errs[rank] = (e1, e2)
+        errs[rank] = (e1, e2, e3)
         dist.destroy_process_group()
     except Exception as ex:  # pragma: no cover
         import traceback
@@ -75,4 +94,4 @@ def test_two_gpu_sequence_and_head_sharding():
     mp.spawn(_worker, args=(world, _free_port(), errs), nprocs=world, join=True)
     for r in range(world):
         assert isinstance(errs[r], tuple), errs[r]
-        assert errs[r][0] < 1e-2 and errs[r][1] < 1e-2, dict(errs)
+        assert errs[r][0] < 1e-2 and errs[r][1] < 1e-2 and errs[r][2] < 1e-2, dict(errs)
