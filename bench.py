@@ -43,10 +43,11 @@ LAYERS = 32
 FALLBACK_HBM_GBS = 6650.0
 
 
-def algorithmic_bytes(bh_kv, bh_q, n_quant, n_bf16):
-    """Bytes one decode call must move: INT4 token = 64+64 B codes + 2+2 B scales,
-    BF16 token = 256+256 B, plus q read and out written (2 x 256 B per query head)."""
-    return bh_kv * (132 * n_quant + 512 * n_bf16) + 512 * bh_q
+def algorithmic_bytes(bh_kv, bh_q, n_quant, n_bf16, k_bits=4, v_bits=4):
+    """Bytes one decode call must move: a quantised token = 16 bytes per bit of width for K and for V
+    (64+64 B at 4 bits) + 2+2 B scales, a BF16 token = 256+256 B, plus q read and out written
+    (2 x 256 B per query head)."""
+    return bh_kv * ((16 * k_bits + 16 * v_bits + 4) * n_quant + 512 * n_bf16) + 512 * bh_q
 
 
 def measured_peak():
@@ -114,11 +115,11 @@ class ClockSampler:
 # workload construction (device)
 # ---------------------------------------------------------------------------
 
-def build_layer(hq, torch, seed, n_prefix, device, b=B, h_q=H_Q, h_kv=H_KV, staging=STAGING):
+def build_layer(hq, torch, seed, n_prefix, device, b=B, h_q=H_Q, h_kv=H_KV, staging=STAGING, k_bits=4, v_bits=4):
     """Seeded K/V/Q -> vertical selection over [0, N-W) -> frozen four-segment cache."""
     from hyquant_b200.synth import gen_torch
     t = gen_torch(b, h_q, h_kv, n_prefix, D, W, RHO, seed, n_qry=256, device=device)
-    layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+    layer = hq.DStageLayerCache(0, k_bits=k_bits, v_bits=v_bits, window_size=W, top_ratio=RHO, use_vert=True)
     layer.update_prefill(t["k"], t["v"])
     layer.save_query_tail(t["q"])
     r = h_q // h_kv
@@ -136,7 +137,7 @@ def build_layer(hq, torch, seed, n_prefix, device, b=B, h_q=H_Q, h_kv=H_KV, stag
 
 def layer_bytes(layer, h_q_total):
     n_bf16 = layer.k_topk.shape[1] + layer._staging_ptr + layer.k_window.shape[1]
-    return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16)
+    return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16, layer.k_bits, layer.v_bits)
 
 
 def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None, overlap=True):
@@ -247,6 +248,22 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
 # ---------------------------------------------------------------------------
 # CPU baseline (oracle port of the reference's PyTorch fallback)
 # ---------------------------------------------------------------------------
+
+def bench_bit_widths(torch, hq, dev, graph):
+    """The decode call at the reference's other cache modes (d_k8v8, d_k4v2, d_k2v4), same shapes as the headline
+    workload: these pairs run the plain kernel of hq_decode_generic.cu (two launches per call: partials, merge)."""
+    out = []
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for kb, vb in ((8, 8), (4, 2), (2, 4)):
+        ls, qq = zip(*[build_layer(hq, torch, 6000 + 16 * kb + vb + i, N_PREFIX, dev, k_bits=kb, v_bits=vb) for i in range(4)])
+        ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=graph, overlap=False)
+        us = ms * 1e3 / cnt
+        bts = layer_bytes(ls[0], B * H_Q)
+        out.append({"k_bits": kb, "v_bits": vb, "prefix": N_PREFIX, "us_per_call": round(us, 2), "bytes_per_call": bts,
+                    "gbps": round(bts / us / 1e3, 1), "kernel": "hq::decode_generic_kernel + hq::lse_merge_kernel"})
+        del ls, qq
+    return out
+
 
 def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
     """Batched decode at Qwen3-32B attention shapes (batch 16, 64 query / 8 KV heads, prefix 32K): the KV heads
@@ -490,7 +507,10 @@ def run_ours(args):
                             "prepare_ms_first_call": round(prep_ms, 2),
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
-    batched = long_ctx = None
+    batched = long_ctx = bit_widths = None
+    if not args.no_extra and rank == 0:
+        bit_widths = bench_bit_widths(torch, hq, dev, not args.no_graph)
+        torch.cuda.empty_cache()
     if not args.no_extra:
         batched = bench_batched_decode(torch, hq, dev, rank, world, dist, not args.no_graph)
         torch.cuda.empty_cache()
@@ -524,6 +544,7 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "sweep": sweep,
             "prefill": prefill,
+            "bit_width_decode": bit_widths,
             "batched_decode": batched,
             "long_context_decode": long_ctx,
         }

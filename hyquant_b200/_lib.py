@@ -22,12 +22,12 @@ ERR_NAMES = {-1: "HQ_ERR_INVALID", -2: "HQ_ERR_UNSUPPORTED", -3: "HQ_ERR_ALIGNME
 # every symbol include/hyquant_b200.h declares
 EXPORTS = [
     "hq_version", "hq_last_error",
-    "hq_quant_pack_int4", "hq_staging_append",
+    "hq_quant_pack", "hq_quant_pack_int4", "hq_staging_append",
     "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static",
     "hq_lse_merge", "hq_lse_merge_strided",
     "hq_vertical_scores",
     "hq_topk",
-    "hq_cache_reorganize",
+    "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
     "hq_prefill_hybrid",
 ]
@@ -43,6 +43,7 @@ class DecodeArgs(C.Structure):
         ("struct_bytes", C.c_int32), ("BH_KV", C.c_int32), ("kv_repeat", C.c_int32), ("head_dim", C.c_int32),
         ("n_quant", C.c_int32), ("n_topk", C.c_int32), ("n_staging", C.c_int32), ("n_window", C.c_int32),
         ("out_dtype", C.c_int32), ("num_splits", C.c_int32), ("sm_scale", C.c_float), ("flags", C.c_int32),
+        ("k_bits", C.c_int32), ("v_bits", C.c_int32),
         ("q", C.c_void_p), ("q_stride", C.c_int64),
         ("k_packed", C.c_void_p), ("v_packed", C.c_void_p), ("kp_stride_bh", C.c_int64), ("vp_stride_bh", C.c_int64),
         ("k_scale", C.c_void_p), ("v_scale", C.c_void_p), ("ks_stride_bh", C.c_int64), ("vs_stride_bh", C.c_int64),
@@ -79,6 +80,8 @@ def _declare(lib):
     lib.hq_version.restype = C.c_char_p
     lib.hq_last_error.restype = C.c_char_p
     lib.hq_quant_pack_int4.argtypes = [vp, i32, i64, i64, i32, i32, vp, i64, vp, i64, i64, i32, vp]
+    lib.hq_quant_pack.argtypes = [vp, i32, i64, i64, i32, i32, i32, vp, i64, vp, i64, i64, i32, vp]
+    lib.hq_lse_merge_partial.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp, vp, vp, vp]
     lib.hq_staging_append.argtypes = [vp, vp, i64, i64, vp, vp, i32, i32, vp]
     lib.hq_decode_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_decode_splitk.argtypes = [C.POINTER(DecodeArgs), vp]
@@ -90,6 +93,8 @@ def _declare(lib):
     lib.hq_topk.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp]
     lib.hq_cache_reorganize.argtypes = [vp, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
                                         vp, vp, i64, vp, vp, i64, i32, vp]
+    lib.hq_cache_reorganize_bits.argtypes = [vp, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
+                                             vp, vp, i64, i64, vp, vp, i64, i32, i32, i32, vp]
     lib.hq_prefill_quant_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_prefill_quant.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, i32,
                                      vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]

@@ -785,6 +785,10 @@ static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace hq
 
+namespace hq {
+int decode_generic_launch(const hq_decode_args* a, int k_bits, int v_bits, float* ws, int64_t ws_floats, cudaStream_t st);
+}
+
 extern "C" int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes) {
   using namespace hq;
   HQ_REQUIRE(bytes && BH_KV > 0 && kv_repeat > 0 && kv_repeat <= 16, HQ_ERR_INVALID,
@@ -814,6 +818,28 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
 
   HQ_REQUIRE(((uintptr_t)a->q & 7) == 0 && a->q_stride % 4 == 0, HQ_ERR_ALIGNMENT,
              "hq_decode_splitk: q rows must be 8-byte aligned");
+  const int k_bits = a->k_bits == 0 ? 4 : a->k_bits, v_bits = a->v_bits == 0 ? 4 : a->v_bits;
+  HQ_REQUIRE((k_bits == 2 || k_bits == 4 || k_bits == 8) && (v_bits == 2 || v_bits == 4 || v_bits == 8), HQ_ERR_UNSUPPORTED,
+             "hq_decode_splitk: bit widths must be 2, 4 or 8 (K%d V%d)", k_bits, v_bits);
+  if (k_bits != 4 || v_bits != 4) {
+    // any other pair: the plain kernel of hq_decode_generic.cu, partials in the same workspace past its header
+    HQ_REQUIRE(a->n_quant == 0 || (a->k_packed && a->v_packed && a->k_scale && a->v_scale), HQ_ERR_INVALID,
+               "hq_decode_splitk: null quantised segment");
+    const void* kss[3] = {a->k_topk, a->k_staging, a->k_window};
+    const void* vss[3] = {a->v_topk, a->v_staging, a->v_window};
+    const int nss[3] = {a->n_topk, a->n_staging, a->n_window};
+    for (int s = 0; s < 3; ++s)
+      HQ_REQUIRE(nss[s] == 0 || (kss[s] && vss[s] && aligned16(kss[s]) && ((uintptr_t)vss[s] % 8) == 0), HQ_ERR_INVALID,
+                 "hq_decode_splitk: BF16 segment %d missing or misaligned", s);
+    int64_t need = 0;
+    hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
+    HQ_REQUIRE(a->workspace && a->workspace_bytes >= need, HQ_ERR_WORKSPACE,
+               "hq_decode_splitk: workspace of %lld bytes needed, %lld given", (long long)need, (long long)a->workspace_bytes);
+    HQ_REQUIRE(((uintptr_t)a->workspace & 255) == 0, HQ_ERR_ALIGNMENT, "hq_decode_splitk: workspace must be 256-byte aligned");
+    const int64_t off = kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256);
+    return decode_generic_launch(a, k_bits, v_bits, (float*)((uint8_t*)a->workspace + off), (a->workspace_bytes - off) / 4 - 8,
+                                 (cudaStream_t)stream);
+  }
   DecodeParams p{};
   p.q = (const __nv_bfloat16*)a->q; p.q_stride = a->q_stride;
   p.n_quant = a->n_quant;

@@ -1,4 +1,4 @@
-// Per-token symmetric INT4 quantise + nibble pack (flush of the staging buffer
+// Per-token symmetric quantise + pack, 8 / 4 / 2 bits (flush of the staging buffer
 // and the quantisation step of the prefill->decode reorganisation).
 //
 // HBM-bound: reads 256 B (bf16) per token, writes 64 B codes + 2 B scale.  One
@@ -8,12 +8,12 @@
 
 namespace hq {
 
-template <typename T>
+template <typename T, int BITS>
 __global__ void __launch_bounds__(256)
-quant_pack_int4_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_stride_n, int BH, int n,
-                       uint8_t* __restrict__ packed, int64_t packed_stride_bh,
-                       __half* __restrict__ scale, int64_t scale_stride_bh,
-                       int64_t dst_off, int scale_mode) {
+quant_pack_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_stride_n, int BH, int n,
+                  uint8_t* __restrict__ packed, int64_t packed_stride_bh,
+                  __half* __restrict__ scale, int64_t scale_stride_bh,
+                  int64_t dst_off, int scale_mode) {
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -24,10 +24,9 @@ quant_pack_int4_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_s
     const T* src = x + bh * x_stride_bh + tok * x_stride_n + lane * 4;
     float v[4];
     load4(src, v);
-    uint16_t code;
-    __half s = quant_row_int4(v, scale_mode, code);
-    uint8_t* prow = packed + bh * packed_stride_bh + (dst_off + tok) * 64;
-    reinterpret_cast<uint16_t*>(prow)[lane] = code;
+    uint32_t code;
+    __half s = quant_row_bits<BITS>(v, scale_mode, code);
+    store_codes<BITS>(packed + bh * packed_stride_bh + (dst_off + tok) * (16 * BITS), lane, code);
     if (lane == 0) scale[bh * scale_stride_bh + dst_off + tok] = s;
   }
 }
@@ -63,40 +62,62 @@ extern "C" int hq_staging_append(const void* k_new, const void* v_new, int64_t k
   return HQ_OK;
 }
 
-extern "C" int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
-                                  int BH, int n, void* packed, int64_t packed_stride_bh,
-                                  void* scale, int64_t scale_stride_bh,
-                                  int64_t dst_token_offset, int scale_mode, void* stream) {
+namespace hq {
+template <int BITS>
+static int launch_quant(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n, int BH, int n, uint8_t* p,
+                        int64_t packed_stride_bh, __half* s, int64_t scale_stride_bh, int64_t dst_off, int scale_mode,
+                        dim3 grid, cudaStream_t st) {
+  dim3 block(256);
+  if (in_dtype == HQ_BF16)
+    quant_pack_kernel<__nv_bfloat16, BITS><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                                   packed_stride_bh, s, scale_stride_bh, dst_off, scale_mode);
+  else if (in_dtype == HQ_F16)
+    quant_pack_kernel<__half, BITS><<<grid, block, 0, st>>>((const __half*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                            packed_stride_bh, s, scale_stride_bh, dst_off, scale_mode);
+  else if (in_dtype == HQ_F32)
+    quant_pack_kernel<float, BITS><<<grid, block, 0, st>>>((const float*)x, x_stride_bh, x_stride_n, BH, n, p,
+                                                           packed_stride_bh, s, scale_stride_bh, dst_off, scale_mode);
+  else
+    HQ_REQUIRE(false, HQ_ERR_UNSUPPORTED, "hq_quant_pack: unknown dtype %d", in_dtype);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}
+}  // namespace hq
+
+extern "C" int hq_quant_pack(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
+                             int BH, int n, int nbits, void* packed, int64_t packed_stride_bh,
+                             void* scale, int64_t scale_stride_bh,
+                             int64_t dst_token_offset, int scale_mode, void* stream) {
   using namespace hq;
-  HQ_REQUIRE(BH >= 0 && n >= 0 && dst_token_offset >= 0, HQ_ERR_INVALID, "hq_quant_pack_int4: negative size");
+  HQ_REQUIRE(BH >= 0 && n >= 0 && dst_token_offset >= 0, HQ_ERR_INVALID, "hq_quant_pack: negative size");
+  HQ_REQUIRE(nbits == 2 || nbits == 4 || nbits == 8, HQ_ERR_UNSUPPORTED, "hq_quant_pack: nbits must be 2, 4 or 8, got %d", nbits);
   if (BH == 0 || n == 0) return HQ_OK;
-  HQ_REQUIRE(x && packed && scale, HQ_ERR_INVALID, "hq_quant_pack_int4: null pointer");
-  HQ_REQUIRE(scale_mode == 0 || scale_mode == 1, HQ_ERR_INVALID, "hq_quant_pack_int4: scale_mode must be 0 or 1");
+  HQ_REQUIRE(x && packed && scale, HQ_ERR_INVALID, "hq_quant_pack: null pointer");
+  HQ_REQUIRE(scale_mode == 0 || scale_mode == 1, HQ_ERR_INVALID, "hq_quant_pack: scale_mode must be 0 or 1");
   const int esz = in_dtype == HQ_F32 ? 4 : 2;
   HQ_REQUIRE(((uintptr_t)x % (4 * esz)) == 0 && (x_stride_bh % 4) == 0 && (x_stride_n % 4) == 0, HQ_ERR_ALIGNMENT,
-             "hq_quant_pack_int4: x rows must be aligned to 4 elements");
-  HQ_REQUIRE(((uintptr_t)packed % 2) == 0 && (packed_stride_bh % 2) == 0, HQ_ERR_ALIGNMENT,
-             "hq_quant_pack_int4: packed rows must be 2-byte aligned");
+             "hq_quant_pack: x rows must be aligned to 4 elements");
+  const int lane_bytes = nbits / 2;      // bytes one lane stores
+  HQ_REQUIRE(((uintptr_t)packed % lane_bytes) == 0 && (packed_stride_bh % lane_bytes) == 0, HQ_ERR_ALIGNMENT,
+             "hq_quant_pack: packed rows must be %d-byte aligned", lane_bytes);
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)BH * n;
   const int warps_per_block = 8;
   int64_t blocks = (rows + warps_per_block - 1) / warps_per_block;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  dim3 grid((unsigned)blocks), block(256);
+  dim3 grid((unsigned)blocks);
   uint8_t* p = (uint8_t*)packed;
   __half* s = (__half*)scale;
-  if (in_dtype == HQ_BF16)
-    quant_pack_int4_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, x_stride_bh, x_stride_n, BH, n, p,
-                                                                  packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
-  else if (in_dtype == HQ_F16)
-    quant_pack_int4_kernel<__half><<<grid, block, 0, st>>>((const __half*)x, x_stride_bh, x_stride_n, BH, n, p,
-                                                           packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
-  else if (in_dtype == HQ_F32)
-    quant_pack_int4_kernel<float><<<grid, block, 0, st>>>((const float*)x, x_stride_bh, x_stride_n, BH, n, p,
-                                                          packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode);
-  else
-    HQ_REQUIRE(false, HQ_ERR_UNSUPPORTED, "hq_quant_pack_int4: unknown dtype %d", in_dtype);
-  HQ_CUDA(cudaGetLastError());
-  return HQ_OK;
+  if (nbits == 8) return launch_quant<8>(x, in_dtype, x_stride_bh, x_stride_n, BH, n, p, packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode, grid, st);
+  if (nbits == 4) return launch_quant<4>(x, in_dtype, x_stride_bh, x_stride_n, BH, n, p, packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode, grid, st);
+  return launch_quant<2>(x, in_dtype, x_stride_bh, x_stride_n, BH, n, p, packed_stride_bh, s, scale_stride_bh, dst_token_offset, scale_mode, grid, st);
+}
+
+extern "C" int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
+                                  int BH, int n, void* packed, int64_t packed_stride_bh,
+                                  void* scale, int64_t scale_stride_bh,
+                                  int64_t dst_token_offset, int scale_mode, void* stream) {
+  return hq_quant_pack(x, in_dtype, x_stride_bh, x_stride_n, BH, n, 4, packed, packed_stride_bh, scale, scale_stride_bh,
+                       dst_token_offset, scale_mode, stream);
 }

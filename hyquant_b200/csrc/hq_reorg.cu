@@ -35,9 +35,9 @@ cache_reorg_kernel(const __nv_bfloat16* __restrict__ keys, const __nv_bfloat16* 
                    int N, int prefix_len, int T, const int64_t* __restrict__ vidx_desc, const int32_t* __restrict__ vidx_asc,
                    __nv_bfloat16* __restrict__ k_topk, __nv_bfloat16* __restrict__ v_topk,
                    __nv_bfloat16* __restrict__ k_window, __nv_bfloat16* __restrict__ v_window,
-                   uint8_t* __restrict__ k_packed, uint8_t* __restrict__ v_packed, int64_t packed_stride_bh,
+                   uint8_t* __restrict__ k_packed, uint8_t* __restrict__ v_packed, int64_t kp_stride_bh, int64_t vp_stride_bh,
                    __half* __restrict__ k_scale, __half* __restrict__ v_scale, int64_t scale_stride_bh,
-                   int scale_mode, int prefix_tiles, int topk_tiles) {
+                   int k_bits, int v_bits, int scale_mode, int prefix_tiles, int topk_tiles) {
   __shared__ int32_t s_slice[kReorgTile];
   __shared__ int s_lo, s_hi;
   const int bh = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -75,11 +75,8 @@ cache_reorg_kernel(const __nv_bfloat16* __restrict__ keys, const __nv_bfloat16* 
       float kv[4], vv[4];
       load4(K + (int64_t)p * 128 + lane * 4, kv);
       load4(V + (int64_t)p * 128 + lane * 4, vv);
-      uint16_t ck, cv;
-      const __half sk = quant_row_int4(kv, scale_mode, ck);
-      const __half sv = quant_row_int4(vv, scale_mode, cv);
-      reinterpret_cast<uint16_t*>(k_packed + bh * packed_stride_bh + (int64_t)dst * 64)[lane] = ck;
-      reinterpret_cast<uint16_t*>(v_packed + bh * packed_stride_bh + (int64_t)dst * 64)[lane] = cv;
+      const __half sk = quant_store_row(k_bits, kv, scale_mode, k_packed + bh * kp_stride_bh + (int64_t)dst * (16 * k_bits), lane);
+      const __half sv = quant_store_row(v_bits, vv, scale_mode, v_packed + bh * vp_stride_bh + (int64_t)dst * (16 * v_bits), lane);
       if (lane == 0) {
         k_scale[bh * scale_stride_bh + dst] = sk;
         v_scale[bh * scale_stride_bh + dst] = sv;
@@ -113,7 +110,7 @@ cache_reorg_kernel(const __nv_bfloat16* __restrict__ keys, const __nv_bfloat16* 
 __global__ void __launch_bounds__(128)
 lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l, const float* __restrict__ acc, int64_t m_stride,
                  int64_t l_stride, int64_t acc_stride, int G, int rows, void* __restrict__ out, int out_dtype,
-                 int64_t out_stride) {
+                 int64_t out_stride, float* __restrict__ out_m, float* __restrict__ out_l, float* __restrict__ out_acc) {
   const int r = blockIdx.x, d = threadIdx.x;
   float M = -INFINITY;
   for (int gI = 0; gI < G; ++gI) M = fmaxf(M, m[gI * m_stride + r]);
@@ -124,19 +121,26 @@ lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l, const
     num += w * acc[gI * acc_stride + (int64_t)r * 128 + d];
     den += w * l[gI * l_stride + r];
   }
-  store_out(out, (int64_t)r * out_stride + d, den > 0.f ? num / den : 0.f, out_dtype);
+  if (out_acc != nullptr) {
+    out_acc[(int64_t)r * 128 + d] = num;
+    if (d == 0) { out_m[r] = M; out_l[r] = den; }
+  } else {
+    store_out(out, (int64_t)r * out_stride + d, den > 0.f ? num / den : 0.f, out_dtype);
+  }
 }
 
 }  // namespace hq
 
-extern "C" int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_bh,
+extern "C" int hq_cache_reorganize_bits(const void* keys, const void* values, int64_t kv_stride_bh,
                                    int BH, int N, int window, int T,
                                    const int64_t* vidx_desc, const int32_t* vidx_asc,
                                    void* k_topk, void* v_topk, void* k_window, void* v_window,
-                                   void* k_packed, void* v_packed, int64_t packed_stride_bh,
+                                   void* k_packed, void* v_packed, int64_t kp_stride_bh, int64_t vp_stride_bh,
                                    void* k_scale, void* v_scale, int64_t scale_stride_bh,
-                                   int scale_mode, void* stream) {
+                                   int k_bits, int v_bits, int scale_mode, void* stream) {
   using namespace hq;
+  HQ_REQUIRE((k_bits == 2 || k_bits == 4 || k_bits == 8) && (v_bits == 2 || v_bits == 4 || v_bits == 8), HQ_ERR_UNSUPPORTED,
+             "hq_cache_reorganize: bit widths must be 2, 4 or 8 (K%d V%d)", k_bits, v_bits);
   HQ_REQUIRE(BH >= 0 && N >= 0 && window >= 0 && window <= N && T >= 0 && T <= N - window, HQ_ERR_INVALID,
              "hq_cache_reorganize: need 0 <= window <= N and 0 <= T <= N - window (N=%d window=%d T=%d)", N, window, T);
   if (BH == 0 || N == 0) return HQ_OK;
@@ -160,10 +164,22 @@ extern "C" int hq_cache_reorganize(const void* keys, const void* values, int64_t
   cache_reorg_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)keys, (const __nv_bfloat16*)values, kv_stride_bh, N, prefix_len, T, vidx_desc, vidx_asc,
       (__nv_bfloat16*)k_topk, (__nv_bfloat16*)v_topk, (__nv_bfloat16*)k_window, (__nv_bfloat16*)v_window,
-      (uint8_t*)k_packed, (uint8_t*)v_packed, packed_stride_bh, (__half*)k_scale, (__half*)v_scale, scale_stride_bh,
-      scale_mode, prefix_tiles, topk_tiles);
+      (uint8_t*)k_packed, (uint8_t*)v_packed, kp_stride_bh, vp_stride_bh, (__half*)k_scale, (__half*)v_scale, scale_stride_bh,
+      k_bits, v_bits, scale_mode, prefix_tiles, topk_tiles);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
+}
+
+extern "C" int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_bh,
+                                   int BH, int N, int window, int T,
+                                   const int64_t* vidx_desc, const int32_t* vidx_asc,
+                                   void* k_topk, void* v_topk, void* k_window, void* v_window,
+                                   void* k_packed, void* v_packed, int64_t packed_stride_bh,
+                                   void* k_scale, void* v_scale, int64_t scale_stride_bh,
+                                   int scale_mode, void* stream) {
+  return hq_cache_reorganize_bits(keys, values, kv_stride_bh, BH, N, window, T, vidx_desc, vidx_asc, k_topk, v_topk, k_window,
+                                  v_window, k_packed, v_packed, packed_stride_bh, packed_stride_bh, k_scale, v_scale,
+                                  scale_stride_bh, 4, 4, scale_mode, stream);
 }
 
 extern "C" int hq_lse_merge_strided(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
@@ -176,7 +192,20 @@ extern "C" int hq_lse_merge_strided(const float* m, const float* l, const float*
   HQ_REQUIRE(out_dtype == HQ_BF16 || out_dtype == HQ_F16 || out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,
              "hq_lse_merge: out_dtype %d", out_dtype);
   lse_merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(m, l, acc, m_stride, l_stride, acc_stride, G, rows, out, out_dtype,
-                                                           out_stride);
+                                                           out_stride, nullptr, nullptr, nullptr);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}
+
+extern "C" int hq_lse_merge_partial(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
+                                    int64_t acc_stride, int G, int rows, float* out_m, float* out_l, float* out_acc,
+                                    void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(G >= 1 && rows >= 0, HQ_ERR_INVALID, "hq_lse_merge_partial: G >= 1 and rows >= 0 required");
+  if (rows == 0) return HQ_OK;
+  HQ_REQUIRE(m && l && acc && out_m && out_l && out_acc, HQ_ERR_INVALID, "hq_lse_merge_partial: null pointer");
+  lse_merge_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(m, l, acc, m_stride, l_stride, acc_stride, G, rows, nullptr, HQ_F32, 0,
+                                                           out_m, out_l, out_acc);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

@@ -114,8 +114,8 @@ class DStageLayerCache:
     def _alloc_prefix(self, BH: int, n: int, device):
         cap = n + max(8 * GROUP_SIZE, n // 8)
         cap = (cap + GROUP_SIZE - 1) // GROUP_SIZE * GROUP_SIZE
-        self._kq = torch.empty(BH, cap, self._D // 2, dtype=torch.int8, device=device)
-        self._vq = torch.empty(BH, cap, self._D // 2, dtype=torch.int8, device=device)
+        self._kq = torch.empty(BH, cap, self._D * self.k_bits // 8, dtype=torch.int8, device=device)
+        self._vq = torch.empty(BH, cap, self._D * self.v_bits // 8, dtype=torch.int8, device=device)
         self._ks = torch.empty(BH, cap, dtype=torch.float16, device=device)
         self._vs = torch.empty(BH, cap, dtype=torch.float16, device=device)
 
@@ -139,8 +139,8 @@ class DStageLayerCache:
         head, an extension of the reference signature) skips the selection and
         freezes exactly those rows in BF16, in the given order."""
         assert self.phase == "prefill" and self._keys is not None
-        if self.k_bits != 4 or self.v_bits != 4:
-            raise HyQuantError(f"K{self.k_bits}/V{self.v_bits} is not built (K4/V4 only)")
+        if self.k_bits not in (2, 4, 8) or self.v_bits not in (2, 4, 8):
+            raise HyQuantError(f"bit widths must be 2, 4 or 8, got K{self.k_bits}/V{self.v_bits}")
         _lib.require_cuda(self._keys, "keys")
         B, H_KV, N, D = self._keys.shape
         if D != 128:
@@ -179,14 +179,14 @@ class DStageLayerCache:
         self.v_topk = torch.empty(BH, T, D, dtype=torch.bfloat16, device=device)
         self.k_window = torch.empty(BH, W, D, dtype=torch.bfloat16, device=device)
         self.v_window = torch.empty(BH, W, D, dtype=torch.bfloat16, device=device)
-        rc = _lib.lib().hq_cache_reorganize(
+        rc = _lib.lib().hq_cache_reorganize_bits(
             keys.data_ptr(), values.data_ptr(), keys.stride(0), BH, N, W, T,
             vidx.data_ptr() if T else None, vasc.data_ptr() if T else None,
             self.k_topk.data_ptr(), self.v_topk.data_ptr(), self.k_window.data_ptr(), self.v_window.data_ptr(),
-            self._kq.data_ptr(), self._vq.data_ptr(), self._kq.stride(0),
+            self._kq.data_ptr(), self._vq.data_ptr(), self._kq.stride(0), self._vq.stride(0),
             self._ks.data_ptr(), self._vs.data_ptr(), self._ks.stride(0),
-            SCALE_MODE, _lib.stream_ptr(device))
-        _lib.check(rc, "hq_cache_reorganize")
+            self.k_bits, self.v_bits, SCALE_MODE, _lib.stream_ptr(device))
+        _lib.check(rc, "hq_cache_reorganize_bits")
         self._n_quant = n_quant
         if dtype != torch.bfloat16:   # keep the reference's attribute dtype for non-bf16 models
             self.k_topk, self.v_topk = self.k_topk.to(dtype), self.v_topk.to(dtype)
@@ -235,8 +235,8 @@ class DStageLayerCache:
         if n + GROUP_SIZE > self._kq.shape[1]:
             self._grow_prefix(n + GROUP_SIZE)
             self._plan = None
-        quantize_per_token_into(self._staging_buf_k, self._kq, self._ks, n)
-        quantize_per_token_into(self._staging_buf_v, self._vq, self._vs, n)
+        quantize_per_token_into(self._staging_buf_k, self._kq, self._ks, n, nbits=self.k_bits)
+        quantize_per_token_into(self._staging_buf_v, self._vq, self._vs, n, nbits=self.v_bits)
         self._n_quant = n + GROUP_SIZE
         self._staging_ptr = 0
 
@@ -248,7 +248,7 @@ class DStageLayerCache:
             return DecodePlan(q2d, self.k_quant_packed, self.v_quant_packed, self.k_scale, self.v_scale,
                               self.k_topk, self.v_topk, self._staging_buf_k[:, :self._staging_ptr],
                               self._staging_buf_v[:, :self._staging_ptr], self.k_window, self.v_window,
-                              kv_repeat, None)
+                              kv_repeat, None, k_bits=self.k_bits, v_bits=self.v_bits)
         p = self._plan
         if p is None or p.kv_repeat != kv_repeat:
             _check_decode_kernel_env()
@@ -259,7 +259,7 @@ class DStageLayerCache:
             # before it may be the one that wrote the whole prefix.
             p = DecodePlan(q2d, self._kq, self._vq, self._ks, self._vs, self.k_topk, self.v_topk,
                            self._staging_buf_k, self._staging_buf_v, self.k_window, self.v_window,
-                           kv_repeat, None, overlap_previous=self.overlap_previous)
+                           kv_repeat, None, overlap_previous=self.overlap_previous, k_bits=self.k_bits, v_bits=self.v_bits)
             p.args.flags = 0
             self._plan = p
             self._plan_fresh = True
@@ -278,8 +278,6 @@ class DStageLayerCache:
         ``partial=(m, l, acc)`` requests the un-normalised softmax state instead
         (sequence-sharded decode).  ``out`` (not in the reference): a [B, H_Q, 1, D] tensor with
         contiguous rows to write into instead of a new one."""
-        if self.k_bits != 4 or self.v_bits != 4:
-            raise HyQuantError(f"K{self.k_bits}/V{self.v_bits} is not built (K4/V4 only)")
         B_, H_Q_, _, D_ = query_states.shape
         q2d = query_states.reshape(B_ * H_Q_, D_)
         plan = self._decode_plan(q2d, kv_repeat)

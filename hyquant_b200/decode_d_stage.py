@@ -34,12 +34,14 @@ SCALE_MODE = 0
 # ----------------------------------------------------------------------------
 
 def quantize_per_token_into(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor,
-                            dst_token_offset: int = 0, scale_mode: Optional[int] = None) -> None:
+                            dst_token_offset: int = 0, scale_mode: Optional[int] = None, nbits: int = 4) -> None:
     """Quantise ``x`` [BH, n, 128] and write codes/scales at token
-    ``dst_token_offset`` of the capacity buffers ``packed`` [BH, cap, 64] int8 and
+    ``dst_token_offset`` of the capacity buffers ``packed`` [BH, cap, 16 * nbits] int8 and
     ``scale`` [BH, cap] fp16 (in-place append; replaces the ``torch.cat`` growth of
     ``_flush_staging_buffer``, reference d_stage_kv_cache.py:209-217)."""
     _lib.require_cuda(x, "x")
+    if nbits not in (2, 4, 8):
+        raise ValueError(f"nbits must be 2, 4, or 8, got {nbits}")
     BH, n, D = x.shape
     if D != 128:
         raise HyQuantError(f"head_dim {D} is not built (128 only)")
@@ -47,32 +49,30 @@ def quantize_per_token_into(x: torch.Tensor, packed: torch.Tensor, scale: torch.
         x = x.contiguous()
     if packed.dtype != torch.int8 or scale.dtype != torch.float16:
         raise HyQuantError("packed must be int8 and scale fp16")
-    if packed.stride(2) != 1 or packed.stride(1) != 64 or scale.stride(1) != 1:
-        raise HyQuantError("capacity buffers must be row-contiguous ([BH, cap, 64] / [BH, cap])")
+    if packed.stride(2) != 1 or packed.stride(1) != 16 * nbits or scale.stride(1) != 1:
+        raise HyQuantError(f"capacity buffers must be row-contiguous ([BH, cap, {16 * nbits}] / [BH, cap])")
     if dst_token_offset + n > packed.shape[1] or dst_token_offset + n > scale.shape[1]:
         raise HyQuantError("append exceeds the capacity of the quantised prefix buffers")
-    rc = _lib.lib().hq_quant_pack_int4(
-        x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), BH, n,
+    rc = _lib.lib().hq_quant_pack(
+        x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), BH, n, nbits,
         packed.data_ptr(), packed.stride(0), scale.data_ptr(), scale.stride(0),
         dst_token_offset, SCALE_MODE if scale_mode is None else scale_mode, _lib.stream_ptr(x.device))
-    _lib.check(rc, "hq_quant_pack_int4")
+    _lib.check(rc, "hq_quant_pack")
 
 
 def quantize_per_token(x: torch.Tensor, nbits: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-token symmetric quantisation (reference decode_d_stage.py:50-77).
 
-    x [BH, N, D] bf16/fp16/fp32 -> (packed [BH, N, D//2] int8, scale [BH, N] fp16).
-    Bit-exact with the reference for nbits=4; 2 and 8 bits are not built.
+    x [BH, N, D] bf16/fp16/fp32 -> (packed [BH, N, D * nbits // 8] int8, scale [BH, N] fp16),
+    bit-exact with the reference for nbits 2, 4 and 8.
     """
     if nbits not in (2, 4, 8):
         raise ValueError(f"nbits must be 2, 4, or 8, got {nbits}")
-    if nbits != 4:
-        raise HyQuantError(f"{nbits}-bit quantisation is not built (K4/V4 only)")
     _lib.require_cuda(x, "x")
     BH, N, D = x.shape
-    packed = torch.empty(BH, N, D // 2, dtype=torch.int8, device=x.device)
+    packed = torch.empty(BH, N, D * nbits // 8, dtype=torch.int8, device=x.device)
     scale = torch.empty(BH, N, dtype=torch.float16, device=x.device)
-    quantize_per_token_into(x, packed, scale, 0)
+    quantize_per_token_into(x, packed, scale, 0, nbits=nbits)
     return packed, scale
 
 
@@ -87,12 +87,27 @@ def _unpack_int4(packed: torch.Tensor, D: int) -> torch.Tensor:
     return out
 
 
+def _unpack_int2(packed: torch.Tensor, D: int) -> torch.Tensor:
+    """[BH, N, D//4] int8 -> [BH, N, D] float32, sign-extended (reference :138-150)."""
+    x = packed.to(torch.int32) & 0xFF
+    out = torch.empty(packed.shape[0], packed.shape[1], D, device=packed.device, dtype=torch.float32)
+    for i in range(4):
+        out[..., i::4] = ((((x >> (2 * i)) & 0x03) << 30) >> 30).float()
+    return out
+
+
 def dequantize_per_token(packed: torch.Tensor, scale: torch.Tensor, D: int, nbits: int) -> torch.Tensor:
     """Inverse of :func:`quantize_per_token` -> fp16 (reference :80-101).  A debugging
-    utility built from torch ops; the decode kernel never materialises this."""
-    if nbits != 4:
-        raise HyQuantError(f"{nbits}-bit quantisation is not built (K4/V4 only)")
-    return (_unpack_int4(packed, D) * scale.float().unsqueeze(-1)).to(torch.float16)
+    utility built from torch ops; the decode kernels never materialise this."""
+    if nbits == 8:
+        q = packed.float()
+    elif nbits == 4:
+        q = _unpack_int4(packed, D)
+    elif nbits == 2:
+        q = _unpack_int2(packed, D)
+    else:
+        raise ValueError(f"nbits must be 2, 4, or 8, got {nbits}")
+    return (q * scale.float().unsqueeze(-1)).to(torch.float16)
 
 
 def _quantize_by_bits(x: torch.Tensor, bits: int):
@@ -147,7 +162,8 @@ class DecodePlan:
 
     def __init__(self, q, k_quant_packed, v_quant_packed, k_scale, v_scale,
                  k_topk, v_topk, k_staging, v_staging, k_window, v_window,
-                 kv_repeat: int, sm_scale: Optional[float], num_splits: int = 0, overlap_previous: bool = False):
+                 kv_repeat: int, sm_scale: Optional[float], num_splits: int = 0, overlap_previous: bool = False,
+                 k_bits: int = 4, v_bits: int = 4):
         """``overlap_previous``: launch with ``HQ_DECODE_OVERLAP_PREVIOUS`` — the kernel's blocks may
         start, and fetch cache units that are older than the newest 128 prefix tokens or lie in the
         vertical-line / window segments, while the kernel launched just before it on the stream is
@@ -168,12 +184,16 @@ class DecodePlan:
         a.BH_KV, a.kv_repeat, a.head_dim = self.BH_KV, kv_repeat, D
         a.sm_scale = float(D ** -0.5 if sm_scale is None else sm_scale)
         a.num_splits = num_splits
-        a.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS if overlap_previous else 0
+        if k_bits not in (2, 4, 8) or v_bits not in (2, 4, 8):
+            raise ValueError(f"bit widths must be 2, 4 or 8, got K{k_bits} V{v_bits}")
+        a.k_bits, a.v_bits = k_bits, v_bits
+        # the launch-overlap prologue belongs to the K4/V4 kernel
+        a.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS if (overlap_previous and k_bits == 4 and v_bits == 4) else 0
         keep = []
         n_quant = 0 if k_quant_packed is None else int(k_quant_packed.shape[1])
         a.n_quant = n_quant
         if n_quant > 0:
-            kp, vp = _seg(k_quant_packed, 64), _seg(v_quant_packed, 64)
+            kp, vp = _seg(k_quant_packed, 16 * k_bits), _seg(v_quant_packed, 16 * v_bits)
             ks = k_scale if k_scale.stride(1) == 1 else k_scale.contiguous()
             vs = v_scale if v_scale.stride(1) == 1 else v_scale.contiguous()
             if ks.dtype != torch.float16 or vs.dtype != torch.float16 or kp.dtype != torch.int8:
@@ -247,10 +267,9 @@ def fused_d_stage_decode(
     """Fused 4-segment decode: quantised prefix + topk + staging + window
     (reference decode_d_stage.py:916-1005).  Returns [BH_Q, D] in q's dtype.
     Inputs are borrowed and never mutated; zero-length segments are allowed."""
-    if k_bits != 4 or v_bits != 4:
-        raise HyQuantError(f"K{k_bits}/V{v_bits} is not built (K4/V4 only)")
     plan = DecodePlan(q, k_quant_packed, v_quant_packed, k_scale, v_scale,
-                      k_topk, v_topk, k_staging, v_staging, k_window, v_window, kv_repeat, sm_scale)
+                      k_topk, v_topk, k_staging, v_staging, k_window, v_window, kv_repeat, sm_scale,
+                      k_bits=k_bits, v_bits=v_bits)
     return plan.run(q)
 
 

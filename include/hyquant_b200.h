@@ -54,12 +54,20 @@ const char* hq_last_error(void);
  * of pre-allocated capacity buffers.
  *
  *   x        [BH, n, 128] in_dtype, row stride x_stride_n, head stride x_stride_bh (elements)
- *   packed   int8  [BH, cap, 64], head stride packed_stride_bh (bytes)
+ *   packed   int8  [BH, cap, 16 * nbits] (64 bytes per token at 4 bits), head stride packed_stride_bh (bytes)
  *   scale    fp16  [BH, cap],     head stride scale_stride_bh (elements)
  *   scale_mode 0: scale = half(max(|x|,1e-5) / 7)            (IEEE divide; CPU-eager PyTorch)
  *              1: scale = half(max(|x|,1e-5) * (1.0f/7.0f))  (CUDA-eager PyTorch)
- * Codes: q = clamp(rint(x / float(scale)), -8, 7); byte = (q[2i] & 15) | (q[2i+1] << 4).
+ * Codes at 4 bits: q = clamp(rint(x / float(scale)), -8, 7); byte = (q[2i] & 15) | (q[2i+1] << 4).
+ * hq_quant_pack takes the bit width (8, 4 or 2: q_max = 127, 7, 1 in place of 7; 8 bits one byte per channel,
+ * 2 bits four channels per byte, lowest bits first), reference quantize_per_token / _pack_int2
+ * (src/ops/decode_d_stage.py:50-77, 129-135).
  */
+int hq_quant_pack(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
+                  int BH, int n, int nbits, void* packed, int64_t packed_stride_bh,
+                  void* scale, int64_t scale_stride_bh,
+                  int64_t dst_token_offset, int scale_mode, void* stream);
+/* nbits = 4 */
 int hq_quant_pack_int4(const void* x, int in_dtype, int64_t x_stride_bh, int64_t x_stride_n,
                        int BH, int n,
                        void* packed, int64_t packed_stride_bh,
@@ -109,9 +117,11 @@ typedef struct hq_decode_args {
   int32_t num_splits;          /* 0 = choose automatically */
   float   sm_scale;            /* softmax scale, e.g. head_dim^-0.5 */
   int32_t flags;               /* 0, or HQ_DECODE_OVERLAP_PREVIOUS */
+  int32_t k_bits;              /* bit width of the quantised K prefix: 8, 4 or 2 (0 = 4) */
+  int32_t v_bits;              /* the same for V.  K4/V4 runs the tensor-core kernel, every other pair a plain one */
   const void* q;               /* bf16 [BH_KV*kv_repeat, 128] */
   int64_t q_stride;            /* elements between query rows */
-  const void* k_packed;        /* int8 [BH_KV, n_quant, 64] */
+  const void* k_packed;        /* int8 [BH_KV, n_quant, 16 * k_bits] (4 bits: 64 bytes per token) */
   const void* v_packed;
   int64_t kp_stride_bh;        /* BYTES between heads */
   int64_t vp_stride_bh;
@@ -168,6 +178,9 @@ int hq_lse_merge(const float* m, const float* l, const float* acc, int G, int ro
  * message per shard (m | l | acc back to back, all-gathered into [G][rows * 130]). */
 int hq_lse_merge_strided(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
                          int64_t acc_stride, int G, int rows, void* out, int out_dtype, int64_t out_stride, void* stream);
+/* The merged state left un-normalised: out_m, out_l fp32 [rows], out_acc fp32 [rows, 128] (a further merge can follow). */
+int hq_lse_merge_partial(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
+                         int64_t acc_stride, int G, int rows, float* out_m, float* out_l, float* out_acc, void* stream);
 
 /* --------------------------------------------------------------------------
  * Vertical-line scores: mean of the last `tail_len` queries, dotted with every
@@ -214,6 +227,14 @@ int hq_cache_reorganize(const void* keys, const void* values, int64_t kv_stride_
                         void* k_packed, void* v_packed, int64_t packed_stride_bh,
                         void* k_scale, void* v_scale, int64_t scale_stride_bh,
                         int scale_mode, void* stream);
+/* The same with a bit width per tensor (8, 4 or 2) and a head stride per packed tensor. */
+int hq_cache_reorganize_bits(const void* keys, const void* values, int64_t kv_stride_bh,
+                             int BH, int N, int window, int T,
+                             const int64_t* vidx_desc, const int32_t* vidx_asc,
+                             void* k_topk, void* v_topk, void* k_window, void* v_window,
+                             void* k_packed, void* v_packed, int64_t kp_stride_bh, int64_t vp_stride_bh,
+                             void* k_scale, void* v_scale, int64_t scale_stride_bh,
+                             int k_bits, int v_bits, int scale_mode, void* stream);
 
 /* --------------------------------------------------------------------------
  * Hybrid prefill, step 1: operand preparation.  Replaces per_block_int8 and the

@@ -74,12 +74,12 @@ def golden_quant():
 
 
 def run_cache_case(name, B, H_Q, H_KV, N, W, rho, seed, dtype, n_append, probe_steps,
-                   n_qry=None):
+                   n_qry=None, k_bits=4, v_bits=4):
     """freeze -> appends (with flushes) -> decode_attention through the reference."""
     case = gen_numpy(B, H_Q, H_KV, N, 128, W, rho, seed, n_qry=n_qry)
     R = H_Q // H_KV
     tt = lambda a: torch.from_numpy(a).to(dtype)
-    lc = DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=rho, use_vert=True)
+    lc = DStageLayerCache(0, k_bits=k_bits, v_bits=v_bits, window_size=W, top_ratio=rho, use_vert=True)
     lc.update_prefill(tt(case.k), tt(case.v))
     lc.save_query_tail(tt(case.q))
     # the indices freeze() will select (same calls as d_stage_kv_cache.py:131-136)
@@ -93,6 +93,7 @@ def run_cache_case(name, B, H_Q, H_KV, N, W, rho, seed, dtype, n_append, probe_s
     out = {
         "meta": np.array([B, H_Q, H_KV, N, W, seed, n_append, -1 if n_qry is None else n_qry], dtype=np.int64),
         "rho": np.array([rho]), "is_bf16": np.array([dtype == torch.bfloat16]),
+        "bits": np.array([k_bits, v_bits], dtype=np.int64),
         "in_sha": np.array([sha(case.q), sha(case.k), sha(case.v), sha(case.q_decode)]),
         "frozen_k_packed_sha": np.array([sha(lc.k_quant_packed.numpy())]),
         "frozen_v_packed_sha": np.array([sha(lc.v_quant_packed.numpy())]),
@@ -148,9 +149,20 @@ def golden_reorder():
          n_rest_valid=nr.numpy(), n_vert_valid=nv.numpy(), RV=np.array([R, V]))
 
 
+def golden_bit_widths():
+    """The cache life cycle at the other bit widths of the reference's modes (d_k8v8, d_k4v2, d_k2v4)."""
+    for kb, vb in ((8, 8), (4, 2), (2, 4)):
+        run_cache_case(f"cache_k{kb}v{vb}_f32", 1, 4, 2, 400, 64, 0.05, 40 + kb + vb, torch.float32, 130, [1, 128, 130],
+                       k_bits=kb, v_bits=vb)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if len(sys.argv) > 1 and sys.argv[1] == "--bit-widths-only":
+        golden_bit_widths()
+        sys.exit(0)
+    golden_bit_widths()
     golden_quant()
     # BASELINE config 0: B=1, 32q/8kv, N=1024, W=128, rho=5%, staging 64, fp32
     run_cache_case("cache_cfg0_f32", 1, 32, 8, 1024, 128, 0.05, 0, torch.float32, 64, [1, 64])

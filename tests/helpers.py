@@ -32,6 +32,7 @@ class CacheCase:
         self.R = H_Q // H_KV
         self.rho = float(g["rho"][0])
         self.is_bf16 = bool(g["is_bf16"][0])
+        self.k_bits, self.v_bits = ([int(x) for x in g["bits"]] if "bits" in g.files else [4, 4])
         case = gen_numpy(B, H_Q, H_KV, N, 128, W, self.rho, seed, n_qry=None if n_qry < 0 else n_qry)
         assert [sha(case.q), sha(case.k), sha(case.v), sha(case.q_decode)] == list(g["in_sha"]), \
             "seeded inputs differ from the ones the fixture was generated with"
@@ -51,7 +52,7 @@ class CacheCase:
         """bf16 fixtures take the reference's selection as given (bf16 scores tie)."""
         own = (not self.is_bf16) if own_selection is None else own_selection
         return orc.freeze(self.k, self.v, self.query_tail, self.R, self.W, self.rho,
-                          round_fn=self.round_fn,
+                          k_bits=self.k_bits, v_bits=self.v_bits, round_fn=self.round_fn,
                           vidx_override=None if own else self.g["frozen_vidx"])
 
 

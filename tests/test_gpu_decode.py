@@ -31,30 +31,35 @@ def to_np(t):
 
 # ---------------------------------------------------------------- quantiser
 
-def test_quantize_matches_reference_fixture_bit_exact():
+@pytest.mark.parametrize("nbits", [2, 4, 8])
+def test_quantize_matches_reference_fixture_bit_exact(nbits):
     g = load("quant_per_token")
     x = orc.bf16_bits_to_f32(g["x_bf16_bits"])
-    p, s = hq.quantize_per_token(t_bf16(x), 4)
-    assert np.array_equal(p.cpu().numpy(), g["bf16_packed4"])
-    assert np.array_equal(s.cpu().numpy().view(np.uint16), g["bf16_scale4"].view(np.uint16))
-    p32, s32 = hq.quantize_per_token(torch.from_numpy(g["x_f32"]).to(DEV), 4)
-    assert np.array_equal(p32.cpu().numpy(), g["f32_packed4"])
-    assert np.array_equal(s32.cpu().numpy().view(np.uint16), g["f32_scale4"].view(np.uint16))
+    p, s = hq.quantize_per_token(t_bf16(x), nbits)
+    assert np.array_equal(p.cpu().numpy(), g[f"bf16_packed{nbits}"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), g[f"bf16_scale{nbits}"].view(np.uint16))
+    p32, s32 = hq.quantize_per_token(torch.from_numpy(g["x_f32"]).to(DEV), nbits)
+    assert np.array_equal(p32.cpu().numpy(), g[f"f32_packed{nbits}"])
+    assert np.array_equal(s32.cpu().numpy().view(np.uint16), g[f"f32_scale{nbits}"].view(np.uint16))
+    deq = hq.dequantize_per_token(p, s, 128, nbits)
+    # a row whose scale overflows fp16 dequantises to 0 * inf = NaN on both sides (the NaN's sign bit is free)
+    assert np.array_equal(deq.cpu().numpy(), g[f"bf16_deq{nbits}"], equal_nan=True)
 
 
+@pytest.mark.parametrize("nbits", [2, 4, 8])
 @pytest.mark.parametrize("shape", [(1, 1, 128), (8, 128, 128), (3, 1000, 128), (128, 128, 128)])
-def test_quantize_matches_oracle_bit_exact(shape):
+def test_quantize_matches_oracle_bit_exact(shape, nbits):
     rng = np.random.Generator(np.random.PCG64(shape[1]))
     x = orc.bf16_round(rng.standard_normal(shape, dtype=np.float32) * rng.uniform(0.01, 30, shape[:2] + (1,)).astype(np.float32))
-    p, s = hq.quantize_per_token(t_bf16(x), 4)
-    po, so = orc.quantize_per_token(x, 4)
+    p, s = hq.quantize_per_token(t_bf16(x), nbits)
+    po, so = orc.quantize_per_token(x, nbits)
     assert np.array_equal(p.cpu().numpy(), po)
     assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
     # CUDA-eager scale rounding mode
     BH, n, _ = shape
-    pk = torch.empty(BH, n, 64, dtype=torch.int8, device=DEV); sc = torch.empty(BH, n, dtype=torch.float16, device=DEV)
-    dd.quantize_per_token_into(t_bf16(x), pk, sc, 0, scale_mode=1)
-    po1, so1 = orc.quantize_per_token(x, 4, reciprocal_scale=True)
+    pk = torch.empty(BH, n, 16 * nbits, dtype=torch.int8, device=DEV); sc = torch.empty(BH, n, dtype=torch.float16, device=DEV)
+    dd.quantize_per_token_into(t_bf16(x), pk, sc, 0, scale_mode=1, nbits=nbits)
+    po1, so1 = orc.quantize_per_token(x, nbits, reciprocal_scale=True)
     assert np.array_equal(pk.cpu().numpy(), po1) and np.array_equal(sc.cpu().numpy().view(np.uint16), so1.view(np.uint16))
 
 
@@ -76,7 +81,7 @@ def test_quantize_empty_and_append_offset():
 
 # ---------------------------------------------------------- decode attention
 
-def build_case(BH_KV, R, n_quant, n_topk, n_staging, n_window, seed):
+def build_case(BH_KV, R, n_quant, n_topk, n_staging, n_window, seed, k_bits=4, v_bits=4):
     """Random four-segment cache (numpy, bf16-exact) + query; oracle LayerCache."""
     rng = np.random.Generator(np.random.PCG64(seed))
     D = 128
@@ -84,9 +89,9 @@ def build_case(BH_KV, R, n_quant, n_topk, n_staging, n_window, seed):
         a = rng.standard_normal((BH_KV, n, D), dtype=np.float32) * scale
         a[..., 5] += 4.0
         return orc.bf16_round(a)
-    kq, ks = orc.quantize_per_token(rnd(n_quant), 4)
-    vq, vs = orc.quantize_per_token(rnd(n_quant), 4)
-    c = orc.LayerCache(B=1, H_KV=BH_KV, D=D, k_bits=4, v_bits=4, k_quant_packed=kq, v_quant_packed=vq,
+    kq, ks = orc.quantize_per_token(rnd(n_quant), k_bits)
+    vq, vs = orc.quantize_per_token(rnd(n_quant), v_bits)
+    c = orc.LayerCache(B=1, H_KV=BH_KV, D=D, k_bits=k_bits, v_bits=v_bits, k_quant_packed=kq, v_quant_packed=vq,
                        k_scale=ks, v_scale=vs, k_topk=rnd(n_topk), v_topk=rnd(n_topk),
                        k_window=rnd(n_window), v_window=rnd(n_window),
                        staging_k=rnd(128), staging_v=rnd(128), staging_ptr=n_staging)
@@ -101,11 +106,11 @@ def run_gpu(c, q, R, **kw):
             t_bf16(c.k_topk), t_bf16(c.v_topk), t_bf16(c.staging_k)[:, :S], t_bf16(c.staging_v)[:, :S],
             t_bf16(c.k_window), t_bf16(c.v_window))
     if kw:
-        plan = dd.DecodePlan(*args, R, None, **kw)
+        plan = dd.DecodePlan(*args, R, None, k_bits=c.k_bits, v_bits=c.v_bits, **kw)
         out = plan.run(args[0])
         ws = plan.ws
     else:
-        out = hq.fused_d_stage_decode(*args, 4, 4, kv_repeat=R)
+        out = hq.fused_d_stage_decode(*args, c.k_bits, c.v_bits, kv_repeat=R)
         ws = dd.decode_workspace(torch.device(DEV, torch.cuda.current_device()), c.H_KV, R)
     torch.cuda.synchronize()
     assert dd.decode_status(ws) == 0
@@ -124,6 +129,33 @@ def test_decode_edge_lengths(n_quant, n_staging):
     c, q = build_case(2, 4, n_quant, 3 if n_quant else 0, n_staging, 128, seed=n_quant * 131 + n_staging)
     ref = orc.decode_attention_exact(q, c, 4).reshape(-1, 128)
     check_close(run_gpu(c, q, 4), ref)
+
+
+@pytest.mark.parametrize("bits", [(8, 8), (4, 2), (2, 4), (8, 4), (2, 2), (4, 8)])
+@pytest.mark.parametrize("R,lens", [(4, (700, 37, 5, 64)), (1, (33, 0, 0, 1)), (8, (0, 9, 127, 128)), (16, (4113, 300, 1, 128)),
+                                    (7, (1, 0, 0, 0))])
+def test_decode_other_bit_widths(bits, R, lens):
+    """The plain kernel behind every (k_bits, v_bits) pair other than 4/4: all segment combinations, GQA ratios
+    up to 16, split invariance and the un-normalised partial mode."""
+    kb, vb = bits
+    nq, nt, ns, nw = lens
+    c, q = build_case(3, R, nq, nt, ns, nw, seed=kb * 100 + vb * 10 + R, k_bits=kb, v_bits=vb)
+    ref = orc.decode_attention_exact(q, c, R).reshape(-1, 128)
+    out = run_gpu(c, q, R)
+    check_close(out, ref)
+    one = run_gpu(c, q, R, num_splits=1)
+    check_close(one, ref)
+    assert max_abs(out, one) < 2e-3
+    # partial mode: (m, l, acc) of the whole cache, normalised on the host
+    ti8 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    S = c.staging_ptr
+    plan = dd.DecodePlan(t_bf16(q.reshape(-1, 128)), ti8(c.k_quant_packed), ti8(c.v_quant_packed), ti8(c.k_scale), ti8(c.v_scale),
+                         t_bf16(c.k_topk), t_bf16(c.v_topk), t_bf16(c.staging_k)[:, :S], t_bf16(c.staging_v)[:, :S],
+                         t_bf16(c.k_window), t_bf16(c.v_window), R, None, k_bits=kb, v_bits=vb)
+    rows = 3 * R
+    m = torch.empty(rows, device=DEV); l = torch.empty(rows, device=DEV); acc = torch.empty(rows, 128, device=DEV)
+    plan.run(t_bf16(q.reshape(-1, 128)), partial=(m, l, acc))
+    check_close((acc / l[:, None]).cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("R", [1, 2, 4, 7, 8, 16])
@@ -189,7 +221,8 @@ def test_decode_strided_inputs_and_out_dtypes():
         check_close(to_np(out), ref)
 
 
-@pytest.mark.parametrize("name", ["cache_cfg0_f32", "cache_small_bf16", "cache_tiny_f32", "cache_short_f32"])
+@pytest.mark.parametrize("name", ["cache_cfg0_f32", "cache_small_bf16", "cache_tiny_f32", "cache_short_f32",
+                                  "cache_k8v8_f32", "cache_k4v2_f32", "cache_k2v4_f32"])
 def test_cache_lifecycle_against_reference_fixture(name):
     """prefill -> freeze -> appends with flushes -> decode through the reference-named
     cache class.  bf16 fixtures: compared with the reference's outputs directly (its
@@ -199,7 +232,7 @@ def test_cache_lifecycle_against_reference_fixture(name):
     g = cc.g
     rb = orc.bf16_round
     k, v, qt = rb(cc.k), rb(cc.v), rb(cc.query_tail)
-    cache = hq.DStageKVCache(num_layers=1, k_bits=4, v_bits_fn=lambda i: 4, window_size=cc.W, top_ratio=cc.rho)
+    cache = hq.DStageKVCache(num_layers=1, k_bits=cc.k_bits, v_bits_fn=lambda i: cc.v_bits, window_size=cc.W, top_ratio=cc.rho)
     layer = cache.get_layer(0)
     cache.update(t_bf16(k), t_bf16(v), 0)
     layer.save_query_tail(t_bf16(cc.q))
@@ -212,7 +245,7 @@ def test_cache_lifecycle_against_reference_fixture(name):
         assert sha(to_np(layer.k_topk)) == g["frozen_k_topk_sha"][0]
     else:
         layer.freeze(kv_repeat=cc.R)
-        own = orc.freeze(k, v, qt, cc.R, cc.W, cc.rho, round_fn=rb)
+        own = orc.freeze(k, v, qt, cc.R, cc.W, cc.rho, k_bits=cc.k_bits, v_bits=cc.v_bits, round_fn=rb)
         gv = None if layer.vertical_indices is None else layer.vertical_indices.cpu().numpy()
         if own.vidx is not None and own.vidx.shape[-1] > 0:
             # the device scores differ from the oracle's in the last bits, which may swap
@@ -220,7 +253,7 @@ def test_cache_lifecycle_against_reference_fixture(name):
             # the oracle so that everything downstream is compared bit-exactly
             for a, b in zip(gv.reshape(-1, gv.shape[-1]), own.vidx.reshape(-1, gv.shape[-1])):
                 assert len(set(a.tolist()) & set(b.tolist())) >= 0.98 * len(a) - 1
-        oc = orc.freeze(k, v, qt, cc.R, cc.W, cc.rho, round_fn=rb, vidx_override=gv)
+        oc = orc.freeze(k, v, qt, cc.R, cc.W, cc.rho, k_bits=cc.k_bits, v_bits=cc.v_bits, round_fn=rb, vidx_override=gv)
         assert np.array_equal(layer.k_quant_packed.cpu().numpy(), oc.k_quant_packed)
         assert np.array_equal(layer.v_quant_packed.cpu().numpy(), oc.v_quant_packed)
         assert np.array_equal(layer.k_scale.cpu().numpy().view(np.uint16), oc.k_scale.view(np.uint16))
@@ -268,7 +301,7 @@ def test_cache_growth_beyond_initial_capacity():
 
 
 def test_unsupported_configurations_fail_loudly(monkeypatch):
-    layer = hq.DStageLayerCache(0, k_bits=8, v_bits=8, window_size=64)
+    layer = hq.DStageLayerCache(0, k_bits=3, v_bits=8, window_size=64)       # widths are 2, 4 or 8
     layer.update_prefill(torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device=DEV),
                          torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(hq.HyQuantError):

@@ -51,6 +51,8 @@ CASES = [
     ("llama", "d_k4v4_vert", 2e-2),
     ("llama", "d_k4v4", 2e-2),
     ("qwen", "hybrid_full", 2e-2),
+    ("llama", "d_k8v8", 1e-3),          # INT8 cache: close to the 16-bit result
+    ("llama", "hybrid_k4v2", 0.5),      # 2-bit V: plumbing check, the mode is lossy by design
     ("llama", "sage_w", 3e-4),
     ("llama", "sage_w0", 3e-4),
     ("llama", "vquant_vert", 3e-4),

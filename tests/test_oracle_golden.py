@@ -27,7 +27,8 @@ def test_pack_unpack_roundtrip():
     assert np.array_equal(orc.unpack_int2(orc.pack_int2(q2)), q2.astype(np.float32))
 
 
-@pytest.mark.parametrize("name", ["cache_cfg0_f32", "cache_small_bf16", "cache_tiny_f32", "cache_short_f32"])
+@pytest.mark.parametrize("name", ["cache_cfg0_f32", "cache_small_bf16", "cache_tiny_f32", "cache_short_f32",
+                                  "cache_k8v8_f32", "cache_k4v2_f32", "cache_k2v4_f32"])
 def test_freeze_append_decode(name):
     cc = CacheCase(name)
     g = cc.g
