@@ -43,7 +43,7 @@ __device__ __forceinline__ int code_at(uint32_t w, int i) {
 template <int BITS, int RMAX>
 __device__ __forceinline__ void k_dot_quant(const uint8_t* row, const float* qs, int R, float (&s)[RMAX]) {
   constexpr int kWords = 4 * BITS;                 // 32-bit words per row
-  constexpr int kPerWord = 32 / BITS;              // codes per word
+  constexpr int kPerWord = 32 / BITS;              // codes per word: 4, 8 or 16 consecutive channels
 #pragma unroll
   for (int w4 = 0; w4 < kWords / 4; ++w4) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(row) + w4);
@@ -51,12 +51,17 @@ __device__ __forceinline__ void k_dot_quant(const uint8_t* row, const float* qs,
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
 #pragma unroll
-      for (int i = 0; i < kPerWord; ++i) {
-        const int c = (w4 * 4 + wi) * kPerWord + i;
-        const float x = (float)code_at<BITS>(ws[wi], i);
+      for (int i4 = 0; i4 < kPerWord / 4; ++i4) {
+        const int c = (w4 * 4 + wi) * kPerWord + 4 * i4;       // 4 channels, one 16-byte read of each query row
+        const float x0 = (float)code_at<BITS>(ws[wi], 4 * i4), x1 = (float)code_at<BITS>(ws[wi], 4 * i4 + 1);
+        const float x2 = (float)code_at<BITS>(ws[wi], 4 * i4 + 2), x3 = (float)code_at<BITS>(ws[wi], 4 * i4 + 3);
 #pragma unroll
-        for (int h = 0; h < RMAX; ++h)
-          if (h < R) s[h] = fmaf(x, qs[h * 128 + c], s[h]);
+        for (int h = 0; h < RMAX; ++h) {
+          if (h < R) {
+            const float4 qv = *reinterpret_cast<const float4*>(qs + h * 128 + c);
+            s[h] = fmaf(x3, qv.w, fmaf(x2, qv.z, fmaf(x1, qv.y, fmaf(x0, qv.x, s[h]))));
+          }
+        }
       }
     }
   }
@@ -67,14 +72,17 @@ __device__ __forceinline__ void k_dot_bf16(const __nv_bfloat16* row, const float
 #pragma unroll 4
   for (int w4 = 0; w4 < 16; ++w4) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(row) + w4);
-    const uint32_t ws[4] = {u.x, u.y, u.z, u.w};
+    const float x[8] = {__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                        __uint_as_float(u.y & 0xFFFF0000u), __uint_as_float(u.z << 16), __uint_as_float(u.z & 0xFFFF0000u),
+                        __uint_as_float(u.w << 16), __uint_as_float(u.w & 0xFFFF0000u)};
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      const float x0 = __uint_as_float(ws[wi] << 16), x1 = __uint_as_float(ws[wi] & 0xFFFF0000u);
-      const int c = (w4 * 4 + wi) * 2;
-#pragma unroll
-      for (int h = 0; h < RMAX; ++h)
-        if (h < R) s[h] = fmaf(x1, qs[h * 128 + c + 1], fmaf(x0, qs[h * 128 + c], s[h]));
+    for (int h = 0; h < RMAX; ++h) {
+      if (h < R) {
+        const float4 qa = *reinterpret_cast<const float4*>(qs + h * 128 + 8 * w4);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + h * 128 + 8 * w4 + 4);
+        s[h] = fmaf(x[3], qa.w, fmaf(x[2], qa.z, fmaf(x[1], qa.y, fmaf(x[0], qa.x, s[h]))));
+        s[h] = fmaf(x[7], qb.w, fmaf(x[6], qb.z, fmaf(x[5], qb.y, fmaf(x[4], qb.x, s[h]))));
+      }
     }
   }
 }
@@ -93,7 +101,7 @@ __device__ __forceinline__ void v_load_quant(const uint8_t* row, int lane, float
 template <int KB, int VB, int RMAX>
 __global__ void __launch_bounds__(kGWarps * 32)
 decode_generic_kernel(const GenericParams p) {
-  __shared__ float qs[RMAX * 128];
+  __shared__ __align__(16) float qs[RMAX * 128];
   __shared__ float mrg_m[kGWarps][RMAX], mrg_l[kGWarps][RMAX];
   extern __shared__ float mrg_acc[];             // [kGWarps][R][128]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -153,8 +161,7 @@ decode_generic_kernel(const GenericParams p) {
       pr[h] *= vscale;                                                     // the token's V scale rides in P
     }
     // ---- P V: this lane owns channels 4 lane .. 4 lane + 3
-    for (int j = 0; j < ntok; ++j) {
-      float v[4];
+    auto load_v = [&](int j, float (&v)[4]) {
       if (seg == 0) {
         v_load_quant<VB>(p.v_packed + head * p.vp_stride_bh + (int64_t)(tok0 + j) * (16 * VB), lane, v);
       } else {
@@ -163,12 +170,24 @@ decode_generic_kernel(const GenericParams p) {
         v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xFFFF0000u);
         v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xFFFF0000u);
       }
+    };
+    constexpr int kJB = 8;                         // tokens in flight: their loads and shuffles overlap
+    for (int j0 = 0; j0 < ntok; j0 += kJB) {
+      float v[kJB][4];
+#pragma unroll
+      for (int jj = 0; jj < kJB; ++jj) {
+        if (j0 + jj < ntok) load_v(j0 + jj, v[jj]);
+        else v[jj][0] = v[jj][1] = v[jj][2] = v[jj][3] = 0.f;
+      }
 #pragma unroll
       for (int h = 0; h < RMAX; ++h) {
         if (h < R) {
-          const float pj = __shfl_sync(0xffffffffu, pr[h], j);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[h][c] = fmaf(pj, v[c], acc[h][c]);
+          for (int jj = 0; jj < kJB; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, pr[h], (j0 + jj) & 31);     // 0 for tokens past ntok
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[h][c] = fmaf(pj, v[jj][c], acc[h][c]);
+          }
         }
       }
     }
