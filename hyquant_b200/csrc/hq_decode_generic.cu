@@ -10,8 +10,8 @@
 // contiguous range of one head's chunks, its 8 warps take them round-robin.  Per chunk: lane = token for the
 // scores (each lane reads its token's K row with 16-byte loads and dots it with the group's query rows,
 // which sit in shared memory as fp32), one online-softmax step in base 2 for the 32 tokens, then lane =
-// 4 channels for P V (every lane reads its 4 channels of each token's V row, the token's probabilities come
-// by shuffle).  Warps and then CTAs merge through the log-sum-exp rule; the splits of a head are merged
+// 4 channels for P V (every lane reads its 4 channels of each token's V row — all of a chunk's V loads are issued
+// before the score phase so that they are in flight during it — and the token's probabilities come by shuffle).  Warps and then CTAs merge through the log-sum-exp rule; the splits of a head are merged
 // by a second, tiny kernel (lse_merge_kernel of hq_reorg.cu).
 #include "hq_common.cuh"
 
@@ -87,17 +87,6 @@ __device__ __forceinline__ void k_dot_bf16(const __nv_bfloat16* row, const float
   }
 }
 
-// this lane's 4 channels (4 lane .. 4 lane + 3) of a quantised V row
-template <int BITS>
-__device__ __forceinline__ void v_load_quant(const uint8_t* row, int lane, float (&v)[4]) {
-  uint32_t w;
-  if (BITS == 8) w = __ldg(reinterpret_cast<const uint32_t*>(row) + lane);
-  else if (BITS == 4) w = __ldg(reinterpret_cast<const uint16_t*>(row) + lane);
-  else w = __ldg(row + lane);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = (float)code_at<BITS>(w, i);
-}
-
 template <int KB, int VB, int RMAX>
 __global__ void __launch_bounds__(kGWarps * 32)
 decode_generic_kernel(const GenericParams p) {
@@ -125,6 +114,32 @@ decode_generic_kernel(const GenericParams p) {
     const int tok0 = cc * 32, ntok = min(32, p.nseg[seg] - tok0);
     const int tok = tok0 + lane;
     const bool ok = lane < ntok;
+    // ---- the chunk's V words first (this lane's 4 channels of every token, coalesced rows): all of them are in
+    // flight while the scores are computed.  BF16 rows are 8 bytes per lane and token and come in two halves.
+    uint32_t vw[32];
+    const uint8_t* vrow0 = nullptr;
+    const uint2* vrow2 = nullptr;
+    if (seg == 0) {
+      vrow0 = p.v_packed + head * p.vp_stride_bh + (int64_t)tok0 * (16 * VB);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        vw[j] = 0u;
+        if (j < ntok) {
+          const uint8_t* row = vrow0 + (int64_t)j * (16 * VB);
+          if (VB == 8) vw[j] = __ldg(reinterpret_cast<const uint32_t*>(row) + lane);
+          else if (VB == 4) vw[j] = __ldg(reinterpret_cast<const uint16_t*>(row) + lane);
+          else vw[j] = __ldg(row + lane);
+        }
+      }
+    } else {
+      vrow2 = reinterpret_cast<const uint2*>(p.vseg[seg - 1] + head * p.vseg_stride[seg - 1] + (int64_t)tok0 * 128) + lane;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        uint2 u = make_uint2(0u, 0u);
+        if (j < ntok) u = __ldg(vrow2 + j * 32);
+        vw[2 * j] = u.x; vw[2 * j + 1] = u.y;
+      }
+    }
     // ---- scores of this lane's token against the group's heads
     float s[RMAX];
 #pragma unroll
@@ -161,32 +176,44 @@ decode_generic_kernel(const GenericParams p) {
       pr[h] *= vscale;                                                     // the token's V scale rides in P
     }
     // ---- P V: this lane owns channels 4 lane .. 4 lane + 3
-    auto load_v = [&](int j, float (&v)[4]) {
-      if (seg == 0) {
-        v_load_quant<VB>(p.v_packed + head * p.vp_stride_bh + (int64_t)(tok0 + j) * (16 * VB), lane, v);
-      } else {
-        const uint2 u = __ldg(reinterpret_cast<const uint2*>(p.vseg[seg - 1] + head * p.vseg_stride[seg - 1] +
-                                                              (int64_t)(tok0 + j) * 128) + lane);
-        v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xFFFF0000u);
-        v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xFFFF0000u);
+    if (seg == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (float)code_at<VB>(vw[j], i);
+#pragma unroll
+        for (int h = 0; h < RMAX; ++h) {
+          if (h < R) {
+            const float pj = __shfl_sync(0xffffffffu, pr[h], j);       // 0 for tokens past ntok
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[h][c] = fmaf(pj, v[c], acc[h][c]);
+          }
+        }
       }
-    };
-    constexpr int kJB = 8;                         // tokens in flight: their loads and shuffles overlap
-    for (int j0 = 0; j0 < ntok; j0 += kJB) {
-      float v[kJB][4];
+    } else {
 #pragma unroll
-      for (int jj = 0; jj < kJB; ++jj) {
-        if (j0 + jj < ntok) load_v(j0 + jj, v[jj]);
-        else v[jj][0] = v[jj][1] = v[jj][2] = v[jj][3] = 0.f;
-      }
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1) {
+          if (ntok <= 16) break;
 #pragma unroll
-      for (int h = 0; h < RMAX; ++h) {
-        if (h < R) {
+          for (int j = 0; j < 16; ++j) {
+            uint2 u = make_uint2(0u, 0u);
+            if (16 + j < ntok) u = __ldg(vrow2 + (16 + j) * 32);
+            vw[2 * j] = u.x; vw[2 * j + 1] = u.y;
+          }
+        }
 #pragma unroll
-          for (int jj = 0; jj < kJB; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, pr[h], (j0 + jj) & 31);     // 0 for tokens past ntok
+        for (int j = 0; j < 16; ++j) {
+          const float v[4] = {__uint_as_float(vw[2 * j] << 16), __uint_as_float(vw[2 * j] & 0xFFFF0000u),
+                              __uint_as_float(vw[2 * j + 1] << 16), __uint_as_float(vw[2 * j + 1] & 0xFFFF0000u)};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[h][c] = fmaf(pj, v[jj][c], acc[h][c]);
+          for (int h = 0; h < RMAX; ++h) {
+            if (h < R) {
+              const float pj = __shfl_sync(0xffffffffu, pr[h], 16 * half + j);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[h][c] = fmaf(pj, v[c], acc[h][c]);
+            }
           }
         }
       }
@@ -281,8 +308,9 @@ int decode_generic_launch(const hq_decode_args* a, int k_bits, int v_bits, float
   p.R = a->kv_repeat;
   p.sml = a->sm_scale * 1.44269504f;
   p.rows = (int64_t)a->BH_KV * a->kv_repeat;
-  // splits: about two CTAs per SM in all, at least one chunk per warp, and the partials must fit the workspace
-  int nsplit = a->num_splits > 0 ? a->num_splits : (2 * sm_count()) / a->BH_KV;
+  // splits: about four CTAs per SM in all (the kernel hides its load latency with resident warps, not with a
+  // prefetch ring), at least one chunk per warp, and the partials must fit the workspace
+  int nsplit = a->num_splits > 0 ? a->num_splits : (4 * sm_count()) / a->BH_KV;
   const int by_work = (p.chunks + kGWarps - 1) / kGWarps;
   if (nsplit > by_work) nsplit = by_work;
   const int64_t by_ws = ws_floats / (p.rows * 130);
