@@ -28,32 +28,10 @@ __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
   v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
 }
 
-// All 32 lanes call this with their 4 channels of one 128-channel token.
-// Returns the fp16 scale (same on every lane) and this lane's 4 codes packed
-// into 16 bits (channels 4l,4l+1 in the low byte, 4l+2,4l+3 in the high byte).
-__device__ __forceinline__ __half quant_row_int4(const float (&v)[4], int scale_mode, uint16_t& code) {
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  amax = fmaxf(amax, 1e-5f);
-  const float s32 = scale_mode == 0 ? __fdiv_rn(amax, 7.0f) : __fmul_rn(amax, __fdiv_rn(1.0f, 7.0f));
-  const __half sh = __float2half_rn(s32);
-  const float sf = __half2float(sh);
-  uint32_t c = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float q = rintf(__fdiv_rn(v[i], sf));
-    q = fminf(fmaxf(q, -8.0f), 7.0f);
-    // NaN (0/0 cannot happen: sf >= half(1e-5/7) > 0; inf/inf gives NaN) -> int conversion yields 0
-    c |= ((uint32_t)(__float2int_rn(q)) & 0xFu) << (4 * i);
-  }
-  code = (uint16_t)c;
-  return sh;
-}
-
-// The same for 8, 4 or 2 bits: the lane's 4 codes come back as 4 bytes (BITS = 8), as 16 bits (4) or as
-// one byte (2), in the low bits of `code`; a token row is 16 * BITS bytes and lane l owns bytes
-// [l * BITS / 2, (l + 1) * BITS / 2).
+// All 32 lanes call this with their 4 channels of one 128-channel token.  Returns the fp16 scale (same on
+// every lane) and this lane's 4 codes in the low bits of `code`: 4 bytes (BITS = 8), 16 bits (4) or one byte (2);
+// a token row is 16 * BITS bytes and lane l owns bytes [l * BITS / 2, (l + 1) * BITS / 2).
+// NaN inputs: 0/0 cannot happen (the scale is >= half(1e-5 / q_max) > 0); inf / inf gives NaN, which converts to code 0.
 template <int BITS>
 __device__ __forceinline__ __half quant_row_bits(const float (&v)[4], int scale_mode, uint32_t& code) {
   constexpr float qmax = (float)((1 << (BITS - 1)) - 1), qmin = -(float)(1 << (BITS - 1));
