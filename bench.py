@@ -223,8 +223,7 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
     def one_step(s):
         xdev.copy_(hin[s], non_blocking=True)
         for li, layer in enumerate(layers):
-            layer.append_staging(kv[li], vv[li])
-            layer.decode_attention(qv[li], r, out=ov[li])
+            layer.decode_step(qv[li], kv[li], vv[li], r, out=ov[li])      # append + attention, one launch
         hout.copy_(odev, non_blocking=True)
         torch.cuda.synchronize()      # the step's result is on the host
 
@@ -533,7 +532,7 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "path": "per step one pinned host message (q/k/v of every layer) to the device, DStageLayerCache.append_staging + decode_attention per layer, one message with every layer's output back to the host"},
+                    "path": "per step one pinned host message (q/k/v of every layer) to the device, DStageLayerCache.decode_step per layer (append_staging + decode_attention as one launch; the patched models' decode path), one message with every layer's output back to the host"},
             "gpu_launches": launches,
             "launch_mode": ("python" if args.no_graph else "cuda graph replay of one token (32 launches)") +
                            ("" if args.no_overlap else "; programmatic dependent launch: a call's blocks start and fetch their first "

@@ -53,6 +53,7 @@ class DecodeArgs(C.Structure):
         ("out", C.c_void_p), ("out_stride", C.c_int64),
         ("partial_m", C.c_void_p), ("partial_l", C.c_void_p), ("partial_acc", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("kn_stride", C.c_int64), ("vn_stride", C.c_int64),
     ]
 
 

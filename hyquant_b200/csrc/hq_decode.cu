@@ -48,11 +48,11 @@ struct DecodeParams {
   const __nv_bfloat16* q; int64_t q_stride;
   const uint8_t* k_packed; const uint8_t* v_packed; int64_t kp_stride_bh, vp_stride_bh;
   const __half* k_scale; const __half* v_scale; int64_t ks_stride_bh, vs_stride_bh;
-  const __nv_bfloat16* kseg[3]; const __nv_bfloat16* vseg[3]; int64_t kseg_stride[3], vseg_stride[3];
-  int nseg[3];                            // tokens in topk / staging / window
+  const __nv_bfloat16* kseg[4]; const __nv_bfloat16* vseg[4]; int64_t kseg_stride[4], vseg_stride[4];
+  int nseg[4];                            // tokens in topk / staging / window / the step's new token (0 or 1)
   int n_quant;
   int uq;                                 // INT4 units
-  int useg[3];                            // BF16 units per segment
+  int useg[4];                            // BF16 units per segment
   int units;                              // total units per head
   int nsplit;
   int R;                                  // kv_repeat
@@ -60,6 +60,7 @@ struct DecodeParams {
   float sml;                              // sm_scale * log2(e)
   void* out; int64_t out_stride;
   float* pm; float* pl; float* pacc;      // partial mode outputs (or null)
+  __nv_bfloat16* stage_k; __nv_bfloat16* stage_v;   // staging buffers, written only when the call carries a new token
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
   int overlap;                            // launched with programmatic stream serialisation
   int uq_stable;                          // INT4 units [0, uq_stable) cannot have been written by the previous kernel
@@ -84,7 +85,10 @@ __device__ __forceinline__ Unit unit_of(const DecodeParams& p, int head, int u) 
   }
   u -= p.uq;
   int s = 0;
-  if (u >= p.useg[0]) { u -= p.useg[0]; s = 1; if (u >= p.useg[1]) { u -= p.useg[1]; s = 2; } }
+  if (u >= p.useg[0]) {
+    u -= p.useg[0]; s = 1;
+    if (u >= p.useg[1]) { u -= p.useg[1]; s = 2; if (u >= p.useg[2]) { u -= p.useg[2]; s = 3; } }
+  }
   r.kind = 1; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, p.nseg[s] - r.tok0);
   r.k = reinterpret_cast<const uint8_t*>(p.kseg[s] + head * p.kseg_stride[s] + (int64_t)r.tok0 * 128);
   r.v = reinterpret_cast<const uint8_t*>(p.vseg[s] + head * p.vseg_stride[s] + (int64_t)r.tok0 * 128);
@@ -244,12 +248,12 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   };
   // A unit is stable when the kernel running just before this one cannot have written it:
-  // INT4 tokens older than the newest 128, vertical-line tokens, window tokens.
+  // INT4 tokens older than the newest 128, vertical-line tokens, window tokens (not staging, not the new token).
   auto stable = [&](int i) -> bool {
     const int u = u_begin + warp + kWarps * i;
     if (u < p.uq) return u < p.uq_stable;
     const int ub = u - p.uq;
-    return ub < p.useg[0] || ub >= p.useg[0] + p.useg[1];
+    return ub < p.useg[0] || (ub >= p.useg[0] + p.useg[1] && ub < p.useg[0] + p.useg[1] + p.useg[2]);
   };
 
   // ---- 2. the query rows and the first bulk copies.
@@ -283,6 +287,15 @@ decode_splitk_kernel(const DecodeParams p) {
     if (lane == 0) {
       for (int i = early; i < kSlots && i < n_my; ++i) issue(i);
     }
+  }
+
+  // The step's new token, if the call carries one, is attended to from where the caller has it (segment 3) and
+  // copied into its staging slot for the calls to come: one warp per head, 16 bytes per lane.
+  if (p.nseg[3] > 0 && split == 0 && warp == 0) {
+    const __nv_bfloat16* src = (lane < 16 ? p.kseg[3] : p.vseg[3]) + head * (lane < 16 ? p.kseg_stride[3] : p.vseg_stride[3]);
+    __nv_bfloat16* dst = (lane < 16 ? p.stage_k : p.stage_v) + head * (lane < 16 ? p.kseg_stride[1] : p.vseg_stride[1]) +
+                         (int64_t)p.nseg[1] * 128;
+    reinterpret_cast<uint4*>(dst)[lane & 15] = __ldg(reinterpret_cast<const uint4*>(src) + (lane & 15));
   }
 
   // ---- 3. query fragments (B operands of S^T = K Q^T) scattered straight into fragment
@@ -822,6 +835,8 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   HQ_REQUIRE((k_bits == 2 || k_bits == 4 || k_bits == 8) && (v_bits == 2 || v_bits == 4 || v_bits == 8), HQ_ERR_UNSUPPORTED,
              "hq_decode_splitk: bit widths must be 2, 4 or 8 (K%d V%d)", k_bits, v_bits);
   if (k_bits != 4 || v_bits != 4) {
+    HQ_REQUIRE(a->k_new == nullptr && a->v_new == nullptr, HQ_ERR_UNSUPPORTED,
+               "hq_decode_splitk: k_new / v_new are taken by the K4/V4 kernel only");
     // any other pair: the plain kernel of hq_decode_generic.cu, partials in the same workspace past its header
     HQ_REQUIRE(a->n_quant == 0 || (a->k_packed && a->v_packed && a->k_scale && a->v_scale), HQ_ERR_INVALID,
                "hq_decode_splitk: null quantised segment");
@@ -852,14 +867,22 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.kp_stride_bh = a->kp_stride_bh; p.vp_stride_bh = a->vp_stride_bh;
   p.k_scale = (const __half*)a->k_scale; p.v_scale = (const __half*)a->v_scale;
   p.ks_stride_bh = a->ks_stride_bh; p.vs_stride_bh = a->vs_stride_bh;
-  const void* ks[3] = {a->k_topk, a->k_staging, a->k_window};
-  const void* vs[3] = {a->v_topk, a->v_staging, a->v_window};
-  const int64_t kst[3] = {a->kt_stride_bh, a->kg_stride_bh, a->kw_stride_bh};
-  const int64_t vst[3] = {a->vt_stride_bh, a->vg_stride_bh, a->vw_stride_bh};
-  const int ns[3] = {a->n_topk, a->n_staging, a->n_window};
+  const bool has_new = a->k_new != nullptr || a->v_new != nullptr;
+  if (has_new) {
+    HQ_REQUIRE(a->k_new && a->v_new && a->k_staging && a->v_staging && a->n_staging < HQ_GROUP_SIZE, HQ_ERR_INVALID,
+               "hq_decode_splitk: a new token needs k_new, v_new, the staging buffers and a free staging slot");
+    HQ_REQUIRE(aligned16(a->k_staging) && aligned16(a->v_staging) && a->kg_stride_bh % 8 == 0 && a->vg_stride_bh % 8 == 0,
+               HQ_ERR_ALIGNMENT, "hq_decode_splitk: staging buffers must be 16-byte aligned");
+  }
+  const void* ks[4] = {a->k_topk, a->k_staging, a->k_window, a->k_new};
+  const void* vs[4] = {a->v_topk, a->v_staging, a->v_window, a->v_new};
+  const int64_t kst[4] = {a->kt_stride_bh, a->kg_stride_bh, a->kw_stride_bh, a->kn_stride};
+  const int64_t vst[4] = {a->vt_stride_bh, a->vg_stride_bh, a->vw_stride_bh, a->vn_stride};
+  const int ns[4] = {a->n_topk, a->n_staging, a->n_window, has_new ? 1 : 0};
+  p.stage_k = (__nv_bfloat16*)a->k_staging; p.stage_v = (__nv_bfloat16*)a->v_staging;
   p.uq = (a->n_quant + kUnitQ - 1) / kUnitQ;
   p.units = p.uq;
-  for (int s = 0; s < 3; ++s) {
+  for (int s = 0; s < 4; ++s) {
     p.nseg[s] = ns[s];
     p.useg[s] = (ns[s] + kUnitB - 1) / kUnitB;
     p.units += p.useg[s];

@@ -286,6 +286,36 @@ class DStageLayerCache:
             return None
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
+    def decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                    kv_repeat: int, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``append_staging(key_states, value_states)`` followed by ``decode_attention(query_states, kv_repeat)``
+        (reference :195-303) as one kernel launch: the decode kernel attends to the new token from where it
+        is and stores it into its staging slot on the way.  Same result as the two calls up to the order of
+        the fp32 partial sums.  The step that fills the staging buffer takes the two-call route, because the
+        reference flushes (quantises the 128 staged tokens) before that step's attention."""
+        B, H_KV, S, D = key_states.shape
+        fused = (S == 1 and self.k_bits == 4 and self.v_bits == 4 and self._staging_ptr < GROUP_SIZE - 1
+                 and key_states.dtype == torch.bfloat16 and value_states.dtype == torch.bfloat16
+                 and self._staging_buf_k.dtype == torch.bfloat16 and key_states.stride(3) == 1 and value_states.stride(3) == 1)
+        if fused:
+            k2, v2 = key_states.reshape(B * H_KV, D), value_states.reshape(B * H_KV, D)
+            fused = (k2.data_ptr() % 16 == 0 and v2.data_ptr() % 16 == 0 and k2.stride(0) % 8 == 0 and v2.stride(0) % 8 == 0)
+        if not fused:
+            self.append_staging(key_states, value_states)
+            return self.decode_attention(query_states, kv_repeat, out=out)
+        B_, H_Q_, _, D_ = query_states.shape
+        q2d = query_states.reshape(B_ * H_Q_, D_)
+        plan = self._decode_plan(q2d, kv_repeat)
+        a = plan.args
+        a.k_new, a.v_new, a.kn_stride, a.vn_stride = k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0)
+        try:
+            res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_))
+        finally:
+            a.k_new = a.v_new = None
+        self._staging_ptr += 1
+        self._seq_len += 1
+        return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
+
     def get_seq_length(self) -> int:
         return self._seq_len
 

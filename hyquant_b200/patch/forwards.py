@@ -71,7 +71,11 @@ def build_attention_forward(family: str, *, mode: str, window_size: int, top_rat
         q_len = int(query_states.shape[2])
         has_d_cache = (d_stage_decode and mode in D_STAGE_MODES and past_key_values is not None
                        and is_d_stage_cache(past_key_values))
-        if has_d_cache:
+        fused_step = None
+        if has_d_cache and q_len == 1 and past_key_values.get_layer(self.layer_idx).phase == "decode":
+            # decode step on a frozen cache: append + attention in one launch (DStageLayerCache.decode_step)
+            fused_step = past_key_values.get_layer(self.layer_idx)
+        elif has_d_cache:
             key_states, value_states = handle_d_stage_cache(self.layer_idx, past_key_values, query_states, key_states,
                                                             value_states, self, sin, cos, cache_position)
         elif past_key_values is not None:
@@ -95,8 +99,11 @@ def build_attention_forward(family: str, *, mode: str, window_size: int, top_rat
             if not has_d_cache:
                 raise HyQuantError(f"mode '{mode}' decodes against a DStageKVCache; pass one as past_key_values "
                                    "(the cache-less quantise/dequantise emulation is not built)")
-            layer_cache = past_key_values.get_layer(self.layer_idx)
-            attn_output = finish(layer_cache.decode_attention(query_states, kv_repeat))
+            if fused_step is not None:
+                attn_output = finish(fused_step.decode_step(query_states, key_states, value_states, kv_repeat))
+            else:
+                layer_cache = past_key_values.get_layer(self.layer_idx)
+                attn_output = finish(layer_cache.decode_attention(query_states, kv_repeat))
         elif mode in D_STAGE_MODES:
             if D_STAGE_MODES[mode]["prefill_kernel"] == "vquant_vert":
                 vidx = compute_vertical_indices(query_states, key_states, window_size, top_ratio, kv_repeat=kv_repeat)

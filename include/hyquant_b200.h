@@ -151,6 +151,11 @@ typedef struct hq_decode_args {
   float*  partial_acc;
   void*   workspace;           /* hq_decode_workspace_bytes(); zero-filled once by the caller */
   int64_t workspace_bytes;
+  /* Optional (K4/V4 only): the step's new token, bf16 [BH_KV, 128] with row strides in elements.  The call
+   * attends to it in addition to the n_staging tokens already in the staging buffers and copies it into
+   * staging slot n_staging, so the caller need not append it first (a fused form of the reference's
+   * append_staging + decode_attention, src/ops/d_stage_kv_cache.py:195-303).  The caller then counts it. */
+  const void* k_new; const void* v_new; int64_t kn_stride; int64_t vn_stride;
 } hq_decode_args;
 
 int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);

@@ -481,3 +481,89 @@ def test_overlapped_launches_back_to_back_in_a_graph():
     for o, w in zip(outs, want):
         assert torch.equal(o, w)
     assert decode_status(plans[0][1].ws) == 0
+
+
+def _dense_yardstick(q, kq, vq, ks, vs, segs, R, heads):
+    """fp32 attention over the dequantised cache of a few kv heads (torch, on the device)."""
+    kd = torch.cat([dd._unpack_int4(kq[heads], 128) * ks[heads].float()[..., None]] + [s[0][heads].float() for s in segs], 1)
+    vd = torch.cat([dd._unpack_int4(vq[heads], 128) * vs[heads].float()[..., None]] + [s[1][heads].float() for s in segs], 1)
+    qh = q.float().reshape(-1, R, 128)[heads]
+    sc = torch.einsum("hrd,hnd->hrn", qh, kd) * 128 ** -0.5
+    return torch.einsum("hrn,hnd->hrd", torch.softmax(sc, -1), vd).reshape(-1, 128)
+
+
+@pytest.mark.parametrize("name,B,H_Q,H_KV,N", [("batched 64q/8kv x 16, 32K", 16, 64, 8, 32768),
+                                                ("long context 32q/2kv x 4, 128K", 4, 32, 2, 131072)])
+def test_full_size_batched_and_long_context_shapes(name, B, H_Q, H_KV, N):
+    """The other two BASELINE decode shapes at full size: the result does not depend on the split count, equals a
+    four-way sequence sharding merged by the LSE kernel, and sampled heads match an fp32 dense computation on the
+    dequantised cache."""
+    g = torch.Generator(device=DEV); g.manual_seed(N + B)
+    BH, R = B * H_KV, H_Q // H_KV
+    T = int((N - 128) * 0.05); nq = N - 128 - T
+    bf = lambda n: torch.randn(BH, n, 128, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    kq, ks = hq.quantize_per_token(bf(nq), 4)
+    vq, vs = hq.quantize_per_token(bf(nq), 4)
+    kt, vt, kw, vw, kst, vst = bf(T), bf(T), bf(128), bf(128), bf(64), bf(64)
+    q = torch.randn(BH * R, 128, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    full = hq.fused_d_stage_decode(q, kq, vq, ks, vs, kt, vt, kst, vst, kw, vw, 4, 4, kv_repeat=R).float()
+    one = dd.DecodePlan(q, kq, vq, ks, vs, kt, vt, kst, vst, kw, vw, R, None, num_splits=1).run(q).float()
+    assert (full - one).abs().max().item() < 1e-2
+    heads = torch.tensor([0, BH // 2, BH - 1], device=DEV)
+    ref = _dense_yardstick(q, kq, vq, ks, vs, [(kt, vt), (kst, vst), (kw, vw)], R, heads)
+    got = full.reshape(BH, R, 128)[heads].reshape(-1, 128)
+    assert (got - ref).abs().max().item() <= MAX_ABS
+    assert ((got - ref) ** 2).sum().item() / (ref ** 2).sum().item() <= REL_MSE
+    G = 4
+    from hyquant_b200 import sharded
+    ms, ls, accs = [], [], []
+    for r, (q0, q1, t0, t1) in enumerate(sharded.sequence_shard_plan(nq, T, G)):
+        last = r == G - 1
+        e = kw[:, :0]
+        plan = dd.DecodePlan(q, kq[:, q0:q1], vq[:, q0:q1], ks[:, q0:q1].contiguous(), vs[:, q0:q1].contiguous(),
+                             kt[:, t0:t1], vt[:, t0:t1], kst if last else e, vst if last else e, kw if last else e,
+                             vw if last else e, R, None)
+        m = torch.empty(BH * R, dtype=torch.float32, device=DEV); l = torch.empty_like(m)
+        acc = torch.empty(BH * R, 128, dtype=torch.float32, device=DEV)
+        plan.run(q, partial=(m, l, acc)); ms.append(m); ls.append(l); accs.append(acc)
+    merged = hq.lse_merge(torch.stack(ms), torch.stack(ls), torch.stack(accs), out_dtype=torch.float32)
+    assert (merged - full).abs().max().item() < 1e-2
+
+
+def test_decode_step_equals_append_then_decode():
+    """`decode_step` (the new token attended to and stored by the decode kernel itself) against the reference's two
+    calls, over 300 steps: same cache contents bit for bit (staging rows, flushed codes and scales), same outputs up
+    to the order of the fp32 partial sums."""
+    import hyquant_b200 as hq
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV, N, W = 2, 8, 2, 2048 + 9, 128
+    R = H_Q // H_KV
+    t = gen_torch(B, H_Q, H_KV, N, 128, W, 0.05, 77, n_qry=W, device="cuda")
+    layers = []
+    for _ in range(2):
+        layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=0.05, use_vert=True)
+        layer.update_prefill(t["k"], t["v"]); layer.save_query_tail(t["q"]); layer.freeze(kv_repeat=R)
+        layers.append(layer)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    worst = 0.0
+    for step in range(300):
+        kn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        vn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        qn = torch.randn(B, H_Q, 1, 128, generator=g, device="cuda").bfloat16()
+        layers[0].append_staging(kn, vn)
+        want = layers[0].decode_attention(qn, R)
+        got = layers[1].decode_step(qn, kn, vn, R)
+        worst = max(worst, float((got.float() - want.float()).abs().max()))
+        assert layers[0]._staging_ptr == layers[1]._staging_ptr and layers[0]._n_quant == layers[1]._n_quant
+    assert worst <= 4e-3, worst
+    a, b = layers
+    assert a.get_seq_length() == b.get_seq_length() == N + 300
+    assert torch.equal(a._staging_buf_k[:, :a._staging_ptr], b._staging_buf_k[:, :b._staging_ptr])
+    assert torch.equal(a._staging_buf_v[:, :a._staging_ptr], b._staging_buf_v[:, :b._staging_ptr])
+    assert torch.equal(a.k_quant_packed, b.k_quant_packed) and torch.equal(a.v_scale, b.v_scale)
+    assert decode_status_of(b) == 0
+
+
+def decode_status_of(layer):
+    from hyquant_b200.decode_d_stage import decode_status
+    return decode_status(layer._plan.ws)
