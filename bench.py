@@ -96,7 +96,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.002)
 
     def start(self):
         if self.nv is not None:
@@ -294,7 +294,7 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
     is sequence-sharded: partial softmax states are all-gathered with NCCL and merged on every rank."""
     from hyquant_b200 import sharded
     b, h_q, h_kv, n = 4, 32, 2, 131072
-    nl, steps, warm = 4, 136, 8
+    nl, steps, warm = 4, 2048, 8                 # 2048 generated tokens: 16 staging flushes per layer
     r = h_q // h_kv
     layers, qs = [], []
     for i in range(nl):
@@ -318,8 +318,7 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
                 layer.append_staging(kn[s], vn[s], tail)
                 layer.decode_attention(q, r)
             else:
-                layer.append_staging(kn[s], vn[s])
-                layer.decode_attention(q, r)
+                layer.decode_step(q, kn[s], vn[s], r)
     for s in range(warm):
         one(s)
     torch.cuda.synchronize()
@@ -344,7 +343,7 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
             "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks, NCCL all-gather of (m, l, acc) + merge",
             "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
             "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
-            "launch_mode": "python (host-driven: append + decode" + (" + all-gather + merge)" if world > 1 else ")"),
+            "launch_mode": "python, host-driven: " + ("append + partial decode + all-gather + merge" if world > 1 else "decode_step (append + decode in one launch)"),
             "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
 
 
@@ -440,7 +439,6 @@ def run_ours(args):
     sampler.start()
     ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph,
                                      overlap=not args.no_overlap)
-    clocks = sampler.stop()
     ms_plain = None
     if not args.no_overlap and not args.no_decode:
         ms_plain, _ = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph, overlap=False)
@@ -448,6 +446,7 @@ def run_ours(args):
         e2e_ms, h2d, d2h = float("nan"), 0, 0
     else:
         e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, args.warmup, 99 + rank, dist)
+    clocks = sampler.stop()      # sampled every 2 ms over the three decode loops (graph, plain launches, e2e)
     e2e_bytes = sum(layer_bytes(l, B * H_Q) for l in layers)     # staging has grown by then; close enough per step
 
     if dist is not None:
@@ -470,7 +469,16 @@ def run_ours(args):
             m, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=not args.no_graph)
             us = m * 1e3 / cnt
             bts = layer_bytes(ls[0], B * H_Q)
-            sweep.append({"prefix": n, "us_per_call": round(us, 3), "gbps": round(bts / us / 1e3, 1),
+            sweep.append({"prefix": n, "staging": STAGING, "us_per_call": round(us, 3), "gbps": round(bts / us / 1e3, 1),
+                          "bytes": bts, "caches": len(ls), "l2": "flushed before each pass over the caches"})
+            del ls, qq
+        # the same call at 32K with the staging buffer empty (right after a flush), one token, full
+        for st_ in (0, 1, 127):
+            ls, qq = zip(*[build_layer(hq, torch, 5500 + st_ + i, N_PREFIX, dev, staging=st_) for i in range(8)])
+            m, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=not args.no_graph)
+            us = m * 1e3 / cnt
+            bts = layer_bytes(ls[0], B * H_Q)
+            sweep.append({"prefix": N_PREFIX, "staging": st_, "us_per_call": round(us, 3), "gbps": round(bts / us / 1e3, 1),
                           "bytes": bts, "caches": len(ls), "l2": "flushed before each pass over the caches"})
             del ls, qq
         del flush
