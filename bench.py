@@ -250,7 +250,7 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
 
 def bench_bit_widths(torch, hq, dev, graph):
     """The decode call at the reference's other cache modes (d_k8v8, d_k4v2, d_k2v4), same shapes as the headline
-    workload: these pairs run the plain kernel of hq_decode_generic.cu (two launches per call: partials, merge)."""
+    workload, plain launches (no graph replay, no launch overlap)."""
     out = []
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for kb, vb in ((8, 8), (4, 2), (2, 4)):
@@ -259,7 +259,7 @@ def bench_bit_widths(torch, hq, dev, graph):
         us = ms * 1e3 / cnt
         bts = layer_bytes(ls[0], B * H_Q)
         out.append({"k_bits": kb, "v_bits": vb, "prefix": N_PREFIX, "us_per_call": round(us, 2), "bytes_per_call": bts,
-                    "gbps": round(bts / us / 1e3, 1), "kernel": "hq::decode_generic_kernel + hq::lse_merge_kernel"})
+                    "gbps": round(bts / us / 1e3, 1), "kernel": "hq::decode_splitk_kernel<1, true, %d, %d>" % (kb, vb)})
         del ls, qq
     return out
 

@@ -38,8 +38,7 @@ namespace hq {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kSlots = 3;
-constexpr int kSlotBytes = 4224;          // K 2048 | V 2048 | k_scale 64 | v_scale 64
-constexpr int kUnitQ = 32;                // INT4 tokens per unit
+constexpr int kUnitQ = 32;                // quantised tokens per unit
 constexpr int kUnitB = 8;                 // BF16 tokens per unit
 constexpr float kLazyRescale = 4.0f;      // rescale only if the max grows by > 2^4
 constexpr int kWsHeaderBytes = 256;       // [0] status word
@@ -68,19 +67,33 @@ struct DecodeParams {
   float* ws_m; float* ws_l; float* ws_acc;
 };
 
+// Shared-memory slot of one unit for a (K bits, V bits) pair.  Quantised unit: 32 token rows of K codes, then 32
+// rows of V codes, then (past the larger of that and a BF16 unit) 32 fp16 K scales and 32 fp16 V scales.  BF16 unit:
+// 8 K rows at 0, 8 V rows at 2048.  K4/V4: K 2048 | V 2048 | k_scale 64 | v_scale 64 = 4224 bytes.
+template <int KB, int VB>
+struct Fmt {
+  static constexpr int kRowK = 16 * KB, kRowV = 16 * VB;                  // bytes per token row (128 channels)
+  static constexpr int kQuant = kUnitQ * (kRowK + kRowV);
+  static constexpr int kData = kQuant > 4096 ? kQuant : 4096;
+  static constexpr int kVOff = kUnitQ * kRowK;
+  static constexpr int kSlot = kData + 128;
+  static constexpr int kCtasPerSm = (kSlot <= 4224) ? 2 : 1;              // shared memory per CTA: 24 slots + 8.6 KB
+};
+
 struct Unit {
   const uint8_t* k; const uint8_t* v;
-  int kind;       // 0 = INT4, 1 = BF16
+  int kind;       // 0 = quantised, 1 = BF16
   int ntok;       // valid tokens
   int tok0;       // first token within its segment
 };
 
+template <int KB, int VB>
 __device__ __forceinline__ Unit unit_of(const DecodeParams& p, int head, int u) {
   Unit r;
   if (u < p.uq) {
     r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, p.n_quant - r.tok0);
-    r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * 64;
-    r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * 64;
+    r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowK;
+    r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowV;
     return r;
   }
   u -= p.uq;
@@ -121,6 +134,35 @@ __device__ __forceinline__ void cvt_nibbles_biased(uint32_t w, uint32_t (&h)[4])
   h[1] = lop3_and_xor(w, 0x00F000F0u, 0x64806480u);
   h[2] = lop3_and_xor(w8, 0x000F000Fu, 0x64086408u);
   h[3] = lop3_and_xor(w8, 0x00F000F0u, 0x64806480u);
+}
+
+// Byte b of `wa` and of `wb` (two's-complement codes of two tokens) -> result b = fp16x2 (code of wa, code of wb), exact.
+__device__ __forceinline__ void cvt_byte_pairs_f16(uint32_t wa, uint32_t wb, uint32_t (&h)[4]) {
+  const uint32_t m01 = prmt(wa, wb, 0x5140u) ^ 0x80808080u;    // a0 b0 a1 b1, each + 128
+  const uint32_t m23 = prmt(wa, wb, 0x7362u) ^ 0x80808080u;    // a2 b2 a3 b3
+  const __half2 c1152 = u32_as_h2(0x64806480u);
+  h[0] = h2_as_u32(__hsub2(u32_as_h2(prmt(m01, 0x64646464u, 0x4140u)), c1152));
+  h[1] = h2_as_u32(__hsub2(u32_as_h2(prmt(m01, 0x64646464u, 0x4342u)), c1152));
+  h[2] = h2_as_u32(__hsub2(u32_as_h2(prmt(m23, 0x64646464u, 0x4140u)), c1152));
+  h[3] = h2_as_u32(__hsub2(u32_as_h2(prmt(m23, 0x64646464u, 0x4342u)), c1152));
+}
+
+// Each 16-bit lane of w carries 2-bit two's-complement codes in its low byte (fields f = 0..3 at bits 2f, 2f+1).
+// Result f is the fp16x2 (lane_lo field f, lane_hi field f) as 1024 + 4^f (2 + code): the magic offset stays in.
+__device__ __forceinline__ void cvt_crumbs_biased(uint32_t w, uint32_t (&h)[4]) {
+  h[0] = lop3_and_xor(w, 0x00030003u, 0x64026402u);
+  h[1] = lop3_and_xor(w, 0x000C000Cu, 0x64086408u);
+  h[2] = lop3_and_xor(w, 0x00300030u, 0x64206420u);
+  h[3] = lop3_and_xor(w, 0x00C000C0u, 0x64806480u);
+}
+// Same fields with the exact integer values.
+__device__ __forceinline__ void cvt_crumbs_f16(uint32_t w, uint32_t (&h)[4]) {
+  uint32_t b[4];
+  cvt_crumbs_biased(w, b);
+  h[0] = h2_as_u32(__hsub2(u32_as_h2(b[0]), u32_as_h2(0x64026402u)));                               // - 1026
+  h[1] = h2_as_u32(__hfma2(u32_as_h2(b[1]), u32_as_h2(0x34003400u), u32_as_h2(0xDC08DC08u)));       // / 4 - 258
+  h[2] = h2_as_u32(__hfma2(u32_as_h2(b[2]), u32_as_h2(0x2C002C00u), u32_as_h2(0xD420D420u)));       // / 16 - 66
+  h[3] = h2_as_u32(__hfma2(u32_as_h2(b[3]), u32_as_h2(0x24002400u), u32_as_h2(0xCC80CC80u)));       // / 64 - 18
 }
 
 __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -193,9 +235,11 @@ __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m
 
 // ---- the kernel -------------------------------------------------------------
 
-template <int NT, bool kScaleTma>
-__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1)
+template <int NT, bool kScaleTma, int KB, int VB>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? Fmt<KB, VB>::kCtasPerSm : 1)
 decode_splitk_kernel(const DecodeParams p) {
+  using F = Fmt<KB, VB>;
+  constexpr int kSlotBytes = F::kSlot;
   extern __shared__ __align__(128) uint8_t smem[];
   // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same |
   //         headC [NT*8] f32 | mbarriers [kWarps][kSlots]
@@ -225,21 +269,21 @@ decode_splitk_kernel(const DecodeParams p) {
   __syncwarp();
 
   auto issue = [&](int i) {   // lane 0 only
-    const Unit un = unit_of(p, head, u_begin + warp + kWarps * i);
+    const Unit un = unit_of<KB, VB>(p, head, u_begin + warp + kWarps * i);
     const int slot = i % kSlots;
     uint8_t* dst = my_ring + slot * kSlotBytes;
     if (un.kind == 0) {
-      const uint32_t bytes = (uint32_t)un.ntok * 64u;
+      const uint32_t kbytes = (uint32_t)un.ntok * F::kRowK, vbytes = (uint32_t)un.ntok * F::kRowV;
       if (kScaleTma) {
         const uint32_t sbytes = (uint32_t)((un.ntok + 7) & ~7) * 2u;
-        mbar_expect_tx(&my_bar[slot], 2 * bytes + 2 * sbytes);
-        bulk_g2s(dst + 4096, p.k_scale + head * p.ks_stride_bh + un.tok0, sbytes, &my_bar[slot]);
-        bulk_g2s(dst + 4160, p.v_scale + head * p.vs_stride_bh + un.tok0, sbytes, &my_bar[slot]);
+        mbar_expect_tx(&my_bar[slot], kbytes + vbytes + 2 * sbytes);
+        bulk_g2s(dst + F::kData, p.k_scale + head * p.ks_stride_bh + un.tok0, sbytes, &my_bar[slot]);
+        bulk_g2s(dst + F::kData + 64, p.v_scale + head * p.vs_stride_bh + un.tok0, sbytes, &my_bar[slot]);
       } else {
-        mbar_expect_tx(&my_bar[slot], 2 * bytes);
+        mbar_expect_tx(&my_bar[slot], kbytes + vbytes);
       }
-      bulk_g2s(dst, un.k, bytes, &my_bar[slot]);
-      bulk_g2s(dst + 2048, un.v, bytes, &my_bar[slot]);
+      bulk_g2s(dst, un.k, kbytes, &my_bar[slot]);
+      bulk_g2s(dst + F::kVOff, un.v, vbytes, &my_bar[slot]);
     } else {
       const uint32_t bytes = (uint32_t)un.ntok * 256u;
       mbar_expect_tx(&my_bar[slot], 2 * bytes);
@@ -248,7 +292,7 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   };
   // A unit is stable when the kernel running just before this one cannot have written it:
-  // INT4 tokens older than the newest 128, vertical-line tokens, window tokens (not staging, not the new token).
+  // quantised tokens older than the newest 128, vertical-line tokens, window tokens (not staging, not the new token).
   auto stable = [&](int i) -> bool {
     const int u = u_begin + warp + kWarps * i;
     if (u < p.uq) return u < p.uq_stable;
@@ -307,21 +351,37 @@ decode_splitk_kernel(const DecodeParams p) {
     const int hd = nt * 8 + warp;
     const float qv[4] = {__uint_as_float(qraw[nt].x << 16), __uint_as_float(qraw[nt].x & 0xFFFF0000u),
                          __uint_as_float(qraw[nt].y << 16), __uint_as_float(qraw[nt].y & 0xFFFF0000u)};
-    // INT4 path: word i of thread tt of a token row covers channels 32 tt + 8 i + m (nibble m);
-    // register r of MMA chunk c = 2 i + odd pairs nibbles (2 odd + r, 2 odd + r + 4).  Odd
-    // nibbles (r = 1) are high nibbles: the query value is pre-divided by 16.
+    // Quantised path.  K codes reach the MMA as 1024 + k (h + code) in fp16, h = 2^(bits - 1) (k = 1 for bytes and low
+    // nibbles, 16 for high nibbles, 1 / 4 / 16 / 64 for the four 2-bit fields of a byte), so the query value is divided
+    // by k and the head's constant sum((1024 + k h) * q / k) is taken off the fp32 score.  The channel that lands in MMA chunk
+    // c, register r, k-slot thread tt, half e depends on how the lanes read a token row:
+    //   8 bits: channel = 64 (c >> 2) + 16 tt + 4 (c & 3) + 2 r + e
+    //   4 bits: channel = 32 tt + 8 (c >> 1) + 4 e + 2 (c & 1) + r            (r = 1: high nibbles)
+    //   2 bits: channel = 32 tt + 16 (c >> 2) + 8 e + 4 ((c >> 1) & 1) + 2 (c & 1) + r   (field 2 (c & 1) + r)
     {
-      const int tt = lane >> 3, i = (lane >> 1) & 3, isB = lane & 1;
       __half* fh = reinterpret_cast<__half*>(fragH);
       float c = 0.f;
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        const int odd = x >> 1, r = x & 1;
-        const float v = fminf(fmaxf(qv[x] * (r ? 0.0625f : 1.0f), -65504.f), 65504.f);
+        const int chn = 4 * lane + x;
+        int cc, r, tt, e;
+        float inv, bias;
+        if (KB == 8) {
+          cc = 4 * (chn >> 6) + ((chn >> 2) & 3); tt = (chn >> 4) & 3; r = (chn >> 1) & 1; e = chn & 1;
+          inv = 1.0f; bias = 1152.f;
+        } else if (KB == 4) {
+          tt = chn >> 5; cc = 2 * ((chn >> 3) & 3) + ((chn >> 1) & 1); e = (chn >> 2) & 1; r = chn & 1;
+          inv = r ? 0.0625f : 1.0f; bias = r ? 1152.f : 1032.f;
+        } else {
+          tt = chn >> 5; cc = 4 * ((chn >> 4) & 1) + 2 * ((chn >> 2) & 1) + ((chn >> 1) & 1); e = (chn >> 3) & 1; r = chn & 1;
+          const int f = 2 * ((chn >> 1) & 1) + r;        // field within the byte: weight 4^f
+          inv = f == 0 ? 1.0f : f == 1 ? 0.25f : f == 2 ? 0.0625f : 0.015625f;
+          bias = f == 0 ? 1026.f : f == 1 ? 1032.f : f == 2 ? 1056.f : 1152.f;
+        }
+        const float v = fminf(fmaxf(qv[x] * inv, -65504.f), 65504.f);
         const __half hv = __float2half_rn(v);
-        fh[((((nt * 8 + 2 * i + odd) * 2 + r) * 32) + 4 * warp + tt) * 2 + isB] = hv;
-        // even channels meet 1032 + code, odd channels meet 1152 + 16 code
-        c += (r ? 1152.f : 1032.f) * __half2float(hv);
+        fh[((((nt * 8 + cc) * 2 + r) * 32) + 4 * warp + tt) * 2 + e] = hv;
+        c += bias * __half2float(hv);
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
@@ -352,7 +412,7 @@ decode_splitk_kernel(const DecodeParams p) {
   bool failed = false;
   int i = 0;
 
-  // ======================= INT4 units =======================================
+  // ======================= quantised units ==================================
   {
     uint32_t Qh[NT][8][2];
     float hc[NT][2];
@@ -387,17 +447,11 @@ decode_splitk_kernel(const DecodeParams p) {
       const int slot = i % kSlots;
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
       const uint8_t* Ks = my_ring + slot * kSlotBytes;
-      const uint8_t* Vs = Ks + 2048;
-      const __half* kss = reinterpret_cast<const __half*>(Ks + 4096);
-      const __half* vss = reinterpret_cast<const __half*>(Ks + 4160);
+      const uint8_t* Vs = Ks + F::kVOff;
+      const __half* kss = reinterpret_cast<const __half*>(Ks + F::kData);
+      const __half* vss = reinterpret_cast<const __half*>(Ks + F::kData + 64);
 
-      // K words of both 16-token chunks: tokens g, g+8, 16+g, 24+g
-      uint4 kw[2][2];
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
-        kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
-      }
+      // scores of both 16-token chunks: this lane holds tokens g, g+8, 16+g, 24+g
       float s[2][NT][4];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch)
@@ -405,20 +459,70 @@ decode_splitk_kernel(const DecodeParams p) {
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int x = 0; x < 4; ++x) s[ch][nt][x] = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      if constexpr (KB == 4) {
+        uint4 kw[2][2];
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          const uint32_t wa = w == 0 ? kw[ch][0].x : w == 1 ? kw[ch][0].y : w == 2 ? kw[ch][0].z : kw[ch][0].w;
-          const uint32_t wb = w == 0 ? kw[ch][1].x : w == 1 ? kw[ch][1].y : w == 2 ? kw[ch][1].z : kw[ch][1].w;
-          uint32_t ha[4], hb[4];
-          cvt_nibbles_biased(wa, ha);
-          cvt_nibbles_biased(wb, hb);
+          kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
+          kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
+        }
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
-            mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            const uint32_t wa = w == 0 ? kw[ch][0].x : w == 1 ? kw[ch][0].y : w == 2 ? kw[ch][0].z : kw[ch][0].w;
+            const uint32_t wb = w == 0 ? kw[ch][1].x : w == 1 ? kw[ch][1].y : w == 2 ? kw[ch][1].z : kw[ch][1].w;
+            uint32_t ha[4], hb[4];
+            cvt_nibbles_biased(wa, ha);
+            cvt_nibbles_biased(wb, hb);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
+              mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
+            }
           }
+        }
+      } else if constexpr (KB == 8) {
+        // a 128-byte row: 16 bytes at 64 h + 16 t; word w of it holds channels 64 h + 16 t + 4 w + (0..3)
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 ka = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 128 + 64 * h + t * 16);
+            const uint4 kb = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 128 + 64 * h + t * 16);
+            const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t xa = wa[w] ^ 0x80808080u, xb = wb[w] ^ 0x80808080u;   // code + 128 in every byte
+              const uint32_t a0 = prmt(xa, 0x64646464u, 0x4140u), a2 = prmt(xa, 0x64646464u, 0x4342u);
+              const uint32_t a1 = prmt(xb, 0x64646464u, 0x4140u), a3 = prmt(xb, 0x64646464u, 0x4342u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+                mma_f16_16816(s[ch][nt], a0, a1, a2, a3, Qh[nt][4 * h + w][0], Qh[nt][4 * h + w][1]);
+            }
+          }
+      } else {
+        // a 32-byte row: 8 bytes at 8 t; word x of it holds channels 32 t + 16 x + m, code m in bits 2m, 2m+1
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          const uint2 ka = *reinterpret_cast<const uint2*>(Ks + (16 * ch + g) * 32 + t * 8);
+          const uint2 kb = *reinterpret_cast<const uint2*>(Ks + (16 * ch + g + 8) * 32 + t * 8);
+          const uint32_t wa[2] = {ka.x, ka.y}, wb[2] = {kb.x, kb.y};
+#pragma unroll
+          for (int x = 0; x < 2; ++x)
+#pragma unroll
+            for (int sh = 0; sh < 2; ++sh) {
+              const uint32_t ua = sh ? wa[x] >> 8 : wa[x], ub = sh ? wb[x] >> 8 : wb[x];
+              uint32_t ra[4], rb[4];
+              cvt_crumbs_biased(ua, ra);
+              cvt_crumbs_biased(ub, rb);
+#pragma unroll
+              for (int pp = 0; pp < 2; ++pp)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                  mma_f16_16816(s[ch][nt], ra[2 * pp], rb[2 * pp], ra[2 * pp + 1], rb[2 * pp + 1],
+                                Qh[nt][4 * x + 2 * sh + pp][0], Qh[nt][4 * x + 2 * sh + pp][1]);
+            }
         }
       }
       float vsc[2][2];
@@ -474,27 +578,71 @@ decode_splitk_kernel(const DecodeParams p) {
           pb[nt][0] = movmatrix_trans(pa);    // (tokens 2t, 2t+1 ; head g)
           pb[nt][1] = movmatrix_trans(pq);    // (tokens 2t+8, 2t+9 ; head g)
         }
-        const uint8_t* vrow = Vs + (16 * ch + 2 * t) * 64 + 8 * g;
-        const uint2 vA = *reinterpret_cast<const uint2*>(vrow);
-        const uint2 vB = *reinterpret_cast<const uint2*>(vrow + 64);
-        const uint2 vC = *reinterpret_cast<const uint2*>(vrow + 8 * 64);
-        const uint2 vD = *reinterpret_cast<const uint2*>(vrow + 9 * 64);
-        const uint32_t wA[2] = {vA.x, vA.y}, wB[2] = {vB.x, vB.y}, wC[2] = {vC.x, vC.y}, wD[2] = {vD.x, vD.y};
+        // V: this lane converts channels 16 g .. 16 g + 15 of tokens 2t, 2t+1, 2t+8, 2t+9 of the chunk; output tile
+        // mt holds channel 16 g + 2 mt in row g and 16 g + 2 mt + 1 in row g + 8, whatever the bit width.
+        const uint8_t* vrow = Vs + (16 * ch + 2 * t) * F::kRowV + 2 * VB * g;
+        if constexpr (VB == 4) {
+          const uint2 vA = *reinterpret_cast<const uint2*>(vrow);
+          const uint2 vB = *reinterpret_cast<const uint2*>(vrow + 64);
+          const uint2 vC = *reinterpret_cast<const uint2*>(vrow + 8 * 64);
+          const uint2 vD = *reinterpret_cast<const uint2*>(vrow + 9 * 64);
+          const uint32_t wA[2] = {vA.x, vA.y}, wB[2] = {vB.x, vB.y}, wC[2] = {vC.x, vC.y}, wD[2] = {vD.x, vD.y};
 #pragma unroll
-        for (int w = 0; w < 2; ++w)
+          for (int w = 0; w < 2; ++w)
 #pragma unroll
-          for (int hl = 0; hl < 2; ++hl) {
-            const uint32_t sel = hl ? 0x7632u : 0x5410u;
+            for (int hl = 0; hl < 2; ++hl) {
+              const uint32_t sel = hl ? 0x7632u : 0x5410u;
+              uint32_t hab[4], hcd[4];
+              cvt_nibbles_f16(prmt(wA[w], wB[w], sel), hab);
+              cvt_nibbles_f16(prmt(wC[w], wD[w], sel), hcd);
+              const int pidx = 2 * w + hl;
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
+                mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+              }
+            }
+        } else if constexpr (VB == 8) {
+          const uint4 vA = *reinterpret_cast<const uint4*>(vrow);
+          const uint4 vB = *reinterpret_cast<const uint4*>(vrow + 128);
+          const uint4 vC = *reinterpret_cast<const uint4*>(vrow + 8 * 128);
+          const uint4 vD = *reinterpret_cast<const uint4*>(vrow + 9 * 128);
+          const uint32_t wA[4] = {vA.x, vA.y, vA.z, vA.w}, wB[4] = {vB.x, vB.y, vB.z, vB.w};
+          const uint32_t wC[4] = {vC.x, vC.y, vC.z, vC.w}, wD[4] = {vD.x, vD.y, vD.z, vD.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {      // word w: channels 16 g + 4 w + (0..3)
             uint32_t hab[4], hcd[4];
-            cvt_nibbles_f16(prmt(wA[w], wB[w], sel), hab);
-            cvt_nibbles_f16(prmt(wC[w], wD[w], sel), hcd);
-            const int pidx = 2 * w + hl;
+            cvt_byte_pairs_f16(wA[w], wB[w], hab);
+            cvt_byte_pairs_f16(wC[w], wD[w], hcd);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
-              mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+              mma_f16_16816(O[nt][2 * w], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
+              mma_f16_16816(O[nt][2 * w + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
             }
           }
+        } else {
+          const uint32_t wA = *reinterpret_cast<const uint32_t*>(vrow);
+          const uint32_t wB = *reinterpret_cast<const uint32_t*>(vrow + 32);
+          const uint32_t wC = *reinterpret_cast<const uint32_t*>(vrow + 8 * 32);
+          const uint32_t wD = *reinterpret_cast<const uint32_t*>(vrow + 9 * 32);
+#pragma unroll
+          for (int hl = 0; hl < 2; ++hl) {   // codes 8 hl .. 8 hl + 7 of the two tokens, one token per 16-bit half
+            const uint32_t sel = hl ? 0x7632u : 0x5410u;
+            const uint32_t mab = prmt(wA, wB, sel), mcd = prmt(wC, wD, sel);
+#pragma unroll
+            for (int sh = 0; sh < 2; ++sh) {
+              uint32_t hab[4], hcd[4];
+              cvt_crumbs_f16(sh ? mab >> 8 : mab, hab);
+              cvt_crumbs_f16(sh ? mcd >> 8 : mcd, hcd);
+              const int pidx = 2 * hl + sh;      // channels 16 g + 8 hl + 4 sh + (0..3)
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
+                mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+              }
+            }
+          }
+        }
       }
       sc_cur = sc_next;
       __syncwarp();
@@ -513,7 +661,7 @@ decode_splitk_kernel(const DecodeParams p) {
         for (int r = 0; r < 2; ++r) Qb[nt][c][r] = fragB[((nt * 8 + c) * 2 + r) * 32 + lane];
 
     for (; i < n_my; ++i) {
-      const Unit un = unit_of(p, head, u_begin + warp + kWarps * i);
+      const Unit un = unit_of<KB, VB>(p, head, u_begin + warp + kWarps * i);
       const int slot = i % kSlots;
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
       uint8_t* Ks = my_ring + slot * kSlotBytes;
@@ -763,19 +911,20 @@ decode_splitk_kernel(const DecodeParams p) {
 
 // ---- host side ---------------------------------------------------------------
 
-static size_t decode_smem_bytes(int NT) {
-  return (size_t)kWarps * kSlots * kSlotBytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 +
+static size_t decode_smem_bytes(int NT, int slot_bytes) {
+  return (size_t)kWarps * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 +
          (size_t)kWarps * kSlots * 8;
 }
 
-template <int NT, bool kScaleTma>
+template <int NT, bool kScaleTma, int KB, int VB>
 static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  const size_t smem = decode_smem_bytes(NT);
+  const size_t smem = decode_smem_bytes(NT, Fmt<KB, VB>::kSlot);
   static thread_local int attr_dev = -1;
   int dev = 0;
   HQ_CUDA(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma, KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
     attr_dev = dev;
   }
   cudaLaunchConfig_t cfg{};
@@ -788,8 +937,19 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.overlap ? 1 : 0;
-  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma>, p));
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB>, p));
   return HQ_OK;
+}
+
+template <int KB, int VB>
+static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st) {
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB>(p, grid, st) : launch_decode<1, false, KB, VB>(p, grid, st);
+  return p.scale_tma ? launch_decode<2, true, KB, VB>(p, grid, st) : launch_decode<2, false, KB, VB>(p, grid, st);
+}
+
+static int slot_bytes_of(int kb, int vb) {
+  const int q = kUnitQ * 16 * (kb + vb);
+  return (q > 4096 ? q : 4096) + 128;
 }
 
 static int max_ctas() { return 4 * sm_count(); }
@@ -797,10 +957,6 @@ static int max_ctas() { return 4 * sm_count(); }
 static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace hq
-
-namespace hq {
-int decode_generic_launch(const hq_decode_args* a, int k_bits, int v_bits, float* ws, int64_t ws_floats, cudaStream_t st);
-}
 
 extern "C" int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes) {
   using namespace hq;
@@ -834,32 +990,11 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   const int k_bits = a->k_bits == 0 ? 4 : a->k_bits, v_bits = a->v_bits == 0 ? 4 : a->v_bits;
   HQ_REQUIRE((k_bits == 2 || k_bits == 4 || k_bits == 8) && (v_bits == 2 || v_bits == 4 || v_bits == 8), HQ_ERR_UNSUPPORTED,
              "hq_decode_splitk: bit widths must be 2, 4 or 8 (K%d V%d)", k_bits, v_bits);
-  if (k_bits != 4 || v_bits != 4) {
-    HQ_REQUIRE(a->k_new == nullptr && a->v_new == nullptr, HQ_ERR_UNSUPPORTED,
-               "hq_decode_splitk: k_new / v_new are taken by the K4/V4 kernel only");
-    // any other pair: the plain kernel of hq_decode_generic.cu, partials in the same workspace past its header
-    HQ_REQUIRE(a->n_quant == 0 || (a->k_packed && a->v_packed && a->k_scale && a->v_scale), HQ_ERR_INVALID,
-               "hq_decode_splitk: null quantised segment");
-    const void* kss[3] = {a->k_topk, a->k_staging, a->k_window};
-    const void* vss[3] = {a->v_topk, a->v_staging, a->v_window};
-    const int nss[3] = {a->n_topk, a->n_staging, a->n_window};
-    for (int s = 0; s < 3; ++s)
-      HQ_REQUIRE(nss[s] == 0 || (kss[s] && vss[s] && aligned16(kss[s]) && ((uintptr_t)vss[s] % 8) == 0), HQ_ERR_INVALID,
-                 "hq_decode_splitk: BF16 segment %d missing or misaligned", s);
-    int64_t need = 0;
-    hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
-    HQ_REQUIRE(a->workspace && a->workspace_bytes >= need, HQ_ERR_WORKSPACE,
-               "hq_decode_splitk: workspace of %lld bytes needed, %lld given", (long long)need, (long long)a->workspace_bytes);
-    HQ_REQUIRE(((uintptr_t)a->workspace & 255) == 0, HQ_ERR_ALIGNMENT, "hq_decode_splitk: workspace must be 256-byte aligned");
-    const int64_t off = kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256);
-    return decode_generic_launch(a, k_bits, v_bits, (float*)((uint8_t*)a->workspace + off), (a->workspace_bytes - off) / 4 - 8,
-                                 (cudaStream_t)stream);
-  }
   DecodeParams p{};
   p.q = (const __nv_bfloat16*)a->q; p.q_stride = a->q_stride;
   p.n_quant = a->n_quant;
   if (a->n_quant > 0) {
-    HQ_REQUIRE(a->k_packed && a->v_packed && a->k_scale && a->v_scale, HQ_ERR_INVALID, "hq_decode_splitk: null INT4 segment");
+    HQ_REQUIRE(a->k_packed && a->v_packed && a->k_scale && a->v_scale, HQ_ERR_INVALID, "hq_decode_splitk: null quantised segment");
     HQ_REQUIRE(aligned16(a->k_packed) && aligned16(a->v_packed) && a->kp_stride_bh % 16 == 0 && a->vp_stride_bh % 16 == 0,
                HQ_ERR_ALIGNMENT, "hq_decode_splitk: packed K/V must be 16-byte aligned with 16-byte head strides");
   }
@@ -903,11 +1038,14 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.out = a->out; p.out_stride = a->out_stride;
   p.pm = a->partial_m; p.pl = a->partial_l; p.pacc = a->partial_acc;
 
-  // splits: one wave of CTAs (2 per SM), at least ~2 units per warp
+  // splits: one wave of CTAs (as many per SM as the slot size of this bit-width pair lets reside), at least ~2 units per warp
   const int sms = sm_count();
+  const int slot_bytes = slot_bytes_of(k_bits, v_bits);
+  const int NT = a->kv_repeat <= 8 ? 1 : 2;
+  const int ctas_per_sm = (slot_bytes <= 4224 && NT == 1) ? 2 : 1;
   int nsplit = a->num_splits;
   if (nsplit <= 0) {
-    const int by_grid = (2 * sms) / a->BH_KV;
+    const int by_grid = (ctas_per_sm * sms) / a->BH_KV;
     const int by_work = (p.units + kWarps - 1) / kWarps;
     nsplit = by_grid < by_work ? by_grid : by_work;
   }
@@ -931,10 +1069,9 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   // keep ws_acc 16-byte aligned
   p.ws_acc = (float*)(((uintptr_t)p.ws_acc + 15) & ~(uintptr_t)15);
 
-  const int NT = a->kv_repeat <= 8 ? 1 : 2;
   // the split-merge staging reuses the ring: weights + l (2 nsplit R) + 32 + warp partial sums (8 R 128) floats
   HQ_REQUIRE(((size_t)2 * nsplit * a->kv_repeat + 36 + (size_t)kWarps * a->kv_repeat * 128) * 4 <=
-                 (size_t)kWarps * kSlots * kSlotBytes,
+                 (size_t)kWarps * kSlots * slot_bytes,
              HQ_ERR_UNSUPPORTED, "hq_decode_splitk: too many splits (%d)", nsplit);
   // scales can ride in the bulk copies when every 32-token group of a row starts on a
   // 16-byte boundary and a row has room for the round-up of its tail to 8 tokens
@@ -943,8 +1080,17 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
                 a->vs_stride_bh % 8 == 0 && a->ks_stride_bh >= nq8 && a->vs_stride_bh >= nq8;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)(a->BH_KV * nsplit));
-  if (NT == 1) return p.scale_tma ? launch_decode<1, true>(p, grid, st) : launch_decode<1, false>(p, grid, st);
-  return p.scale_tma ? launch_decode<2, true>(p, grid, st) : launch_decode<2, false>(p, grid, st);
+  switch (k_bits * 16 + v_bits) {
+    case 0x44: return launch_decode_bits<4, 4>(p, NT, grid, st);
+    case 0x88: return launch_decode_bits<8, 8>(p, NT, grid, st);
+    case 0x84: return launch_decode_bits<8, 4>(p, NT, grid, st);
+    case 0x82: return launch_decode_bits<8, 2>(p, NT, grid, st);
+    case 0x48: return launch_decode_bits<4, 8>(p, NT, grid, st);
+    case 0x42: return launch_decode_bits<4, 2>(p, NT, grid, st);
+    case 0x28: return launch_decode_bits<2, 8>(p, NT, grid, st);
+    case 0x24: return launch_decode_bits<2, 4>(p, NT, grid, st);
+    default: return launch_decode_bits<2, 2>(p, NT, grid, st);
+  }
 }
 
 // ---- decode without caller-provided scratch -----------------------------------------------

@@ -294,7 +294,7 @@ class DStageLayerCache:
         the fp32 partial sums.  The step that fills the staging buffer takes the two-call route, because the
         reference flushes (quantises the 128 staged tokens) before that step's attention."""
         B, H_KV, S, D = key_states.shape
-        fused = (S == 1 and self.k_bits == 4 and self.v_bits == 4 and self._staging_ptr < GROUP_SIZE - 1
+        fused = (S == 1 and self._staging_ptr < GROUP_SIZE - 1
                  and key_states.dtype == torch.bfloat16 and value_states.dtype == torch.bfloat16
                  and self._staging_buf_k.dtype == torch.bfloat16 and key_states.stride(3) == 1 and value_states.stride(3) == 1)
         if fused:

@@ -109,7 +109,7 @@ typedef struct hq_decode_args {
   int32_t BH_KV;               /* batch * kv heads */
   int32_t kv_repeat;           /* query heads per kv head (1..16) */
   int32_t head_dim;            /* 128 */
-  int32_t n_quant;             /* INT4 prefix tokens */
+  int32_t n_quant;             /* quantised prefix tokens */
   int32_t n_topk;              /* frozen BF16 vertical-line tokens */
   int32_t n_staging;           /* live tokens in the staging buffer (0..128) */
   int32_t n_window;            /* BF16 window tokens */
@@ -118,7 +118,7 @@ typedef struct hq_decode_args {
   float   sm_scale;            /* softmax scale, e.g. head_dim^-0.5 */
   int32_t flags;               /* 0, or HQ_DECODE_OVERLAP_PREVIOUS */
   int32_t k_bits;              /* bit width of the quantised K prefix: 8, 4 or 2 (0 = 4) */
-  int32_t v_bits;              /* the same for V.  K4/V4 runs the tensor-core kernel, every other pair a plain one */
+  int32_t v_bits;              /* the same for V; every pair is one instantiation of the same kernel */
   const void* q;               /* bf16 [BH_KV*kv_repeat, 128] */
   int64_t q_stride;            /* elements between query rows */
   const void* k_packed;        /* int8 [BH_KV, n_quant, 16 * k_bits] (4 bits: 64 bytes per token) */
@@ -151,7 +151,7 @@ typedef struct hq_decode_args {
   float*  partial_acc;
   void*   workspace;           /* hq_decode_workspace_bytes(); zero-filled once by the caller */
   int64_t workspace_bytes;
-  /* Optional (K4/V4 only): the step's new token, bf16 [BH_KV, 128] with row strides in elements.  The call
+  /* Optional: the step's new token, bf16 [BH_KV, 128] with row strides in elements.  The call
    * attends to it in addition to the n_staging tokens already in the staging buffers and copies it into
    * staging slot n_staging, so the caller need not append it first (a fused form of the reference's
    * append_staging + decode_attention, src/ops/d_stage_kv_cache.py:195-303).  The caller then counts it. */
