@@ -250,12 +250,13 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
 
 def bench_bit_widths(torch, hq, dev, graph):
     """The decode call at the reference's other cache modes (d_k8v8, d_k4v2, d_k2v4), same shapes as the headline
-    workload, plain launches (no graph replay, no launch overlap)."""
+    workload and the same launch pattern (graph replay, each launch overlapping the end of the one before), on four
+    caches with an L2 flush between steps."""
     out = []
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    for kb, vb in ((8, 8), (4, 2), (2, 4)):
+    for kb, vb in ((8, 8), (4, 2), (2, 4), (4, 4)):      # 4/4 again: this leg's launch pattern for comparison
         ls, qq = zip(*[build_layer(hq, torch, 6000 + 16 * kb + vb + i, N_PREFIX, dev, k_bits=kb, v_bits=vb) for i in range(4)])
-        ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=graph, overlap=False)
+        ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, flush=flush, graph=graph)
         us = ms * 1e3 / cnt
         bts = layer_bytes(ls[0], B * H_Q)
         out.append({"k_bits": kb, "v_bits": vb, "prefix": N_PREFIX, "us_per_call": round(us, 2), "bytes_per_call": bts,
