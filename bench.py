@@ -292,60 +292,78 @@ def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
 def bench_long_context_decode(torch, hq, dev, rank, world, dist):
     """Long-context decode at GLM-4-9B attention shapes (batch 4, 32 query / 2 KV heads, prefix 128K): each step
     appends one token per layer (a staging flush every 128 tokens) and decodes.  With more than one rank the prefix
-    is sequence-sharded: partial softmax states are all-gathered with NCCL and merged on every rank."""
+    is sequence-sharded and the partial softmax states are exchanged and merged by one kernel over peer memory
+    (``hq_peer_exchange_merge``); the NCCL all-gather + merge form is timed after it for comparison."""
     from hyquant_b200 import sharded
     b, h_q, h_kv, n = 4, 32, 2, 131072
     nl, steps, warm = 4, 2048, 8                 # 2048 generated tokens: 16 staging flushes per layer
     r = h_q // h_kv
     layers, qs = [], []
+    px = sharded.PeerExchange(rows=b * h_q) if world > 1 else None
     for i in range(nl):
         full, qd = build_layer(hq, torch, 9000 + i, n, dev, b=b, h_q=h_q, h_kv=h_kv)     # same seed on every rank
         if world > 1:
             shard = sharded.shard_layer_sequence(full, world, rank)
             del full
-            layers.append(sharded.SequenceShardedLayer(shard))
+            layers.append(sharded.SequenceShardedLayer(shard, exchange=px))
         else:
             layers.append(full)
         qs.append(qd)
     torch.cuda.empty_cache()
     g = torch.Generator(device=dev); g.manual_seed(4242)
-    kn = torch.randn(steps + warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
-    vn = torch.randn(steps + warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    n_nccl = 256 if world > 1 else 0
+    kn = torch.randn(steps + n_nccl + 2 * warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
+    vn = torch.randn(steps + n_nccl + 2 * warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
     tail = rank == world - 1
 
+    outs = [torch.empty_like(q) for q in qs]
+
     def one(s):
-        for layer, q in zip(layers, qs):
+        for layer, q, o in zip(layers, qs, outs):
             if world > 1:
-                layer.append_staging(kn[s], vn[s], tail)
-                layer.decode_attention(q, r)
+                layer.decode_step(q, kn[s], vn[s], r, tail, out=o)
             else:
-                layer.decode_step(q, kn[s], vn[s], r)
-    for s in range(warm):
-        one(s)
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
+                layer.decode_step(q, kn[s], vn[s], r, out=o)
+
+    def timed(s0, count):
+        for s in range(s0, s0 + warm):
+            one(s)
         torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for s in range(warm, warm + steps):
-        one(s)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
-    us = ms * 1e3 / (steps * nl)
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(s0 + warm, s0 + warm + count):
+            one(s)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        return ms * 1e3 / (count * nl)
+
+    us = timed(0, steps)
+    res_extra = {}
+    if world > 1:
+        status = px.status()
+        for layer in layers:
+            layer.exchange = "nccl"
+        res_extra = {"us_per_layer_token_nccl_allgather": round(timed(steps + warm, n_nccl), 2), "peer_exchange_status": status}
+        px.close()
     full_bytes = algorithmic_bytes(b * h_kv, b * h_q, n - W - int((n - W) * RHO), int((n - W) * RHO) + W + 64)
-    return {"workload": "batch 4, 32q/2kv, d=128, prefix 131072, W=128, rho=5%, K4V4; per step and layer: append one "
-                        "token (flush at 128) + decode", "layers": nl, "steps": steps,
-            "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks, NCCL all-gather of (m, l, acc) + merge",
-            "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
-            "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
-            "launch_mode": "python, host-driven: " + ("append + partial decode + all-gather + merge" if world > 1 else "decode_step (append + decode in one launch)"),
-            "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
+    out = {"workload": "batch 4, 32q/2kv, d=128, prefix 131072, W=128, rho=5%, K4V4; per step and layer: append one "
+                       "token (flush at 128) + decode", "layers": nl, "steps": steps,
+           "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks; (m, l, acc) stored into the peers' "
+                       "buffers over NVLink and merged by the same kernel",
+           "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
+           "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
+           "launch_mode": "python, host-driven: " + ("partial decode (taking the new token on the tail rank) + exchange-merge, two launches" if world > 1 else "decode_step (append + decode in one launch)"),
+           "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
+    out.update(res_extra)
+    return out
 
 
 def build_cpu_layer(seed=1015, n_prefix=N_PREFIX):

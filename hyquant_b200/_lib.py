@@ -30,6 +30,8 @@ EXPORTS = [
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
     "hq_prefill_hybrid",
+    "hq_peer_exchange_bytes", "hq_peer_slot", "hq_peer_exchange_merge", "hq_peer_status",
+    "hq_peer_buffer_create", "hq_peer_buffer_open", "hq_peer_buffer_close", "hq_peer_buffer_destroy",
 ]
 
 
@@ -72,6 +74,15 @@ class PrefillArgs(C.Structure):
     ]
 
 
+class PeerExchangeArgs(C.Structure):
+    """Mirror of ``hq_peer_exchange_args``."""
+    _fields_ = [
+        ("struct_bytes", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32), ("rows", C.c_int32),
+        ("seq", C.c_uint32), ("out_dtype", C.c_int32), ("out_stride", C.c_int64), ("out", C.c_void_p),
+        ("timeout_ns", C.c_int64), ("bufs", C.c_void_p * 16),
+    ]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -103,6 +114,14 @@ def _declare(lib):
                                                 vp, vp, vp, vp, vp, vp]
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
+    lib.hq_peer_exchange_bytes.argtypes = [i32, i32, C.POINTER(i64)]
+    lib.hq_peer_slot.argtypes = [vp, i32, i32, C.c_uint32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
+    lib.hq_peer_exchange_merge.argtypes = [C.POINTER(PeerExchangeArgs), vp]
+    lib.hq_peer_status.argtypes = [vp, C.POINTER(C.c_int)]
+    lib.hq_peer_buffer_create.argtypes = [i64, C.POINTER(vp), C.c_char_p]
+    lib.hq_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.hq_peer_buffer_close.argtypes = [vp]
+    lib.hq_peer_buffer_destroy.argtypes = [vp]
     for name in EXPORTS:
         if name not in ("hq_version", "hq_last_error"):
             getattr(lib, name).restype = C.c_int

@@ -287,7 +287,7 @@ class DStageLayerCache:
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
     def decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
-                    kv_repeat: int, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    kv_repeat: int, *, out: Optional[torch.Tensor] = None, partial=None) -> torch.Tensor:
         """``append_staging(key_states, value_states)`` followed by ``decode_attention(query_states, kv_repeat)``
         (reference :195-303) as one kernel launch: the decode kernel attends to the new token from where it
         is and stores it into its staging slot on the way.  Same result as the two calls up to the order of
@@ -302,18 +302,20 @@ class DStageLayerCache:
             fused = (k2.data_ptr() % 16 == 0 and v2.data_ptr() % 16 == 0 and k2.stride(0) % 8 == 0 and v2.stride(0) % 8 == 0)
         if not fused:
             self.append_staging(key_states, value_states)
-            return self.decode_attention(query_states, kv_repeat, out=out)
+            return self.decode_attention(query_states, kv_repeat, out=out, partial=partial)
         B_, H_Q_, _, D_ = query_states.shape
         q2d = query_states.reshape(B_ * H_Q_, D_)
         plan = self._decode_plan(q2d, kv_repeat)
         a = plan.args
         a.k_new, a.v_new, a.kn_stride, a.vn_stride = k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0)
         try:
-            res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_))
+            res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial)
         finally:
             a.k_new = a.v_new = None
         self._staging_ptr += 1
         self._seq_len += 1
+        if partial is not None:
+            return None
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
     def get_seq_length(self) -> int:

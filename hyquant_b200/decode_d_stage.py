@@ -233,8 +233,8 @@ class DecodePlan:
         qb = q if (q.dtype == torch.bfloat16 and q.stride(1) == 1) else q.to(torch.bfloat16).contiguous()
         a.q, a.q_stride = qb.data_ptr(), qb.stride(0)
         if partial is not None:
-            m, l, acc = partial
-            a.partial_m, a.partial_l, a.partial_acc = m.data_ptr(), l.data_ptr(), acc.data_ptr()
+            # fp32 tensors, or raw device addresses (slots of a peer-exchange buffer)
+            a.partial_m, a.partial_l, a.partial_acc = [x if isinstance(x, int) else x.data_ptr() for x in partial]
             a.out, a.out_stride, a.out_dtype = None, 0, _lib.HQ_F32
         else:
             if out is None:

@@ -9,14 +9,18 @@ single-GPU result):
 * Sequence shards (very long prefixes) — contiguous 128-token-aligned ranges of the INT4
   prefix and contiguous ranges of the BF16 vertical-line segment per rank; window and
   staging live on the last rank, which also receives the staging flushes.  Each rank runs
-  the decode kernel in partial mode, the un-normalised softmax states ``(m, l, acc)`` are
-  all-gathered (NCCL over NVLink; 66.5 KB per rank at B=4, 32 query heads) and merged by
-  ``hq_lse_merge`` on every rank.
+  the decode kernel in partial mode; the un-normalised softmax states ``(m, l, acc)``
+  (66.5 KB per rank at B=4, 32 query heads) are exchanged and merged on every rank by one
+  kernel that stores them into the peers' buffers over NVLink and waits for theirs
+  (:class:`PeerExchange`, ``hq_peer_exchange_merge``).  ``exchange="nccl"`` keeps the plain
+  form for comparison: one ``all_gather_into_tensor`` followed by ``hq_lse_merge``.
 """
 
 from __future__ import annotations
 
 from typing import List, Optional, Tuple
+
+import ctypes as C
 
 import torch
 
@@ -88,6 +92,93 @@ def shard_layer_sequence(layer, world: int, rank: int):
     return s
 
 
+class PeerExchange:
+    """Exchange buffers of a process group on one node, for ``hq_peer_exchange_merge``.
+
+    Every rank allocates one buffer (``cudaMalloc`` inside the library), the 64-byte CUDA IPC handles are
+    all-gathered through ``torch.distributed`` and each rank maps its peers' buffers.  ``rows`` = batch x query
+    heads of the calls that will use it.  One instance serves any number of layers: calls are numbered by
+    ``next_seq()``, and every rank must make the same calls in the same order on one stream."""
+
+    def __init__(self, rows: int, group=None, timeout_s: float = 2.0):
+        import torch.distributed as dist
+        from . import _lib
+        self._lib = _lib.lib()
+        self.group, self.rows = group, rows
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.timeout_ns = int(timeout_s * 1e9)
+        nbytes = C.c_int64()
+        _lib.check(self._lib.hq_peer_exchange_bytes(self.world, rows, C.byref(nbytes)), "hq_peer_exchange_bytes")
+        self.nbytes = nbytes.value
+        self._local = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        _lib.check(self._lib.hq_peer_buffer_create(self.nbytes, C.byref(self._local), handle), "hq_peer_buffer_create")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for j, h in enumerate(handles):
+            if j == self.rank:
+                self.ptrs.append(self._local.value)
+                continue
+            p = C.c_void_p()
+            _lib.check(self._lib.hq_peer_buffer_open(h, C.byref(p)), "hq_peer_buffer_open")
+            self.ptrs.append(p.value)
+            self._opened.append(p.value)
+        dist.barrier(group=group)          # every buffer exists, is zero-filled and mapped before the first call
+        self.seq = 0
+        self._slots = {}
+        self._args = _lib.PeerExchangeArgs()
+        a = self._args
+        a.struct_bytes, a.world, a.rank, a.rows, a.timeout_ns = C.sizeof(_lib.PeerExchangeArgs), self.world, self.rank, rows, self.timeout_ns
+        for j, ptr in enumerate(self.ptrs):
+            a.bufs[j] = ptr
+
+    def next_seq(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    def slot(self, seq: int) -> Tuple[int, int, int]:
+        """Device addresses of this rank's ``m``, ``l``, ``acc`` for call ``seq`` (where the decode kernel writes)."""
+        from . import _lib
+        got = self._slots.get(seq & 1)
+        if got is None:
+            m, l, acc = C.c_void_p(), C.c_void_p(), C.c_void_p()
+            _lib.check(self._lib.hq_peer_slot(self._local, self.world, self.rows, seq, self.rank, C.byref(m), C.byref(l),
+                                              C.byref(acc)), "hq_peer_slot")
+            got = self._slots[seq & 1] = (m.value, l.value, acc.value)
+        return got
+
+    def exchange_merge(self, seq: int, out: torch.Tensor):
+        from . import _lib
+        a = self._args
+        a.seq, a.out, a.out_stride, a.out_dtype = seq, out.data_ptr(), out.stride(0), _lib.dtype_code(out.dtype)
+        rc = self._lib.hq_peer_exchange_merge(C.byref(a), _lib.stream_ptr(out.device))
+        if rc != 0:
+            _lib.check(rc, "hq_peer_exchange_merge")
+
+    def status(self) -> int:
+        """The buffer's status word (bit 1: a wait for a peer ran out); synchronises the device."""
+        from . import _lib
+        word = C.c_int(0)
+        _lib.check(self._lib.hq_peer_status(self._local, C.byref(word)), "hq_peer_status")
+        return word.value
+
+    def close(self):
+        """Unmap the peers' buffers and free the local one; every rank calls it (it synchronises the group first)."""
+        import torch.distributed as dist
+        if self._local.value is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for ptr in self._opened:
+            self._lib.hq_peer_buffer_close(ptr)
+        dist.barrier(group=self.group)
+        self._lib.hq_peer_buffer_destroy(self._local)
+        self._local = C.c_void_p()
+        self._opened = []
+
+
 class SequenceShardedLayer:
     """One rank's shard of a frozen layer cache plus the merge step.
 
@@ -95,22 +186,51 @@ class SequenceShardedLayer:
     ranges (empty window/staging on every rank but the last).  ``decode_attention``
     returns the full result on every rank."""
 
-    def __init__(self, layer, group=None):
+    def __init__(self, layer, group=None, exchange="nccl"):
+        """``exchange``: a :class:`PeerExchange` (one kernel exchanges and merges over peer memory), or ``"nccl"``
+        (all-gather, then merge)."""
         self.layer = layer
         self.group = group
+        self.exchange = exchange
         self._bufs = None
 
     def append_staging(self, key_states, value_states, is_tail_rank: bool):
         if is_tail_rank:
             self.layer.append_staging(key_states, value_states)
 
-    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int) -> torch.Tensor:
-        """Partial decode over this rank's shard, one all-gather of the per-rank message
-        ``m [rows] | l [rows] | acc [rows, D]`` (the kernel writes straight into it), merge on every rank."""
+    def decode_step(self, query_states, key_states, value_states, kv_repeat: int, is_tail_rank: bool,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``append_staging`` + ``decode_attention``; on the tail rank the decode kernel takes the new token
+        itself (``DStageLayerCache.decode_step``), the other ranks have nothing to append."""
+        return self.decode_attention(query_states, kv_repeat, out=out, new_kv=(key_states, value_states) if is_tail_rank else None)
+
+    def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, out: Optional[torch.Tensor] = None,
+                         new_kv=None) -> torch.Tensor:
+        """Partial decode over this rank's shard, exchange of the per-rank message
+        ``m [rows] | l [rows] | acc [rows, D]`` (the kernel writes straight into it), merge on every rank.
+        ``out``: an optional [B, H_Q, 1, D] tensor with contiguous rows to write into."""
         import torch.distributed as dist
         from . import _lib
         B, H_Q, _, D = query_states.shape
         rows = B * H_Q
+
+        def partial_decode(partial):
+            if new_kv is not None:
+                self.layer.decode_step(query_states, new_kv[0], new_kv[1], kv_repeat, partial=partial)
+            else:
+                self.layer.decode_attention(query_states, kv_repeat, partial=partial)
+
+        if out is None:
+            out = torch.empty(B, H_Q, 1, D, dtype=query_states.dtype, device=query_states.device)
+        out2 = out.view(rows, D)
+        if isinstance(self.exchange, PeerExchange):
+            px = self.exchange
+            if px.rows != rows:
+                raise ValueError(f"the exchange buffers were made for {px.rows} query rows, this call has {rows}")
+            seq = px.next_seq()
+            partial_decode(px.slot(seq))
+            px.exchange_merge(seq, out2)
+            return out
         world = dist.get_world_size(self.group)
         if self._bufs is None or self._bufs[0].numel() != rows * (D + 2):
             dev = query_states.device
@@ -118,12 +238,11 @@ class SequenceShardedLayer:
             self._bufs = (msg, torch.empty(world, rows * (D + 2), dtype=torch.float32, device=dev))
         msg, gathered = self._bufs
         m, l, acc = msg[:rows], msg[rows:2 * rows], msg[2 * rows:].view(rows, D)
-        self.layer.decode_attention(query_states, kv_repeat, partial=(m, l, acc))
+        partial_decode((m, l, acc))
         dist.all_gather_into_tensor(gathered, msg, group=self.group)
-        out = torch.empty(rows, D, dtype=query_states.dtype, device=query_states.device)
         base, fl, stride = gathered.data_ptr(), 4, gathered.stride(0)
         rc = _lib.lib().hq_lse_merge_strided(base, base + fl * rows, base + fl * 2 * rows, stride, stride, stride, world, rows,
-                                             out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0),
-                                             _lib.stream_ptr(out.device))
+                                             out2.data_ptr(), _lib.dtype_code(out2.dtype), out2.stride(0),
+                                             _lib.stream_ptr(out2.device))
         _lib.check(rc, "hq_lse_merge_strided")
-        return out.reshape(B, H_Q, 1, D)
+        return out

@@ -187,6 +187,38 @@ int hq_lse_merge_strided(const float* m, const float* l, const float* acc, int64
 int hq_lse_merge_partial(const float* m, const float* l, const float* acc, int64_t m_stride, int64_t l_stride,
                          int64_t acc_stride, int G, int rows, float* out_m, float* out_l, float* out_acc, void* stream);
 
+/* ---- sequence-sharded decode: exchange + merge over peer memory, one launch per call ----------------------
+ * No counterpart in the reference (its decode call, src/ops/d_stage_kv_cache.py:219-303, runs on one GPU).
+ * Each rank holds a shard of the sequence, runs hq_decode_splitk in partial mode with partial_m / partial_l /
+ * partial_acc pointing into its own exchange buffer (hq_peer_slot), then launches hq_peer_exchange_merge: the
+ * kernel stores the rank's (m, l, acc) rows into every peer's buffer through peer pointers (plain stores over
+ * NVLink, no multicast), raises a per-row flag with the call's sequence number, waits for the peers' flags with a
+ * time limit and writes the merged, normalised result.  A wait that runs out sets bit 1 of the buffer's first
+ * word (the status) and the call completes with whatever arrived.
+ *   bufs[j]: rank j's exchange buffer as addressable from this process (bufs[rank] is the local one);
+ *   seq: 1, 2, 3, ... - the same value on every rank for the same call; rows = batch * query heads.
+ * hq_peer_buffer_create / open / close / destroy allocate an exchange buffer with cudaMalloc (zero-filled) and
+ * share it between the processes of one node through a 64-byte CUDA IPC handle. */
+typedef struct hq_peer_exchange_args {
+  int32_t struct_bytes;
+  int32_t world, rank, rows;
+  uint32_t seq;
+  int32_t out_dtype;
+  int64_t out_stride;          /* elements between output rows */
+  void*   out;                 /* out_dtype [rows, 128] */
+  int64_t timeout_ns;          /* limit of the wait for the peers; 0 = 2 s */
+  void*   bufs[16];
+} hq_peer_exchange_args;
+int hq_peer_exchange_bytes(int world, int rows, int64_t* bytes);
+int hq_peer_slot(void* buf, int world, int rows, uint32_t seq, int rank, float** m, float** l, float** acc);
+int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stream);
+int hq_peer_status(const void* buf, int* status);     /* synchronising read of the local buffer's status word */
+int hq_peer_buffer_create(int64_t bytes, void** ptr, void* handle64);
+int hq_peer_buffer_open(const void* handle64, void** ptr);
+int hq_peer_buffer_close(void* ptr);
+int hq_peer_buffer_destroy(void* ptr);
+
+
 /* --------------------------------------------------------------------------
  * Vertical-line scores: mean of the last `tail_len` queries, dotted with every
  * candidate key.  Replaces the mean/matmul/einsum of compute_vertical_indices
