@@ -35,8 +35,10 @@
 
 namespace hq {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
+// Warps per CTA: 8 with one n8 tile of query heads (GQA ratio <= 8: 2 CTAs per SM at <= 128 registers when the slots
+// are small enough for two); with two tiles (ratios 9..16, 32 fp32 accumulators more per thread) 6, so that 2 CTAs of
+// 192 threads fit an SM at <= 168 registers, or 8 when the slot size allows one CTA per SM anyway.
+__host__ __device__ constexpr int warps_of(int NT, int ctas_per_sm) { return (NT == 2 && ctas_per_sm == 2) ? 6 : 8; }
 constexpr int kSlots = 3;
 constexpr int kUnitQ = 32;                // quantised tokens per unit
 constexpr int kUnitB = 8;                 // BF16 tokens per unit
@@ -236,9 +238,12 @@ __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m
 // ---- the kernel -------------------------------------------------------------
 
 template <int NT, bool kScaleTma, int KB, int VB>
-__global__ void __launch_bounds__(kThreads, NT == 1 ? Fmt<KB, VB>::kCtasPerSm : 1)
+__global__ void __launch_bounds__(warps_of(NT, Fmt<KB, VB>::kCtasPerSm) * 32, Fmt<KB, VB>::kCtasPerSm)
 decode_splitk_kernel(const DecodeParams p) {
   using F = Fmt<KB, VB>;
+  constexpr int kWarps = warps_of(NT, F::kCtasPerSm), kThreads = kWarps * 32;
+  constexpr int kQItems = NT * 8;                                   // (tile, head) pairs whose query row is loaded
+  constexpr int kQIter = (kQItems + kWarps - 1) / kWarps;           // per warp: items warp, warp + kWarps, ...
   constexpr int kSlotBytes = F::kSlot;
   extern __shared__ __align__(128) uint8_t smem[];
   // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same |
@@ -305,14 +310,14 @@ decode_splitk_kernel(const DecodeParams p) {
   // traffic.  Overlapped launch: the previous kernel may still be running, so only stable
   // units are requested; then this grid waits for the previous one to complete (its q,
   // staging and workspace writes are visible after that) and requests the rest.
-  uint2 qraw[NT];
+  uint2 qraw[kQIter];
   auto load_q = [&]() {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int hd = nt * 8 + warp;
-      qraw[nt] = make_uint2(0u, 0u);
-      if (hd < p.R)
-        qraw[nt] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
+    for (int k = 0; k < kQIter; ++k) {
+      const int hd = warp + k * kWarps;
+      qraw[k] = make_uint2(0u, 0u);
+      if (hd < kQItems && hd < p.R)
+        qraw[k] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
     }
   };
   if (!p.overlap) {
@@ -345,12 +350,14 @@ decode_splitk_kernel(const DecodeParams p) {
   // ---- 3. query fragments (B operands of S^T = K Q^T) scattered straight into fragment
   // order, permuted along the channel axis to match the order in which channels fall out
   // of the K loads; plus the per-head offset constant of the biased K codes.
-  // This thread holds channels 4*lane + x (x = 0..3) of head nt*8 + warp.
+  // This thread holds channels 4*lane + x (x = 0..3) of head hd = warp + k * kWarps (tile hd / 8, column hd % 8).
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int hd = nt * 8 + warp;
-    const float qv[4] = {__uint_as_float(qraw[nt].x << 16), __uint_as_float(qraw[nt].x & 0xFFFF0000u),
-                         __uint_as_float(qraw[nt].y << 16), __uint_as_float(qraw[nt].y & 0xFFFF0000u)};
+  for (int k = 0; k < kQIter; ++k) {
+    const int hd = warp + k * kWarps;
+    if (hd >= kQItems) break;
+    const int nt = hd >> 3, col = hd & 7;
+    const float qv[4] = {__uint_as_float(qraw[k].x << 16), __uint_as_float(qraw[k].x & 0xFFFF0000u),
+                         __uint_as_float(qraw[k].y << 16), __uint_as_float(qraw[k].y & 0xFFFF0000u)};
     // Quantised path.  K codes reach the MMA as 1024 + k (h + code) in fp16, h = 2^(bits - 1) (k = 1 for bytes and low
     // nibbles, 16 for high nibbles, 1 / 4 / 16 / 64 for the four 2-bit fields of a byte), so the query value is divided
     // by k and the head's constant sum((1024 + k h) * q / k) is taken off the fp32 score.  The channel that lands in MMA chunk
@@ -380,7 +387,7 @@ decode_splitk_kernel(const DecodeParams p) {
         }
         const float v = fminf(fmaxf(qv[x] * inv, -65504.f), 65504.f);
         const __half hv = __float2half_rn(v);
-        fh[((((nt * 8 + cc) * 2 + r) * 32) + 4 * warp + tt) * 2 + e] = hv;
+        fh[((((nt * 8 + cc) * 2 + r) * 32) + 4 * col + tt) * 2 + e] = hv;
         c += bias * __half2float(hv);
       }
 #pragma unroll
@@ -391,8 +398,8 @@ decode_splitk_kernel(const DecodeParams p) {
     // chunk c = 2 i + odd takes channels 4 odd + (0,1 | 2,3) of it.
     {
       const int j = lane >> 1, tt = j & 3, i = j >> 2, odd = lane & 1;
-      fragB[((nt * 8 + 2 * i + odd) * 2 + 0) * 32 + 4 * warp + tt] = qraw[nt].x;
-      fragB[((nt * 8 + 2 * i + odd) * 2 + 1) * 32 + 4 * warp + tt] = qraw[nt].y;
+      fragB[((nt * 8 + 2 * i + odd) * 2 + 0) * 32 + 4 * col + tt] = qraw[k].x;
+      fragB[((nt * 8 + 2 * i + odd) * 2 + 1) * 32 + 4 * col + tt] = qraw[k].y;
     }
   }
   __syncthreads();
@@ -753,9 +760,10 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   __syncthreads();
 
+  constexpr int kRowThreads = kThreads / 128 * 128;      // threads that write output rows, 128 per row at a time
   const int d = tid & 127;
   const bool single = (p.nsplit == 1);
-  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
@@ -888,7 +896,7 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   }
   __syncthreads();
-  for (int hd = tid >> 7; hd < p.R; hd += kThreads / 128) {
+  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
     float acc = 0.f;
     if (fast) {
       for (int w = hd; w < kWarps; w += p.R) acc += red[(size_t)w * 128 + d];
@@ -912,8 +920,8 @@ decode_splitk_kernel(const DecodeParams p) {
 // ---- host side ---------------------------------------------------------------
 
 static size_t decode_smem_bytes(int NT, int slot_bytes) {
-  return (size_t)kWarps * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 +
-         (size_t)kWarps * kSlots * 8;
+  const int w = warps_of(NT, slot_bytes <= 4224 ? 2 : 1);
+  return (size_t)w * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 + (size_t)w * kSlots * 8;
 }
 
 template <int NT, bool kScaleTma, int KB, int VB>
@@ -929,7 +937,7 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(warps_of(NT, Fmt<KB, VB>::kCtasPerSm) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -1042,7 +1050,8 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   const int sms = sm_count();
   const int slot_bytes = slot_bytes_of(k_bits, v_bits);
   const int NT = a->kv_repeat <= 8 ? 1 : 2;
-  const int ctas_per_sm = (slot_bytes <= 4224 && NT == 1) ? 2 : 1;
+  const int ctas_per_sm = slot_bytes <= 4224 ? 2 : 1;
+  const int kWarps = warps_of(NT, ctas_per_sm);
   int nsplit = a->num_splits;
   if (nsplit <= 0) {
     const int by_grid = (ctas_per_sm * sms) / a->BH_KV;

@@ -3,20 +3,19 @@
 // Sequence sharding (no counterpart in the reference, whose decode call is
 // src/ops/d_stage_kv_cache.py:219-303 on one GPU) leaves every rank with the un-normalised softmax state
 // (m, l, acc) of its shard; the result is their log-sum-exp merge.  Instead of a collective followed by a merge
-// kernel, every rank launches this one kernel: block r writes row r of the local state into slot [rank] of every
-// peer's exchange buffer with plain stores through NVLink (peer pointers, no multicast), publishes it with a
-// system-scope release store of the call's sequence number into the peer's flag word for (rank, r), waits - with a
-// time limit - for the same flag from every peer, and merges row r from the slots of its own buffer.
+// kernel, every rank launches this one kernel.  Thread d of the block of row r stores element d of the row into
+// slot [rank] of every peer's exchange buffer with plain 8-byte stores through NVLink (peer pointers, no multicast):
+// each store carries the fp32 value and the call's sequence number, so a word is valid exactly when its upper half
+// equals the sequence number and no fence or separate flag is needed.  The same thread then polls - with a time
+// limit - the words the peers store for (r, d) in its own buffer and merges them.
 //
 // Exchange buffer of one rank (all ranks use the same layout):
-//   [0, 256)                                  header: word 0 = status (bit 1: a wait ran out)
-//   flags  u32 [2][world][rows_pad]           sequence number of the last call whose row has arrived
-//   slots  f32 [2][world][msg]                msg = m [rows] | l [rows] | acc [rows][128], rounded up to 64 floats
-// Two parities (seq & 1): a rank can be at most one call ahead of a peer, because its wait needs the peer's flags of the
-// same call, and the peer raises them only after its kernel of the call before has finished (stream order).
-//
-// The local partial is produced directly in slot [seq & 1][rank] of the local buffer by the decode kernel
-// (hq_peer_slot gives the pointers for partial_m / partial_l / partial_acc).
+//   [0, 256)                        header: word 0 = status (bit 1: a wait ran out)
+//   local f32 [2][msg]              the rank's own state of a call, m [rows] | l [rows] | acc [rows][128], written by
+//                                   the decode kernel (hq_peer_slot gives partial_m / partial_l / partial_acc)
+//   recv  {f32, u32} [2][world][rows * 130]   what the peers store: the same elements, each with the sequence number
+// Two parities (seq & 1): a rank can be at most one call ahead of a peer, because its wait needs the peer's words of
+// the same call, and the peer stores them only after its kernel of the call before has finished (stream order).
 #include <cstring>
 
 #include "hq_common.cuh"
@@ -27,16 +26,15 @@ constexpr int kPeerMaxWorld = 16;
 constexpr int kPeerHeaderBytes = 256;
 
 struct PeerLayout {
-  int64_t rows_pad, msg, flags_off, slots_off, bytes;
+  int64_t elems, msg, local_off, recv_off, bytes;
 };
 __host__ __device__ inline PeerLayout peer_layout(int world, int rows) {
   PeerLayout L;
-  L.rows_pad = (rows + 31) / 32 * 32;
-  L.msg = ((int64_t)rows * 130 + 63) / 64 * 64;
-  L.flags_off = kPeerHeaderBytes;
-  L.slots_off = L.flags_off + 2 * (int64_t)world * L.rows_pad * 4;
-  L.slots_off = (L.slots_off + 255) / 256 * 256;
-  L.bytes = L.slots_off + 2 * (int64_t)world * L.msg * 4;
+  L.elems = (int64_t)rows * 130;
+  L.msg = (L.elems + 63) / 64 * 64;
+  L.local_off = kPeerHeaderBytes;
+  L.recv_off = L.local_off + 2 * L.msg * 4;
+  L.bytes = L.recv_off + 2 * (int64_t)world * L.msg * 8;
   return L;
 }
 
@@ -48,12 +46,12 @@ struct PeerParams {
   int64_t timeout_ns;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_pair_sys(uint2* p, float v, uint32_t seq) {
+  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -62,62 +60,70 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Grid: at most as many blocks as are resident at once; a block first pushes and publishes all of its rows and only
-// then waits, so every rank's flags are raised without depending on anything another rank does.
+// Poll one word until it carries `seq`; gives up (returns 0 and sets *expired) after the time limit.
+__device__ __forceinline__ float wait_pair(const uint2* p, uint32_t seq, int64_t timeout_ns, bool* expired) {
+  uint2 v = ld_pair_sys(p);
+  if (v.y != seq && !*expired) {
+    const uint64_t t0 = global_timer_ns();
+    int spins = 0;
+    while ((v = ld_pair_sys(p)).y != seq) {
+      if ((++spins & 63) == 0 && (int64_t)(global_timer_ns() - t0) > timeout_ns) { *expired = true; break; }
+    }
+  }
+  return v.y == seq ? __uint_as_float(v.x) : 0.f;
+}
+
+// Grid: at most as many blocks as are resident at once; a block first stores all of its rows to the peers and only
+// then waits, so every rank's words are on their way without depending on anything another rank does.
 __global__ void __launch_bounds__(128)
 peer_exchange_merge_kernel(const PeerParams p) {
   const int d = threadIdx.x;
   const PeerLayout L = peer_layout(p.world, p.rows);
   const int par = (int)(p.seq & 1u);
   uint8_t* mine = p.bufs[p.rank];
-  const int64_t slot_of_me = ((int64_t)par * p.world + p.rank) * L.msg;
-  const float* my_slot = reinterpret_cast<const float*>(mine + L.slots_off) + slot_of_me;
-  uint8_t* peer = (d < p.world && d != p.rank) ? p.bufs[d] : nullptr;     // thread d publishes to / waits for rank d
+  const float* local = reinterpret_cast<const float*>(mine + L.local_off) + (int64_t)par * L.msg;
+  const int64_t my_recv = ((int64_t)par * p.world + p.rank) * L.msg;      // slot [par][rank] in a peer's recv region
 
   for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
-    const float my_m = my_slot[r], my_l = my_slot[p.rows + r], my_a = my_slot[2 * (int64_t)p.rows + (int64_t)r * 128 + d];
-    // 1. push row r to every peer
+    const int64_t ia = 2 * (int64_t)p.rows + (int64_t)r * 128 + d;
+    const float my_a = local[ia];
+    float my_ml = 0.f;
+    if (d < 2) my_ml = local[d * p.rows + r];                              // thread 0: m, thread 1: l
     for (int j = 0; j < p.world; ++j) {
       if (j == p.rank) continue;
-      float* dst = reinterpret_cast<float*>(p.bufs[j] + L.slots_off) + slot_of_me;
-      dst[2 * (int64_t)p.rows + (int64_t)r * 128 + d] = my_a;
-      if (d == 0) { dst[r] = my_m; dst[p.rows + r] = my_l; }
-    }
-    __syncthreads();
-    // 2. publish: the barrier orders every thread's stores before thread d's fence + release store
-    if (peer != nullptr) {
-      __threadfence_system();
-      st_release_sys(reinterpret_cast<uint32_t*>(peer + L.flags_off) + ((int64_t)par * p.world + p.rank) * L.rows_pad + r, p.seq);
+      uint2* dst = reinterpret_cast<uint2*>(p.bufs[j] + L.recv_off) + my_recv;
+      st_pair_sys(dst + ia, my_a, p.seq);
+      if (d < 2) st_pair_sys(dst + d * p.rows + r, my_ml, p.seq);
     }
   }
 
-  const float* slots = reinterpret_cast<const float*>(mine + L.slots_off) + (int64_t)par * p.world * L.msg;
+  const uint2* recv = reinterpret_cast<const uint2*>(mine + L.recv_off) + (int64_t)par * p.world * L.msg;
+  bool expired = false;
   for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
-    // 3. wait for row r of every peer, with a time limit
-    if (peer != nullptr) {
-      const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + L.flags_off) + ((int64_t)par * p.world + d) * L.rows_pad + r;
-      const uint64_t t0 = global_timer_ns();
-      bool ok = true;
-      while (ld_acquire_sys(flag) != p.seq) {
-        if ((int64_t)(global_timer_ns() - t0) > p.timeout_ns) { ok = false; break; }
-        __nanosleep(20);
-      }
-      if (!ok) atomicOr(reinterpret_cast<int*>(mine), 2);
-    }
-    __syncthreads();
-    // 4. merge row r over the ranks' slots in the local buffer
+    const int64_t ia = 2 * (int64_t)p.rows + (int64_t)r * 128 + d;
+    float mj[kPeerMaxWorld];
     float M = -INFINITY;
-    for (int j = 0; j < p.world; ++j) M = fmaxf(M, __ldcg(slots + j * L.msg + r));
+#pragma unroll
+    for (int j = 0; j < kPeerMaxWorld; ++j) {
+      if (j < p.world) {
+        mj[j] = j == p.rank ? local[r] : wait_pair(recv + j * L.msg + r, p.seq, p.timeout_ns, &expired);
+        M = fmaxf(M, mj[j]);
+      }
+    }
     float num = 0.f, den = 0.f;
-    for (int j = 0; j < p.world; ++j) {
-      const float* s = slots + j * L.msg;
-      const float mj = __ldcg(s + r);
-      const float w = (mj == -INFINITY) ? 0.f : ex2f(mj - M);
-      num += w * __ldcg(s + 2 * (int64_t)p.rows + (int64_t)r * 128 + d);
-      den += w * __ldcg(s + p.rows + r);
+#pragma unroll
+    for (int j = 0; j < kPeerMaxWorld; ++j) {
+      if (j < p.world) {
+        const float w = (mj[j] == -INFINITY) ? 0.f : ex2f(mj[j] - M);
+        const float lj = j == p.rank ? local[p.rows + r] : wait_pair(recv + j * L.msg + p.rows + r, p.seq, p.timeout_ns, &expired);
+        const float aj = j == p.rank ? local[ia] : wait_pair(recv + j * L.msg + ia, p.seq, p.timeout_ns, &expired);
+        num += w * aj;
+        den += w * lj;
+      }
     }
     store_out(p.out, (int64_t)r * p.out_stride + d, den > 0.f ? num / den : 0.f, p.out_dtype);
   }
+  if (expired) atomicOr(reinterpret_cast<int*>(mine), 2);
 }
 
 }  // namespace hq
@@ -130,13 +136,22 @@ extern "C" int hq_peer_exchange_bytes(int world, int rows, int64_t* bytes) {
   return HQ_OK;
 }
 
-extern "C" int hq_peer_slot(void* buf, int world, int rows, uint32_t seq, int rank, float** m, float** l, float** acc) {
+extern "C" int hq_peer_slot(void* buf, int world, int rows, uint32_t seq, float** m, float** l, float** acc) {
   using namespace hq;
-  HQ_REQUIRE(buf && m && l && acc && world >= 1 && world <= kPeerMaxWorld && rank >= 0 && rank < world && rows >= 1,
-             HQ_ERR_INVALID, "hq_peer_slot: bad argument");
+  HQ_REQUIRE(buf && m && l && acc && world >= 1 && world <= kPeerMaxWorld && rows >= 1, HQ_ERR_INVALID,
+             "hq_peer_slot: bad argument");
   const PeerLayout L = peer_layout(world, rows);
-  float* s = reinterpret_cast<float*>((uint8_t*)buf + L.slots_off) + ((int64_t)(seq & 1u) * world + rank) * L.msg;
+  float* s = reinterpret_cast<float*>((uint8_t*)buf + L.local_off) + (int64_t)(seq & 1u) * L.msg;
   *m = s; *l = s + rows; *acc = s + 2 * (int64_t)rows;
+  return HQ_OK;
+}
+
+extern "C" int hq_peer_recv_slot(void* buf, int world, int rows, uint32_t seq, int src_rank, void** words) {
+  using namespace hq;
+  HQ_REQUIRE(buf && words && world >= 1 && world <= kPeerMaxWorld && src_rank >= 0 && src_rank < world && rows >= 1,
+             HQ_ERR_INVALID, "hq_peer_recv_slot: bad argument");
+  const PeerLayout L = peer_layout(world, rows);
+  *words = (uint8_t*)buf + L.recv_off + (((int64_t)(seq & 1u) * world + src_rank) * L.msg) * 8;
   return HQ_OK;
 }
 
@@ -158,7 +173,7 @@ extern "C" int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stre
   p.world = a->world; p.rank = a->rank; p.rows = a->rows; p.seq = a->seq;
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_stride = a->out_stride;
   p.timeout_ns = a->timeout_ns > 0 ? a->timeout_ns : 2000000000ll;
-  const int resident = 8 * sm_count();          // 128-thread blocks with 40 registers: at least 8 per SM
+  const int resident = 8 * sm_count();          // 128-thread blocks: at least 8 per SM
   peer_exchange_merge_kernel<<<a->rows < resident ? a->rows : resident, 128, 0, (cudaStream_t)stream>>>(p);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;

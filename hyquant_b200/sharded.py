@@ -144,7 +144,7 @@ class PeerExchange:
         got = self._slots.get(seq & 1)
         if got is None:
             m, l, acc = C.c_void_p(), C.c_void_p(), C.c_void_p()
-            _lib.check(self._lib.hq_peer_slot(self._local, self.world, self.rows, seq, self.rank, C.byref(m), C.byref(l),
+            _lib.check(self._lib.hq_peer_slot(self._local, self.world, self.rows, seq, C.byref(m), C.byref(l),
                                               C.byref(acc)), "hq_peer_slot")
             got = self._slots[seq & 1] = (m.value, l.value, acc.value)
         return got

@@ -191,9 +191,9 @@ int hq_lse_merge_partial(const float* m, const float* l, const float* acc, int64
  * No counterpart in the reference (its decode call, src/ops/d_stage_kv_cache.py:219-303, runs on one GPU).
  * Each rank holds a shard of the sequence, runs hq_decode_splitk in partial mode with partial_m / partial_l /
  * partial_acc pointing into its own exchange buffer (hq_peer_slot), then launches hq_peer_exchange_merge: the
- * kernel stores the rank's (m, l, acc) rows into every peer's buffer through peer pointers (plain stores over
- * NVLink, no multicast), raises a per-row flag with the call's sequence number, waits for the peers' flags with a
- * time limit and writes the merged, normalised result.  A wait that runs out sets bit 1 of the buffer's first
+ * kernel stores the rank's (m, l, acc) elements into every peer's buffer through peer pointers (plain 8-byte stores
+ * over NVLink, no multicast; each carries the value and the call's sequence number), polls its own buffer for the
+ * peers' elements with a time limit and writes the merged, normalised result.  A wait that runs out sets bit 1 of the buffer's first
  * word (the status) and the call completes with whatever arrived.
  *   bufs[j]: rank j's exchange buffer as addressable from this process (bufs[rank] is the local one);
  *   seq: 1, 2, 3, ... - the same value on every rank for the same call; rows = batch * query heads.
@@ -210,7 +210,10 @@ typedef struct hq_peer_exchange_args {
   void*   bufs[16];
 } hq_peer_exchange_args;
 int hq_peer_exchange_bytes(int world, int rows, int64_t* bytes);
-int hq_peer_slot(void* buf, int world, int rows, uint32_t seq, int rank, float** m, float** l, float** acc);
+int hq_peer_slot(void* buf, int world, int rows, uint32_t seq, float** m, float** l, float** acc);
+/* Where rank src_rank's elements of call seq arrive in `buf`: rows * 130 words of {fp32 value, uint32 seq}, in the
+ * order m [rows] | l [rows] | acc [rows][128] (for tests and tools; the kernel addresses it itself). */
+int hq_peer_recv_slot(void* buf, int world, int rows, uint32_t seq, int src_rank, void** words);
 int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stream);
 int hq_peer_status(const void* buf, int* status);     /* synchronising read of the local buffer's status word */
 int hq_peer_buffer_create(int64_t bytes, void** ptr, void* handle64);

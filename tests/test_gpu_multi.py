@@ -118,17 +118,29 @@ def _peer_buffers(world, rows):
     return [torch.zeros(n.value, dtype=torch.uint8, device="cuda") for _ in range(world)]
 
 
-def _slot_views(buf, world, rows, seq, src):
-    """Torch views of (flags, m, l, acc) of rank ``src`` for call ``seq`` inside an exchange buffer."""
+def _local_views(buf, world, rows, seq):
+    """Torch views of a rank's own (m, l, acc) of call ``seq`` inside its exchange buffer."""
     import ctypes as C
     from hyquant_b200 import _lib
     m, l, acc = C.c_void_p(), C.c_void_p(), C.c_void_p()
-    _lib.check(_lib.lib().hq_peer_slot(buf.data_ptr(), world, rows, seq, src, C.byref(m), C.byref(l), C.byref(acc)), "hq_peer_slot")
+    _lib.check(_lib.lib().hq_peer_slot(buf.data_ptr(), world, rows, seq, C.byref(m), C.byref(l), C.byref(acc)), "hq_peer_slot")
     f32 = buf.view(torch.float32)
     o = (m.value - buf.data_ptr()) // 4
-    rows_pad = (rows + 31) // 32 * 32
-    fo = 256 // 4 + ((seq & 1) * world + src) * rows_pad
-    return buf.view(torch.int32)[fo:fo + rows], f32[o:o + rows], f32[o + rows:o + 2 * rows], f32[o + 2 * rows:o + 130 * rows].view(rows, 128)
+    return f32[o:o + rows], f32[o + rows:o + 2 * rows], f32[o + 2 * rows:o + 130 * rows].view(rows, 128)
+
+
+def _recv_view(buf, world, rows, seq, src):
+    """Torch view [rows * 130, 2] (int32: value bits, sequence number) of what rank ``src`` stores for call ``seq``."""
+    import ctypes as C
+    from hyquant_b200 import _lib
+    w = C.c_void_p()
+    _lib.check(_lib.lib().hq_peer_recv_slot(buf.data_ptr(), world, rows, seq, src, C.byref(w)), "hq_peer_recv_slot")
+    o = (w.value - buf.data_ptr()) // 4
+    return buf.view(torch.int32)[o:o + 2 * 130 * rows].view(130 * rows, 2)
+
+
+def _message(m, l, acc):
+    return torch.cat([m, l, acc.reshape(-1)]).contiguous().view(torch.int32)
 
 
 def _run_exchange(bufs, world, rank, rows, seq, out, timeout_ns=0):
@@ -144,8 +156,8 @@ def _run_exchange(bufs, world, rank, rows, seq, out, timeout_ns=0):
 
 @pytest.mark.parametrize("rows,world", [(16, 2), (128, 4), (1500, 3)])
 def test_peer_exchange_kernel_one_gpu(rows, world):
-    """The exchange + merge kernel of rank 0 with the peers' buffers in this GPU's own memory and their rows and flags
-    already in place (no second kernel to wait for): it must deliver rank 0's rows and flags to every peer buffer
+    """The exchange + merge kernel of rank 0 with the peers' buffers in this GPU's own memory and their words
+    already in place (no second kernel to wait for): it must deliver rank 0's words to every peer buffer
     and write the log-sum-exp merge of all ranks' partials."""
     import hyquant_b200 as hq
     g = torch.Generator(device="cuda").manual_seed(rows + world)
@@ -158,23 +170,24 @@ def test_peer_exchange_kernel_one_gpu(rows, world):
     want = hq.lse_merge(m, l, acc, out_dtype=torch.float32)
     bufs = _peer_buffers(world, rows)
     for seq in (1, 2, 3):
-        for src in range(world):
-            fl, sm, sl, sa = _slot_views(bufs[0], world, rows, seq, src)
-            sm.copy_(m[src]); sl.copy_(l[src]); sa.copy_(acc[src])
-            if src != 0:
-                fl.fill_(seq)
+        lm, ll, la = _local_views(bufs[0], world, rows, seq)
+        lm.copy_(m[0]); ll.copy_(l[0]); la.copy_(acc[0])
+        for src in range(1, world):
+            rv = _recv_view(bufs[0], world, rows, seq, src)
+            rv[:, 0] = _message(m[src], l[src], acc[src])
+            rv[:, 1] = seq
         out = torch.empty(rows, 128, dtype=torch.float32, device="cuda")
         _run_exchange(bufs, world, 0, rows, seq, out)
         torch.cuda.synchronize()
         assert torch.allclose(out, want, rtol=1e-5, atol=1e-6)
         for j in range(1, world):
-            fl, sm, sl, sa = _slot_views(bufs[j], world, rows, seq, 0)
-            assert torch.equal(fl, torch.full_like(fl, seq)) and torch.equal(sm, m[0]) and torch.equal(sl, l[0]) and torch.equal(sa, acc[0])
+            rv = _recv_view(bufs[j], world, rows, seq, 0)
+            assert torch.equal(rv[:, 0], _message(m[0], l[0], acc[0])) and bool((rv[:, 1] == seq).all())
         assert int(bufs[0].view(torch.int32)[0]) == 0
 
 
 def test_peer_exchange_wait_runs_out():
-    """A peer that never raises its flags: the wait ends at its time limit, bit 1 of the status word is set and
+    """A peer that never stores its words: the wait ends at its time limit, bit 1 of the status word is set and
     the device stays usable."""
     world, rows = 2, 8
     bufs = _peer_buffers(world, rows)
