@@ -56,6 +56,8 @@ class DecodeArgs(C.Structure):
         ("partial_m", C.c_void_p), ("partial_l", C.c_void_p), ("partial_acc", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("kn_stride", C.c_int64), ("vn_stride", C.c_int64),
+        ("peer_bufs", C.c_void_p), ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_seq", C.c_uint32),
+        ("peer_reserved", C.c_int32), ("peer_timeout_ns", C.c_int64),
     ]
 
 

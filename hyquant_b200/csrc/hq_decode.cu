@@ -32,6 +32,7 @@
 // workspace with an atomic ticket: the last CTA of a head does the
 // log-sum-exp merge and writes the output, so there is no second launch.
 #include "hq_common.cuh"
+#include "hq_peer.cuh"
 
 namespace hq {
 
@@ -61,6 +62,7 @@ struct DecodeParams {
   float sml;                              // sm_scale * log2(e)
   void* out; int64_t out_stride;
   float* pm; float* pl; float* pacc;      // partial mode outputs (or null)
+  PeerGroup peer;                         // peer.world > 1: exchange the state with the other sequence shards and merge
   __nv_bfloat16* stage_k; __nv_bfloat16* stage_v;   // staging buffers, written only when the call carries a new token
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
   int overlap;                            // launched with programmatic stream serialisation
@@ -233,6 +235,94 @@ __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m
         for (int mt = 0; mt < 8; ++mt) { O[nt][mt][j] *= alpha; O[nt][mt][2 + j] *= alpha; }
       }
   }
+}
+
+// Sequence-sharded call: channel d of query row `row` of this shard's un-normalised state goes to every peer, the
+// peers' arrive in this rank's exchange buffer, and the merged, normalised value is the output.
+// The rows of a thread are handled in two passes - first every row is sent, then every row is awaited - so that the
+// one-way NVLink latency is paid once per call and not once per row.
+__device__ __forceinline__ void peer_send(const DecodeParams& p, int row, int d, float m, float l, float acc) {
+  const PeerLayout L = peer_layout(p.peer.world, p.peer.rows);
+  peer_push(p.peer, L, 2 * (int64_t)p.peer.rows + (int64_t)row * 128 + d, acc);
+  if (d == 0) { peer_push(p.peer, L, row, m); peer_push(p.peer, L, p.peer.rows + row, l); }
+}
+// Floats of shared-memory scratch peer_receive_all needs for `world` ranks and R query heads per kv head.
+__host__ __device__ constexpr int peer_scratch_floats(int world, int R) { return 3 * (world - 1) * R + 3 * R + R * 128; }
+
+// Second pass for the R rows of kv-head `head`, by the whole CTA: (1) the peers' m and l words are polled by all threads
+// in parallel into shared memory, (2) one thread per row turns them into merge weights and the denominator, (3) every
+// thread keeps several acc loads in flight over its (row, peer) pairs and accumulates into its own shared-memory
+// cells.  `local(hd, d, m, l, acc)` recomputes this rank's values of row hd, channel d.
+template <int kThreads, class LocalFn>
+__device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* sm, int head, int tid, LocalFn local) {
+  const PeerGroup& g = p.peer;
+  const PeerLayout L = peer_layout(g.world, g.rows);
+  const int R = p.R, np = g.world - 1;
+  float* s_m = sm; float* s_l = s_m + np * R; float* s_w = s_l + np * R;
+  float* s_M = s_w + np * R; float* s_den = s_M + R; float* s_w0 = s_den + R; float* s_acc = s_w0 + R;
+  const uint2* recv = reinterpret_cast<const uint2*>(g.bufs[g.rank] + L.recv_off) + (int64_t)(g.seq & 1u) * g.world * L.msg;
+  const int64_t row0 = (int64_t)head * R;
+  bool expired = false;
+  for (int idx = tid; idx < np * R * 2; idx += kThreads) {
+    const int jj = idx / (2 * R), rem = idx - jj * 2 * R, which = rem >= R ? 1 : 0, row = rem - which * R;
+    const int j = jj < g.rank ? jj : jj + 1;
+    const float v = wait_pair(recv + j * L.msg + (int64_t)which * g.rows + row0 + row, g.seq, g.timeout_ns, &expired);
+    (which ? s_l : s_m)[jj * R + row] = v;
+  }
+  __syncthreads();
+  if (tid < R) {
+    float m, l, a;
+    local(tid, 0, m, l, a);
+    float M = m;
+    for (int jj = 0; jj < np; ++jj) M = fmaxf(M, s_m[jj * R + tid]);
+    const float w0 = (m == -INFINITY) ? 0.f : ex2f(m - M);
+    float den = w0 * l;
+    for (int jj = 0; jj < np; ++jj) {
+      const float mj = s_m[jj * R + tid];
+      const float w = (mj == -INFINITY) ? 0.f : ex2f(mj - M);
+      s_w[jj * R + tid] = w;
+      den += w * s_l[jj * R + tid];
+    }
+    s_w0[tid] = w0; s_den[tid] = den;
+  }
+  __syncthreads();
+  constexpr int kRowThreads = kThreads / 128 * 128, G = kRowThreads / 128;
+  if (tid < kRowThreads) {
+    const int d = tid & 127, g0 = tid >> 7;
+    int mine = 0;
+    for (int hd = g0; hd < R; hd += G, ++mine) {
+      float m, l, a;
+      local(hd, d, m, l, a);
+      s_acc[hd * 128 + d] = s_w0[hd] * a;
+    }
+    const int n_items = mine * np;
+    constexpr int kFly = 8;
+    for (int it0 = 0; it0 < n_items; it0 += kFly) {
+      uint2 v[kFly];
+#pragma unroll
+      for (int u = 0; u < kFly; ++u) {
+        const int it = it0 + u < n_items ? it0 + u : n_items - 1;
+        const int k = it / np, jj = it - k * np, hd = g0 + k * G, j = jj < g.rank ? jj : jj + 1;
+        v[u] = ld_pair_sys(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + d);
+      }
+#pragma unroll
+      for (int u = 0; u < kFly; ++u) {
+        const int it = it0 + u;
+        if (it < n_items) {
+          const int k = it / np, jj = it - k * np, hd = g0 + k * G, j = jj < g.rank ? jj : jj + 1;
+          const float val = v[u].y == g.seq ? __uint_as_float(v[u].x)
+                                            : wait_pair(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + d, g.seq,
+                                                        g.timeout_ns, &expired);
+          s_acc[hd * 128 + d] += s_w[jj * R + hd] * val;
+        }
+      }
+    }
+    for (int hd = g0; hd < R; hd += G) {
+      const float den = s_den[hd];
+      store_out(p.out, (row0 + hd) * p.out_stride + d, den > 0.f ? s_acc[hd * 128 + d] / den : 0.f, p.out_dtype);
+    }
+  }
+  if (expired) atomicOr(reinterpret_cast<int*>(g.bufs[g.rank]), 2);
 }
 
 // ---- the kernel -------------------------------------------------------------
@@ -763,21 +853,29 @@ decode_splitk_kernel(const DecodeParams p) {
   constexpr int kRowThreads = kThreads / 128 * 128;      // threads that write output rows, 128 per row at a time
   const int d = tid & 127;
   const bool single = (p.nsplit == 1);
-  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
-    float M = -INFINITY;
+  const bool peers = p.peer.world > 1;
+  // this CTA's merge of its warps for head hd, channel dd
+  auto cta_row = [&](int hd, int dd, float& M, float& l, float& acc) {
+    M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
-    float acc = 0.f, l = 0.f;
+    acc = 0.f; l = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
       const float mw = mrg_m[w * NT * 8 + hd];
       const float wt = (mw == -INFINITY) ? 0.f : ex2f(mw - M);
-      acc += wt * mrg_o[((size_t)(w * NT * 8 + hd)) * 128 + d];
+      acc += wt * mrg_o[((size_t)(w * NT * 8 + hd)) * 128 + dd];
       l += wt * mrg_l[w * NT * 8 + hd];
     }
+  };
+  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
+    float M, l, acc;
+    cta_row(hd, d, M, l, acc);
     const int64_t qrow = (int64_t)head * p.R + hd;
     if (single) {
-      if (p.pacc) {
+      if (peers) {
+        peer_send(p, (int)qrow, d, M, l, acc);       // every row is sent before any is awaited
+      } else if (p.pacc) {
         p.pacc[qrow * 128 + d] = acc;
         if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
       } else {
@@ -789,7 +887,10 @@ decode_splitk_kernel(const DecodeParams p) {
       if (d == 0) { p.ws_m[prow] = M; p.ws_l[prow] = l; }
     }
   }
-  if (single) return;
+  if (single) {
+    if (peers) peer_receive_all<kThreads>(p, mrg_o + (size_t)kWarps * NT * 8 * 128, head, tid, cta_row);
+    return;
+  }
 
   // ======================= merge the splits (last CTA of the head) ===========
   // Ticket: the CTA barrier orders every thread's partial stores before thread 0's
@@ -896,23 +997,31 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   }
   __syncthreads();
-  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
-    float acc = 0.f;
+  // the head's merge of all splits for head hd, channel dd
+  auto head_row = [&](int hd, int dd, float& M, float& l, float& acc) {
+    acc = 0.f;
     if (fast) {
-      for (int w = hd; w < kWarps; w += p.R) acc += red[(size_t)w * 128 + d];
+      for (int w = hd; w < kWarps; w += p.R) acc += red[(size_t)w * 128 + dd];
     } else {
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + d];
+      for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + dd];
     }
-    const float l = sm_L[hd];
+    M = sm_M[hd]; l = sm_L[hd];
+  };
+  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
+    float M, l, acc;
+    head_row(hd, d, M, l, acc);
     const int64_t qrow = (int64_t)head * p.R + hd;
-    if (p.pacc) {
+    if (peers) {
+      peer_send(p, (int)qrow, d, M, l, acc);
+    } else if (p.pacc) {
       p.pacc[qrow * 128 + d] = acc;
-      if (d == 0) { p.pm[qrow] = sm_M[hd]; p.pl[qrow] = l; }
+      if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
     } else {
       store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
     }
   }
+  if (peers) peer_receive_all<kThreads>(p, red + (size_t)kWarps * p.R * 128, head, tid, head_row);
   if (tid == 0) p.counters[head] = 0;   // ready for the next launch on this workspace
 }
 
@@ -1045,6 +1154,21 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.sml = a->sm_scale * 1.44269504f;
   p.out = a->out; p.out_stride = a->out_stride;
   p.pm = a->partial_m; p.pl = a->partial_l; p.pacc = a->partial_acc;
+  p.peer.world = 0;
+  if (a->peer_world > 1) {
+    HQ_REQUIRE(!partial && a->out != nullptr, HQ_ERR_INVALID, "hq_decode_splitk: a peer exchange writes the merged result to out");
+    HQ_REQUIRE(a->peer_world <= kPeerMaxWorld && a->peer_rank >= 0 && a->peer_rank < a->peer_world && a->peer_bufs != nullptr &&
+                   a->peer_seq != 0, HQ_ERR_INVALID, "hq_decode_splitk: peer_world %d peer_rank %d (seq starts at 1)",
+               a->peer_world, a->peer_rank);
+    for (int j = 0; j < a->peer_world; ++j) {
+      HQ_REQUIRE(a->peer_bufs[j] != nullptr && ((uintptr_t)a->peer_bufs[j] & 255) == 0, HQ_ERR_ALIGNMENT,
+                 "hq_decode_splitk: peer buffer %d null or not 256-byte aligned", j);
+      p.peer.bufs[j] = (uint8_t*)a->peer_bufs[j];
+    }
+    p.peer.world = a->peer_world; p.peer.rank = a->peer_rank; p.peer.seq = a->peer_seq;
+    p.peer.rows = a->BH_KV * a->kv_repeat;
+    p.peer.timeout_ns = a->peer_timeout_ns > 0 ? a->peer_timeout_ns : 2000000000ll;
+  }
 
   // splits: one wave of CTAs (as many per SM as the slot size of this bit-width pair lets reside), at least ~2 units per warp
   const int sms = sm_count();
@@ -1079,7 +1203,8 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.ws_acc = (float*)(((uintptr_t)p.ws_acc + 15) & ~(uintptr_t)15);
 
   // the split-merge staging reuses the ring: weights + l (2 nsplit R) + 32 + warp partial sums (8 R 128) floats
-  HQ_REQUIRE(((size_t)2 * nsplit * a->kv_repeat + 36 + (size_t)kWarps * a->kv_repeat * 128) * 4 <=
+  const size_t peer_floats = p.peer.world > 1 ? (size_t)peer_scratch_floats(p.peer.world, a->kv_repeat) : 0;
+  HQ_REQUIRE(((size_t)2 * nsplit * a->kv_repeat + 36 + (size_t)kWarps * NT * 8 * 128 + 2 * (size_t)kWarps * NT * 8 + peer_floats) * 4 <=
                  (size_t)kWarps * kSlots * slot_bytes,
              HQ_ERR_UNSUPPORTED, "hq_decode_splitk: too many splits (%d)", nsplit);
   // scales can ride in the bulk copies when every 32-token group of a row starts on a

@@ -18,112 +18,35 @@
 // the same call, and the peer stores them only after its kernel of the call before has finished (stream order).
 #include <cstring>
 
-#include "hq_common.cuh"
+#include "hq_peer.cuh"
 
 namespace hq {
 
-constexpr int kPeerMaxWorld = 16;
-constexpr int kPeerHeaderBytes = 256;
-
-struct PeerLayout {
-  int64_t elems, msg, local_off, recv_off, bytes;
-};
-__host__ __device__ inline PeerLayout peer_layout(int world, int rows) {
-  PeerLayout L;
-  L.elems = (int64_t)rows * 130;
-  L.msg = (L.elems + 63) / 64 * 64;
-  L.local_off = kPeerHeaderBytes;
-  L.recv_off = L.local_off + 2 * L.msg * 4;
-  L.bytes = L.recv_off + 2 * (int64_t)world * L.msg * 8;
-  return L;
-}
-
 struct PeerParams {
-  uint8_t* bufs[kPeerMaxWorld];
-  int world, rank, rows;
-  uint32_t seq;
+  PeerGroup g;
   void* out; int out_dtype; int64_t out_stride;
-  int64_t timeout_ns;
 };
-
-__device__ __forceinline__ void st_pair_sys(uint2* p, float v, uint32_t seq) {
-  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
-}
-__device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Poll one word until it carries `seq`; gives up (returns 0 and sets *expired) after the time limit.
-__device__ __forceinline__ float wait_pair(const uint2* p, uint32_t seq, int64_t timeout_ns, bool* expired) {
-  uint2 v = ld_pair_sys(p);
-  if (v.y != seq && !*expired) {
-    const uint64_t t0 = global_timer_ns();
-    int spins = 0;
-    while ((v = ld_pair_sys(p)).y != seq) {
-      if ((++spins & 63) == 0 && (int64_t)(global_timer_ns() - t0) > timeout_ns) { *expired = true; break; }
-    }
-  }
-  return v.y == seq ? __uint_as_float(v.x) : 0.f;
-}
 
 // Grid: at most as many blocks as are resident at once; a block first stores all of its rows to the peers and only
 // then waits, so every rank's words are on their way without depending on anything another rank does.
 __global__ void __launch_bounds__(128)
 peer_exchange_merge_kernel(const PeerParams p) {
   const int d = threadIdx.x;
-  const PeerLayout L = peer_layout(p.world, p.rows);
-  const int par = (int)(p.seq & 1u);
-  uint8_t* mine = p.bufs[p.rank];
-  const float* local = reinterpret_cast<const float*>(mine + L.local_off) + (int64_t)par * L.msg;
-  const int64_t my_recv = ((int64_t)par * p.world + p.rank) * L.msg;      // slot [par][rank] in a peer's recv region
+  const PeerGroup& g = p.g;
+  const PeerLayout L = peer_layout(g.world, g.rows);
+  const float* local = reinterpret_cast<const float*>(g.bufs[g.rank] + L.local_off) + (int64_t)(g.seq & 1u) * L.msg;
 
-  for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
-    const int64_t ia = 2 * (int64_t)p.rows + (int64_t)r * 128 + d;
-    const float my_a = local[ia];
-    float my_ml = 0.f;
-    if (d < 2) my_ml = local[d * p.rows + r];                              // thread 0: m, thread 1: l
-    for (int j = 0; j < p.world; ++j) {
-      if (j == p.rank) continue;
-      uint2* dst = reinterpret_cast<uint2*>(p.bufs[j] + L.recv_off) + my_recv;
-      st_pair_sys(dst + ia, my_a, p.seq);
-      if (d < 2) st_pair_sys(dst + d * p.rows + r, my_ml, p.seq);
-    }
+  for (int r = blockIdx.x; r < g.rows; r += gridDim.x) {
+    const int64_t ia = 2 * (int64_t)g.rows + (int64_t)r * 128 + d;
+    peer_push(g, L, ia, local[ia]);
+    if (d < 2) peer_push(g, L, d * g.rows + r, local[d * g.rows + r]);      // thread 0: m, thread 1: l
   }
-
-  const uint2* recv = reinterpret_cast<const uint2*>(mine + L.recv_off) + (int64_t)par * p.world * L.msg;
   bool expired = false;
-  for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
-    const int64_t ia = 2 * (int64_t)p.rows + (int64_t)r * 128 + d;
-    float mj[kPeerMaxWorld];
-    float M = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kPeerMaxWorld; ++j) {
-      if (j < p.world) {
-        mj[j] = j == p.rank ? local[r] : wait_pair(recv + j * L.msg + r, p.seq, p.timeout_ns, &expired);
-        M = fmaxf(M, mj[j]);
-      }
-    }
-    float num = 0.f, den = 0.f;
-#pragma unroll
-    for (int j = 0; j < kPeerMaxWorld; ++j) {
-      if (j < p.world) {
-        const float w = (mj[j] == -INFINITY) ? 0.f : ex2f(mj[j] - M);
-        const float lj = j == p.rank ? local[p.rows + r] : wait_pair(recv + j * L.msg + p.rows + r, p.seq, p.timeout_ns, &expired);
-        const float aj = j == p.rank ? local[ia] : wait_pair(recv + j * L.msg + ia, p.seq, p.timeout_ns, &expired);
-        num += w * aj;
-        den += w * lj;
-      }
-    }
-    store_out(p.out, (int64_t)r * p.out_stride + d, den > 0.f ? num / den : 0.f, p.out_dtype);
+  for (int r = blockIdx.x; r < g.rows; r += gridDim.x) {
+    const float v = peer_merge(g, L, r, d, local[r], local[g.rows + r], local[2 * (int64_t)g.rows + (int64_t)r * 128 + d], &expired);
+    store_out(p.out, (int64_t)r * p.out_stride + d, v, p.out_dtype);
   }
-  if (expired) atomicOr(reinterpret_cast<int*>(mine), 2);
+  if (expired) atomicOr(reinterpret_cast<int*>(g.bufs[g.rank]), 2);
 }
 
 }  // namespace hq
@@ -168,11 +91,11 @@ extern "C" int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stre
   for (int j = 0; j < a->world; ++j) {
     HQ_REQUIRE(a->bufs[j] != nullptr && ((uintptr_t)a->bufs[j] & 255) == 0, HQ_ERR_ALIGNMENT,
                "hq_peer_exchange_merge: buffer %d null or not 256-byte aligned", j);
-    p.bufs[j] = (uint8_t*)a->bufs[j];
+    p.g.bufs[j] = (uint8_t*)a->bufs[j];
   }
-  p.world = a->world; p.rank = a->rank; p.rows = a->rows; p.seq = a->seq;
+  p.g.world = a->world; p.g.rank = a->rank; p.g.rows = a->rows; p.g.seq = a->seq;
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_stride = a->out_stride;
-  p.timeout_ns = a->timeout_ns > 0 ? a->timeout_ns : 2000000000ll;
+  p.g.timeout_ns = a->timeout_ns > 0 ? a->timeout_ns : 2000000000ll;
   const int resident = 8 * sm_count();          // 128-thread blocks: at least 8 per SM
   peer_exchange_merge_kernel<<<a->rows < resident ? a->rows : resident, 128, 0, (cudaStream_t)stream>>>(p);
   HQ_CUDA(cudaGetLastError());

@@ -271,7 +271,7 @@ class DStageLayerCache:
         return p
 
     def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, *, partial=None,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, peer=None) -> torch.Tensor:
         """Attention of one new token over the four segments (reference :219-303).
 
         query_states [B, H_Q, 1, D] -> [B, H_Q, 1, D] in the query dtype.
@@ -281,13 +281,13 @@ class DStageLayerCache:
         B_, H_Q_, _, D_ = query_states.shape
         q2d = query_states.reshape(B_ * H_Q_, D_)
         plan = self._decode_plan(q2d, kv_repeat)
-        res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial)
+        res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial, peer=peer)
         if partial is not None:
             return None
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
     def decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
-                    kv_repeat: int, *, out: Optional[torch.Tensor] = None, partial=None) -> torch.Tensor:
+                    kv_repeat: int, *, out: Optional[torch.Tensor] = None, partial=None, peer=None) -> torch.Tensor:
         """``append_staging(key_states, value_states)`` followed by ``decode_attention(query_states, kv_repeat)``
         (reference :195-303) as one kernel launch: the decode kernel attends to the new token from where it
         is and stores it into its staging slot on the way.  Same result as the two calls up to the order of
@@ -302,14 +302,14 @@ class DStageLayerCache:
             fused = (k2.data_ptr() % 16 == 0 and v2.data_ptr() % 16 == 0 and k2.stride(0) % 8 == 0 and v2.stride(0) % 8 == 0)
         if not fused:
             self.append_staging(key_states, value_states)
-            return self.decode_attention(query_states, kv_repeat, out=out, partial=partial)
+            return self.decode_attention(query_states, kv_repeat, out=out, partial=partial, peer=peer)
         B_, H_Q_, _, D_ = query_states.shape
         q2d = query_states.reshape(B_ * H_Q_, D_)
         plan = self._decode_plan(q2d, kv_repeat)
         a = plan.args
         a.k_new, a.v_new, a.kn_stride, a.vn_stride = k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0)
         try:
-            res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial)
+            res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial, peer=peer)
         finally:
             a.k_new = a.v_new = None
         self._staging_ptr += 1

@@ -226,10 +226,18 @@ class DecodePlan:
         self._keep = keep
         self._fn = _lib.lib().hq_decode_splitk
 
-    def run(self, q: torch.Tensor, out: Optional[torch.Tensor] = None, partial=None) -> torch.Tensor:
+    def run(self, q: torch.Tensor, out: Optional[torch.Tensor] = None, partial=None, peer=None) -> torch.Tensor:
         """Launch on the current stream.  ``partial=(m, l, acc)`` fp32 tensors
-        selects the un-normalised (sequence-sharded) output."""
+        selects the un-normalised (sequence-sharded) output.  ``peer=(exchange, seq)``
+        (a ``sharded.PeerExchange`` and the call's sequence number): this call covers one
+        sequence shard; the kernel exchanges its state with the other ranks and ``out`` is
+        the merged result."""
         a = self.args
+        if peer is not None:
+            px, seq = peer
+            a.peer_bufs, a.peer_world, a.peer_rank, a.peer_seq, a.peer_timeout_ns = px.bufs_addr, px.world, px.rank, seq, px.timeout_ns
+        else:
+            a.peer_world = 0
         qb = q if (q.dtype == torch.bfloat16 and q.stride(1) == 1) else q.to(torch.bfloat16).contiguous()
         a.q, a.q_stride = qb.data_ptr(), qb.stride(0)
         if partial is not None:

@@ -133,6 +133,8 @@ class PeerExchange:
         a.struct_bytes, a.world, a.rank, a.rows, a.timeout_ns = C.sizeof(_lib.PeerExchangeArgs), self.world, self.rank, rows, self.timeout_ns
         for j, ptr in enumerate(self.ptrs):
             a.bufs[j] = ptr
+        self._bufs_arr = (C.c_void_p * 16)(*self.ptrs)
+        self.bufs_addr = C.addressof(self._bufs_arr)     # for hq_decode_args.peer_bufs
 
     def next_seq(self) -> int:
         self.seq += 1
@@ -186,12 +188,14 @@ class SequenceShardedLayer:
     ranges (empty window/staging on every rank but the last).  ``decode_attention``
     returns the full result on every rank."""
 
-    def __init__(self, layer, group=None, exchange="nccl"):
-        """``exchange``: a :class:`PeerExchange` (one kernel exchanges and merges over peer memory), or ``"nccl"``
-        (all-gather, then merge)."""
+    def __init__(self, layer, group=None, exchange="nccl", fused=True):
+        """``exchange``: a :class:`PeerExchange` (exchange and merge over peer memory), or ``"nccl"``
+        (all-gather, then merge).  With a PeerExchange, ``fused`` picks between the decode kernel doing the exchange
+        and the merge itself (one launch per call) and a second kernel doing them (``hq_peer_exchange_merge``)."""
         self.layer = layer
         self.group = group
         self.exchange = exchange
+        self.fused = fused
         self._bufs = None
 
     def append_staging(self, key_states, value_states, is_tail_rank: bool):
@@ -214,11 +218,11 @@ class SequenceShardedLayer:
         B, H_Q, _, D = query_states.shape
         rows = B * H_Q
 
-        def partial_decode(partial):
+        def partial_decode(partial, out=None, peer=None):
             if new_kv is not None:
-                self.layer.decode_step(query_states, new_kv[0], new_kv[1], kv_repeat, partial=partial)
+                self.layer.decode_step(query_states, new_kv[0], new_kv[1], kv_repeat, partial=partial, out=out, peer=peer)
             else:
-                self.layer.decode_attention(query_states, kv_repeat, partial=partial)
+                self.layer.decode_attention(query_states, kv_repeat, partial=partial, out=out, peer=peer)
 
         if out is None:
             out = torch.empty(B, H_Q, 1, D, dtype=query_states.dtype, device=query_states.device)
@@ -228,8 +232,11 @@ class SequenceShardedLayer:
             if px.rows != rows:
                 raise ValueError(f"the exchange buffers were made for {px.rows} query rows, this call has {rows}")
             seq = px.next_seq()
-            partial_decode(px.slot(seq))
-            px.exchange_merge(seq, out2)
+            if self.fused:
+                partial_decode(None, out=out, peer=(px, seq))
+            else:
+                partial_decode(px.slot(seq))
+                px.exchange_merge(seq, out2)
             return out
         world = dist.get_world_size(self.group)
         if self._bufs is None or self._bufs[0].numel() != rows * (D + 2):

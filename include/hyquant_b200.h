@@ -156,6 +156,14 @@ typedef struct hq_decode_args {
    * staging slot n_staging, so the caller need not append it first (a fused form of the reference's
    * append_staging + decode_attention, src/ops/d_stage_kv_cache.py:195-303).  The caller then counts it. */
   const void* k_new; const void* v_new; int64_t kn_stride; int64_t vn_stride;
+  /* Optional: sequence-sharded decode in one launch.  With peer_world > 1 the call covers this rank's shard of the
+   * sequence, stores its un-normalised softmax state into the peers' exchange buffers (peer_bufs[j]: rank j's buffer
+   * of hq_peer_exchange_bytes(peer_world, BH_KV * kv_repeat) bytes as addressable from this process), waits - with
+   * the time limit - for theirs and writes the merged, normalised result to `out`, like hq_peer_exchange_merge
+   * below but without a second launch.  peer_seq = 1, 2, 3, ..., the same on every rank for the same call, shared
+   * with hq_peer_exchange_merge calls on the same buffers.  partial_* must be NULL. */
+  void* const* peer_bufs; int32_t peer_world; int32_t peer_rank; uint32_t peer_seq; int32_t peer_reserved;
+  int64_t peer_timeout_ns;     /* 0 = 2 s */
 } hq_decode_args;
 
 int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);

@@ -81,6 +81,7 @@ def _worker(rank, world, port, errs):
         shp = sharded.SequenceShardedLayer(sh.layer, exchange=px)
         e4 = 0.0
         for step in range(150):                                  # crosses a staging flush on the tail rank
+            shp.fused = step % 3 != 0                            # decode kernel exchanges itself / second kernel does
             q_s = torch.randn(2, 8, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
             kn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
             vn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
@@ -196,3 +197,55 @@ def test_peer_exchange_wait_runs_out():
     torch.cuda.synchronize()
     assert int(bufs[0].view(torch.int32)[0]) == 2
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+
+
+class _FakeExchange:
+    """What DecodePlan.run needs from a PeerExchange, over buffers in this GPU's own memory."""
+
+    def __init__(self, bufs, world, rank, timeout_ns=0):
+        import ctypes as C
+        self._arr = (C.c_void_p * 16)(*[b.data_ptr() for b in bufs])
+        self.bufs_addr, self.world, self.rank, self.timeout_ns = C.addressof(self._arr), world, rank, timeout_ns
+
+
+@pytest.mark.parametrize("R,BH", [(4, 4), (16, 2)])
+def test_decode_with_in_kernel_exchange_one_gpu(R, BH):
+    """Rank 0 of a two-way sequence split, with rank 1's state already in rank 0's exchange buffer: the decode
+    kernel must store rank 0's state into rank 1's buffer and write the merge, which equals the unsplit decode."""
+    import hyquant_b200 as hq
+    from hyquant_b200 import decode_d_stage as dd, sharded
+    nq, nt, ns, nw = 5000, 200, 37, 128
+    c = _build("cuda", BH, nq, nt, ns, nw, seed=9)
+    g = torch.Generator(device="cuda").manual_seed(10)
+    q = torch.randn(BH * R, 128, generator=g, device="cuda").to(torch.bfloat16)
+    full = hq.fused_d_stage_decode(q, c["kq"], c["vq"], c["ks"], c["vs"], c["kt"], c["vt"], c["kst"], c["vst"],
+                                   c["kw"], c["vw"], 4, 4, kv_repeat=R).float()
+    world, rows = 2, BH * R
+    plans = []
+    e = c["kw"][:, :0]
+    for rank in range(world):
+        q0, q1, t0, t1 = sharded.sequence_shard_plan(nq, nt, world)[rank]
+        last = rank == world - 1
+        plans.append(dd.DecodePlan(q, c["kq"][:, q0:q1], c["vq"][:, q0:q1], c["ks"][:, q0:q1].contiguous(), c["vs"][:, q0:q1].contiguous(),
+                                   c["kt"][:, t0:t1], c["vt"][:, t0:t1], c["kst"] if last else e, c["vst"] if last else e,
+                                   c["kw"] if last else e, c["vw"] if last else e, R, None))
+    m1 = torch.empty(rows, device="cuda"); l1 = torch.empty_like(m1); a1 = torch.empty(rows, 128, device="cuda")
+    plans[1].run(q, partial=(m1, l1, a1))
+    m0 = torch.empty(rows, device="cuda"); l0 = torch.empty_like(m0); a0 = torch.empty(rows, 128, device="cuda")
+    plans[0].run(q, partial=(m0, l0, a0))
+    bufs = _peer_buffers(world, rows)
+    for seq in (1, 2):
+        rv = _recv_view(bufs[0], world, rows, seq, 1)
+        rv[:, 0] = _message(m1, l1, a1)
+        rv[:, 1] = seq
+        out = torch.empty(rows, 128, dtype=torch.float32, device="cuda")
+        plans[0].run(q, out=out, peer=(_FakeExchange(bufs, world, 0), seq))
+        torch.cuda.synchronize()
+        assert (out - full).abs().max().item() < 1e-2
+        sent = _recv_view(bufs[1], world, rows, seq, 0)
+        assert bool((sent[:, 1] == seq).all())
+        assert torch.equal(sent[:, 0], _message(m0, l0, a0))           # the same state as the partial-mode call
+        assert int(bufs[0].view(torch.int32)[0]) == 0
+    # and a call without a peer afterwards is the plain one again
+    assert torch.equal(plans[0].run(q, out=torch.empty(rows, 128, dtype=torch.float32, device="cuda")),
+                       plans[0].run(q, out=torch.empty(rows, 128, dtype=torch.float32, device="cuda")))
