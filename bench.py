@@ -292,9 +292,9 @@ def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
 def bench_long_context_decode(torch, hq, dev, rank, world, dist):
     """Long-context decode at GLM-4-9B attention shapes (batch 4, 32 query / 2 KV heads, prefix 128K): each step
     appends one token per layer (a staging flush every 128 tokens) and decodes.  With more than one rank the prefix
-    is sequence-sharded and the decode kernel itself exchanges the partial softmax states over peer memory and merges
-    them (one launch per layer and token); the two-launch form (``hq_peer_exchange_merge``) and the NCCL all-gather +
-    merge form are timed after it for comparison."""
+    is sequence-sharded; the partial softmax states are exchanged over peer memory and merged by one small kernel
+    after the decode kernel (``hq_peer_exchange_merge``).  The form in which the decode kernel does the exchange
+    itself and the NCCL all-gather + merge form are timed after it for comparison."""
     from hyquant_b200 import sharded
     b, h_q, h_kv, n = 4, 32, 2, 131072
     nl, steps, warm = 4, 2048, 8                 # 2048 generated tokens: 16 staging flushes per layer
@@ -350,23 +350,23 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
     res_extra = {}
     if world > 1:
         for layer in layers:
-            layer.fused = False
+            layer.fused = True
         us_two = timed(steps + warm, n_nccl)
         status = px.status()
         for layer in layers:
             layer.exchange = "nccl"
-        res_extra = {"us_per_layer_token_exchange_in_second_kernel": round(us_two, 2),
+        res_extra = {"us_per_layer_token_exchange_inside_decode_kernel": round(us_two, 2),
                      "us_per_layer_token_nccl_allgather": round(timed(steps + n_nccl + 2 * warm, n_nccl), 2),
                      "peer_exchange_status": status}
         px.close()
     full_bytes = algorithmic_bytes(b * h_kv, b * h_q, n - W - int((n - W) * RHO), int((n - W) * RHO) + W + 64)
     out = {"workload": "batch 4, 32q/2kv, d=128, prefix 131072, W=128, rho=5%, K4V4; per step and layer: append one "
                        "token (flush at 128) + decode", "layers": nl, "steps": steps,
-           "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks; the decode kernel stores (m, l, acc) into the "
-                       "peers' buffers over NVLink, waits for theirs and merges",
+           "sharding": "single GPU" if world == 1 else f"sequence-sharded over {world} ranks; one kernel stores (m, l, acc) into the peers' "
+                       "buffers over NVLink, waits for theirs and merges",
            "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
            "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
-           "launch_mode": "python, host-driven: " + ("one launch per layer and token (decode of the shard, taking the new token on the tail rank, + exchange + merge)" if world > 1 else "decode_step (append + decode in one launch)"),
+           "launch_mode": "python, host-driven: " + ("two launches per layer and token (decode of the shard, taking the new token on the tail rank; exchange + merge)" if world > 1 else "decode_step (append + decode in one launch)"),
            "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
     out.update(res_extra)
     return out

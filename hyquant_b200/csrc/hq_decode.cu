@@ -251,7 +251,7 @@ __host__ __device__ constexpr int peer_scratch_floats(int world, int R) { return
 
 // Second pass for the R rows of kv-head `head`, by the whole CTA: (1) the peers' m and l words are polled by all threads
 // in parallel into shared memory, (2) one thread per row turns them into merge weights and the denominator, (3) every
-// thread keeps several acc loads in flight over its (row, peer) pairs and accumulates into its own shared-memory
+// thread keeps sixteen acc loads in flight over its (row, peer) pairs and accumulates into its own shared-memory
 // cells.  `local(hd, d, m, l, acc)` recomputes this rank's values of row hd, channel d.
 template <int kThreads, class LocalFn>
 __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* sm, int head, int tid, LocalFn local) {
@@ -296,7 +296,7 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
       s_acc[hd * 128 + d] = s_w0[hd] * a;
     }
     const int n_items = mine * np;
-    constexpr int kFly = 8;
+    constexpr int kFly = 16;
     for (int it0 = 0; it0 < n_items; it0 += kFly) {
       uint2 v[kFly];
 #pragma unroll

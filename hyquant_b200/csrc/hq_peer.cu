@@ -96,7 +96,12 @@ extern "C" int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stre
   p.g.world = a->world; p.g.rank = a->rank; p.g.rows = a->rows; p.g.seq = a->seq;
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_stride = a->out_stride;
   p.g.timeout_ns = a->timeout_ns > 0 ? a->timeout_ns : 2000000000ll;
-  const int resident = 8 * sm_count();          // 128-thread blocks: at least 8 per SM
+  static thread_local int per_sm = 0;            // blocks of this kernel that are resident on one SM at a time
+  if (per_sm == 0) {
+    HQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, peer_exchange_merge_kernel, 128, 0));
+    if (per_sm < 1) per_sm = 1;
+  }
+  const int resident = per_sm * sm_count();
   peer_exchange_merge_kernel<<<a->rows < resident ? a->rows : resident, 128, 0, (cudaStream_t)stream>>>(p);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;

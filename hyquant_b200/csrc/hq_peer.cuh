@@ -70,13 +70,24 @@ __device__ __forceinline__ float peer_merge(const PeerGroup& g, const PeerLayout
                                             float my_a, bool* expired) {
   const uint2* recv = reinterpret_cast<const uint2*>(g.bufs[g.rank] + L.recv_off) + (int64_t)(g.seq & 1u) * g.world * L.msg;
   const int64_t ia = 2 * (int64_t)g.rows + (int64_t)r * 128 + d;
-  float mj[kPeerMaxWorld];
+  // every peer's three words are requested before any is looked at: one round trip when they have all arrived
+  uint2 wm[kPeerMaxWorld], wl[kPeerMaxWorld], wa[kPeerMaxWorld];
+#pragma unroll
+  for (int j = 0; j < kPeerMaxWorld; ++j) {
+    if (j < g.world && j != g.rank) {
+      wm[j] = ld_pair_sys(recv + j * L.msg + r);
+      wl[j] = ld_pair_sys(recv + j * L.msg + g.rows + r);
+      wa[j] = ld_pair_sys(recv + j * L.msg + ia);
+    }
+  }
   float M = my_m;
 #pragma unroll
   for (int j = 0; j < kPeerMaxWorld; ++j) {
     if (j < g.world && j != g.rank) {
-      mj[j] = wait_pair(recv + j * L.msg + r, g.seq, g.timeout_ns, expired);
-      M = fmaxf(M, mj[j]);
+      if (wm[j].y != g.seq) wm[j].x = __float_as_uint(wait_pair(recv + j * L.msg + r, g.seq, g.timeout_ns, expired));
+      if (wl[j].y != g.seq) wl[j].x = __float_as_uint(wait_pair(recv + j * L.msg + g.rows + r, g.seq, g.timeout_ns, expired));
+      if (wa[j].y != g.seq) wa[j].x = __float_as_uint(wait_pair(recv + j * L.msg + ia, g.seq, g.timeout_ns, expired));
+      M = fmaxf(M, __uint_as_float(wm[j].x));
     }
   }
   const float w0 = (my_m == -INFINITY) ? 0.f : ex2f(my_m - M);
@@ -84,9 +95,10 @@ __device__ __forceinline__ float peer_merge(const PeerGroup& g, const PeerLayout
 #pragma unroll
   for (int j = 0; j < kPeerMaxWorld; ++j) {
     if (j < g.world && j != g.rank) {
-      const float w = (mj[j] == -INFINITY) ? 0.f : ex2f(mj[j] - M);
-      num += w * wait_pair(recv + j * L.msg + ia, g.seq, g.timeout_ns, expired);
-      den += w * wait_pair(recv + j * L.msg + g.rows + r, g.seq, g.timeout_ns, expired);
+      const float mj = __uint_as_float(wm[j].x);
+      const float w = (mj == -INFINITY) ? 0.f : ex2f(mj - M);
+      num += w * __uint_as_float(wa[j].x);
+      den += w * __uint_as_float(wl[j].x);
     }
   }
   return den > 0.f ? num / den : 0.f;

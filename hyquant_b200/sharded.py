@@ -188,10 +188,13 @@ class SequenceShardedLayer:
     ranges (empty window/staging on every rank but the last).  ``decode_attention``
     returns the full result on every rank."""
 
-    def __init__(self, layer, group=None, exchange="nccl", fused=True):
+    def __init__(self, layer, group=None, exchange="nccl", fused=False):
         """``exchange``: a :class:`PeerExchange` (exchange and merge over peer memory), or ``"nccl"``
-        (all-gather, then merge).  With a PeerExchange, ``fused`` picks between the decode kernel doing the exchange
-        and the merge itself (one launch per call) and a second kernel doing them (``hq_peer_exchange_merge``)."""
+        (all-gather, then merge).  With a PeerExchange, ``fused`` picks between a second small kernel doing the
+        exchange and the merge with one block per query row (``hq_peer_exchange_merge``, the default: measured
+        faster at 2 and 8 GPUs) and the decode kernel doing them itself in the block that finishes a kv-head (one
+        launch per call; few blocks do all the waiting, which costs more than the launch it saves when there are
+        few kv-heads with many query heads each)."""
         self.layer = layer
         self.group = group
         self.exchange = exchange

@@ -81,7 +81,7 @@ def _worker(rank, world, port, errs):
         shp = sharded.SequenceShardedLayer(sh.layer, exchange=px)
         e4 = 0.0
         for step in range(150):                                  # crosses a staging flush on the tail rank
-            shp.fused = step % 3 != 0                            # decode kernel exchanges itself / second kernel does
+            shp.fused = step % 3 == 0                            # second kernel exchanges / decode kernel does it itself
             q_s = torch.randn(2, 8, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
             kn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
             vn = torch.randn(2, 2, 1, 128, generator=g2, device=dev).to(torch.bfloat16)
