@@ -540,12 +540,14 @@ def run_ours(args):
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
     batched = long_ctx = bit_widths = None
-    if not args.no_extra and rank == 0:
+    legs = set() if args.no_extra else set(args.extra_legs.split(","))
+    if "bits" in legs and rank == 0:
         bit_widths = bench_bit_widths(torch, hq, dev, not args.no_graph)
         torch.cuda.empty_cache()
-    if not args.no_extra:
+    if "batched" in legs:
         batched = bench_batched_decode(torch, hq, dev, rank, world, dist, not args.no_graph)
         torch.cuda.empty_cache()
+    if "long" in legs:
         long_ctx = bench_long_context_decode(torch, hq, dev, rank, world, dist)
         torch.cuda.empty_cache()
     if rank == 0:
@@ -605,7 +607,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layer caches per step (32 = the workload; fewer for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="launch every decode call plainly (no programmatic dependent launch)")
-    ap.add_argument("--no-extra", action="store_true", help="skip the batched (64q/8kv x 16) and 128K long-context decode legs")
+    ap.add_argument("--no-extra", action="store_true", help="skip the bit-width, batched (64q/8kv x 16) and 128K long-context decode legs")
+    ap.add_argument("--extra-legs", default="bits,batched,long", help="which of those legs to run (comma-separated)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

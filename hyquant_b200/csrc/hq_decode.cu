@@ -327,7 +327,7 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
 
 // ---- the kernel -------------------------------------------------------------
 
-template <int NT, bool kScaleTma, int KB, int VB>
+template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
 __global__ void __launch_bounds__(warps_of(NT, Fmt<KB, VB>::kCtasPerSm) * 32, Fmt<KB, VB>::kCtasPerSm)
 decode_splitk_kernel(const DecodeParams p) {
   using F = Fmt<KB, VB>;
@@ -853,7 +853,7 @@ decode_splitk_kernel(const DecodeParams p) {
   constexpr int kRowThreads = kThreads / 128 * 128;      // threads that write output rows, 128 per row at a time
   const int d = tid & 127;
   const bool single = (p.nsplit == 1);
-  const bool peers = p.peer.world > 1;
+  constexpr bool peers = kPeer;       // instantiated apart, so that the exchange code costs the plain kernel no registers
   // this CTA's merge of its warps for head hd, channel dd
   auto cta_row = [&](int hd, int dd, float& M, float& l, float& acc) {
     M = -INFINITY;
@@ -873,7 +873,7 @@ decode_splitk_kernel(const DecodeParams p) {
     cta_row(hd, d, M, l, acc);
     const int64_t qrow = (int64_t)head * p.R + hd;
     if (single) {
-      if (peers) {
+      if constexpr (peers) {
         peer_send(p, (int)qrow, d, M, l, acc);       // every row is sent before any is awaited
       } else if (p.pacc) {
         p.pacc[qrow * 128 + d] = acc;
@@ -888,7 +888,7 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   }
   if (single) {
-    if (peers) peer_receive_all<kThreads>(p, mrg_o + (size_t)kWarps * NT * 8 * 128, head, tid, cta_row);
+    if constexpr (peers) peer_receive_all<kThreads>(p, mrg_o + (size_t)kWarps * NT * 8 * 128, head, tid, cta_row);
     return;
   }
 
@@ -1012,7 +1012,7 @@ decode_splitk_kernel(const DecodeParams p) {
     float M, l, acc;
     head_row(hd, d, M, l, acc);
     const int64_t qrow = (int64_t)head * p.R + hd;
-    if (peers) {
+    if constexpr (peers) {
       peer_send(p, (int)qrow, d, M, l, acc);
     } else if (p.pacc) {
       p.pacc[qrow * 128 + d] = acc;
@@ -1021,7 +1021,7 @@ decode_splitk_kernel(const DecodeParams p) {
       store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
     }
   }
-  if (peers) peer_receive_all<kThreads>(p, red + (size_t)kWarps * p.R * 128, head, tid, head_row);
+  if constexpr (peers) peer_receive_all<kThreads>(p, red + (size_t)kWarps * p.R * 128, head, tid, head_row);
   if (tid == 0) p.counters[head] = 0;   // ready for the next launch on this workspace
 }
 
@@ -1033,14 +1033,14 @@ static size_t decode_smem_bytes(int NT, int slot_bytes) {
   return (size_t)w * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 + (size_t)w * kSlots * 8;
 }
 
-template <int NT, bool kScaleTma, int KB, int VB>
+template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
 static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   const size_t smem = decode_smem_bytes(NT, Fmt<KB, VB>::kSlot);
   static thread_local int attr_dev = -1;
   int dev = 0;
   HQ_CUDA(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma, KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma, KB, VB, kPeer>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
     attr_dev = dev;
   }
@@ -1054,14 +1054,17 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.overlap ? 1 : 0;
-  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB>, p));
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB, kPeer>, p));
   return HQ_OK;
 }
 
 template <int KB, int VB>
 static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st) {
-  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB>(p, grid, st) : launch_decode<1, false, KB, VB>(p, grid, st);
-  return p.scale_tma ? launch_decode<2, true, KB, VB>(p, grid, st) : launch_decode<2, false, KB, VB>(p, grid, st);
+  if (p.peer.world > 1) {   // the exchanging instantiations exist with directly loaded scales only (any alignment)
+    return NT == 1 ? launch_decode<1, false, KB, VB, true>(p, grid, st) : launch_decode<2, false, KB, VB, true>(p, grid, st);
+  }
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, false>(p, grid, st) : launch_decode<1, false, KB, VB, false>(p, grid, st);
+  return p.scale_tma ? launch_decode<2, true, KB, VB, false>(p, grid, st) : launch_decode<2, false, KB, VB, false>(p, grid, st);
 }
 
 static int slot_bytes_of(int kb, int vb) {
