@@ -41,7 +41,9 @@ namespace hq {
 // 192 threads fit an SM at <= 168 registers, or 8 when the slot size allows one CTA per SM anyway.
 __host__ __device__ constexpr int warps_of(int NT, int ctas_per_sm) { return (NT == 2 && ctas_per_sm == 2) ? 6 : 8; }
 constexpr int kSlots = 3;
-constexpr int kUnitQ = 32;                // quantised tokens per unit
+// quantised tokens per unit: 32, or 16 when 32 rows of K and V codes would not fit the 4 KB of a BF16 unit (every pair
+// with an 8-bit side), so that every pair keeps a 4224-byte slot and two CTAs per SM
+__host__ __device__ constexpr int unit_tokens(int kb, int vb) { return 32 * 16 * (kb + vb) > 4096 ? 16 : 32; }
 constexpr int kUnitB = 8;                 // BF16 tokens per unit
 constexpr float kLazyRescale = 4.0f;      // rescale only if the max grows by > 2^4
 constexpr int kWsHeaderBytes = 256;       // [0] status word
@@ -77,6 +79,7 @@ struct DecodeParams {
 template <int KB, int VB>
 struct Fmt {
   static constexpr int kRowK = 16 * KB, kRowV = 16 * VB;                  // bytes per token row (128 channels)
+  static constexpr int kUnitQ = unit_tokens(KB, VB), kChunks = kUnitQ / 16;   // 16-token MMA chunks per unit
   static constexpr int kQuant = kUnitQ * (kRowK + kRowV);
   static constexpr int kData = kQuant > 4096 ? kQuant : 4096;
   static constexpr int kVOff = kUnitQ * kRowK;
@@ -95,6 +98,7 @@ template <int KB, int VB>
 __device__ __forceinline__ Unit unit_of(const DecodeParams& p, int head, int u) {
   Unit r;
   if (u < p.uq) {
+    constexpr int kUnitQ = Fmt<KB, VB>::kUnitQ;
     r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, p.n_quant - r.tok0);
     r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowK;
     r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowV;
@@ -334,7 +338,7 @@ decode_splitk_kernel(const DecodeParams p) {
   constexpr int kWarps = warps_of(NT, F::kCtasPerSm), kThreads = kWarps * 32;
   constexpr int kQItems = NT * 8;                                   // (tile, head) pairs whose query row is loaded
   constexpr int kQIter = (kQItems + kWarps - 1) / kWarps;           // per warp: items warp, warp + kWarps, ...
-  constexpr int kSlotBytes = F::kSlot;
+  constexpr int kSlotBytes = F::kSlot, kUnitQ = F::kUnitQ, kChunks = F::kChunks;
   extern __shared__ __align__(128) uint8_t smem[];
   // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same |
   //         headC [NT*8] f32 | mbarriers [kWarps][kSlots]
@@ -529,7 +533,7 @@ decode_splitk_kernel(const DecodeParams p) {
       const int u = u_begin + warp + kWarps * ii;
       if (u >= p.uq) return 0u;
       const int tok = u * kUnitQ + lane;
-      if (tok >= p.n_quant) return 0u;
+      if (lane >= kUnitQ || tok >= p.n_quant) return 0u;
       const uint16_t ks = __half_as_ushort(p.k_scale[head * p.ks_stride_bh + tok]);
       const uint16_t vs = __half_as_ushort(p.v_scale[head * p.vs_stride_bh + tok]);
       return (uint32_t)ks | ((uint32_t)vs << 16);
@@ -549,24 +553,24 @@ decode_splitk_kernel(const DecodeParams p) {
       const __half* vss = reinterpret_cast<const __half*>(Ks + F::kData + 64);
 
       // scores of both 16-token chunks: this lane holds tokens g, g+8, 16+g, 24+g
-      float s[2][NT][4];
+      float s[kChunks][NT][4];
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch)
+      for (int ch = 0; ch < kChunks; ++ch)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int x = 0; x < 4; ++x) s[ch][nt][x] = 0.f;
       if constexpr (KB == 4) {
-        uint4 kw[2][2];
+        uint4 kw[kChunks][2];
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
+        for (int ch = 0; ch < kChunks; ++ch) {
           kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
           kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
         }
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
 #pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
+          for (int ch = 0; ch < kChunks; ++ch) {
             const uint32_t wa = w == 0 ? kw[ch][0].x : w == 1 ? kw[ch][0].y : w == 2 ? kw[ch][0].z : kw[ch][0].w;
             const uint32_t wb = w == 0 ? kw[ch][1].x : w == 1 ? kw[ch][1].y : w == 2 ? kw[ch][1].z : kw[ch][1].w;
             uint32_t ha[4], hb[4];
@@ -582,7 +586,7 @@ decode_splitk_kernel(const DecodeParams p) {
       } else if constexpr (KB == 8) {
         // a 128-byte row: 16 bytes at 64 h + 16 t; word w of it holds channels 64 h + 16 t + 4 w + (0..3)
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch)
+        for (int ch = 0; ch < kChunks; ++ch)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint4 ka = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 128 + 64 * h + t * 16);
@@ -601,7 +605,7 @@ decode_splitk_kernel(const DecodeParams p) {
       } else {
         // a 32-byte row: 8 bytes at 8 t; word x of it holds channels 32 t + 16 x + m, code m in bits 2m, 2m+1
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
+        for (int ch = 0; ch < kChunks; ++ch) {
           const uint2 ka = *reinterpret_cast<const uint2*>(Ks + (16 * ch + g) * 32 + t * 8);
           const uint2 kb = *reinterpret_cast<const uint2*>(Ks + (16 * ch + g + 8) * 32 + t * 8);
           const uint32_t wa[2] = {ka.x, ka.y}, wb[2] = {kb.x, kb.y};
@@ -622,9 +626,9 @@ decode_splitk_kernel(const DecodeParams p) {
             }
         }
       }
-      float vsc[2][2];
+      float vsc[kChunks][2];
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      for (int ch = 0; ch < kChunks; ++ch) {
         const int tokA = 16 * ch + g, tokB = tokA + 8;
         const bool okA = tokA < ntok, okB = tokB < ntok;
         float ksA, ksB;
@@ -654,11 +658,15 @@ decode_splitk_kernel(const DecodeParams p) {
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
-          mx[nt][j] = group_max(fmaxf(fmaxf(s[0][nt][j], s[0][nt][2 + j]), fmaxf(s[1][nt][j], s[1][nt][2 + j])));
+        {
+          float v = fmaxf(s[0][nt][j], s[0][nt][2 + j]);
+          if constexpr (kChunks == 2) v = fmaxf(v, fmaxf(s[kChunks - 1][nt][j], s[kChunks - 1][nt][2 + j]));
+          mx[nt][j] = group_max(v);
+        }
       lazy_rescale<NT>(mx, m_ref, l_part, O);
 
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      for (int ch = 0; ch < kChunks; ++ch) {
         uint32_t pb[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -1068,7 +1076,7 @@ static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStre
 }
 
 static int slot_bytes_of(int kb, int vb) {
-  const int q = kUnitQ * 16 * (kb + vb);
+  const int q = unit_tokens(kb, vb) * 16 * (kb + vb);
   return (q > 4096 ? q : 4096) + 128;
 }
 
@@ -1135,6 +1143,7 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   const int64_t vst[4] = {a->vt_stride_bh, a->vg_stride_bh, a->vw_stride_bh, a->vn_stride};
   const int ns[4] = {a->n_topk, a->n_staging, a->n_window, has_new ? 1 : 0};
   p.stage_k = (__nv_bfloat16*)a->k_staging; p.stage_v = (__nv_bfloat16*)a->v_staging;
+  const int kUnitQ = unit_tokens(k_bits, v_bits);
   p.uq = (a->n_quant + kUnitQ - 1) / kUnitQ;
   p.units = p.uq;
   for (int s = 0; s < 4; ++s) {
