@@ -49,6 +49,43 @@ def test_argument_validation_without_gpu():
     assert lib.hq_lse_merge(None, None, None, 0, 4, None, 0, 0, None) == -1
 
 
+def test_peer_exchange_layout_and_validation_without_gpu():
+    """The address arithmetic of the exchange buffer (no memory is touched): the local state and every
+    (parity, source rank) receive slot lie inside the buffer and do not overlap; bad arguments are refused."""
+    lib = _lib.lib()
+    world, rows = 8, 128
+    n = C.c_int64(0)
+    assert lib.hq_peer_exchange_bytes(world, rows, C.byref(n)) == 0
+    assert lib.hq_peer_exchange_bytes(17, rows, C.byref(n)) == -1 and lib.hq_peer_exchange_bytes(0, rows, C.byref(n)) == -1
+    assert lib.hq_peer_exchange_bytes(world, rows, C.byref(n)) == 0
+    base = 1 << 20                                            # a made-up, 256-byte aligned device address
+    spans = [(base, base + 256)]                              # the header
+    for seq in (1, 2):
+        m, l, acc = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        assert lib.hq_peer_slot(base, world, rows, seq, C.byref(m), C.byref(l), C.byref(acc)) == 0
+        assert l.value == m.value + 4 * rows and acc.value == m.value + 8 * rows and acc.value % 16 == 0
+        spans.append((m.value, m.value + 4 * 130 * rows))
+        for src in range(world):
+            w = C.c_void_p()
+            assert lib.hq_peer_recv_slot(base, world, rows, seq, src, C.byref(w)) == 0
+            assert w.value % 8 == 0
+            spans.append((w.value, w.value + 8 * 130 * rows))
+    w = C.c_void_p()
+    assert lib.hq_peer_recv_slot(base, world, rows, 1, world, C.byref(w)) == -1
+    # same parity, same slot: calls seq and seq + 2 reuse it
+    w2 = C.c_void_p()
+    lib.hq_peer_recv_slot(base, world, rows, 1, 3, C.byref(w)); lib.hq_peer_recv_slot(base, world, rows, 3, 3, C.byref(w2))
+    assert w.value == w2.value
+    spans.sort()
+    assert spans[0][0] == base and spans[-1][1] <= base + n.value
+    assert all(a1 <= b0 for (_, a1), (b0, _) in zip(spans, spans[1:]))
+    a = _lib.PeerExchangeArgs()
+    a.struct_bytes = C.sizeof(_lib.PeerExchangeArgs) - 8
+    assert lib.hq_peer_exchange_merge(C.byref(a), None) == -1
+    a.struct_bytes, a.world, a.rank, a.rows, a.seq = C.sizeof(_lib.PeerExchangeArgs), 2, 0, 4, 0
+    assert lib.hq_peer_exchange_merge(C.byref(a), None) == -1                  # seq starts at 1
+
+
 def test_product_path_has_no_cpu_fallback():
     x = torch.zeros(1, 4, 128)
     with pytest.raises(hq.HyQuantError):
