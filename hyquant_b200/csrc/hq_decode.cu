@@ -329,6 +329,41 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
   if (expired) atomicOr(reinterpret_cast<int*>(g.bufs[g.rank]), 2);
 }
 
+// Last block of a head, GQA ratios that do not divide the warp count: this warp's weighted sum of the partial rows
+// (split s0 + j * kWarps, head hd + hh), H heads x J splits fetched per step, into its slot of `red` [kWarps][R][128].
+template <int H, int J, int kWarps>
+__device__ __forceinline__ void merge_rows(const DecodeParams& p, int64_t base, const float* sm_w, float* red, int warp, int lane) {
+  for (int s0 = warp; s0 < p.nsplit; s0 += J * kWarps) {
+    for (int hd = 0; hd < p.R; hd += H) {
+      float4 v[H][J];
+#pragma unroll
+      for (int hh = 0; hh < H; ++hh)
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          const int s2 = s0 + j * kWarps;
+          v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (s2 < p.nsplit && hd + hh < p.R)
+            v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
+        }
+#pragma unroll
+      for (int hh = 0; hh < H; ++hh) {
+        if (hd + hh < p.R) {
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < J; ++j) {
+            const int s2 = s0 + j * kWarps;
+            const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
+            a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
+          }
+          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
+          if (s0 >= J * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
+          *dst = a;
+        }
+      }
+    }
+  }
+}
+
 // ---- the kernel -------------------------------------------------------------
 
 template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
@@ -970,35 +1005,14 @@ decode_splitk_kernel(const DecodeParams p) {
     }
     reinterpret_cast<float4*>(red + (size_t)warp * 128)[lane] = a;     // partial of head warp % R
   } else {
-    // generic GQA ratio: warp w sums splits w, w+8, ... of every head, 16 independent reads at a time
-    for (int s0 = warp; s0 < p.nsplit; s0 += 8 * kWarps) {
-      for (int hd = 0; hd < p.R; hd += 2) {
-        float4 v[2][8];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int s2 = s0 + j * kWarps;
-            v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (s2 < p.nsplit && hd + hh < p.R)
-              v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
-          }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          if (hd + hh >= p.R) break;
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int s2 = s0 + j * kWarps;
-            const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
-            a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
-          }
-          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
-          if (s0 >= 8 * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
-          *dst = a;
-        }
-      }
-    }
+    // generic GQA ratio: warp w sums splits w, w + kWarps, ... of every head.  Every step is one round trip to L2, so
+    // the (heads, splits) block fetched per step is as large as the registers allow (32 rows with two head tiles, 16
+    // with one) and shaped by how many splits a warp has: few splits -> many heads at once.
+    const int jneed = (p.nsplit + kWarps - 1) / kWarps;
+    constexpr int kRowsInFlight = NT == 2 ? 32 : 16;
+    if (jneed <= 2) merge_rows<kRowsInFlight / 2, 2, kWarps>(p, base, sm_w, red, warp, lane);
+    else if (jneed <= 4) merge_rows<kRowsInFlight / 4, 4, kWarps>(p, base, sm_w, red, warp, lane);
+    else merge_rows<kRowsInFlight / 8, 8, kWarps>(p, base, sm_w, red, warp, lane);
     if (warp >= p.nsplit) {   // a warp without splits still owns a slot of `red`
       for (int hd = 0; hd < p.R; ++hd)
         reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
