@@ -18,9 +18,10 @@ resident in HBM; ``e2e`` drives the reference-named cache API per layer with the
 new token's q/k/v coming from pinned host memory and the attention output read
 back to the host inside the timed region.
 
-``--impl reference`` times the CPU restatement of the reference's own PyTorch
-fallback path (oracle/hq_oracle.py) on the host cores, on one layer call per
-step of the same workload.
+``--impl reference`` times the reference's own CPU path (its PyTorch fallback of
+``DStageLayerCache.decode_attention``, fp32, all host threads) on one layer call per step of
+the same workload, from the untracked copy of the reference under ``oracle/_ref`` when it is
+there (``oracle/make_ref.py``), else the torch-CPU restatement in ``oracle/``.
 """
 
 from __future__ import annotations
@@ -57,7 +58,7 @@ def measured_peak():
             return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s: no measured peak file beside bench.py)"
 
 
 class ClockSampler:
@@ -140,8 +141,11 @@ def layer_bytes(layer, h_q_total):
     return algorithmic_bytes(layer.k_window.shape[0], h_q_total, layer._n_quant, n_bf16, layer.k_bits, layer.v_bits)
 
 
-def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None, overlap=True):
-    """K steps of (one decode launch per layer), device-timed; returns ms total, launches.
+def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, graph=True, kv_repeat=None, overlap=True,
+                      repeats=1):
+    """K steps of (one decode launch per layer), device-timed; returns ms for the K steps, launches in them.
+    ``repeats`` > 1 times the K-step block that many times back to back (each bracketed by its own events) and
+    returns the median, so that a short block is not judged from one sample.
     ``flush``: a buffer larger than L2 that is rewritten before every step (outside the
     timed events) when the step's own caches do not exceed L2."""
     r = H_Q // H_KV if kv_repeat is None else kv_repeat
@@ -177,25 +181,28 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, g
         step_fn = g.replay
         step_fn()
         torch.cuda.synchronize()
-    if flush is None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            step_fn()
-        e1.record()
-        torch.cuda.synchronize()
-        total = e0.elapsed_time(e1)
-    else:
-        evs = []
-        for _ in range(steps):
-            flush.zero_()
+    totals = []
+    for _ in range(max(1, repeats)):
+        if flush is None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            step_fn()
+            for _ in range(steps):
+                step_fn()
             e1.record()
-            evs.append((e0, e1))
-        torch.cuda.synchronize()
-        total = sum(a.elapsed_time(b) for a, b in evs)
+            torch.cuda.synchronize()
+            totals.append(e0.elapsed_time(e1))
+        else:
+            evs = []
+            for _ in range(steps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step_fn()
+                e1.record()
+                evs.append((e0, e1))
+            torch.cuda.synchronize()
+            totals.append(sum(a.elapsed_time(b) for a, b in evs))
+    total = float(np.median(totals))
     if dist is not None:
         dist.barrier()
     return total, steps * len(plans)
@@ -265,18 +272,38 @@ def bench_bit_widths(torch, hq, dev, graph):
     return out
 
 
+SHARD_TOL = 5e-3      # a sharded result may differ from the single-GPU one by the order of fp32 partial sums only
+
+
 def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
     """Batched decode at Qwen3-32B attention shapes (batch 16, 64 query / 8 KV heads, prefix 32K): the KV heads
-    are split over the ranks, each rank decodes its heads, nothing is exchanged.  Total work is fixed."""
+    are split over the ranks, each rank decodes its heads, nothing is exchanged.  Total work is fixed.
+    Before the timing, one full cache (same seed on every rank) is decoded whole and as this rank's head group
+    (``sharded.shard_layer_heads``); the two must agree."""
+    from hyquant_b200 import sharded
     b, h_q, h_kv, n = 16, 64, 8, 32768
     if h_kv % world:
         return None
     hq_l, hkv_l = h_q // world, h_kv // world
+    r = h_q // h_kv
+    err = None
+    if world > 1:
+        full, qd = build_layer(hq, torch, 7700, n, dev, b=b, h_q=h_q, h_kv=h_kv)
+        ref = full.decode_attention(qd, r).float()
+        mine = sharded.shard_layer_heads(full, world, rank)
+        del full
+        h0, h1 = sharded.kv_head_range(h_kv, world, rank)
+        got = mine.decode_attention(qd[:, h0 * r:h1 * r].contiguous(), r).float()
+        t = (got - ref[:, h0 * r:h1 * r]).abs().max().reshape(1).double()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err = float(t[0])
+        del mine, ref, got
+        torch.cuda.empty_cache()
     caches = 4
     ls, qq = zip(*[build_layer(hq, torch, 7000 + 10 * i + rank, n, dev, b=b, h_q=hq_l, h_kv=hkv_l) for i in range(caches)])
     bts = layer_bytes(ls[0], b * hq_l)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if caches * bts < (256 << 20) else None
-    ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, dist, flush=flush, graph=graph, kv_repeat=h_q // h_kv)
+    ms, cnt = time_kernel_steps(torch, list(ls), list(qq), 10, 3, dist, flush=flush, graph=graph, kv_repeat=r, repeats=5)
     if dist is not None:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -286,6 +313,7 @@ def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
             "sharding": f"kv heads over {world} rank(s), {hkv_l} per rank, no collective", "scaling": "strong",
             "us_per_call": round(us, 2), "bytes_per_call_per_rank": bts,
             "gbps_all_ranks": round(bts * world / us / 1e3, 1), "caches_per_rank": caches,
+            "sharded_max_abs_err": err, "sharded_ok": err is None or err <= SHARD_TOL,
             "l2": "caches exceed L2" if flush is None else "flushed before each pass"}
 
 
@@ -294,16 +322,18 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
     appends one token per layer (a staging flush every 128 tokens) and decodes.  With more than one rank the prefix
     is sequence-sharded; the partial softmax states are exchanged over peer memory and merged by one small kernel
     after the decode kernel (``hq_peer_exchange_merge``).  The form in which the decode kernel does the exchange
-    itself and the NCCL all-gather + merge form are timed after it for comparison."""
+    itself and the NCCL all-gather + merge form are timed after it for comparison.  Before the timing every rank
+    decodes the full cache once and each of the three sharded forms once; the results must agree."""
     from hyquant_b200 import sharded
     b, h_q, h_kv, n = 4, 32, 2, 131072
     nl, steps, warm = 4, 2048, 8                 # 2048 generated tokens: 16 staging flushes per layer
     r = h_q // h_kv
-    layers, qs = [], []
+    layers, qs, refs = [], [], []
     px = sharded.PeerExchange(rows=b * h_q) if world > 1 else None
     for i in range(nl):
         full, qd = build_layer(hq, torch, 9000 + i, n, dev, b=b, h_q=h_q, h_kv=h_kv)     # same seed on every rank
         if world > 1:
+            refs.append(full.decode_attention(qd, r).float())
             shard = sharded.shard_layer_sequence(full, world, rank)
             del full
             layers.append(sharded.SequenceShardedLayer(shard, exchange=px))
@@ -311,6 +341,20 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
             layers.append(full)
         qs.append(qd)
     torch.cuda.empty_cache()
+    errs = {}
+    if world > 1:
+        for form in ("peer_exchange_kernel", "exchange_inside_decode_kernel", "nccl_allgather"):
+            worst = 0.0
+            for layer, q, ref in zip(layers, qs, refs):
+                layer.exchange = "nccl" if form == "nccl_allgather" else px
+                layer.fused = form == "exchange_inside_decode_kernel"
+                worst = max(worst, float((layer.decode_attention(q, r).float() - ref).abs().max()))
+            t = torch.tensor([worst], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            errs[form] = float(t[0])
+        for layer in layers:
+            layer.exchange, layer.fused = px, False
+        del refs
     g = torch.Generator(device=dev); g.manual_seed(4242)
     n_nccl = 256 if world > 1 else 0
     kn = torch.randn(steps + 2 * n_nccl + 3 * warm, b, h_kv, 1, D, generator=g, device=dev).to(torch.bfloat16)
@@ -357,7 +401,8 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
             layer.exchange = "nccl"
         res_extra = {"us_per_layer_token_exchange_inside_decode_kernel": round(us_two, 2),
                      "us_per_layer_token_nccl_allgather": round(timed(steps + n_nccl + 2 * warm, n_nccl), 2),
-                     "peer_exchange_status": status}
+                     "peer_exchange_status": status, "sharded_max_abs_err": errs,
+                     "sharded_ok": status == 0 and all(e <= SHARD_TOL for e in errs.values())}
         px.close()
     full_bytes = algorithmic_bytes(b * h_kv, b * h_q, n - W - int((n - W) * RHO), int((n - W) * RHO) + W + 64)
     out = {"workload": "batch 4, 32q/2kv, d=128, prefix 131072, W=128, rho=5%, K4V4; per step and layer: append one "
@@ -369,6 +414,119 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
            "launch_mode": "python, host-driven: " + ("two launches per layer and token (decode of the shard, taking the new token on the tail rank; exchange + merge)" if world > 1 else "decode_step (append + decode in one launch)"),
            "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
     out.update(res_extra)
+    return out
+
+
+def bench_prefill_heads(torch, hq, dev, rank, world, dist, n=32768):
+    """The 32K hybrid prefill with its KV-head groups over the ranks (8 KV heads -> 8 / world per rank with their
+    query heads; every (batch, kv-head) is independent, so nothing is exchanged).  Total work is fixed.  Times the
+    attention kernel and, separately, the whole call including operand preparation, max over ranks."""
+    from hyquant_b200.sage_unified import PrefillPlan
+    from hyquant_b200.synth import gen_torch
+    from hyquant_b200 import sharded
+    if H_KV % world:
+        return None
+    r = H_Q // H_KV
+    t = gen_torch(1, H_Q, H_KV, n, D, W, RHO, 2000 + n.bit_length(), n_qry=n, device=dev)     # same seed on every rank
+    h0, h1 = sharded.kv_head_range(H_KV, world, rank)
+    q, k, v = t["q"][:, h0 * r:h1 * r], t["k"][:, h0:h1], t["v"][:, h0:h1]
+    vidx = hq.compute_vertical_indices(q[:, :, -256:].mean(dim=2, keepdim=True), k, W, RHO, kv_repeat=r)
+
+    def whole():
+        return PrefillPlan(q, k, v, vidx, W, None, True)
+
+    plan = whole()
+    for _ in range(2):
+        plan.run()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    reps = 3
+    e[0].record()
+    for _ in range(reps):
+        plan.run()
+    e[1].record()
+    e[2].record()
+    for _ in range(reps):
+        whole().run()
+    e[3].record()
+    torch.cuda.synchronize()
+    plan.check_status()
+    ms = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    flops = 4.0 * H_Q * D * n * (n + 1) / 2
+    return {"workload": f"hybrid prefill, B=1, 32q/8kv, d=128, seq {n}, W=128, rho=5%", "scaling": "strong",
+            "sharding": f"kv heads over {world} rank(s), {H_KV // world} per rank with their query heads, no collective",
+            "ms_kernel": round(float(ms[0]), 3), "ms_with_preparation": round(float(ms[1]), 3),
+            "tflops_all_ranks": round(flops / float(ms[0]) / 1e9, 1)}
+
+
+# ---------------------------------------------------------------------------
+# the reference's own kernels on this GPU (Triton, compiled for sm_100 by the installed Triton)
+# ---------------------------------------------------------------------------
+
+def reference_dir():
+    p = os.path.join(ROOT, "oracle", "_ref")
+    return p if os.path.isdir(os.path.join(p, "src", "ops")) else None
+
+
+def bench_reference_triton(torch, hq, dev, layer, q_decode, prefill_seqs):
+    """The reference's Triton kernels on the same inputs, as the kernel to beat: its split-K decode on the headline
+    cache (the reference's ``DStageLayerCache`` filled with this library's segments) and its
+    ``sage_vertical_attention_v2`` (the whole call, as the reference has no separate preparation) at the prefill
+    sizes.  Needs the untracked copy of the reference under ``oracle/_ref``."""
+    ref = reference_dir()
+    if ref is None:
+        return {"unavailable": "oracle/_ref is absent (oracle/make_ref.py makes it where the reference checkout is)"}
+    sys.path.insert(0, ref)
+    os.environ.pop("HYBRID_ATTN_DECODE_KERNEL", None)
+    try:
+        from src.ops.d_stage_kv_cache import DStageLayerCache as RefLayer
+        from src.ops.sage_unified import sage_vertical_attention_v2 as ref_prefill
+    except Exception as e:      # e.g. no Triton on this machine
+        return {"unavailable": f"the reference does not import here: {type(e).__name__}: {e}"}
+    from hyquant_b200.synth import gen_torch
+    out = {}
+    r = H_Q // H_KV
+    rl = RefLayer(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+    rl._B, rl._H_KV, rl._D, rl.phase = B, H_KV, D, "decode"
+    rl.k_quant_packed, rl.v_quant_packed, rl.k_scale, rl.v_scale = layer.k_quant_packed, layer.v_quant_packed, layer.k_scale, layer.v_scale
+    rl.k_topk, rl.v_topk, rl.k_window, rl.v_window = layer.k_topk, layer.v_topk, layer.k_window, layer.v_window
+    rl._staging_buf_k, rl._staging_buf_v, rl._staging_ptr = layer._staging_buf_k, layer._staging_buf_v, layer._staging_ptr
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    theirs = rl.decode_attention(q_decode, r)
+    ours = layer.decode_attention(q_decode, r)
+    out["decode_us_per_call_32k"] = round(timed(lambda: rl.decode_attention(q_decode, r), 100) * 1e3, 2)
+    out["decode_ours_us_per_call_same_loop"] = round(timed(lambda: layer.decode_attention(q_decode, r), 100) * 1e3, 2)
+    out["decode_max_abs_diff_ours_vs_reference"] = float((ours.float() - theirs.float()).abs().max())
+    out["decode_note"] = ("python-driven back-to-back calls on one cache (L2-warm); the reference's call is two torch.cat + two Triton "
+                          "launches (_splitk_partial_kernel, _splitk_reduce_kernel)")
+    for n in prefill_seqs:
+        t = gen_torch(1, H_Q, H_KV, n, D, W, RHO, 2000 + n.bit_length(), n_qry=n, device=dev)
+        vidx = hq.compute_vertical_indices(t["q"][:, :, -256:].mean(dim=2, keepdim=True), t["k"], W, RHO, kv_repeat=r)
+        theirs = ref_prefill(t["q"], t["k"], t["v"], vidx, window_size=W)
+        ours = hq.sage_vertical_attention_v2(t["q"], t["k"], t["v"], vidx, window_size=W)
+        d = ours.float() - theirs.float()
+        out[f"prefill_ms_{n}"] = round(timed(lambda: ref_prefill(t["q"], t["k"], t["v"], vidx, window_size=W), 3), 3)
+        out[f"prefill_ours_ms_{n}_whole_call"] = round(timed(lambda: hq.sage_vertical_attention_v2(t["q"], t["k"], t["v"], vidx, window_size=W), 3), 3)
+        out[f"prefill_max_abs_diff_{n}"] = float(d.abs().max())
+        out[f"prefill_rel_mse_{n}"] = float((d ** 2).sum() / (theirs.float() ** 2).sum())
+        del t, theirs, ours, d
+        torch.cuda.empty_cache()
     return out
 
 
@@ -389,24 +547,59 @@ def build_cpu_layer(seed=1015, n_prefix=N_PREFIX):
 
 
 def time_cpu_calls(calls, warmup):
-    """Seconds per decode-attention call of the reference's CPU path (torch-CPU
-    restatement, fp32, all intra-op threads), and the call's algorithmic bytes."""
+    """Seconds per decode-attention call of the reference's CPU path on the host cores (fp32, all intra-op
+    threads), the call's algorithmic bytes, the threads used and what ran: "reference" = the reference's own
+    ``DStageLayerCache`` (PyTorch fallback, HYBRID_ATTN_DECODE_KERNEL=pytorch) from ``oracle/_ref``, built by its own
+    ``freeze`` from the same seeded K/V; "port" = the torch-CPU restatement in ``oracle/`` when that copy is absent."""
     import torch
-    from oracle import hq_oracle_torch as ot
     torch.set_num_threads(os.cpu_count() or 1)
-    c, qd = build_cpu_layer()
     r = H_Q // H_KV
-    segs = ot.from_numpy_cache(c)
-    q = torch.from_numpy(qd)
+    ref = reference_dir()
+    if ref is not None:
+        try:
+            sys.path.insert(0, ref)
+            os.environ["HYBRID_ATTN_DECODE_KERNEL"] = "pytorch"
+            from src.ops.d_stage_kv_cache import DStageLayerCache as RefLayer
+        except Exception:
+            ref = None
+    if ref is not None:
+        from hyquant_b200.synth import gen_numpy
+        case = gen_numpy(B, H_Q, H_KV, N_PREFIX, D, W, RHO, 1015, n_qry=256)
+        layer = RefLayer(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+        layer.update_prefill(torch.from_numpy(case.k), torch.from_numpy(case.v))
+        layer.save_query_tail(torch.from_numpy(case.q))
+        layer.freeze(kv_repeat=r)
+        g = torch.Generator(); g.manual_seed(1022)
+        for _ in range(STAGING):
+            layer.append_staging(torch.randn(B, H_KV, 1, D, generator=g), torch.randn(B, H_KV, 1, D, generator=g))
+        q = torch.from_numpy(case.q_decode)
+        fn = lambda: layer.decode_attention(q, r)      # noqa: E731
+        nbytes = algorithmic_bytes(B * H_KV, B * H_Q, layer.k_quant_packed.shape[1],
+                                   layer.k_topk.shape[1] + layer._staging_ptr + layer.k_window.shape[1])
+        kind = "reference"
+    else:
+        from oracle import hq_oracle_torch as ot
+        c, qd = build_cpu_layer()
+        segs = ot.from_numpy_cache(c)
+        q = torch.from_numpy(qd)
+        fn = lambda: ot.decode_attention_fallback(q, *segs, B, H_KV, r)      # noqa: E731
+        nbytes = algorithmic_bytes(B * H_KV, B * H_Q, c.k_quant_packed.shape[1],
+                                   c.k_topk.shape[1] + c.staging_ptr + c.k_window.shape[1])
+        kind = "port"
     for _ in range(warmup):
-        ot.decode_attention_fallback(q, *segs, B, H_KV, r)
+        fn()
     t0 = time.perf_counter()
     for _ in range(calls):
-        ot.decode_attention_fallback(q, *segs, B, H_KV, r)
+        fn()
     dt = (time.perf_counter() - t0) / calls
-    nbytes = algorithmic_bytes(B * H_KV, B * H_Q, c.k_quant_packed.shape[1],
-                               c.k_topk.shape[1] + c.staging_ptr + c.k_window.shape[1])
-    return dt, nbytes, torch.get_num_threads()
+    return dt, nbytes, torch.get_num_threads(), kind
+
+
+CPU_SAMPLE = {"reference": "decode-attention calls of one layer (1/32 of a token) of the same 32K workload through the reference's own "
+                           "DStageLayerCache (PyTorch fallback path, fp32, cache frozen by the reference from the same seeded K/V), "
+                           "intra-op threads = cores",
+              "port": "decode-attention calls of one layer (1/32 of a token) of the same 32K workload, torch-CPU restatement of the "
+                      "reference's PyTorch fallback in fp32, intra-op threads = cores"}
 
 
 CONFIG = {"workload": "decode attention, Llama-3.1-8B shapes (B=1, 32q/8kv, d=128), prefix 32768, W=128, rho=5%, "
@@ -420,16 +613,15 @@ def run_reference(args):
     if rank != 0:
         return
     calls = max(1, args.steps)
-    dt, nbytes, cores = time_cpu_calls(calls, max(1, min(args.warmup, 2)))
+    dt, nbytes, cores, kind = time_cpu_calls(calls, max(1, min(args.warmup, 2)))
     gbs = nbytes / dt / 1e9
     line = {
         "impl": "reference", "metric": "decode_attn_hbm_gbps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": calls, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": CONFIG,
         "us_per_call": dt * 1e6,
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": "one layer's decode-attention call per step (1/32 of a token) of the same 32K workload, "
-                                   "torch-CPU restatement of the reference's PyTorch fallback in fp32, intra-op threads = cores"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"{calls} step(s), each one of the " + CPU_SAMPLE[kind]},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -462,11 +654,14 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
     sampler.start()
+    # the K-step block is timed `repeats` times back to back and the median is reported, so that the
+    # headline does not rest on one 10 ms sample
     ms, launches = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph,
-                                     overlap=not args.no_overlap)
+                                     overlap=not args.no_overlap, repeats=args.repeats)
     ms_plain = None
     if not args.no_overlap and not args.no_decode:
-        ms_plain, _ = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph, overlap=False)
+        ms_plain, _ = time_kernel_steps(torch, layers, qs, args.steps, args.warmup, dist, graph=not args.no_graph, overlap=False,
+                                        repeats=min(3, args.repeats))
     if args.no_e2e:
         e2e_ms, h2d, d2h = float("nan"), 0, 0
     else:
@@ -518,29 +713,41 @@ def run_ours(args):
             pass
         for n in [int(x) for x in args.prefill_seq.split(",")]:
             t = gen_torch(1, H_Q, H_KV, n, D, W, RHO, 2000 + n.bit_length(), n_qry=n, device=dev)
-            t0 = time.perf_counter()
             vidx = hq.compute_vertical_indices(t["q"][:, :, -256:].mean(dim=2, keepdim=True), t["k"], W, RHO, kv_repeat=H_Q // H_KV)
             plan = PrefillPlan(t["q"], t["k"], t["v"], vidx, W, None, True)
-            torch.cuda.synchronize()
-            prep_ms = (time.perf_counter() - t0) * 1e3
             for _ in range(2):
                 plan.run()
             torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             reps = 5 if n <= 8192 else 3
-            e0.record()
+            ev[0].record()
             for _ in range(reps):
                 plan.run()
-            e1.record()
+            ev[1].record()
+            # the whole call as the reference's entry point makes it: vertical-line selection, quantisation, V transpose,
+            # vertical gather and the attention kernel (device time; the allocator serves the buffers from its cache)
+            ev[2].record()
+            for _ in range(reps):
+                vi = hq.compute_vertical_indices(t["q"][:, :, -256:].mean(dim=2, keepdim=True), t["k"], W, RHO, kv_repeat=H_Q // H_KV)
+                PrefillPlan(t["q"], t["k"], t["v"], vi, W, None, True).run()
+            ev[3].record()
             torch.cuda.synchronize()
-            ms_ = e0.elapsed_time(e1) / reps
+            plan.check_status()
+            ms_, ms_all = ev[0].elapsed_time(ev[1]) / reps, ev[2].elapsed_time(ev[3]) / reps
             prefill.append({"seq": n, "ms": round(ms_, 3), "tflops": round(plan.flops / ms_ / 1e9, 1),
                             "frac_of_measured_bf16_sustained": None if not bf16_peak else round(plan.flops / ms_ / 1e9 / bf16_peak, 3),
-                            "prepare_ms_first_call": round(prep_ms, 2),
+                            "ms_with_selection_and_preparation": round(ms_all, 3),
+                            "tflops_with_selection_and_preparation": round(plan.flops / ms_all / 1e9, 1),
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
-    batched = long_ctx = bit_widths = None
+    batched = long_ctx = bit_widths = prefill_heads = ref_triton = None
     legs = set() if args.no_extra else set(args.extra_legs.split(","))
+    if "reference" in legs and rank == 0:
+        ref_triton = bench_reference_triton(torch, hq, dev, layers[0], qs[0], [int(x) for x in args.prefill_seq.split(",")])
+        torch.cuda.empty_cache()
+    if "prefill_heads" in legs and (world > 1 or args.prefill_heads_single):
+        prefill_heads = bench_prefill_heads(torch, hq, dev, rank, world, dist)
+        torch.cuda.empty_cache()
     if "bits" in legs and rank == 0:
         bit_widths = bench_bit_widths(torch, hq, dev, not args.no_graph)
         torch.cuda.empty_cache()
@@ -553,10 +760,9 @@ def run_ours(args):
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            dt, nb, cores = time_cpu_calls(5, 1)
-            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                   "sample": "5 decode-attention calls of one layer of the same 32K workload (torch-CPU restatement of "
-                             "the reference's PyTorch fallback in fp32, intra-op threads = cores)", "ms_per_call": dt * 1e3}
+            dt, nb, cores, kind = time_cpu_calls(5, 1)
+            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+                   "sample": "5 " + CPU_SAMPLE[kind], "ms_per_call": dt * 1e3}
         line = {
             "metric": "decode_attn_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -581,10 +787,16 @@ def run_ours(args):
             "bit_width_decode": bit_widths,
             "batched_decode": batched,
             "long_context_decode": long_ctx,
+            "prefill_kv_head_groups": prefill_heads,
+            "reference_triton_sm100": ref_triton,
         }
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+    bad = [name for name, leg in (("batched_decode", batched), ("long_context_decode", long_ctx))
+           if leg is not None and leg.get("sharded_ok") is False]
+    if bad:
+        raise SystemExit(f"sharded result differs from the single-GPU result (or a peer wait ran out) in: {bad}")
 
 
 # DRAM bytes per launch of the decode kernel from an ncu capture of this workload
@@ -608,7 +820,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="launch every decode call plainly (no programmatic dependent launch)")
     ap.add_argument("--no-extra", action="store_true", help="skip the bit-width, batched (64q/8kv x 16) and 128K long-context decode legs")
-    ap.add_argument("--extra-legs", default="bits,batched,long", help="which of those legs to run (comma-separated)")
+    ap.add_argument("--extra-legs", default="bits,batched,long,prefill_heads,reference",
+                    help="which of those legs to run (comma-separated); prefill_heads = the 32K prefill with its KV-head groups "
+                         "over the ranks (N > 1), reference = the reference's Triton kernels on the same inputs (needs oracle/_ref)")
+    ap.add_argument("--prefill-heads-single", action="store_true", help="run the prefill_heads leg on one GPU too")
+    ap.add_argument("--repeats", type=int, default=10, help="times the K-step block is timed; the median is reported")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

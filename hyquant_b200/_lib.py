@@ -23,12 +23,13 @@ ERR_NAMES = {-1: "HQ_ERR_INVALID", -2: "HQ_ERR_UNSUPPORTED", -3: "HQ_ERR_ALIGNME
 EXPORTS = [
     "hq_version", "hq_last_error",
     "hq_quant_pack", "hq_quant_pack_int4", "hq_staging_append",
-    "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static",
+    "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static", "hq_decode_static_status",
     "hq_lse_merge", "hq_lse_merge_strided",
     "hq_vertical_scores",
     "hq_topk",
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
-    "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
+    "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_quant_blocks", "hq_per_block_int8",
+    "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
     "hq_prefill_hybrid",
     "hq_peer_exchange_bytes", "hq_peer_slot", "hq_peer_recv_slot", "hq_peer_exchange_merge", "hq_peer_status",
     "hq_peer_buffer_create", "hq_peer_buffer_open", "hq_peer_buffer_close", "hq_peer_buffer_destroy",
@@ -100,6 +101,7 @@ def _declare(lib):
     lib.hq_decode_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_decode_splitk.argtypes = [C.POINTER(DecodeArgs), vp]
     lib.hq_decode_splitk_static.argtypes = [C.POINTER(DecodeArgs), vp]
+    lib.hq_decode_static_status.argtypes = [C.POINTER(C.c_int)]
     lib.hq_lse_merge.argtypes = [vp, vp, vp, i32, i32, vp, i32, i64, vp]
     lib.hq_lse_merge_strided.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp, i32, i64, vp]
     lib.hq_vertical_scores.argtypes = [vp, i32, i64, i64, i64, i32, i32, i32, i32,
@@ -112,6 +114,8 @@ def _declare(lib):
     lib.hq_prefill_quant_workspace_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_prefill_quant.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, i32,
                                      vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    lib.hq_prefill_quant_blocks.argtypes = lib.hq_prefill_quant.argtypes
+    lib.hq_per_block_int8.argtypes = [vp, i64, i64, i64, i32, i32, i32, i32, C.c_float, vp, vp, i64, i64, i64, vp, vp]
     lib.hq_prefill_vertical_prepare.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, i64, i64,
                                                 vp, vp, vp, vp, vp, vp]
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]

@@ -1266,21 +1266,15 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBy
 // ignored.  The first call on each device looks up the array's device address (with that
 // device current); make that first call outside any stream capture.  Every call shares the one
 // array, so two calls that may overlap on the GPU (different streams, or different host threads
-// without ordering between their streams) race; keep them in one stream.  The ticket and status
-// words are cleared in-stream before each launch.  A shape whose scratch need exceeds 4 MiB is
-// rejected with HQ_ERR_WORKSPACE.  No cudaMalloc / cudaFree or allocating library call is made.
-extern "C" int hq_decode_splitk_static(const hq_decode_args* a, void* stream) {
-  using namespace hq;
-  HQ_REQUIRE(a != nullptr, HQ_ERR_INVALID, "hq_decode_splitk_static: null args");
-  HQ_REQUIRE(a->struct_bytes == (int32_t)sizeof(hq_decode_args), HQ_ERR_INVALID,
-             "hq_decode_splitk_static: struct_bytes %d != %d", a->struct_bytes, (int)sizeof(hq_decode_args));
-  if (a->BH_KV == 0) return HQ_OK;
-  int64_t need = 0;
-  const int rc = hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
-  if (rc != HQ_OK) return rc;
-  HQ_REQUIRE(need <= kStaticScratchBytes, HQ_ERR_WORKSPACE,
-             "hq_decode_splitk_static: this shape needs %lld bytes of scratch, the built-in array holds %lld; "
-             "use hq_decode_splitk with a caller workspace", (long long)need, (long long)kStaticScratchBytes);
+// without ordering between their streams) race; keep them in one stream.  The ticket words are
+// cleared in-stream before each launch; the status word (bit 0: a bounded wait ran out) is NOT,
+// so it accumulates over calls until hq_decode_static_status reads and clears it.  A shape whose
+// scratch need exceeds 4 MiB is rejected with HQ_ERR_WORKSPACE.  No cudaMalloc / cudaFree or
+// allocating library call is made.
+namespace hq {
+// Device address of the array on the current device.  The table is filled without locking: two threads
+// that race here both store the same address, which the runtime returns for the lifetime of the context.
+static int static_scratch(void** out) {
   constexpr int kMaxDev = 64;
   static void* dev_ptr[kMaxDev] = {nullptr};
   int dev = 0;
@@ -1292,11 +1286,46 @@ extern "C" int hq_decode_splitk_static(const hq_decode_args* a, void* stream) {
     HQ_REQUIRE(p != nullptr, HQ_ERR_CUDA, "hq_decode_splitk_static: no device address for the scratch array");
     dev_ptr[dev] = p;
   }
-  const int64_t head = kWsHeaderBytes + align_up((int64_t)a->BH_KV * 4, 256);
-  HQ_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, (size_t)head, (cudaStream_t)stream));
+  *out = dev_ptr[dev];
+  return HQ_OK;
+}
+}  // namespace hq
+
+extern "C" int hq_decode_splitk_static(const hq_decode_args* a, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(a != nullptr, HQ_ERR_INVALID, "hq_decode_splitk_static: null args");
+  HQ_REQUIRE(a->struct_bytes == (int32_t)sizeof(hq_decode_args), HQ_ERR_INVALID,
+             "hq_decode_splitk_static: struct_bytes %d != %d", a->struct_bytes, (int)sizeof(hq_decode_args));
+  HQ_REQUIRE((a->flags & ~HQ_DECODE_OVERLAP_PREVIOUS) == 0, HQ_ERR_INVALID, "hq_decode_splitk_static: unknown flags 0x%x", a->flags);
+  if (a->BH_KV == 0) return HQ_OK;
+  int64_t need = 0;
+  const int rc = hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
+  if (rc != HQ_OK) return rc;
+  HQ_REQUIRE(need <= kStaticScratchBytes, HQ_ERR_WORKSPACE,
+             "hq_decode_splitk_static: this shape needs %lld bytes of scratch, the built-in array holds %lld; "
+             "use hq_decode_splitk with a caller workspace", (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int rs = static_scratch(&scratch);
+  if (rs != HQ_OK) return rs;
+  // the tickets (one word per head, after the header that holds the status word) must start at zero
+  HQ_CUDA(cudaMemsetAsync((uint8_t*)scratch + kWsHeaderBytes, 0, (size_t)align_up((int64_t)a->BH_KV * 4, 256), (cudaStream_t)stream));
   hq_decode_args b = *a;
   b.flags = 0;                       // the kernel's predecessor in the stream is the memset above
-  b.workspace = dev_ptr[dev];
+  b.workspace = scratch;
   b.workspace_bytes = kStaticScratchBytes;
   return hq_decode_splitk(&b, stream);
+}
+
+// Synchronising read-and-clear of the status word of the built-in scratch array on the current device
+// (0 = every bounded wait of the hq_decode_splitk_static calls since the last read completed; bit 0 = one ran
+// out, and the output of that call is not valid).
+extern "C" int hq_decode_static_status(int* status) {
+  using namespace hq;
+  HQ_REQUIRE(status != nullptr, HQ_ERR_INVALID, "hq_decode_static_status: null pointer");
+  void* scratch = nullptr;
+  const int rs = static_scratch(&scratch);
+  if (rs != HQ_OK) return rs;
+  HQ_CUDA(cudaMemcpy(status, scratch, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) HQ_CUDA(cudaMemset(scratch, 0, sizeof(int)));
+  return HQ_OK;
 }

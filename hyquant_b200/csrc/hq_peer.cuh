@@ -28,13 +28,18 @@ struct PeerGroup {
   int64_t timeout_ns;
 };
 
+// A word of the exchange is {fp32 value, uint32 sequence number} and is valid exactly when its upper half equals the
+// call's sequence number.  That needs the two halves to become visible together, so each word moves as ONE 8-byte
+// scalar access (naturally aligned b64 accesses are single-copy atomic; the elements of a .v2.b32 access are not
+// guaranteed to be).
 __device__ __forceinline__ void st_pair_sys(uint2* p, float v, uint32_t seq) {
-  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+  const uint64_t w = (uint64_t)__float_as_uint(v) | ((uint64_t)seq << 32);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
+  uint64_t w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;

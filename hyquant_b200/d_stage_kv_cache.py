@@ -25,7 +25,8 @@ import torch
 
 from . import _lib
 from ._lib import HyQuantError
-from .decode_d_stage import GROUP_SIZE, SCALE_MODE, DecodePlan, quantize_per_token_into
+from . import decode_d_stage as _dd
+from .decode_d_stage import GROUP_SIZE, DecodePlan, quantize_per_token_into
 from .patch._common import topk_indices, vertical_scores, vertical_topk_count
 
 try:
@@ -185,7 +186,7 @@ class DStageLayerCache:
             self.k_topk.data_ptr(), self.v_topk.data_ptr(), self.k_window.data_ptr(), self.v_window.data_ptr(),
             self._kq.data_ptr(), self._vq.data_ptr(), self._kq.stride(0), self._vq.stride(0),
             self._ks.data_ptr(), self._vs.data_ptr(), self._ks.stride(0),
-            self.k_bits, self.v_bits, SCALE_MODE, _lib.stream_ptr(device))
+            self.k_bits, self.v_bits, _dd.SCALE_MODE, _lib.stream_ptr(device))
         _lib.check(rc, "hq_cache_reorganize_bits")
         self._n_quant = n_quant
         if dtype != torch.bfloat16:   # keep the reference's attribute dtype for non-bf16 models

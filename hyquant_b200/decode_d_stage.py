@@ -7,7 +7,7 @@ conventions); the device work is done by the sm_100a kernels behind the C ABI
 What differs from the reference by design:
   * one kernel launch per decode call (split-K partials and their log-sum-exp
     merge are fused), no ``torch.cat`` of the BF16 segments;
-  * only K4/V4 is built; other bit widths raise ``HyQuantError``;
+  * K and V prefixes in 8, 4 or 2 bits, every pair by the same kernel;
   * CUDA tensors only — there is no CPU or PyTorch fallback.
 """
 
@@ -24,9 +24,11 @@ from ._lib import DecodeArgs, HyQuantError
 _LOG2_E = 1.44269504
 GROUP_SIZE = 128  # staging flush threshold (tokens); reference decode_d_stage.py:19
 
-# scale rounding mode of the quantiser: 0 = IEEE divide by 7 (CPU-eager PyTorch,
-# what the golden vectors pin), 1 = multiply by fp32(1/7) (CUDA-eager PyTorch)
-SCALE_MODE = 0
+# Scale rounding of the quantiser.  1 (default) = max|x| * fp32(1 / q_max): what eager PyTorch computes on a CUDA
+# device, i.e. the reference's production path (its quantiser always runs on the GPU; pinned by the fixtures the
+# reference produced on a B200).  0 = IEEE max|x| / q_max: eager PyTorch on the CPU, what the fixtures produced by
+# running the reference on the CPU pin.  The two differ in the last bit of an fp16 scale in rare cases.
+SCALE_MODE = 1
 
 
 # ----------------------------------------------------------------------------

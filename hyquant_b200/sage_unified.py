@@ -38,8 +38,63 @@ def _prep_inputs(q, k, v):
     return bf(q), bf(k), bf(v), B, H_q, H_kv, N
 
 
-def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smooth_k: bool):
-    """Operand preparation (``hq_prefill_quant``): returns q_i8, q_bf, q_scale, k_i8, k_bf, k_scale, k_mean."""
+# INT8 scale granularity of the prefill: "row" = one scale per query row and per key row (the default: an outlier
+# row costs its neighbours no precision), "block" = the reference's one scale per 128 query rows / 64 key rows
+# (per_block_int8, quant_per_block.py:49-101).
+SCALE_GRANULARITY = "row"
+
+
+def per_block_int8(q: torch.Tensor, k: torch.Tensor, km: Optional[torch.Tensor] = None, BLKQ: int = 128, BLKK: int = 64,
+                   sm_scale: Optional[float] = None, tensor_layout: str = "HND"):
+    """The reference's block quantiser (vendor/sageattention/triton/quant_per_block.py:49-101), same signature
+    and results bit for bit: returns (q_int8, q_scale [B,H_q,ceil(L/BLKQ)] fp32, k_int8, k_scale [B,H_kv,ceil(L/BLKK)]).
+    q is scaled by ``sm_scale * log2(e)`` before quantising; ``km`` (the key mean, [B,H_kv,1,D]) is subtracted from k
+    in the input dtype first.  bf16 inputs."""
+    for name, t in (("q", q), ("k", k)):
+        _lib.require_cuda(t, name)
+        if t.dtype != torch.bfloat16:
+            raise HyQuantError("per_block_int8 is built for bf16 inputs")
+    if tensor_layout == "NHD":
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
+        km = None if km is None else km.transpose(1, 2)
+    elif tensor_layout != "HND":
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    if q.shape[-1] != 128:
+        raise HyQuantError(f"head_dim {q.shape[-1]} is not built (128 only)")
+    if sm_scale is None:
+        sm_scale = q.shape[-1] ** -0.5
+    lib = _lib.lib()
+
+    def one(x, blk, mul, mean):
+        ok = x.stride(3) == 1 and all(s % 8 == 0 for s in x.stride()[:3]) and x.data_ptr() % 16 == 0
+        x = x if ok else x.contiguous()
+        B, H, L, _ = x.shape
+        xi = torch.empty(B, H, L, 128, dtype=torch.int8, device=x.device)
+        sc = torch.empty(B, H, (L + blk - 1) // blk, dtype=torch.float32, device=x.device)
+        mp = None
+        if mean is not None:
+            mean = mean.to(torch.bfloat16).reshape(B * H, 128).contiguous()
+            mp = mean.data_ptr()
+        rc = lib.hq_per_block_int8(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), B, H, L, blk, float(mul), mp,
+                                   xi.data_ptr(), xi.stride(0), xi.stride(1), xi.stride(2), sc.data_ptr(),
+                                   _lib.stream_ptr(x.device))
+        _lib.check(rc, "hq_per_block_int8")
+        return xi, sc
+
+    qi, qs = one(q, BLKQ, sm_scale * _LOG2_E, None)
+    ki, ks = one(k, BLKK, 1.0, km)
+    if tensor_layout == "NHD":
+        qi, ki = qi.transpose(1, 2), ki.transpose(1, 2)
+    return qi, qs, ki, ks
+
+
+def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smooth_k: bool,
+                      scale_granularity: Optional[str] = None):
+    """Operand preparation (``hq_prefill_quant`` / ``hq_prefill_quant_blocks``): returns q_i8, q_bf, q_scale, k_i8,
+    k_bf, k_scale, k_mean; the scale arrays hold one value per row either way."""
+    gran = SCALE_GRANULARITY if scale_granularity is None else scale_granularity
+    if gran not in ("row", "block"):
+        raise ValueError(f"scale_granularity must be 'row' or 'block', got {gran!r}")
     B, H_q, N, _ = qb.shape
     H_kv = kb.shape[1]
     dev = qb.device
@@ -55,12 +110,13 @@ def quantize_operands(qb: torch.Tensor, kb: torch.Tensor, sm_scale: float, smoot
     nb = C.c_int64(0)
     _lib.check(lib.hq_prefill_quant_workspace_bytes(B, H_kv, C.byref(nb)), "hq_prefill_quant_workspace_bytes")
     ws = torch.empty(int(nb.value), dtype=torch.uint8, device=dev)
-    rc = lib.hq_prefill_quant(qb.data_ptr(), qb.stride(0), qb.stride(1), qb.stride(2),
-                              kb.data_ptr(), kb.stride(0), kb.stride(1), kb.stride(2),
-                              B, H_q, H_kv, N, float(sm_scale), 1 if smooth_k else 0,
-                              q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr(),
-                              k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr(), k_mean.data_ptr(),
-                              ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev))
+    fn = lib.hq_prefill_quant if gran == "row" else lib.hq_prefill_quant_blocks
+    rc = fn(qb.data_ptr(), qb.stride(0), qb.stride(1), qb.stride(2),
+            kb.data_ptr(), kb.stride(0), kb.stride(1), kb.stride(2),
+            B, H_q, H_kv, N, float(sm_scale), 1 if smooth_k else 0,
+            q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr(),
+            k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr(), k_mean.data_ptr(),
+            ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "hq_prefill_quant")
     return q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean
 
@@ -70,7 +126,7 @@ class PrefillPlan:
     plus the filled ``hq_prefill_args``; ``run()`` launches only the attention kernel."""
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                 window_size: int, sm_scale: Optional[float], smooth_k: bool):
+                 window_size: int, sm_scale: Optional[float], smooth_k: bool, scale_granularity: Optional[str] = None):
         dtype = q.dtype
         qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
         dev = q.device
@@ -79,7 +135,7 @@ class PrefillPlan:
         if sm_scale is None:
             sm_scale = 128 ** -0.5
         nqb, nkb = (N + 127) // 128, (N + 63) // 64
-        q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k)
+        q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean = quantize_operands(qb, kb, sm_scale, smooth_k, scale_granularity)
         T = 0
         vert_k = vert_vt = nvv = vasc = None
         Npad = (N + 63) // 64 * 64
@@ -135,10 +191,11 @@ class PrefillPlan:
 
 
 def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                   window_size: int, sm_scale: Optional[float], smooth_k: bool) -> torch.Tensor:
+                   window_size: int, sm_scale: Optional[float], smooth_k: bool,
+                   scale_granularity: Optional[str] = None) -> torch.Tensor:
     """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
     vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
-    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k).run()
+    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, scale_granularity).run()
 
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,

@@ -92,6 +92,37 @@ def shard_layer_sequence(layer, world: int, rank: int):
     return s
 
 
+def shard_layer_heads(layer, world: int, rank: int):
+    """This rank's KV-head group of a frozen ``DStageLayerCache`` that holds the whole cache: a new layer cache
+    owning copies of kv-heads ``kv_head_range(H_KV, world, rank)`` of every batch entry (all four segments).  Its
+    decode output equals rows ``[h0 * R, h1 * R)`` of every batch entry of the full cache's output; nothing is
+    exchanged between ranks."""
+    from .d_stage_kv_cache import DStageLayerCache
+    if layer.phase != "decode":
+        raise ValueError("shard_layer_heads needs a frozen cache")
+    B, H_KV = layer._B, layer._H_KV
+    h0, h1 = kv_head_range(H_KV, world, rank)
+    dev = layer._kq.device
+    idx = (torch.arange(B, device=dev)[:, None] * H_KV + torch.arange(h0, h1, device=dev)[None, :]).reshape(-1)
+    s = DStageLayerCache(layer.layer_idx, layer.k_bits, layer.v_bits, layer.window_size, layer.top_ratio, layer.use_vert)
+    s._B, s._H_KV, s._D = B, h1 - h0, layer._D
+    n = layer._n_quant
+    s._alloc_prefix(idx.numel(), n, dev)
+    for dst, src in ((s._kq, layer._kq), (s._vq, layer._vq), (s._ks, layer._ks), (s._vs, layer._vs)):
+        dst[:, :n].copy_(src[idx, :n])
+    s._n_quant = n
+    s.k_topk, s.v_topk = layer.k_topk[idx].contiguous(), layer.v_topk[idx].contiguous()
+    s.k_window, s.v_window = layer.k_window[idx].contiguous(), layer.v_window[idx].contiguous()
+    s._staging_buf_k, s._staging_buf_v = layer._staging_buf_k[idx].contiguous(), layer._staging_buf_v[idx].contiguous()
+    s._staging_ptr = layer._staging_ptr
+    s._seq_len = layer._seq_len
+    if layer.vertical_indices is not None:
+        s.vertical_indices = layer.vertical_indices[:, h0:h1].contiguous()
+    s._lib = layer._lib
+    s.phase = "decode"
+    return s
+
+
 class PeerExchange:
     """Exchange buffers of a process group on one node, for ``hq_peer_exchange_merge``.
 

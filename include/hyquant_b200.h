@@ -177,8 +177,11 @@ int hq_decode_splitk(const hq_decode_args* args, void* stream);
  * need more than 4 MiB of scratch (see hq_decode_workspace_bytes) fail with HQ_ERR_WORKSPACE.
  * The first call on a device resolves the array's device address: make it before any stream
  * capture.  All calls share the array, so calls that can overlap on the GPU race — issue them
- * in one stream.  Allocates nothing. */
+ * in one stream.  Allocates nothing.  The ticket words are cleared in-stream before every call; the
+ * status word (bit 0: a bounded device wait ran out, that call's output is invalid) is left to accumulate
+ * until hq_decode_static_status, a synchronising call, reads and clears it. */
 int hq_decode_splitk_static(const hq_decode_args* args, void* stream);
+int hq_decode_static_status(int* status);
 
 /* --------------------------------------------------------------------------
  * Log-sum-exp merge of G shards' partials (the algebra of _splitk_reduce_kernel,
@@ -301,6 +304,28 @@ int hq_prefill_quant(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
                      void* q_i8, void* q_bf, float* q_scale,
                      void* k_i8, void* k_bf, float* k_scale, void* k_mean,
                      void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The same preparation with the reference's scale granularity: one scale per block of 128 query rows and per
+ * block of 64 key rows (per_block_int8 with BLKQ = 128, BLKK = 64, quant_per_block.py:49-101).  The scale arrays
+ * keep the per-row layout above (a block's scale repeated for each of its rows), so hq_prefill_hybrid runs
+ * unchanged on either. */
+int hq_prefill_quant_blocks(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
+                            const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn,
+                            int B, int H_Q, int H_KV, int N, float sm_scale, int smooth_k,
+                            void* q_i8, void* q_bf, float* q_scale,
+                            void* k_i8, void* k_bf, float* k_scale, void* k_mean,
+                            void* workspace, int64_t workspace_bytes, void* stream);
+
+/* One tensor through the reference's block quantiser, quant_per_block_int8_kernel
+ * (src/ops/vendor/sageattention/triton/quant_per_block.py:21-47), bit for bit (the two fp32 divisions are the
+ * approximate div.full.f32 the Triton kernel compiles to):
+ *   x bf16 [B,H,L,128] (strides in elements), mean bf16 [B*H,128] or NULL (x - mean rounded to bf16 first, as
+ *   per_block_int8 forms k - km in the input dtype, :53-54), mul: the factor applied before quantising
+ *   (sm_scale * log2(e) for queries, 1 for keys);
+ *   x_i8 int8 [B,H,L,128] (strides in elements, multiples of 8); scale fp32 [B,H,ceil(L/blk)]. */
+int hq_per_block_int8(const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, int B, int H, int L, int blk,
+                      float mul, const void* mean, void* x_i8, int64_t o_sb, int64_t o_sh, int64_t o_sn,
+                      float* scale, void* stream);
 
 /* Step 2: vertical-line bookkeeping.  Replaces reorder_kv_for_vertical
  * (src/ops/sage_unified.py:499-547) without expanding K/V to query heads:

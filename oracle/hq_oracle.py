@@ -15,10 +15,14 @@ Pinning status
   writes ``tests/golden/*.npz``; ``tests/test_oracle_golden.py`` replays them).
 * rest/vertical reorder + per-query-block counts of the hybrid prefill
   (``reorder_kv_for_vertical``): PINNED the same way (it is eager PyTorch).
-* per-block INT8 quantiser and the hybrid prefill kernel itself: PARITY
-  UNPINNED — the reference implements them only as Triton GPU kernels that
-  cannot execute in a GPU-less container, and the reference ships no golden
-  vectors.  They are restated from the source text.
+* per-block INT8 quantiser and the hybrid prefill kernels, and the Triton split-K decode: PINNED against
+  outputs of the reference's own Triton kernels executed on a B200 (``tests/golden/make_golden_gpu.py``
+  runs them from the untracked copy ``oracle/_ref`` and writes ``tests/golden/*_gpu.npz``;
+  ``tests/test_oracle_golden_gpu.py`` replays them here): the hybrid prefill restatement agrees with the
+  Triton kernel to one bf16 ulp of the output (about 85 % of the outputs bit for bit), the block quantiser
+  to the rounding of the approximate fp32 division Triton compiles to (scales within 1 ulp, fewer than
+  1e-3 of the codes off by one), the decode output within 2e-4, and the codes and scales of a cache frozen
+  by the reference on the device (CUDA-eager PyTorch) hash-equal.
 
 bf16 tensors are represented as float32 arrays holding bf16-exact values
 (see :func:`bf16_round`); fp16 tensors as ``np.float16``.
@@ -240,12 +244,13 @@ class LayerCache:
     staging_ptr: int = 0
     seq_len: int = 0
     vidx: Optional[np.ndarray] = field(default=None)   # [B, H_KV, T] for inspection
+    reciprocal_scale: bool = False                      # quantiser rounding of CUDA-eager PyTorch (see quantize_per_token)
 
 
 def freeze(keys: np.ndarray, values: np.ndarray, query_tail: Optional[np.ndarray],
            kv_repeat: int, window_size: int, top_ratio: float,
            k_bits: int = 4, v_bits: int = 4, use_vert: bool = True,
-           round_fn=None, vidx_override: Optional[np.ndarray] = None) -> LayerCache:
+           round_fn=None, vidx_override: Optional[np.ndarray] = None, reciprocal_scale: bool = False) -> LayerCache:
     """Prefill -> decode transition.  d_stage_kv_cache.py:106-189.
 
     ``keys/values`` [B, H_KV, N, D]; ``query_tail`` [B, H_Q, <=W, D] (what
@@ -291,8 +296,8 @@ def freeze(keys: np.ndarray, values: np.ndarray, query_tail: Optional[np.ndarray
             v_topk = np.zeros((BH, 0, D), dtype=keys.dtype)
             k_compact = k_prefix.reshape(BH, prefix_len, D)
             v_compact = v_prefix.reshape(BH, prefix_len, D)
-        kq, ks = quantize_per_token(k_compact, k_bits)
-        vq, vs = quantize_per_token(v_compact, v_bits)
+        kq, ks = quantize_per_token(k_compact, k_bits, reciprocal_scale)
+        vq, vs = quantize_per_token(v_compact, v_bits, reciprocal_scale)
     else:
         kq = np.zeros((BH, 0, pk[k_bits]), dtype=np.int8)
         vq = np.zeros((BH, 0, pk[v_bits]), dtype=np.int8)
@@ -307,14 +312,14 @@ def freeze(keys: np.ndarray, values: np.ndarray, query_tail: Optional[np.ndarray
         k_window=k_window, v_window=v_window,
         staging_k=np.zeros((BH, GROUP_SIZE, D), dtype=keys.dtype),
         staging_v=np.zeros((BH, GROUP_SIZE, D), dtype=keys.dtype),
-        staging_ptr=0, seq_len=N, vidx=vidx,
+        staging_ptr=0, seq_len=N, vidx=vidx, reciprocal_scale=reciprocal_scale,
     )
 
 
 def flush_staging(c: LayerCache) -> None:
     """d_stage_kv_cache.py:209-217 — quantise all 128 slots, append to the prefix."""
-    kp, ks = quantize_per_token(c.staging_k, c.k_bits)
-    vp, vs = quantize_per_token(c.staging_v, c.v_bits)
+    kp, ks = quantize_per_token(c.staging_k, c.k_bits, c.reciprocal_scale)
+    vp, vs = quantize_per_token(c.staging_v, c.v_bits, c.reciprocal_scale)
     c.k_quant_packed = np.concatenate([c.k_quant_packed, kp], axis=1)
     c.v_quant_packed = np.concatenate([c.v_quant_packed, vp], axis=1)
     c.k_scale = np.concatenate([c.k_scale, ks], axis=1)
@@ -434,7 +439,8 @@ def decode_partials(q: np.ndarray, k_all: np.ndarray, v_all: np.ndarray, sm_scal
 
 # ----------------------------------------------------------------------------
 # a12 — per-block INT8 quantiser (vendor/sageattention/triton/quant_per_block.py:21-101)
-# PARITY UNPINNED (Triton-only in the reference).
+# The Triton kernel divides with the approximate div.full.f32; IEEE division here differs from it in
+# the last bit of a scale and, through that, in fewer than 1e-3 of the codes by one step.
 # ----------------------------------------------------------------------------
 
 def quant_per_block_int8(x: np.ndarray, blk: int, sm_scale: float = 1.0) -> Tuple[np.ndarray, np.ndarray]:
@@ -537,7 +543,7 @@ def hybrid_prefill_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray,
                              sm_scale: Optional[float] = None, smooth_k: bool = True,
                              round_fn=None) -> np.ndarray:
     """Restatement of ``sage_vertical_attention_v2`` (sage_unified.py:550-622)
-    with the kernel ``_attn_fwd_vertical_v2`` (:398-496).  PARITY UNPINNED.
+    with the kernel ``_attn_fwd_vertical_v2`` (:398-496).
 
     q [B, H_q, N, D], k/v [B, H_kv, N, D] (float32 holding input-dtype-exact
     values), vertical_indices [B, H_q, T] int64.  ``round_fn`` rounds to the
