@@ -8,11 +8,12 @@
 //
 // Work decomposition.  Each head's tokens are cut into ~4 KB "units" (32 INT4
 // tokens, or 8 BF16 tokens), so units are balanced in BYTES across segment
-// kinds.  A CTA owns a contiguous range of one head's units; its 8 warps take
-// units round-robin.  Every warp runs its own 3-slot ring: lane 0 issues 1-D
-// bulk copies (TMA engine, mbarrier complete_tx) for the units ahead, the warp
-// consumes the current one straight from shared memory.  No CTA-wide barrier
-// is needed in the main loop.
+// kinds.  A CTA (one per SM, 16 warps) owns a contiguous range of one head's
+// units; its warps take units round-robin.  Every warp runs its own 3-slot ring:
+// lane 0 issues 1-D bulk copies (TMA engine, mbarrier complete_tx) for the units
+// ahead, the warp consumes the current one straight from shared memory.  No
+// CTA-wide barrier is needed before or in the main loop: every warp reads the
+// query fragments it needs straight from global memory.
 //
 // Math.  Scores are computed transposed, S^T = K Q^T, with tokens on the MMA M
 // axis and the kv-group's query heads on the N axis (N = 8 per tile, so GQA
@@ -22,8 +23,14 @@
 // the MMA sees 1032 + code (low nibbles) or 1152 + 16 code (high nibbles, with
 // q/16 on the other operand) and the per-head constant 1032 sum(q_even) +
 // 1152 sum(q_odd/16) is subtracted from the fp32 score, which removes half of
-// the conversion instructions.  V is converted exactly (offset subtracted per
-// element) because its products accumulate over the whole sequence.  The
+// the conversion instructions.  V codes reach the MMA as fp16 SUBNORMALS: the
+// field (code + h) of an element, left where it is in the low 8 bits of a 16-bit
+// lane, is the fp16 value (code + h) 2^-24 (bits 0-3), 2^-20 (bits 4-7) and so on,
+// exactly, with no conversion arithmetic at all.  The small offset h (8 at 4 bits)
+// is taken off once at the end as h * sum(p~), that sum coming from one extra MMA
+// per 16 tokens against an all-ones operand; the power of two is a per-tile
+// constant (tiles are built from fields of one position) applied at the end too,
+// and the BF16 segments feed the same accumulators with P scaled by it.  The
 // per-token K scale multiplies the fp32 score, the per-token V scale is folded
 // into P before the PV product.
 // BF16 segments use mma.sync bf16.  All segments share one online softmax in
@@ -31,15 +38,23 @@
 // fp32 registers.  Warps merge through shared memory, CTAs through a fp32
 // workspace with an atomic ticket: the last CTA of a head does the
 // log-sum-exp merge and writes the output, so there is no second launch.
+#include <stdlib.h>
+
 #include "hq_common.cuh"
 #include "hq_peer.cuh"
 
 namespace hq {
 
-// Warps per CTA: 8 with one n8 tile of query heads (GQA ratio <= 8: 2 CTAs per SM at <= 128 registers when the slots
-// are small enough for two); with two tiles (ratios 9..16, 32 fp32 accumulators more per thread) 6, so that 2 CTAs of
-// 192 threads fit an SM at <= 168 registers, or 8 when the slot size allows one CTA per SM anyway.
-__host__ __device__ constexpr int warps_of(int NT, int ctas_per_sm) { return (NT == 2 && ctas_per_sm == 2) ? 6 : 8; }
+// One CTA per SM.  Warps per CTA: 16 with one n8 tile of query heads (GQA ratio <= 8; 128 registers per thread fill
+// the register file), 12 with two tiles (ratios 9..16: 32 fp32 accumulators more per thread, <= 168 registers).  Half
+// as many CTAs as two per SM would give means half as many split-K partials to merge per head.
+#ifndef HQ_DEC_WARPS1
+#define HQ_DEC_WARPS1 16
+#endif
+#ifndef HQ_DEC_WARPS2
+#define HQ_DEC_WARPS2 12
+#endif
+__host__ __device__ constexpr int warps_of(int NT) { return NT == 2 ? HQ_DEC_WARPS2 : HQ_DEC_WARPS1; }
 constexpr int kSlots = 3;
 // quantised tokens per unit: 32, or 16 when 32 rows of K and V codes would not fit the 4 KB of a BF16 unit (every pair
 // with an 8-bit side), so that every pair keeps a 4224-byte slot and two CTAs per SM
@@ -47,6 +62,12 @@ __host__ __device__ constexpr int unit_tokens(int kb, int vb) { return 32 * 16 *
 constexpr int kUnitB = 8;                 // BF16 tokens per unit
 constexpr float kLazyRescale = 4.0f;      // rescale only if the max grows by > 2^4
 constexpr int kWsHeaderBytes = 256;       // [0] status word
+// Between the main loop and the final stores every 128-channel row (warp merge area, split-K partials in the workspace,
+// the last block's sums) is kept in POSITION order: channel 16 g + c sits at position 8 c + g.  The 8 lanes g of an MMA
+// row group then write 8 consecutive words (rows padded to 132 words keep the two head pairs of a warp apart), where
+// channel order put them 16 words apart, on two banks.  Channel order comes back at the stores that leave the kernel.
+constexpr int kMrgStride = 132;
+__host__ __device__ constexpr int chan_of_pos(int pos) { return 16 * (pos & 7) + (pos >> 3); }
 
 struct DecodeParams {
   const __nv_bfloat16* q; int64_t q_stride;
@@ -59,6 +80,8 @@ struct DecodeParams {
   int useg[4];                            // BF16 units per segment
   int units;                              // total units per head
   int nsplit;
+  int BH;                                 // heads of the call (grid = BH * nsplit blocks, split-major)
+  int last_share;                         // share of a head's last split in 1/256 of an even share
   int R;                                  // kv_repeat
   int out_dtype;
   float sml;                              // sm_scale * log2(e)
@@ -84,7 +107,36 @@ struct Fmt {
   static constexpr int kData = kQuant > 4096 ? kQuant : 4096;
   static constexpr int kVOff = kUnitQ * kRowK;
   static constexpr int kSlot = kData + 128;
-  static constexpr int kCtasPerSm = (kSlot <= 4224) ? 2 : 1;              // shared memory per CTA: 24 slots + 8.6 KB
+};
+
+// How the V codes of a (bit width) reach the P V product as fp16 subnormals, and which channel lands where.
+// This lane handles channels 16 g .. 16 g + 15 (g = lane / 4) of the tokens of its MMA k-slots.  Output tile mt
+// (0..7) has two rows per lane (MMA rows g and g + 8); tile mt, row r holds local channel chan(mt, r), every element
+// of the tile carries the factor 2^-exp2(mt) and the code offset kOff:
+//   8 bits: byte + 128 in bits 0-7            -> one factor; tile mt = channels 2 mt, 2 mt + 1
+//   4 bits: (nibble ^ 8) in bits 0-3 / 4-7    -> tile 2 p + b: nibble b and nibble b + 2 of 16-bit group p
+//   2 bits: (field ^ 2) in bits 2 f, 2 f + 1  -> tile 4 hl + f: field f of the low and of the high byte of group hl
+template <int VB> struct VFmt;
+template <> struct VFmt<8> {
+  static constexpr float kOff = 128.f;
+  static constexpr int kScales = 1;
+  __host__ __device__ static constexpr int exp2(int) { return 24; }
+  __host__ __device__ static constexpr int chan(int mt, int r) { return 2 * mt + r; }
+  __host__ __device__ static constexpr int scale_idx(int) { return 0; }
+};
+template <> struct VFmt<4> {
+  static constexpr float kOff = 8.f;
+  static constexpr int kScales = 2;
+  __host__ __device__ static constexpr int exp2(int mt) { return (mt & 1) ? 20 : 24; }
+  __host__ __device__ static constexpr int chan(int mt, int r) { return 4 * (mt >> 1) + 2 * r + (mt & 1); }
+  __host__ __device__ static constexpr int scale_idx(int mt) { return mt & 1; }
+};
+template <> struct VFmt<2> {
+  static constexpr float kOff = 2.f;
+  static constexpr int kScales = 4;
+  __host__ __device__ static constexpr int exp2(int mt) { return 24 - 2 * (mt & 3); }
+  __host__ __device__ static constexpr int chan(int mt, int r) { return 8 * (mt >> 2) + 4 * r + (mt & 3); }
+  __host__ __device__ static constexpr int scale_idx(int mt) { return mt & 3; }
 };
 
 struct Unit {
@@ -220,7 +272,7 @@ __device__ __forceinline__ float group_sum(float v) {
 // maximum of the new scores for this thread's two heads of tile nt.
 template <int NT>
 __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m_ref)[NT][2], float (&l_part)[NT][2],
-                                             float (&O)[NT][8][4]) {
+                                             float (&O)[NT][8][4], float (&Lt)[NT][4]) {
   bool need = false;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -235,6 +287,7 @@ __device__ __forceinline__ void lazy_rescale(const float (&mx)[NT][2], float (&m
         const float alpha = (nm == -INFINITY) ? 1.0f : ex2f(m_ref[nt][j] - nm);   // m_ref=-inf -> 0
         m_ref[nt][j] = nm;
         l_part[nt][j] *= alpha;
+        Lt[nt][j] *= alpha; Lt[nt][2 + j] *= alpha;
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) { O[nt][mt][j] *= alpha; O[nt][mt][2 + j] *= alpha; }
       }
@@ -256,7 +309,8 @@ __host__ __device__ constexpr int peer_scratch_floats(int world, int R) { return
 // Second pass for the R rows of kv-head `head`, by the whole CTA: (1) the peers' m and l words are polled by all threads
 // in parallel into shared memory, (2) one thread per row turns them into merge weights and the denominator, (3) every
 // thread keeps sixteen acc loads in flight over its (row, peer) pairs and accumulates into its own shared-memory
-// cells.  `local(hd, d, m, l, acc)` recomputes this rank's values of row hd, channel d.
+// cells.  `local(hd, d, m, l, acc)` recomputes this rank's values of row hd at POSITION d (channel chan_of_pos(d)): rows are
+// held in position order inside the kernel, the exchange buffers are in channel order.
 template <int kThreads, class LocalFn>
 __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* sm, int head, int tid, LocalFn local) {
   const PeerGroup& g = p.peer;
@@ -307,7 +361,7 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
       for (int u = 0; u < kFly; ++u) {
         const int it = it0 + u < n_items ? it0 + u : n_items - 1;
         const int k = it / np, jj = it - k * np, hd = g0 + k * G, j = jj < g.rank ? jj : jj + 1;
-        v[u] = ld_pair_sys(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + d);
+        v[u] = ld_pair_sys(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + chan_of_pos(d));
       }
 #pragma unroll
       for (int u = 0; u < kFly; ++u) {
@@ -315,7 +369,7 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
         if (it < n_items) {
           const int k = it / np, jj = it - k * np, hd = g0 + k * G, j = jj < g.rank ? jj : jj + 1;
           const float val = v[u].y == g.seq ? __uint_as_float(v[u].x)
-                                            : wait_pair(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + d, g.seq,
+                                            : wait_pair(recv + j * L.msg + 2 * (int64_t)g.rows + (row0 + hd) * 128 + chan_of_pos(d), g.seq,
                                                         g.timeout_ns, &expired);
           s_acc[hd * 128 + d] += s_w[jj * R + hd] * val;
         }
@@ -323,57 +377,40 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
     }
     for (int hd = g0; hd < R; hd += G) {
       const float den = s_den[hd];
-      store_out(p.out, (row0 + hd) * p.out_stride + d, den > 0.f ? s_acc[hd * 128 + d] / den : 0.f, p.out_dtype);
+      store_out(p.out, (row0 + hd) * p.out_stride + chan_of_pos(d), den > 0.f ? s_acc[hd * 128 + d] / den : 0.f, p.out_dtype);
     }
   }
   if (expired) atomicOr(reinterpret_cast<int*>(g.bufs[g.rank]), 2);
 }
 
-// Last block of a head, GQA ratios that do not divide the warp count: this warp's weighted sum of the partial rows
-// (split s0 + j * kWarps, head hd + hh), H heads x J splits fetched per step, into its slot of `red` [kWarps][R][128].
-template <int H, int J, int kWarps>
-__device__ __forceinline__ void merge_rows(const DecodeParams& p, int64_t base, const float* sm_w, float* red, int warp, int lane) {
-  for (int s0 = warp; s0 < p.nsplit; s0 += J * kWarps) {
-    for (int hd = 0; hd < p.R; hd += H) {
-      float4 v[H][J];
-#pragma unroll
-      for (int hh = 0; hh < H; ++hh)
-#pragma unroll
-        for (int j = 0; j < J; ++j) {
-          const int s2 = s0 + j * kWarps;
-          v[hh][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (s2 < p.nsplit && hd + hh < p.R)
-            v[hh][j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)s2 * p.R + hd + hh) * 128) + lane);
-        }
-#pragma unroll
-      for (int hh = 0; hh < H; ++hh) {
-        if (hd + hh < p.R) {
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int j = 0; j < J; ++j) {
-            const int s2 = s0 + j * kWarps;
-            const float wt = s2 < p.nsplit ? sm_w[s2 * p.R + hd + hh] : 0.f;
-            a.x += wt * v[hh][j].x; a.y += wt * v[hh][j].y; a.z += wt * v[hh][j].z; a.w += wt * v[hh][j].w;
-          }
-          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd + hh) * 128) + lane;
-          if (s0 >= J * kWarps) { const float4 o = *dst; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
-          *dst = a;
-        }
-      }
-    }
-  }
-}
-
 // ---- the kernel -------------------------------------------------------------
 
+// The four 16-bit-lane fields of a word as fp16 subnormals, offset binary: result k = ((nibble k) ^ 8) * 2^-24 for k = 0, 2
+// (bits 0-3) and * 2^-20 for k = 1, 3 (bits 4-7).
+__device__ __forceinline__ void cvt_nibbles_subnormal(uint32_t w, uint32_t (&h)[4]) {
+  const uint32_t w8 = w >> 8;
+  h[0] = lop3_and_xor(w, 0x000F000Fu, 0x00080008u);
+  h[1] = lop3_and_xor(w, 0x00F000F0u, 0x00800080u);
+  h[2] = lop3_and_xor(w8, 0x000F000Fu, 0x00080008u);
+  h[3] = lop3_and_xor(w8, 0x00F000F0u, 0x00800080u);
+}
+// 2-bit fields f = 0..3 of the low byte of each 16-bit lane: result f = ((field f) ^ 2) * 2^(2 f - 24)
+__device__ __forceinline__ void cvt_crumbs_subnormal(uint32_t w, uint32_t (&h)[4]) {
+  h[0] = lop3_and_xor(w, 0x00030003u, 0x00020002u);
+  h[1] = lop3_and_xor(w, 0x000C000Cu, 0x00080008u);
+  h[2] = lop3_and_xor(w, 0x00300030u, 0x00200020u);
+  h[3] = lop3_and_xor(w, 0x00C000C0u, 0x00800080u);
+}
+
 template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
-__global__ void __launch_bounds__(warps_of(NT, Fmt<KB, VB>::kCtasPerSm) * 32, Fmt<KB, VB>::kCtasPerSm)
+__global__ void __launch_bounds__(warps_of(NT) * 32, 1)
 decode_splitk_kernel(const DecodeParams p) {
   using F = Fmt<KB, VB>;
-  constexpr int kWarps = warps_of(NT, F::kCtasPerSm), kThreads = kWarps * 32;
+  using VF = VFmt<VB>;
+  constexpr int kWarps = warps_of(NT), kThreads = kWarps * 32;
+  constexpr int kSlotBytes = F::kSlot, kUnitQ = F::kUnitQ, kChunks = F::kChunks;
   constexpr int kQItems = NT * 8;                                   // (tile, head) pairs whose query row is loaded
   constexpr int kQIter = (kQItems + kWarps - 1) / kWarps;           // per warp: items warp, warp + kWarps, ...
-  constexpr int kSlotBytes = F::kSlot, kUnitQ = F::kUnitQ, kChunks = F::kChunks;
   extern __shared__ __align__(128) uint8_t smem[];
   // layout: ring [kWarps][kSlots][kSlotBytes] | fragH [NT][8][2][32] u32 | fragB same |
   //         headC [NT*8] f32 | mbarriers [kWarps][kSlots]
@@ -386,11 +423,19 @@ decode_splitk_kernel(const DecodeParams p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int head = blockIdx.x / p.nsplit;
-  const int split = blockIdx.x - head * p.nsplit;
-  const int u_begin = (int)(((int64_t)split * p.units) / p.nsplit);
-  const int u_end = (int)(((int64_t)(split + 1) * p.units) / p.nsplit);
-  const int n_my = (u_end - u_begin - warp + kWarps - 1) / kWarps;   // units u_begin + warp + 8 i
+  // Blocks are numbered split-major, so that the blocks the hardware starts last are the LAST split of every head, and
+  // that split may be a small one (p.last_share / 256 of an even share, the other splits the rest): when the heads
+  // do not fill the SMs evenly (128 heads on 148 SMs), the SMs left over work through the small splits while the others
+  // each do one large one.
+  const int split = blockIdx.x / p.BH;
+  const int head = blockIdx.x - split * p.BH;
+  int u_begin, u_end;
+  {
+    const int64_t parts = (int64_t)(p.nsplit - 1) * 256 + p.last_share;          // in 1/256 of an even share
+    u_begin = (int)(((int64_t)split * 256 * p.units) / parts);
+    u_end = split + 1 == p.nsplit ? p.units : (int)(((int64_t)(split + 1) * 256 * p.units) / parts);
+  }
+  const int n_my = (u_end - u_begin - warp + kWarps - 1) / kWarps;   // units u_begin + warp + kWarps i
   uint8_t* my_ring = ring + warp * (kSlots * kSlotBytes);
   uint64_t* my_bar = bars + warp * kSlots;
 
@@ -402,9 +447,37 @@ decode_splitk_kernel(const DecodeParams p) {
   }
   __syncwarp();
 
+  // Requested by lane 0 of the warp that consumes it.  (One producer warp serving every ring, a lane per ring, was
+  // measured slower: the bulk-copy instructions of one warp issue one after the other and cannot keep 15 rings fed.)
+  // The lane's instructions are a serial chain that holds up its warp, so the common case - a full quantised unit -
+  // is kept to one multiply-add per address on bases computed once.
+  const uint8_t* const kq_base = p.k_packed + head * p.kp_stride_bh;
+  const uint8_t* const vq_base = p.v_packed + head * p.vp_stride_bh;
+  const __half* const ks_base = p.k_scale + head * p.ks_stride_bh;
+  const __half* const vs_base = p.v_scale + head * p.vs_stride_bh;
+  const uint32_t ring_u32 = smem_u32(my_ring), bar_u32 = smem_u32(my_bar);
+  const int uq_full = p.n_quant / kUnitQ;            // quantised units with all their tokens
+  auto bulk_raw = [](uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar) : "memory");
+  };
   auto issue = [&](int i) {   // lane 0 only
-    const Unit un = unit_of<KB, VB>(p, head, u_begin + warp + kWarps * i);
+    const int u = u_begin + warp + kWarps * i;
     const int slot = i % kSlots;
+    if (u < uq_full) {
+      const uint32_t dst = ring_u32 + slot * kSlotBytes, bar = bar_u32 + slot * 8;
+      const int64_t tok0 = (int64_t)u * kUnitQ;
+      constexpr uint32_t kb = kUnitQ * F::kRowK, vb = kUnitQ * F::kRowV, sb = kUnitQ * 2;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kScaleTma ? kb + vb + 2 * sb : kb + vb) : "memory");
+      if (kScaleTma) {
+        bulk_raw(dst + F::kData, ks_base + tok0, sb, bar);
+        bulk_raw(dst + F::kData + 64, vs_base + tok0, sb, bar);
+      }
+      bulk_raw(dst, kq_base + tok0 * F::kRowK, kb, bar);
+      bulk_raw(dst + F::kVOff, vq_base + tok0 * F::kRowV, vb, bar);
+      return;
+    }
+    const Unit un = unit_of<KB, VB>(p, head, u);
     uint8_t* dst = my_ring + slot * kSlotBytes;
     if (un.kind == 0) {
       const uint32_t kbytes = (uint32_t)un.ntok * F::kRowK, vbytes = (uint32_t)un.ntok * F::kRowV;
@@ -535,10 +608,13 @@ decode_splitk_kernel(const DecodeParams p) {
 
   float O[NT][8][4];
   float m_ref[NT][2], l_part[NT][2];
+  float Lt[NT][4];          // sum of the fp16 P~ values the quantised V tiles were multiplied with ([0], [1]: heads 2t, 2t+1)
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) { m_ref[nt][j] = -INFINITY; l_part[nt][j] = 0.f; }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) Lt[nt][x] = 0.f;
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
@@ -602,6 +678,15 @@ decode_splitk_kernel(const DecodeParams p) {
           kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
           kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
         }
+#ifdef HQ_DEC_SPLITCHAIN
+        float s2[kChunks][NT][4];        // second accumulator chain: halves the depth of dependent MMAs
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) s2[ch][nt][x] = 0.f;
+#endif
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
 #pragma unroll
@@ -613,11 +698,24 @@ decode_splitk_kernel(const DecodeParams p) {
             cvt_nibbles_biased(wb, hb);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
+#ifdef HQ_DEC_SPLITCHAIN
+              mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
+              mma_f16_16816(s2[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
+#else
               mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
               mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
+#endif
             }
           }
         }
+#ifdef HQ_DEC_SPLITCHAIN
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) s[ch][nt][x] += s2[ch][nt][x];
+#endif
       } else if constexpr (KB == 8) {
         // a 128-byte row: 16 bytes at 64 h + 16 t; word w of it holds channels 64 h + 16 t + 4 w + (0..3)
 #pragma unroll
@@ -698,7 +796,7 @@ decode_splitk_kernel(const DecodeParams p) {
           if constexpr (kChunks == 2) v = fmaxf(v, fmaxf(s[kChunks - 1][nt][j], s[kChunks - 1][nt][2 + j]));
           mx[nt][j] = group_max(v);
         }
-      lazy_rescale<NT>(mx, m_ref, l_part, O);
+      lazy_rescale<NT>(mx, m_ref, l_part, O, Lt);
 
 #pragma unroll
       for (int ch = 0; ch < kChunks; ++ch) {
@@ -717,9 +815,11 @@ decode_splitk_kernel(const DecodeParams p) {
           const uint32_t pq = pack_f16x2(pr[2] * vsc[ch][1], pr[3] * vsc[ch][1]);   // token g + 8
           pb[nt][0] = movmatrix_trans(pa);    // (tokens 2t, 2t+1 ; head g)
           pb[nt][1] = movmatrix_trans(pq);    // (tokens 2t+8, 2t+9 ; head g)
+          // sum over the chunk's tokens of the P~ values as the tensor core sees them, for the offset of the V codes
+          mma_f16_16816(Lt[nt], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, pb[nt][0], pb[nt][1]);
         }
-        // V: this lane converts channels 16 g .. 16 g + 15 of tokens 2t, 2t+1, 2t+8, 2t+9 of the chunk; output tile
-        // mt holds channel 16 g + 2 mt in row g and 16 g + 2 mt + 1 in row g + 8, whatever the bit width.
+        // V: this lane takes channels 16 g .. 16 g + 15 of tokens 2t, 2t+1, 2t+8, 2t+9 of the chunk; which of them
+        // land in which output tile is VFmt<VB>::chan.  The codes are used where they lie, as fp16 subnormals.
         const uint8_t* vrow = Vs + (16 * ch + 2 * t) * F::kRowV + 2 * VB * g;
         if constexpr (VB == 4) {
           const uint2 vA = *reinterpret_cast<const uint2*>(vrow);
@@ -733,13 +833,13 @@ decode_splitk_kernel(const DecodeParams p) {
             for (int hl = 0; hl < 2; ++hl) {
               const uint32_t sel = hl ? 0x7632u : 0x5410u;
               uint32_t hab[4], hcd[4];
-              cvt_nibbles_f16(prmt(wA[w], wB[w], sel), hab);
-              cvt_nibbles_f16(prmt(wC[w], wD[w], sel), hcd);
-              const int pidx = 2 * w + hl;
+              cvt_nibbles_subnormal(prmt(wA[w], wB[w], sel), hab);
+              cvt_nibbles_subnormal(prmt(wC[w], wD[w], sel), hcd);
+              const int pidx = 2 * w + hl;      // 16-bit group: channels 16 g + 4 pidx + (0..3) = nibbles 0..3
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
-                mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
-                mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+                mma_f16_16816(O[nt][2 * pidx], hab[0], hab[2], hcd[0], hcd[2], pb[nt][0], pb[nt][1]);       // nibbles 0, 2
+                mma_f16_16816(O[nt][2 * pidx + 1], hab[1], hab[3], hcd[1], hcd[3], pb[nt][0], pb[nt][1]);   // nibbles 1, 3
               }
             }
         } else if constexpr (VB == 8) {
@@ -750,14 +850,17 @@ decode_splitk_kernel(const DecodeParams p) {
           const uint32_t wA[4] = {vA.x, vA.y, vA.z, vA.w}, wB[4] = {vB.x, vB.y, vB.z, vB.w};
           const uint32_t wC[4] = {vC.x, vC.y, vC.z, vC.w}, wD[4] = {vD.x, vD.y, vD.z, vD.w};
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {      // word w: channels 16 g + 4 w + (0..3)
-            uint32_t hab[4], hcd[4];
-            cvt_byte_pairs_f16(wA[w], wB[w], hab);
-            cvt_byte_pairs_f16(wC[w], wD[w], hcd);
+          for (int w = 0; w < 4; ++w) {      // word w: channels 16 g + 4 w + (0..3), one byte each
+            const uint32_t ab01 = prmt(wA[w], wB[w], 0x5140u) ^ 0x80808080u;    // a0 b0 a1 b1, each + 128
+            const uint32_t ab23 = prmt(wA[w], wB[w], 0x7362u) ^ 0x80808080u;    // a2 b2 a3 b3
+            const uint32_t cd01 = prmt(wC[w], wD[w], 0x5140u) ^ 0x80808080u;
+            const uint32_t cd23 = prmt(wC[w], wD[w], 0x7362u) ^ 0x80808080u;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              mma_f16_16816(O[nt][2 * w], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
-              mma_f16_16816(O[nt][2 * w + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
+              mma_f16_16816(O[nt][2 * w], prmt(ab01, 0u, 0x4140u), prmt(ab01, 0u, 0x4342u), prmt(cd01, 0u, 0x4140u),
+                            prmt(cd01, 0u, 0x4342u), pb[nt][0], pb[nt][1]);
+              mma_f16_16816(O[nt][2 * w + 1], prmt(ab23, 0u, 0x4140u), prmt(ab23, 0u, 0x4342u), prmt(cd23, 0u, 0x4140u),
+                            prmt(cd23, 0u, 0x4342u), pb[nt][0], pb[nt][1]);
             }
           }
         } else {
@@ -769,18 +872,16 @@ decode_splitk_kernel(const DecodeParams p) {
           for (int hl = 0; hl < 2; ++hl) {   // codes 8 hl .. 8 hl + 7 of the two tokens, one token per 16-bit half
             const uint32_t sel = hl ? 0x7632u : 0x5410u;
             const uint32_t mab = prmt(wA, wB, sel), mcd = prmt(wC, wD, sel);
+            uint32_t ab0[4], ab1[4], cd0[4], cd1[4];       // low byte (codes 8 hl + 0..3) and high byte (8 hl + 4..7)
+            cvt_crumbs_subnormal(mab, ab0);
+            cvt_crumbs_subnormal(mab >> 8, ab1);
+            cvt_crumbs_subnormal(mcd, cd0);
+            cvt_crumbs_subnormal(mcd >> 8, cd1);
 #pragma unroll
-            for (int sh = 0; sh < 2; ++sh) {
-              uint32_t hab[4], hcd[4];
-              cvt_crumbs_f16(sh ? mab >> 8 : mab, hab);
-              cvt_crumbs_f16(sh ? mcd >> 8 : mcd, hcd);
-              const int pidx = 2 * hl + sh;      // channels 16 g + 8 hl + 4 sh + (0..3)
+            for (int f = 0; f < 4; ++f)
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                mma_f16_16816(O[nt][2 * pidx], hab[0], hab[1], hcd[0], hcd[1], pb[nt][0], pb[nt][1]);
-                mma_f16_16816(O[nt][2 * pidx + 1], hab[2], hab[3], hcd[2], hcd[3], pb[nt][0], pb[nt][1]);
-              }
-            }
+              for (int nt = 0; nt < NT; ++nt)
+                mma_f16_16816(O[nt][4 * hl + f], ab0[f], ab1[f], cd0[f], cd1[f], pb[nt][0], pb[nt][1]);
           }
         }
       }
@@ -838,8 +939,9 @@ decode_splitk_kernel(const DecodeParams p) {
           s[nt][j] = ok ? s[nt][j] * p.sml : -INFINITY;
           mx[nt][j] = group_max(s[nt][j]);
         }
-      lazy_rescale<NT>(mx, m_ref, l_part, O);
-      uint32_t pb[NT];
+      lazy_rescale<NT>(mx, m_ref, l_part, O, Lt);
+      // P^T operand once per factor the quantised tiles carry (the accumulators are shared with them)
+      uint32_t pb[NT][VF::kScales];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const float m0 = m_ref[nt][0] == -INFINITY ? 0.f : m_ref[nt][0];
@@ -847,21 +949,29 @@ decode_splitk_kernel(const DecodeParams p) {
         const float p0 = ex2f(s[nt][0] - m0), p1 = ex2f(s[nt][1] - m1);
         l_part[nt][0] += p0;
         l_part[nt][1] += p1;
-        pb[nt] = movmatrix_trans(pack_bf16x2(p0, p1));     // (tokens 2t, 2t+1 ; head g)
+#pragma unroll
+        for (int sc = 0; sc < VF::kScales; ++sc) {
+          const float f = VB == 8 ? 5.9604644775390625e-08f               // 2^-24
+                                  : VB == 4 ? (sc ? 9.5367431640625e-07f : 5.9604644775390625e-08f)      // 2^-20, 2^-24
+                                            : (sc == 0 ? 5.9604644775390625e-08f : sc == 1 ? 2.384185791015625e-07f
+                                               : sc == 2 ? 9.5367431640625e-07f : 3.814697265625e-06f);   // 2^(2 sc - 24)
+          pb[nt][sc] = movmatrix_trans(pack_bf16x2(p0 * f, p1 * f));     // (tokens 2t, 2t+1 ; head g)
+        }
       }
       const uint8_t* va = Vs + (2 * t) * 256 + 32 * g;
       const uint4 a0 = *reinterpret_cast<const uint4*>(va);
       const uint4 a1 = *reinterpret_cast<const uint4*>(va + 16);
       const uint4 b0 = *reinterpret_cast<const uint4*>(va + 256);
       const uint4 b1 = *reinterpret_cast<const uint4*>(va + 256 + 16);
-      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};     // word m: channels 16 g + 2 m, + 1
       const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) {
-        const uint32_t r0 = prmt(wa[mt], wb[mt], 0x5410u);   // channel 16g+2mt   of tokens (2t, 2t+1)
-        const uint32_t r1 = prmt(wa[mt], wb[mt], 0x7632u);   // channel 16g+2mt+1
+        const int c0 = VF::chan(mt, 0), c1 = VF::chan(mt, 1);          // local channels of the tile's two rows
+        const uint32_t r0 = prmt(wa[c0 >> 1], wb[c0 >> 1], (c0 & 1) ? 0x7632u : 0x5410u);   // channel c0 of tokens (2t, 2t+1)
+        const uint32_t r1 = prmt(wa[c1 >> 1], wb[c1 >> 1], (c1 & 1) ? 0x7632u : 0x5410u);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma_bf16_1688(O[nt][mt], r0, r1, pb[nt]);
+        for (int nt = 0; nt < NT; ++nt) mma_bf16_1688(O[nt][mt], r0, r1, pb[nt][VF::scale_idx(mt)]);
       }
       __syncwarp();
       if (lane == 0 && i + kSlots < n_my) {
@@ -873,22 +983,41 @@ decode_splitk_kernel(const DecodeParams p) {
   if (failed && lane == 0) atomicOr(p.status, 1);
 
   // ======================= merge the warps ===================================
+  // Two barriers: the warps' maxima first, then every warp writes its sums already weighted by 2^(m_warp - m_block), so
+  // that a row of the block is a plain sum over the warps (one exponential per thread and head instead of one per
+  // thread, head and warp).
   __syncthreads();   // every ring slot is drained (each issued unit was waited for) unless `failed`
   float* mrg_m = reinterpret_cast<float*>(smem);                 // [kWarps][NT*8]
   float* mrg_l = mrg_m + kWarps * NT * 8;                        // [kWarps][NT*8]
-  float* mrg_o = mrg_l + kWarps * NT * 8;                        // [kWarps][NT*8][128]
+  float* mrg_o = mrg_l + kWarps * NT * 8;                        // [kWarps][NT*8][kMrgStride], position order
+  if (g == 0) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) mrg_m[warp * NT * 8 + nt * 8 + 2 * t + j] = m_ref[nt][j];
+  }
+  __syncthreads();
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int hd = nt * 8 + 2 * t + j;
-      const float lsum = group_sum(l_part[nt][j]);
-      if (g == 0) { mrg_m[warp * NT * 8 + hd] = m_ref[nt][j]; mrg_l[warp * NT * 8 + hd] = lsum; }
-      if (hd < p.R) {
-        float* orow = mrg_o + ((size_t)(warp * NT * 8 + hd)) * 128 + 16 * g;
+      float M = -INFINITY;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt)
-          *reinterpret_cast<float2*>(orow + 2 * mt) = make_float2(O[nt][mt][j], O[nt][mt][2 + j]);
+      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
+      const float wt = (m_ref[nt][j] == -INFINITY) ? 0.f : ex2f(m_ref[nt][j] - M);
+      const float lsum = group_sum(l_part[nt][j]);
+      if (g == 0) mrg_l[warp * NT * 8 + hd] = lsum * wt;
+      if (hd < p.R) {
+        // true values: the tile's power of two back, the code offset times the sum of the quantised tokens' P~ off
+        float* orow = mrg_o + ((size_t)(warp * NT * 8 + hd)) * kMrgStride + g;
+        const float corr = VF::kOff * Lt[nt][j] * wt;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          const float up = (VF::exp2(mt) == 24 ? 16777216.f : VF::exp2(mt) == 22 ? 4194304.f : VF::exp2(mt) == 20 ? 1048576.f : 262144.f) * wt;
+          orow[8 * VF::chan(mt, 0)] = fmaf(O[nt][mt][j], up, -corr);
+          orow[8 * VF::chan(mt, 1)] = fmaf(O[nt][mt][2 + j], up, -corr);
+        }
       }
     }
   __syncthreads();
@@ -897,18 +1026,15 @@ decode_splitk_kernel(const DecodeParams p) {
   const int d = tid & 127;
   const bool single = (p.nsplit == 1);
   constexpr bool peers = kPeer;       // instantiated apart, so that the exchange code costs the plain kernel no registers
-  // this CTA's merge of its warps for head hd, channel dd
+  // this CTA's state for head hd at position dd
   auto cta_row = [&](int hd, int dd, float& M, float& l, float& acc) {
     M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
     acc = 0.f; l = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
-      const float mw = mrg_m[w * NT * 8 + hd];
-      const float wt = (mw == -INFINITY) ? 0.f : ex2f(mw - M);
-      acc += wt * mrg_o[((size_t)(w * NT * 8 + hd)) * 128 + dd];
-      l += wt * mrg_l[w * NT * 8 + hd];
+      M = fmaxf(M, mrg_m[w * NT * 8 + hd]);
+      acc += mrg_o[((size_t)(w * NT * 8 + hd)) * kMrgStride + dd];
+      l += mrg_l[w * NT * 8 + hd];
     }
   };
   for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
@@ -917,12 +1043,12 @@ decode_splitk_kernel(const DecodeParams p) {
     const int64_t qrow = (int64_t)head * p.R + hd;
     if (single) {
       if constexpr (peers) {
-        peer_send(p, (int)qrow, d, M, l, acc);       // every row is sent before any is awaited
+        peer_send(p, (int)qrow, chan_of_pos(d), M, l, acc);       // every row is sent before any is awaited
       } else if (p.pacc) {
-        p.pacc[qrow * 128 + d] = acc;
+        p.pacc[qrow * 128 + chan_of_pos(d)] = acc;
         if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
       } else {
-        store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
+        store_out(p.out, qrow * p.out_stride + chan_of_pos(d), l > 0.f ? acc / l : 0.f, p.out_dtype);
       }
     } else {
       const int64_t prow = ((int64_t)head * p.nsplit + split) * p.R + hd;
@@ -931,7 +1057,7 @@ decode_splitk_kernel(const DecodeParams p) {
     }
   }
   if (single) {
-    if constexpr (peers) peer_receive_all<kThreads>(p, mrg_o + (size_t)kWarps * NT * 8 * 128, head, tid, cta_row);
+    if constexpr (peers) peer_receive_all<kThreads>(p, mrg_o + (size_t)kWarps * NT * 8 * kMrgStride, head, tid, cta_row);
     return;
   }
 
@@ -946,104 +1072,74 @@ decode_splitk_kernel(const DecodeParams p) {
   }
   __syncthreads();
   if (!s_last) return;
-  float* sm_w = reinterpret_cast<float*>(smem);             // [nsplit * R]  m, then weights 2^(m - M)
-  float* sm_l = sm_w + p.nsplit * p.R;                      // [nsplit * R]
-  float* sm_M = sm_l + p.nsplit * p.R;                      // [16]
-  float* sm_L = sm_M + 16;                                  // [16]
-  float* red = sm_w + ((2 * p.nsplit * p.R + 32 + 3) & ~3); // [kWarps][R][128], 16-byte aligned
+  // One warp per query head, no shared memory and no block barrier: lane s fetches (m, l) of split s, every lane the
+  // four positions 4 lane .. 4 lane + 3 of every split's row - all requested before any is used, so the merge costs one
+  // round trip to L2 - the weights 2^(m_s - M) are formed once per split and handed round by shuffles.  More splits
+  // than a round holds go in several rounds with the usual running rescale.
+  float* res = reinterpret_cast<float*>(smem);              // [R][kMrgStride] merged rows, for the exchange below only
+  float* res_ml = res + (size_t)p.R * kMrgStride;            // [R][2]
   const int64_t base = (int64_t)head * p.nsplit * p.R;
-  const int nitems = p.nsplit * p.R;            // partial rows of this head: row k = split * R + head
-  // When R divides the warp count, warp w only ever meets head w % R (rows w, w+8, ...), so one
-  // accumulator per warp suffices and every partial row can be requested up front, in the same
-  // round trip to L2 as the maxima and sums.
-  const bool fast = (kWarps % p.R) == 0;
-  constexpr int kPre = 20;
-  float4 pre[kPre];
-  if (fast) {
-#pragma unroll
-    for (int j = 0; j < kPre; ++j) {
-      const int k = warp + j * kWarps;
-      pre[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (k < nitems) pre[j] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + k) * 128) + lane);
-    }
-  }
-  for (int x = tid; x < nitems; x += kThreads) {
-    sm_w[x] = __ldcg(p.ws_m + base + x);
-    sm_l[x] = __ldcg(p.ws_l + base + x);
-  }
-  __syncthreads();
-  // weights: warp `hd` (mod 8) reduces over the splits of head hd
+  constexpr int kRound = 20;          // splits per round: their rows are all in flight at once (80 registers)
   for (int hd = warp; hd < p.R; hd += kWarps) {
-    float M = -INFINITY;
-    for (int s2 = lane; s2 < p.nsplit; s2 += 32) M = fmaxf(M, sm_w[s2 * p.R + hd]);
+    float M = -INFINITY, den = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < p.nsplit; s0 += kRound) {
+      const int ns = min(kRound, p.nsplit - s0);
+      float ms = -INFINITY, ls = 0.f;
+      if (lane < ns) {
+        ms = __ldcg(p.ws_m + base + (int64_t)(s0 + lane) * p.R + hd);
+        ls = __ldcg(p.ws_l + base + (int64_t)(s0 + lane) * p.R + hd);
+      }
+      float4 v[kRound];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float L = 0.f;
-    for (int s2 = lane; s2 < p.nsplit; s2 += 32) {
-      const float ms = sm_w[s2 * p.R + hd];
-      const float wt = (ms == -INFINITY) ? 0.f : ex2f(ms - M);
-      sm_w[s2 * p.R + hd] = wt;
-      L += wt * sm_l[s2 * p.R + hd];
-    }
+      for (int x = 0; x < kRound; ++x) {
+        v[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (x < ns) v[x] = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + (int64_t)(s0 + x) * p.R + hd) * 128) + lane);
+      }
+      float Mc = ms;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    if (lane == 0) { sm_M[hd] = M; sm_L[hd] = L; }
-  }
-  __syncthreads();
-  if (fast) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int o = 16; o > 0; o >>= 1) Mc = fmaxf(Mc, __shfl_xor_sync(0xffffffffu, Mc, o));
+      const float Mn = fmaxf(M, Mc);
+      const float keep = (M == -INFINITY) ? 0.f : ex2f(M - Mn);
+      const float wt = (ms == -INFINITY) ? 0.f : ex2f(ms - Mn);
+      float dl = wt * ls;
 #pragma unroll
-    for (int j = 0; j < kPre; ++j) {
-      const int k = warp + j * kWarps;
-      const float wt = k < nitems ? sm_w[k] : 0.f;
-      a.x += wt * pre[j].x; a.y += wt * pre[j].y; a.z += wt * pre[j].z; a.w += wt * pre[j].w;
-    }
-    for (int k = warp + kPre * kWarps; k < nitems; k += kWarps) {
-      const float wt = sm_w[k];
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (base + k) * 128) + lane);
-      a.x += wt * v.x; a.y += wt * v.y; a.z += wt * v.z; a.w += wt * v.w;
-    }
-    reinterpret_cast<float4*>(red + (size_t)warp * 128)[lane] = a;     // partial of head warp % R
-  } else {
-    // generic GQA ratio: warp w sums splits w, w + kWarps, ... of every head.  Every step is one round trip to L2, so
-    // the (heads, splits) block fetched per step is as large as the registers allow (32 rows with two head tiles, 16
-    // with one) and shaped by how many splits a warp has: few splits -> many heads at once.
-    const int jneed = (p.nsplit + kWarps - 1) / kWarps;
-    constexpr int kRowsInFlight = NT == 2 ? 32 : 16;
-    if (jneed <= 2) merge_rows<kRowsInFlight / 2, 2, kWarps>(p, base, sm_w, red, warp, lane);
-    else if (jneed <= 4) merge_rows<kRowsInFlight / 4, 4, kWarps>(p, base, sm_w, red, warp, lane);
-    else merge_rows<kRowsInFlight / 8, 8, kWarps>(p, base, sm_w, red, warp, lane);
-    if (warp >= p.nsplit) {   // a warp without splits still owns a slot of `red`
-      for (int hd = 0; hd < p.R; ++hd)
-        reinterpret_cast<float4*>(red + ((size_t)warp * p.R + hd) * 128)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-  }
-  __syncthreads();
-  // the head's merge of all splits for head hd, channel dd
-  auto head_row = [&](int hd, int dd, float& M, float& l, float& acc) {
-    acc = 0.f;
-    if (fast) {
-      for (int w = hd; w < kWarps; w += p.R) acc += red[(size_t)w * 128 + dd];
-    } else {
+      for (int o = 16; o > 0; o >>= 1) dl += __shfl_xor_sync(0xffffffffu, dl, o);
+      den = den * keep + dl;
+      acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) acc += red[((size_t)w * p.R + hd) * 128 + dd];
+      for (int x = 0; x < kRound; ++x) {
+        const float wx = __shfl_sync(0xffffffffu, wt, x);       // 0 for x >= ns
+        acc.x += wx * v[x].x; acc.y += wx * v[x].y; acc.z += wx * v[x].z; acc.w += wx * v[x].w;
+      }
+      M = Mn;
     }
-    M = sm_M[hd]; l = sm_L[hd];
-  };
-  for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
-    float M, l, acc;
-    head_row(hd, d, M, l, acc);
     const int64_t qrow = (int64_t)head * p.R + hd;
+    const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
     if constexpr (peers) {
-      peer_send(p, (int)qrow, d, M, l, acc);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        res[(size_t)hd * kMrgStride + 4 * lane + x] = a4[x];
+        peer_send(p, (int)qrow, chan_of_pos(4 * lane + x), M, den, a4[x]);
+      }
+      if (lane == 0) { res_ml[2 * hd] = M; res_ml[2 * hd + 1] = den; }
     } else if (p.pacc) {
-      p.pacc[qrow * 128 + d] = acc;
-      if (d == 0) { p.pm[qrow] = M; p.pl[qrow] = l; }
+#pragma unroll
+      for (int x = 0; x < 4; ++x) p.pacc[qrow * 128 + chan_of_pos(4 * lane + x)] = a4[x];
+      if (lane == 0) { p.pm[qrow] = M; p.pl[qrow] = den; }
     } else {
-      store_out(p.out, qrow * p.out_stride + d, l > 0.f ? acc / l : 0.f, p.out_dtype);
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) store_out(p.out, qrow * p.out_stride + chan_of_pos(4 * lane + x), a4[x] * inv, p.out_dtype);
     }
   }
-  if constexpr (peers) peer_receive_all<kThreads>(p, red + (size_t)kWarps * p.R * 128, head, tid, head_row);
+  if constexpr (peers) {
+    __syncthreads();
+    auto head_row = [&](int hd, int dd, float& M, float& l, float& acc) {
+      M = res_ml[2 * hd]; l = res_ml[2 * hd + 1]; acc = res[(size_t)hd * kMrgStride + dd];
+    };
+    peer_receive_all<kThreads>(p, res_ml + 2 * p.R, head, tid, head_row);
+  }
   if (tid == 0) p.counters[head] = 0;   // ready for the next launch on this workspace
 }
 
@@ -1051,7 +1147,7 @@ decode_splitk_kernel(const DecodeParams p) {
 // ---- host side ---------------------------------------------------------------
 
 static size_t decode_smem_bytes(int NT, int slot_bytes) {
-  const int w = warps_of(NT, slot_bytes <= 4224 ? 2 : 1);
+  const int w = warps_of(NT);
   return (size_t)w * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 + (size_t)w * kSlots * 8;
 }
 
@@ -1068,7 +1164,7 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(warps_of(NT, Fmt<KB, VB>::kCtasPerSm) * 32);
+  cfg.blockDim = dim3(warps_of(NT) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -1080,6 +1176,7 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   return HQ_OK;
 }
 
+#ifndef HQ_DEC_FAST_BUILD
 template <int KB, int VB>
 static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st) {
   if (p.peer.world > 1) {   // the exchanging instantiations exist with directly loaded scales only (any alignment)
@@ -1088,6 +1185,7 @@ static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStre
   if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, false>(p, grid, st) : launch_decode<1, false, KB, VB, false>(p, grid, st);
   return p.scale_tma ? launch_decode<2, true, KB, VB, false>(p, grid, st) : launch_decode<2, false, KB, VB, false>(p, grid, st);
 }
+#endif
 
 static int slot_bytes_of(int kb, int vb) {
   const int q = unit_tokens(kb, vb) * 16 * (kb + vb);
@@ -1196,24 +1294,45 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
     p.peer.timeout_ns = a->peer_timeout_ns > 0 ? a->peer_timeout_ns : 2000000000ll;
   }
 
-  // splits: one wave of CTAs (as many per SM as the slot size of this bit-width pair lets reside), at least ~2 units per warp
+  // splits: one wave of blocks, one per SM, about one unit per warp at least; the blocks' partials live in the
+  // workspace (sized for BH + 4 x SMs blocks), the merge of a head's splits needs no staging memory
   const int sms = sm_count();
-  const int slot_bytes = slot_bytes_of(k_bits, v_bits);
   const int NT = a->kv_repeat <= 8 ? 1 : 2;
-  const int ctas_per_sm = slot_bytes <= 4224 ? 2 : 1;
-  const int kWarps = warps_of(NT, ctas_per_sm);
+  const int kWarps = warps_of(NT);
+  const int split_cap = (int)(((int64_t)a->BH_KV + max_ctas()) / a->BH_KV);
+  bool force_direct_scales = false;
   int nsplit = a->num_splits;
+  int last_share = 256;
   if (nsplit <= 0) {
-    const int by_grid = (ctas_per_sm * sms) / a->BH_KV;
+    const int by_grid = sms / a->BH_KV;
     const int by_work = (p.units + kWarps - 1) / kWarps;
     nsplit = by_grid < by_work ? by_grid : by_work;
+    if (nsplit > split_cap) nsplit = split_cap;
+    // SMs left over by an even split (sms - BH * nsplit) take one more, small split of every head: a fraction
+    // 0.8 * spare / sms of the head (the 0.8 pays for the fixed cost of the extra blocks), if that is worth a block
+    const int spare = sms - a->BH_KV * nsplit;
+    if (nsplit >= 1 && nsplit == by_grid && nsplit + 1 <= split_cap && spare * 16 >= sms) {
+      const double f = 0.8 * spare / sms;
+      if (f * p.units >= 4.0 * kWarps) {
+        last_share = (int)(f * nsplit * 256.0 / (1.0 - f) + 0.5);
+        nsplit += 1;
+      }
+    }
   }
+#ifdef HQ_DEC_FAST_BUILD
+  if (const char* e = getenv("HQ_DEC_NSPLIT")) nsplit = atoi(e);
+  if (getenv("HQ_DEC_NOSCALETMA")) force_direct_scales = true;
+#endif
   if (nsplit < 1) nsplit = 1;
   if (nsplit > p.units && p.units > 0) nsplit = p.units;
-  if ((int64_t)nsplit * a->BH_KV > (int64_t)a->BH_KV + max_ctas()) nsplit = (int)(((int64_t)a->BH_KV + max_ctas()) / a->BH_KV);
+  if (nsplit > split_cap) nsplit = split_cap;
   if (nsplit < 1) nsplit = 1;
   p.nsplit = nsplit;
-
+  p.BH = a->BH_KV;
+  p.last_share = last_share;
+#ifdef HQ_DEC_FAST_BUILD
+  if (const char* e = getenv("HQ_DEC_LAST")) p.last_share = atoi(e);
+#endif
   int64_t need = 0;
   hq_decode_workspace_bytes(a->BH_KV, a->kv_repeat, &need);
   HQ_REQUIRE(a->workspace && a->workspace_bytes >= need, HQ_ERR_WORKSPACE,
@@ -1228,18 +1347,18 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   // keep ws_acc 16-byte aligned
   p.ws_acc = (float*)(((uintptr_t)p.ws_acc + 15) & ~(uintptr_t)15);
 
-  // the split-merge staging reuses the ring: weights + l (2 nsplit R) + 32 + warp partial sums (8 R 128) floats
-  const size_t peer_floats = p.peer.world > 1 ? (size_t)peer_scratch_floats(p.peer.world, a->kv_repeat) : 0;
-  HQ_REQUIRE(((size_t)2 * nsplit * a->kv_repeat + 36 + (size_t)kWarps * NT * 8 * 128 + 2 * (size_t)kWarps * NT * 8 + peer_floats) * 4 <=
-                 (size_t)kWarps * kSlots * slot_bytes,
-             HQ_ERR_UNSUPPORTED, "hq_decode_splitk: too many splits (%d)", nsplit);
   // scales can ride in the bulk copies when every 32-token group of a row starts on a
   // 16-byte boundary and a row has room for the round-up of its tail to 8 tokens
   const int64_t nq8 = ((int64_t)a->n_quant + 7) & ~(int64_t)7;
-  p.scale_tma = a->n_quant > 0 && aligned16(a->k_scale) && aligned16(a->v_scale) && a->ks_stride_bh % 8 == 0 &&
+  p.scale_tma = !force_direct_scales && a->n_quant > 0 && aligned16(a->k_scale) && aligned16(a->v_scale) && a->ks_stride_bh % 8 == 0 &&
                 a->vs_stride_bh % 8 == 0 && a->ks_stride_bh >= nq8 && a->vs_stride_bh >= nq8;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)(a->BH_KV * nsplit));
+#ifdef HQ_DEC_FAST_BUILD      // development builds: the K4/V4 instantiations only
+  HQ_REQUIRE(k_bits == 4 && v_bits == 4 && p.peer.world <= 1, HQ_ERR_UNSUPPORTED, "hq_decode_splitk: development build (K4/V4, no peers)");
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true, 4, 4, false>(p, grid, st) : launch_decode<1, false, 4, 4, false>(p, grid, st);
+  return p.scale_tma ? launch_decode<2, true, 4, 4, false>(p, grid, st) : launch_decode<2, false, 4, 4, false>(p, grid, st);
+#else
   switch (k_bits * 16 + v_bits) {
     case 0x44: return launch_decode_bits<4, 4>(p, NT, grid, st);
     case 0x88: return launch_decode_bits<8, 8>(p, NT, grid, st);
@@ -1251,6 +1370,7 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
     case 0x24: return launch_decode_bits<2, 4>(p, NT, grid, st);
     default: return launch_decode_bits<2, 2>(p, NT, grid, st);
   }
+#endif
 }
 
 // ---- decode without caller-provided scratch -----------------------------------------------
@@ -1329,3 +1449,4 @@ extern "C" int hq_decode_static_status(int* status) {
   if (*status != 0) HQ_CUDA(cudaMemset(scratch, 0, sizeof(int)));
   return HQ_OK;
 }
+
