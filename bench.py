@@ -734,7 +734,24 @@ def run_ours(args):
             torch.cuda.synchronize()
             plan.check_status()
             ms_, ms_all = ev[0].elapsed_time(ev[1]) / reps, ev[2].elapsed_time(ev[3]) / reps
+            # the reference's sage_fp8_attention entry point (INT8 Q K^T, no vertical lines or window): FP8 P V on
+            # kind::f8f6f4 with the exact running maximum its arithmetic needs, and the same call with BF16 P V
+            pv = {}
+            for tag, fp8 in (("fp8_pv", True), ("bf16_pv", False)):
+                pl = PrefillPlan(t["q"], t["k"], t["v"], None, 0, None, True, pv_fp8=fp8)
+                pl.run()
+                torch.cuda.synchronize()
+                f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                f0.record()
+                for _ in range(reps):
+                    pl.run()
+                f1.record()
+                torch.cuda.synchronize()
+                pl.check_status()
+                pv[tag] = round(f0.elapsed_time(f1) / reps, 3)
+                del pl
             prefill.append({"seq": n, "ms": round(ms_, 3), "tflops": round(plan.flops / ms_ / 1e9, 1),
+                            "sage_fp8_attention_ms": pv,
                             "frac_of_measured_bf16_sustained": None if not bf16_peak else round(plan.flops / ms_ / 1e9 / bf16_peak, 3),
                             "ms_with_selection_and_preparation": round(ms_all, 3),
                             "tflops_with_selection_and_preparation": round(plan.flops / ms_all / 1e9, 1),

@@ -29,7 +29,7 @@ EXPORTS = [
     "hq_topk",
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_quant_blocks", "hq_per_block_int8",
-    "hq_prefill_vertical_prepare", "hq_prefill_transpose_v",
+    "hq_prefill_vertical_prepare", "hq_prefill_transpose_v", "hq_prefill_quant_v_fp8",
     "hq_prefill_hybrid",
     "hq_peer_exchange_bytes", "hq_peer_slot", "hq_peer_recv_slot", "hq_peer_exchange_merge", "hq_peer_status",
     "hq_peer_buffer_create", "hq_peer_buffer_open", "hq_peer_buffer_close", "hq_peer_buffer_destroy",
@@ -74,6 +74,7 @@ class PrefillArgs(C.Structure):
         ("nv_valid", C.c_void_p),
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sn", C.c_int64),
         ("status", C.c_void_p),
+        ("v_t8", C.c_void_p), ("v_scale8", C.c_void_p), ("pv_fp8", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
@@ -119,6 +120,7 @@ def _declare(lib):
     lib.hq_prefill_vertical_prepare.argtypes = [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, i64, i64,
                                                 vp, vp, vp, vp, vp, vp]
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
+    lib.hq_prefill_quant_v_fp8.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
     lib.hq_peer_exchange_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_peer_slot.argtypes = [vp, i32, i32, C.c_uint32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]

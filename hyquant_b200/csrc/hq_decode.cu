@@ -56,6 +56,7 @@ namespace hq {
 #endif
 __host__ __device__ constexpr int warps_of(int NT) { return NT == 2 ? HQ_DEC_WARPS2 : HQ_DEC_WARPS1; }
 constexpr int kSlots = 3;
+constexpr int kScaleLanes = 8;            // lanes of a warp that fetch a unit's scales (16 bytes each)
 // quantised tokens per unit: 32, or 16 when 32 rows of K and V codes would not fit the 4 KB of a BF16 unit (every pair
 // with an 8-bit side), so that every pair keeps a 4224-byte slot and two CTAs per SM
 __host__ __device__ constexpr int unit_tokens(int kb, int vb) { return 32 * 16 * (kb + vb) > 4096 ? 16 : 32; }
@@ -442,7 +443,7 @@ decode_splitk_kernel(const DecodeParams p) {
   // ---- 1. barriers
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) mbar_init(&my_bar[s], 1);
+    for (int s = 0; s < kSlots; ++s) mbar_init(&my_bar[s], kScaleTma ? 1 + kScaleLanes : 1);
     fence_mbar_init();
   }
   __syncwarp();
@@ -461,34 +462,42 @@ decode_splitk_kernel(const DecodeParams p) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar) : "memory");
   };
-  auto issue = [&](int i) {   // lane 0 only
+  // The two code tensors of a unit travel as bulk copies (lane 0).  Its scales - 64 bytes each - do not: the copy
+  // engine takes about as long to accept a 64-byte request as a 2 KB one, and at four requests per unit it is the
+  // requests, not the bytes, that it runs out of.  Lanes 0..7 fetch them as 16-byte asynchronous copies (lanes 0-3
+  // the K scales, 4-7 the V scales) and let the slot's barrier count their completion (one arrival per lane, which
+  // the barrier's arrival count includes; a lane with nothing to copy arrives at once).
+  auto scale_copies = [&](int slot, int64_t tok0, int ntok) {     // lanes 0..7, kScaleTma only
+    const int c = lane & 3;
+    if (8 * c < ntok) {
+      const __half* src = (lane < 4 ? ks_base : vs_base) + tok0 + 8 * c;
+      const uint32_t dst = ring_u32 + slot * kSlotBytes + F::kData + (lane < 4 ? 0 : 64) + 16 * c;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_u32 + slot * 8) : "memory");
+  };
+  auto issue = [&](int i) {   // the whole warp
     const int u = u_begin + warp + kWarps * i;
     const int slot = i % kSlots;
     if (u < uq_full) {
-      const uint32_t dst = ring_u32 + slot * kSlotBytes, bar = bar_u32 + slot * 8;
       const int64_t tok0 = (int64_t)u * kUnitQ;
-      constexpr uint32_t kb = kUnitQ * F::kRowK, vb = kUnitQ * F::kRowV, sb = kUnitQ * 2;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kScaleTma ? kb + vb + 2 * sb : kb + vb) : "memory");
-      if (kScaleTma) {
-        bulk_raw(dst + F::kData, ks_base + tok0, sb, bar);
-        bulk_raw(dst + F::kData + 64, vs_base + tok0, sb, bar);
+      if (lane == 0) {
+        const uint32_t dst = ring_u32 + slot * kSlotBytes, bar = bar_u32 + slot * 8;
+        constexpr uint32_t kb = kUnitQ * F::kRowK, vb = kUnitQ * F::kRowV;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
+        bulk_raw(dst, kq_base + tok0 * F::kRowK, kb, bar);
+        bulk_raw(dst + F::kVOff, vq_base + tok0 * F::kRowV, vb, bar);
       }
-      bulk_raw(dst, kq_base + tok0 * F::kRowK, kb, bar);
-      bulk_raw(dst + F::kVOff, vq_base + tok0 * F::kRowV, vb, bar);
+      if (kScaleTma && lane < kScaleLanes) scale_copies(slot, tok0, kUnitQ);
       return;
     }
     const Unit un = unit_of<KB, VB>(p, head, u);
+    if (kScaleTma && lane < kScaleLanes) scale_copies(slot, un.kind == 0 ? un.tok0 : 0, un.kind == 0 ? un.ntok : 0);
+    if (lane != 0) return;
     uint8_t* dst = my_ring + slot * kSlotBytes;
     if (un.kind == 0) {
       const uint32_t kbytes = (uint32_t)un.ntok * F::kRowK, vbytes = (uint32_t)un.ntok * F::kRowV;
-      if (kScaleTma) {
-        const uint32_t sbytes = (uint32_t)((un.ntok + 7) & ~7) * 2u;
-        mbar_expect_tx(&my_bar[slot], kbytes + vbytes + 2 * sbytes);
-        bulk_g2s(dst + F::kData, p.k_scale + head * p.ks_stride_bh + un.tok0, sbytes, &my_bar[slot]);
-        bulk_g2s(dst + F::kData + 64, p.v_scale + head * p.vs_stride_bh + un.tok0, sbytes, &my_bar[slot]);
-      } else {
-        mbar_expect_tx(&my_bar[slot], kbytes + vbytes);
-      }
+      mbar_expect_tx(&my_bar[slot], kbytes + vbytes);
       bulk_g2s(dst, un.k, kbytes, &my_bar[slot]);
       bulk_g2s(dst + F::kVOff, un.v, vbytes, &my_bar[slot]);
     } else {
@@ -524,20 +533,14 @@ decode_splitk_kernel(const DecodeParams p) {
   };
   if (!p.overlap) {
     load_q();
-    if (lane == 0) {
-      for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
-    }
+    for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
   } else {
     int early = 0;
-    if (lane == 0) {
-      while (early < kSlots && early < n_my && stable(early)) { issue(early); ++early; }
-    }
+    while (early < kSlots && early < n_my && stable(early)) { issue(early); ++early; }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     load_q();
-    if (lane == 0) {
-      for (int i = early; i < kSlots && i < n_my; ++i) issue(i);
-    }
+    for (int i = early; i < kSlots && i < n_my; ++i) issue(i);
   }
 
   // The step's new token, if the call carries one, is attended to from where the caller has it (segment 3) and
@@ -887,7 +890,7 @@ decode_splitk_kernel(const DecodeParams p) {
       }
       sc_cur = sc_next;
       __syncwarp();
-      if (lane == 0 && i + kSlots < n_my) issue(i + kSlots);
+      if (i + kSlots < n_my) issue(i + kSlots);
     }
   }
 
@@ -974,8 +977,8 @@ decode_splitk_kernel(const DecodeParams p) {
         for (int nt = 0; nt < NT; ++nt) mma_bf16_1688(O[nt][mt], r0, r1, pb[nt][VF::scale_idx(mt)]);
       }
       __syncwarp();
-      if (lane == 0 && i + kSlots < n_my) {
-        if (patched) fence_proxy_async_smem();   // generic-proxy writes above precede the next async write
+      if (i + kSlots < n_my) {
+        if (patched && lane == 0) fence_proxy_async_smem();   // generic-proxy writes above precede the next async write
         issue(i + kSlots);
       }
     }

@@ -55,6 +55,17 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st);
 int prefill_tc_prepare_v(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t, cudaStream_t st);
 int prefill_tc_prepare_vertical(const int32_t* vasc, int B, int H_Q, int H_KV, int N, int T, const void* k_bf, const void* v,
                                 int64_t v_sb, int64_t v_sh, int64_t v_sn, void* xk, void* xvt, cudaStream_t st);
+int prefill_tc_prepare_v_fp8(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t8, float* v_scale,
+                             void* amax_scratch, cudaStream_t st);
+}
+
+extern "C" int hq_prefill_quant_v_fp8(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
+                                      void* v_t8, float* v_scale, void* amax_scratch, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(v && v_t8 && v_scale && amax_scratch && B > 0 && H_KV > 0 && N > 0, HQ_ERR_INVALID, "hq_prefill_quant_v_fp8: bad arguments");
+  HQ_REQUIRE(aligned16(v) && aligned16(v_t8) && v_sb % 8 == 0 && v_sh % 8 == 0 && v_sn % 8 == 0, HQ_ERR_ALIGNMENT,
+             "hq_prefill_quant_v_fp8: rows must be 16-byte aligned");
+  return prefill_tc_prepare_v_fp8(v, v_sb, v_sh, v_sn, B, H_KV, N, v_t8, v_scale, amax_scratch, (cudaStream_t)stream);
 }
 
 extern "C" int hq_prefill_transpose_v(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
@@ -95,11 +106,17 @@ extern "C" int hq_prefill_hybrid(const hq_prefill_args* a, void* stream) {
   HQ_REQUIRE(a->head_dim == 128, HQ_ERR_UNSUPPORTED, "hq_prefill_hybrid: head_dim %d (only 128 is built)", a->head_dim);
   HQ_REQUIRE(a->B > 0 && a->H_Q > 0 && a->H_KV > 0 && a->N > 0 && a->H_Q % a->H_KV == 0 && a->window >= 0 && a->T >= 0,
              HQ_ERR_INVALID, "hq_prefill_hybrid: bad sizes");
-  HQ_REQUIRE(a->q_i8 && a->q_bf && a->q_scale && a->k_i8 && a->k_bf && a->k_scale && a->k_bias && a->v_t && a->out && a->status,
+  HQ_REQUIRE(a->q_i8 && a->q_bf && a->q_scale && a->k_i8 && a->k_bf && a->k_scale && a->k_bias && a->out && a->status,
              HQ_ERR_INVALID, "hq_prefill_hybrid: null pointer");
+  if (a->pv_fp8) {
+    HQ_REQUIRE(a->v_t8 && a->v_scale8 && aligned16(a->v_t8), HQ_ERR_INVALID, "hq_prefill_hybrid: FP8 P V needs v_t8 (16-byte aligned) and v_scale8");
+    HQ_REQUIRE(a->T == 0, HQ_ERR_UNSUPPORTED, "hq_prefill_hybrid: FP8 P V is built without vertical lines (T must be 0)");
+  } else {
+    HQ_REQUIRE(a->v_t != nullptr, HQ_ERR_INVALID, "hq_prefill_hybrid: v_t is null");
+  }
   HQ_REQUIRE(a->T == 0 || (a->vert_k && a->vert_vt && a->nv_valid), HQ_ERR_INVALID,
              "hq_prefill_hybrid: vertical arguments missing");
-  HQ_REQUIRE(aligned16(a->q_i8) && aligned16(a->q_bf) && aligned16(a->k_i8) && aligned16(a->k_bf) && aligned16(a->v_t) &&
+  HQ_REQUIRE(aligned16(a->q_i8) && aligned16(a->q_bf) && aligned16(a->k_i8) && aligned16(a->k_bf) && (a->pv_fp8 || aligned16(a->v_t)) &&
                  aligned16(a->k_scale) && aligned16(a->k_bias) && aligned16(a->out) && a->o_sn % 8 == 0 && a->o_sh % 8 == 0 && a->o_sb % 8 == 0,
              HQ_ERR_ALIGNMENT, "hq_prefill_hybrid: operand rows must be 16-byte aligned");
   HQ_REQUIRE(a->out_dtype == HQ_BF16 || a->out_dtype == HQ_F16 || a->out_dtype == HQ_F32, HQ_ERR_UNSUPPORTED,

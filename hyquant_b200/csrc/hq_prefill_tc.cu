@@ -30,6 +30,7 @@ namespace hq {
 
 struct PrefillTcParams {
   const float* q_scale; const float* k_scale;      // [B,H_Q,Npad], [B,H_KV,Npad]
+  const float* v_scale;                            // FP8 P V: [B,H_KV,128], one per channel
   const int* nv_valid;
   void* out; int out_dtype; int64_t o_sb, o_sh, o_sn;
   int B, H_Q, H_KV, N, Npad, W, T, Tpad, nqb, nkb;
@@ -114,6 +115,11 @@ struct TcItemIter {
 // if the reference moves, and write the tile's P against the reference as it then stands.  Called by whole
 // warps; kept out of line so that the common path keeps its registers.
 struct TcSlowResult { float m_ref, l; bool ok; };
+// FP8 P V (the arithmetic of the reference's sm_90 kernel, vendor/sageattention/csrc/qattn/attn_utils.cuh:30,354-458 and
+// qk_int_sv_f8_cuda_sm90.cu:259-364): P~ = 2^(s - m + 8.807) against the EXACT running maximum m (so P~ <= 448, the largest
+// e4m3 value), the row sum taken in fp32 before P~ is rounded to e4m3.
+constexpr float kFp8Offset = 8.807f;
+template <bool kFp8>
 __device__ __noinline__ TcSlowResult tc_slow_tile(uint32_t tS, uint32_t tO, const float4* ks4, const float4* kb4, bool is_i8,
                                                   float esc, uint32_t mlo, uint32_t mhi, float m_ref, float l,
                                                   uint64_t* pv_bar, uint32_t pv_parity, volatile int* abort_flag) {
@@ -167,22 +173,36 @@ __device__ __noinline__ TcSlowResult tc_slow_tile(uint32_t tS, uint32_t tO, cons
     if (grow) { l *= alpha; m_ref = mx; }
   }
   const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-  uint32_t pk[32];
   float rs[4] = {0.f, 0.f, 0.f, 0.f};
+  if constexpr (kFp8) {
+    uint32_t pk[16];
+    const float off = kFp8Offset - mu;
 #pragma unroll
-  for (int c = 0; c < 64; c += 2) {
-    const float p0 = ex2f(fmaf(x[c], esc, -mu)), p1 = ex2f(fmaf(x[c + 1], esc, -mu));
-    rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
-    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);       // low half = even column
-    pk[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+    for (int c = 0; c < 64; c += 4) {
+      const float p0 = ex2f(fmaf(x[c], esc, off)), p1 = ex2f(fmaf(x[c + 1], esc, off));
+      const float p2 = ex2f(fmaf(x[c + 2], esc, off)), p3 = ex2f(fmaf(x[c + 3], esc, off));
+      rs[0] += p0; rs[1] += p1; rs[2] += p2; rs[3] += p3;
+      pk[c >> 2] = tc::pack_e4m3x4(p0, p1, p2, p3);
+    }
+    tc::tmem_st16(tS, pk);
+  } else {
+    uint32_t pk[32];
+#pragma unroll
+    for (int c = 0; c < 64; c += 2) {
+      const float p0 = ex2f(fmaf(x[c], esc, -mu)), p1 = ex2f(fmaf(x[c + 1], esc, -mu));
+      rs[c & 3] += p0; rs[(c & 3) + 1] += p1;
+      __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);       // low half = even column
+      pk[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+    }
+    tc::tmem_st32(tS, pk);
   }
-  tc::tmem_st32(tS, pk);
   tc::tmem_wait_st();
   res.m_ref = m_ref;
   res.l = l + (rs[0] + rs[1]) + (rs[2] + rs[3]);
   return res;
 }
 
+template <bool kFp8>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant__ CUtensorMap mQb,
                   const __grid_constant__ CUtensorMap mKi, const __grid_constant__ CUtensorMap mKb,
@@ -285,7 +305,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         if (!cv.done() && mbar_test_wait(v_empty + cv.stage, cv.par ^ 1u)) {
           uint8_t* sV = smem + TcSmem::V + cv.stage * 16384;
           uint64_t* full = v_full + cv.stage;
-          mbar_expect_tx(full, 16384);
+          mbar_expect_tx(full, kFp8 ? 8192 : 16384);      // FP8: V^T tiles of 64 one-byte keys
           if (cv.kind == 1) tc::tma_load_2d(sV, &mXv, cv.j * 64, (int)((bhq0 + cv.hh) * 128), full);
           else tc::tma_load_2d(sV, &mVt, (cv.kind == 0 ? 0 : wla) + cv.j * 64, (int)(bhk * 128), full);
           cv.next(plan);
@@ -310,11 +330,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       constexpr uint32_t idesc_i8 = tc::make_idesc(2, tc::kFmtS8, tc::kFmtS8, 128, 64);
       constexpr uint32_t idesc_qk = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 64);
       constexpr uint32_t idesc_pv = tc::make_idesc(1, tc::kFmtBF16, tc::kFmtBF16, 128, 128);
+      constexpr uint32_t idesc_pv8 = tc::make_idesc(1, tc::kFmtE4M3, tc::kFmtE4M3, 128, 128);
       bool ok = tc::mbar_wait_abortable(q_full, 0, abort_flag, 100);
       // operand descriptors differ only in their start-address field (16-byte units)
       const uint64_t dQi = tc::smem_desc_k128(smem + TcSmem::Qi + h * 16384, 0);
       const uint64_t dQb = tc::smem_desc_k128(smem + TcSmem::Qb + h * 32768, 0);
-      const uint64_t dK = tc::smem_desc_k128(smem + TcSmem::K, 0), dV = tc::smem_desc_k128(smem + TcSmem::V, 0);
+      const uint64_t dK = tc::smem_desc_k128(smem + TcSmem::K, 0);
+      const uint64_t dV = kFp8 ? tc::smem_desc_k64(smem + TcSmem::V, 0) : tc::smem_desc_k128(smem + TcSmem::V, 0);
       const uint32_t tS = tmem_base + kColS + 128u * h, tO = tmem_base + kColO + 128u * h;
       const int n_t = plan.n_tiles(h);
       TcItemIter cq, cp;
@@ -361,7 +383,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         tc::fence_after_sync();
         const uint32_t aP = tS + 64u * (t & 1);
         const uint64_t bV = dV + (uint64_t)(cp.stage * 1024);
-        if (t > 0) {
+        if constexpr (kFp8) {     // 64 keys = two K steps of 32 e4m3: 8 columns of P, 32 bytes of a V^T row each
+#pragma unroll
+          for (int k = 0; k < 2; ++k) tc::mma_f8_ts(tO, aP + 8 * k, bV + 2 * k, idesc_pv8, (t > 0 || k > 0) ? 1u : 0u);
+        } else if (t > 0) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) tc::mma_bf16_ts(tO, aP + 8 * k, bV + 2 * k, idesc_pv, 1u);
         } else {
@@ -413,63 +438,124 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
       // The row maximum is not computed: a P value above 2^8 would show in the row sum of the tile, which
       // is then > 2^8.  Only then (and for a row's first finite scores) the scores are read from tensor
       // memory again, the maximum is taken, O is rescaled, the reference moves and the pass is repeated.
-      uint32_t pk[32];
-      float lsum;
-      {
-        uint32_t sr[64];
-        tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-        tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-        tc::tmem_wait_ld();
-        const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-        const float2 esc2 = make_float2(esc, esc), nmu2 = make_float2(-mu, -mu);
-        float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
-        if (is_i8) {
+      if constexpr (kFp8) {
+        // FP8 P V: the exact running maximum is part of the arithmetic (P~ must not pass 448), so the tile's row
+        // maximum is taken first; a row whose maximum grows goes through the out-of-line path, which rescales O.
+        uint32_t pk8[16];
+        float lsum;
+        bool grow;
+        {
+          uint32_t sr[64];
+          tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+          tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+          tc::tmem_wait_ld();
+          float* y = reinterpret_cast<float*>(sr);            // the scores in exponent units, in place
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (is_i8) {
 #pragma unroll
-          for (int c4 = 0; c4 < 16; ++c4) {
-            const float4 kk = ks4[c4], bb = kb4[c4];
-            // bits(i + 0x4B400000) = 12582912 + i for |i| < 2^22; the bias row carries -12582912 * scale (or -inf)
-            const float2 a01 = make_float2(__int_as_float((int)sr[4 * c4] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 1] + 0x4B400000));
-            const float2 a23 = make_float2(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 3] + 0x4B400000));
-            const float2 y01 = ffma2(ffma2(a01, make_float2(kk.x, kk.y), make_float2(bb.x, bb.y)), esc2, nmu2);
-            const float2 y23 = ffma2(ffma2(a23, make_float2(kk.z, kk.w), make_float2(bb.z, bb.w)), esc2, nmu2);
-            const float2 p01 = make_float2(ex2f(y01.x), ex2f(y01.y)), p23 = make_float2(ex2f(y23.x), ex2f(y23.y));
-            rsa = fadd2(rsa, p01);
-            rsb = fadd2(rsb, p23);
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(p01.x, p01.y), h1 = __floats2bfloat162_rn(p23.x, p23.y);   // low half = even column
-            pk[2 * c4] = *reinterpret_cast<uint32_t*>(&h0);
-            pk[2 * c4 + 1] = *reinterpret_cast<uint32_t*>(&h1);
-          }
-        } else {
+            for (int c4 = 0; c4 < 16; ++c4) {
+              const float4 kk = ks4[c4], bb = kb4[c4];
+              const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, bv[4] = {bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-          for (int c2 = 0; c2 < 32; ++c2) {
-            const uint32_t mw = c2 < 16 ? mlo : mhi;
-            float2 y = ffma2(make_float2(__uint_as_float(sr[2 * c2]), __uint_as_float(sr[2 * c2 + 1])), esc2, nmu2);
-            if ((mw >> ((2 * c2) & 31)) & 1u) y.x = -INFINITY;
-            if ((mw >> ((2 * c2 + 1) & 31)) & 1u) y.y = -INFINITY;
-            const float2 pp = make_float2(ex2f(y.x), ex2f(y.y));
-            if (c2 & 1) rsb = fadd2(rsb, pp); else rsa = fadd2(rsa, pp);
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(pp.x, pp.y);
-            pk[c2] = *reinterpret_cast<uint32_t*>(&h0);
+              for (int e = 0; e < 4; ++e) {
+                y[4 * c4 + e] = fmaf(__int_as_float((int)sr[4 * c4 + e] + 0x4B400000), kv[e], bv[e]) * esc;
+                mx4[e] = fmaxf(mx4[e], y[4 * c4 + e]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+              const uint32_t mw = c < 32 ? mlo : mhi;
+              y[c] = ((mw >> (c & 31)) & 1u) ? -INFINITY : y[c] * esc;
+              mx4[c & 3] = fmaxf(mx4[c & 3], y[c]);
+            }
           }
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          grow = mx > m_ref;                                   // also true for a row's first finite maximum
+          const float off = kFp8Offset - (m_ref == -INFINITY ? 0.f : m_ref);
+          float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int c = 0; c < 64; c += 4) {
+            const float p0 = ex2f(y[c] + off), p1 = ex2f(y[c + 1] + off), p2 = ex2f(y[c + 2] + off), p3 = ex2f(y[c + 3] + off);
+            rs[0] += p0; rs[1] += p1; rs[2] += p2; rs[3] += p3;
+            pk8[c >> 2] = tc::pack_e4m3x4(p0, p1, p2, p3);
+          }
+          lsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
         }
-        lsum = (rsa.x + rsa.y) + (rsb.x + rsb.y);
-      }
-      const bool need = m_ref == -INFINITY || !(lsum <= 256.f);
-      if (__any_sync(0xffffffffu, need)) {
-        // out of line: the maximum, the move of the reference and the tile's P against the new reference
-        const bool wait_pv = t > 0;
-        const TcSlowResult sr2 = tc_slow_tile(lane_base + colS + slot * 64, lane_base + colO, ks4, kb4, is_i8, esc, mlo, mhi, m_ref, l,
-                                              wait_pv ? pv_done + 2 * h + ((t - 1) & 1) : nullptr, (uint32_t)(((t - 1) >> 1) & 1),
-                                              abort_flag);
-        ok = sr2.ok;
-        if (!ok) break;
-        m_ref = sr2.m_ref;
-        l = sr2.l;
+        if (__any_sync(0xffffffffu, grow)) {
+          const bool wait_pv = t > 0;
+          const TcSlowResult sr2 = tc_slow_tile<true>(lane_base + colS + slot * 64, lane_base + colO, ks4, kb4, is_i8, esc, mlo, mhi, m_ref, l,
+                                                      wait_pv ? pv_done + 2 * h + ((t - 1) & 1) : nullptr, (uint32_t)(((t - 1) >> 1) & 1),
+                                                      abort_flag);
+          ok = sr2.ok;
+          if (!ok) break;
+          m_ref = sr2.m_ref;
+          l = sr2.l;
+        } else {
+          l += lsum;
+          // P~ as e4m3 over the first 16 columns of the S buffer just read: row r in lane r, keys 4c .. 4c+3 in column c
+          tc::tmem_st16(lane_base + colS + slot * 64, pk8);
+          tc::tmem_wait_st();
+        }
       } else {
-        l += lsum;
-        // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
-        tc::tmem_st32(lane_base + colS + slot * 64, pk);
-        tc::tmem_wait_st();
+        uint32_t pk[32];
+        float lsum;
+        {
+          uint32_t sr[64];
+          tc::tmem_ld32(lane_base + colS + slot * 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+          tc::tmem_ld32(lane_base + colS + slot * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+          tc::tmem_wait_ld();
+          const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+          const float2 esc2 = make_float2(esc, esc), nmu2 = make_float2(-mu, -mu);
+          float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
+          if (is_i8) {
+  #pragma unroll
+            for (int c4 = 0; c4 < 16; ++c4) {
+              const float4 kk = ks4[c4], bb = kb4[c4];
+              // bits(i + 0x4B400000) = 12582912 + i for |i| < 2^22; the bias row carries -12582912 * scale (or -inf)
+              const float2 a01 = make_float2(__int_as_float((int)sr[4 * c4] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 1] + 0x4B400000));
+              const float2 a23 = make_float2(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 3] + 0x4B400000));
+              const float2 y01 = ffma2(ffma2(a01, make_float2(kk.x, kk.y), make_float2(bb.x, bb.y)), esc2, nmu2);
+              const float2 y23 = ffma2(ffma2(a23, make_float2(kk.z, kk.w), make_float2(bb.z, bb.w)), esc2, nmu2);
+              const float2 p01 = make_float2(ex2f(y01.x), ex2f(y01.y)), p23 = make_float2(ex2f(y23.x), ex2f(y23.y));
+              rsa = fadd2(rsa, p01);
+              rsb = fadd2(rsb, p23);
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(p01.x, p01.y), h1 = __floats2bfloat162_rn(p23.x, p23.y);   // low half = even column
+              pk[2 * c4] = *reinterpret_cast<uint32_t*>(&h0);
+              pk[2 * c4 + 1] = *reinterpret_cast<uint32_t*>(&h1);
+            }
+          } else {
+  #pragma unroll
+            for (int c2 = 0; c2 < 32; ++c2) {
+              const uint32_t mw = c2 < 16 ? mlo : mhi;
+              float2 y = ffma2(make_float2(__uint_as_float(sr[2 * c2]), __uint_as_float(sr[2 * c2 + 1])), esc2, nmu2);
+              if ((mw >> ((2 * c2) & 31)) & 1u) y.x = -INFINITY;
+              if ((mw >> ((2 * c2 + 1) & 31)) & 1u) y.y = -INFINITY;
+              const float2 pp = make_float2(ex2f(y.x), ex2f(y.y));
+              if (c2 & 1) rsb = fadd2(rsb, pp); else rsa = fadd2(rsa, pp);
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(pp.x, pp.y);
+              pk[c2] = *reinterpret_cast<uint32_t*>(&h0);
+            }
+          }
+          lsum = (rsa.x + rsa.y) + (rsb.x + rsb.y);
+        }
+        const bool need = m_ref == -INFINITY || !(lsum <= 256.f);
+        if (__any_sync(0xffffffffu, need)) {
+          // out of line: the maximum, the move of the reference and the tile's P against the new reference
+          const bool wait_pv = t > 0;
+          const TcSlowResult sr2 = tc_slow_tile<false>(lane_base + colS + slot * 64, lane_base + colO, ks4, kb4, is_i8, esc, mlo, mhi, m_ref, l,
+                                                wait_pv ? pv_done + 2 * h + ((t - 1) & 1) : nullptr, (uint32_t)(((t - 1) >> 1) & 1),
+                                                abort_flag);
+          ok = sr2.ok;
+          if (!ok) break;
+          m_ref = sr2.m_ref;
+          l = sr2.l;
+        } else {
+          l += lsum;
+          // P over the first 32 columns of the S buffer just read: row r in lane r, keys 2c, 2c+1 in column c
+          tc::tmem_st32(lane_base + colS + slot * 64, pk);
+          tc::tmem_wait_st();
+        }
       }
       tc::fence_before_sync();
       tc::mbar_arrive(p_ready + sl);
@@ -480,6 +566,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
     if (ok && n_tiles > 0) {
       tc::fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float* vsc = kFp8 ? p.v_scale + bhk * 128 : nullptr;        // FP8 P V: the channel scales of V come back here
       const int hq = (int)(bhq - (int64_t)b * p.H_Q);
       const int64_t base = b * p.o_sb + hq * p.o_sh + (int64_t)row * p.o_sn;
 #pragma unroll
@@ -487,6 +574,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
         uint32_t o[32];
         tc::tmem_ld32(lane_base + colO + ch * 32, o);
         tc::tmem_wait_ld();
+        if constexpr (kFp8) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * __ldg(vsc + ch * 32 + x));
+        }
         if (row < p.N) {
           if (p.out_dtype == HQ_BF16) {
             uint32_t w[16];
@@ -579,8 +670,12 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   if ((rc = tc::make_map_2d(&mQb, a->q_bf, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, qrows, 256, 64, 128))) return rc;
   if ((rc = tc::make_map_2d(&mKi, a->k_i8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, 128, krows, 128, 128, 64))) return rc;
   if ((rc = tc::make_map_2d(&mKb, a->k_bf, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, krows, 256, 64, 64))) return rc;
-  if ((rc = tc::make_map_2d(&mVt, a->v_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Npad, (uint64_t)a->B * a->H_KV * 128,
-                            (uint64_t)Npad * 2, 64, 128))) return rc;
+  const bool fp8 = a->pv_fp8 != 0;
+  if (fp8) {       // V^T as e4m3 bytes: 64-key tiles are 64-byte rows, 64-byte swizzle
+    if ((rc = tc::make_map_2d(&mVt, a->v_t8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)Npad, (uint64_t)a->B * a->H_KV * 128,
+                              (uint64_t)Npad, 64, 128, 64))) return rc;
+  } else if ((rc = tc::make_map_2d(&mVt, a->v_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Npad, (uint64_t)a->B * a->H_KV * 128,
+                                   (uint64_t)Npad * 2, 64, 128))) return rc;
   if ((rc = tc::make_map_2d(&mKs, a->k_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)Npad, (uint64_t)a->B * a->H_KV,
                             (uint64_t)Npad * 4, 64, 1, false))) return rc;
   if ((rc = tc::make_map_2d(&mKbs, a->k_bias, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)Npad, (uint64_t)a->B * a->H_Q,
@@ -593,7 +688,7 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
     mXk = mKb; mXv = mVt;
   }
   PrefillTcParams p{};
-  p.q_scale = a->q_scale; p.k_scale = a->k_scale;
+  p.q_scale = a->q_scale; p.k_scale = a->k_scale; p.v_scale = a->v_scale8;
   p.nv_valid = a->nv_valid;
   p.out = a->out; p.out_dtype = a->out_dtype; p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_sn = a->o_sn;
   p.B = a->B; p.H_Q = a->H_Q; p.H_KV = a->H_KV; p.N = N; p.Npad = Npad; p.W = a->window; p.T = T; p.Tpad = Tpad;
@@ -605,12 +700,69 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
   int dev = 0;
   HQ_CUDA(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    HQ_CUDA(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    HQ_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    HQ_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_dev = dev;
   }
   const int R = a->H_Q / a->H_KV;
   dim3 grid((unsigned)p.nqb, (unsigned)(a->H_KV * ((R + 1) / 2)), (unsigned)a->B);   // two query heads of a KV group per CTA
-  prefill_tc_kernel<<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, mKbs, p);
+  if (fp8) prefill_tc_kernel<true><<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, mKbs, p);
+  else prefill_tc_kernel<false><<<grid, kTcThreads, smem, st>>>(mQi, mQb, mKi, mKb, mVt, mXk, mXv, mKs, mKbs, p);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
+}
+
+// ---- FP8 P V: V^T as e4m3 with one scale per channel ----------------------------------------------------------
+// The reference's per_channel_fp8 (vendor/sageattention/quant.py:134-166 with MeanScaleKernel, csrc/fused/fused.cu:318-429,
+// smooth_v off): scale[b, h, d] = max_n |v[b, h, n, d]| / 448, code = e4m3(v * (448 / max)), stored transposed.
+__global__ void __launch_bounds__(256)
+v_amax_kernel(const __nv_bfloat16* __restrict__ v, int64_t sb, int64_t sh, int64_t sn, int H, int N, unsigned* __restrict__ amax_bits) {
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int d = threadIdx.x & 127, half = threadIdx.x >> 7;
+  const int rows_per = (N + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per, r1 = min(N, r0 + rows_per);
+  const __nv_bfloat16* base = v + b * sb + h * sh + d;
+  float m = 0.f;
+  for (int r = r0 + half; r < r1; r += 2) m = fmaxf(m, fabsf(__bfloat162float(base[(int64_t)r * sn])));
+  atomicMax(amax_bits + (int64_t)bh * 128 + d, __float_as_uint(m));       // non-negative floats order like their bit patterns
+}
+
+// v [B,H_KV,N,128] (strided) -> vt8 [B,H_KV,128,Npad] e4m3 (columns >= N zero), scale [B,H_KV,128] = amax / 448
+__global__ void __launch_bounds__(256)
+transpose_v_fp8_kernel(const __nv_bfloat16* __restrict__ v, int64_t sb, int64_t sh, int64_t sn, int H, int N, int Npad,
+                       const unsigned* __restrict__ amax_bits, uint8_t* __restrict__ vt8, float* __restrict__ scale) {
+  __shared__ float tile[64][129];
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H, key0 = blockIdx.x * 64, tid = threadIdx.x;
+  for (int x = tid; x < 64 * 16; x += 256) {
+    const int r = x >> 4, c = (x & 15) * 8;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (key0 + r < N) raw = __ldg(reinterpret_cast<const uint4*>(v + b * sb + h * sh + (int64_t)(key0 + r) * sn + c));
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[r][c + j] = __bfloat162float(e[j]);
+  }
+  __syncthreads();
+  for (int x = tid; x < 128 * 4; x += 256) {
+    const int d = x >> 2, k16 = (x & 3) * 16;
+    const float amax = __uint_as_float(amax_bits[(int64_t)bh * 128 + d]);
+    const float recip = amax > 0.f ? 448.f / amax : 0.f;
+    if (blockIdx.x == 0 && k16 == 0) scale[(int64_t)bh * 128 + d] = amax / 448.f;
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = tc::pack_e4m3x4(tile[k16 + 4 * j][d] * recip, tile[k16 + 4 * j + 1][d] * recip, tile[k16 + 4 * j + 2][d] * recip,
+                             tile[k16 + 4 * j + 3][d] * recip);
+    *reinterpret_cast<uint4*>(vt8 + ((int64_t)bh * 128 + d) * Npad + key0 + k16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+int prefill_tc_prepare_v_fp8(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t8, float* v_scale,
+                             void* amax_scratch, cudaStream_t st) {
+  const int Npad = (N + 63) / 64 * 64;
+  HQ_CUDA(cudaMemsetAsync(amax_scratch, 0, (size_t)B * H_KV * 128 * 4, st));
+  v_amax_kernel<<<dim3(64, B * H_KV), 256, 0, st>>>((const __nv_bfloat16*)v, sb, sh, sn, H_KV, N, (unsigned*)amax_scratch);
+  transpose_v_fp8_kernel<<<dim3(Npad / 64, B * H_KV), 256, 0, st>>>((const __nv_bfloat16*)v, sb, sh, sn, H_KV, N, Npad,
+                                                                   (const unsigned*)amax_scratch, (uint8_t*)v_t8, v_scale);
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
 }

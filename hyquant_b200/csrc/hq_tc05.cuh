@@ -27,9 +27,11 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major tensor [rows][cols] of `esz`-byte elements, row pitch `pitch_bytes`;
-// box = [box_cols][box_rows]; 128-byte swizzle (box_cols * esz must be 128) or none.
+// box = [box_cols][box_rows]; swizzle: 128 (box_cols * esz must be 128), 64 (box_cols * esz must be 64) or 0 = none
+// (`true` is taken as 128, `false` as none).
 inline int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int esz, uint64_t cols, uint64_t rows,
-                       uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true) {
+                       uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, int swizzle = 128) {
+  if (swizzle == 1) swizzle = 128;
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return HQ_ERR_CUDA; }
   const cuuint64_t dims[2] = {cols, rows};
@@ -37,7 +39,7 @@ inline int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt,
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with %d (cols=%llu rows=%llu pitch=%llu box=%ux%u esz=%d)", (int)r,
@@ -114,6 +116,21 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// four floats -> four e4m3 bytes (round to nearest even, saturating to +-448), first argument in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));      // first source -> upper byte
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -132,12 +149,25 @@ __device__ __forceinline__ uint64_t smem_desc_k128(const void* tile, uint32_t k_
   return d;
 }
 
+// The same for a K-major tile whose rows are 64 bytes, 64-byte swizzle (8-row groups 512 bytes apart, tile base
+// 512-byte aligned): the 64-key tiles of 8-bit V^T.
+__device__ __forceinline__ uint64_t smem_desc_k64(const void* tile, uint32_t k_byte_offset) {
+  const uint32_t addr = smem_u32(tile) + k_byte_offset;
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;                            // 64-byte swizzle
+  return d;
+}
+
 // instruction descriptor: D format (1 = f32, 2 = s32), A/B element formats, K-major operands, M x N
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t dfmt, uint32_t afmt, uint32_t bfmt, uint32_t M, uint32_t N) {
   return (dfmt << 4) | (afmt << 7) | (bfmt << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 constexpr uint32_t kFmtBF16 = 1;   // kind::f16: 0 = f16, 1 = bf16
 constexpr uint32_t kFmtS8 = 1;     // kind::i8 : 0 = u8, 1 = s8
+constexpr uint32_t kFmtE4M3 = 0;   // kind::f8f6f4: 0 = e4m3, 1 = e5m2
 
 __device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -151,6 +181,14 @@ __device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// kind::f8f6f4, A operand (M x 32 e4m3: row r in tensor-memory lane r, four elements per 32-bit column) from tensor memory
+__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }

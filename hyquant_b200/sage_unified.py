@@ -126,7 +126,10 @@ class PrefillPlan:
     plus the filled ``hq_prefill_args``; ``run()`` launches only the attention kernel."""
 
     def __init__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
-                 window_size: int, sm_scale: Optional[float], smooth_k: bool, scale_granularity: Optional[str] = None):
+                 window_size: int, sm_scale: Optional[float], smooth_k: bool, scale_granularity: Optional[str] = None,
+                 pv_fp8: bool = False):
+        """``pv_fp8``: the P V product in FP8 E4M3 with the reference's ``sage_fp8_attention`` arithmetic (V^T quantised
+        per channel, P~ = 2^(s - m + 8.807) against the exact running maximum); not built together with vertical lines."""
         dtype = q.dtype
         qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
         dev = q.device
@@ -139,9 +142,19 @@ class PrefillPlan:
         T = 0
         vert_k = vert_vt = nvv = vasc = None
         Npad = (N + 63) // 64 * 64
-        v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
-        _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
-                                              v_t.data_ptr(), st), "hq_prefill_transpose_v")
+        v_t = v_t8 = v_sc8 = None
+        if pv_fp8:
+            if vertical_indices is not None and vertical_indices.shape[-1] > 0:
+                raise HyQuantError("FP8 P V is not built together with vertical lines")
+            v_t8 = torch.empty(B, H_kv, 128, Npad, dtype=torch.uint8, device=dev)
+            v_sc8 = torch.empty(B, H_kv, 128, dtype=torch.float32, device=dev)
+            scratch = torch.empty(B * H_kv * 128, dtype=torch.int32, device=dev)
+            _lib.check(lib.hq_prefill_quant_v_fp8(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
+                                                  v_t8.data_ptr(), v_sc8.data_ptr(), scratch.data_ptr(), st), "hq_prefill_quant_v_fp8")
+        else:
+            v_t = torch.empty(B, H_kv, 128, Npad, dtype=torch.bfloat16, device=dev)
+            _lib.check(lib.hq_prefill_transpose_v(vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), B, H_kv, N,
+                                                  v_t.data_ptr(), st), "hq_prefill_transpose_v")
         prefix_len = max(0, N - window_size)
         if vertical_indices is not None and vertical_indices.shape[-1] > 0 and prefix_len > 0:
             if tuple(vertical_indices.shape[:2]) != (B, H_q):
@@ -169,14 +182,18 @@ class PrefillPlan:
         a.q_i8, a.q_bf, a.q_scale = q_i8.data_ptr(), q_bf.data_ptr(), q_sc.data_ptr()
         a.k_i8, a.k_bf, a.k_scale = k_i8.data_ptr(), k_bf.data_ptr(), k_sc.data_ptr()
         a.k_bias = k_bias.data_ptr()
-        a.v_t = v_t.data_ptr()
+        if pv_fp8:
+            a.v_t8, a.v_scale8, a.pv_fp8 = v_t8.data_ptr(), v_sc8.data_ptr(), 1
+        else:
+            a.v_t = v_t.data_ptr()
         if T:
             a.vert_k, a.vert_vt, a.nv_valid = vert_k.data_ptr(), vert_vt.data_ptr(), nvv.data_ptr()
         a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         a.status = self.status.data_ptr()
         self.args, self.out, self.device = a, out, dev
-        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, k_bias, nvv, v_t)
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, k_bias, nvv, v_t, v_t8, v_sc8)
+        self.v_t8, self.v_scale8 = v_t8, v_sc8
         self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
 
     def run(self) -> torch.Tensor:
@@ -192,10 +209,10 @@ class PrefillPlan:
 
 def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: Optional[torch.Tensor],
                    window_size: int, sm_scale: Optional[float], smooth_k: bool,
-                   scale_granularity: Optional[str] = None) -> torch.Tensor:
+                   scale_granularity: Optional[str] = None, pv_fp8: bool = False) -> torch.Tensor:
     """Causal attention [B,H_q,N,D] with INT8 QK^T on the non-vertical prefix and BF16 on the
     vertical lines and the window.  ``vertical_indices`` int64 [B,H_q,T] (any order) or None."""
-    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, scale_granularity).run()
+    return PrefillPlan(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, scale_granularity, pv_fp8).run()
 
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,
@@ -223,9 +240,15 @@ def full_attention_fp16_triton(q, k, v, tensor_layout: str = "HND", is_causal: b
     return out.transpose(1, 2) if tensor_layout == "NHD" else out
 
 
-def sage_fp8_attention(q, k, v, *, is_causal: bool = True, sm_scale: Optional[float] = None, smooth_k: bool = True):
-    """INT8 QK causal attention without vertical lines or window (reference sage_fp8_attention.py:15-45).
-    The P V product of this build runs in BF16 on the tcgen05 path."""
+def sage_fp8_attention(q, k, v, *, is_causal: bool = True, sm_scale: Optional[float] = None, smooth_k: bool = True,
+                       pv_fp8: bool = True):
+    """INT8 Q K^T + FP8 P V causal attention without vertical lines or window (reference sage_fp8_attention.py:15-45,
+    whose kernel exists for sm_90a only).  P V follows that kernel's arithmetic on the tcgen05 ``kind::f8f6f4`` path:
+    V^T in E4M3 with one scale per channel (``max|v| / 448``), ``P~ = 2^(s - m + 8.807)`` rounded to E4M3 against the
+    exact running maximum, the row sum in fp32 before the rounding, ``O = acc / l * v_scale``.  Q K^T is this library's
+    INT8 path (one scale per row; the diagonal 128-query block in BF16).  FP8 P V costs accuracy (about 1e-3 rel-MSE
+    against exact attention on Gaussian V, where BF16 P V gives 3e-6); ``pv_fp8=False`` runs the same call with BF16
+    P V."""
     if not is_causal:
         raise HyQuantError("only causal attention is built")
-    return hybrid_prefill(q, k, v, None, 0, sm_scale, smooth_k)
+    return hybrid_prefill(q, k, v, None, 0, sm_scale, smooth_k, pv_fp8=pv_fp8)

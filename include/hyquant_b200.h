@@ -372,8 +372,23 @@ typedef struct hq_prefill_args {
   const int32_t* nv_valid;
   void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements (multiples of 8) */
   int32_t* status;             /* device word, zeroed by the caller; bit 1 = a bounded wait expired */
+  /* FP8 P V (pv_fp8 != 0; T must be 0): P~ = 2^(s - m + 8.807) rounded to e4m3 against the exact running maximum,
+   * V^T as e4m3 with one scale per channel (hq_prefill_quant_v_fp8), the product on tcgen05 kind::f8f6f4, the row sum
+   * in fp32 before the cast - the arithmetic of the reference's sage_fp8_attention
+   * (src/ops/sage_fp8_attention.py:15-45 -> vendor/sageattention/core_sm90.py:116-165,
+   *  csrc/qattn/attn_utils.cuh:30,354-458, csrc/qattn/qk_int_sv_f8_cuda_sm90.cu:259-364,490-515). v_t is not used then. */
+  const void* v_t8;            /* e4m3 [B,H_KV,128,Npad] */
+  const float* v_scale8;       /* fp32 [B,H_KV,128] */
+  int32_t pv_fp8; int32_t reserved0;
 } hq_prefill_args;
 int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
+
+/* V for the FP8 P V product: the reference's per_channel_fp8 with smooth_v off
+ * (vendor/sageattention/quant.py:134-166; MeanScaleKernel, csrc/fused/fused.cu:318-429):
+ *   v bf16 [B,H_KV,N,128] -> v_t8 e4m3 [B,H_KV,128,Npad] (transposed, columns >= N zero), v_scale fp32 [B,H_KV,128] =
+ *   max_n |v| / 448.  amax_scratch: B * H_KV * 128 * 4 bytes of device scratch (cleared here, in stream). */
+int hq_prefill_quant_v_fp8(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
+                           void* v_t8, float* v_scale, void* amax_scratch, void* stream);
 
 #ifdef __cplusplus
 }

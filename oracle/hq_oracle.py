@@ -604,6 +604,76 @@ def hybrid_prefill_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray,
     return rf(out.reshape(B, H_q, N, D))
 
 
+# ----------------------------------------------------------------------------
+# a13 — FP8 P V (src/ops/sage_fp8_attention.py:15-45 -> vendor/sageattention/core_sm90.py:116-165)
+# ----------------------------------------------------------------------------
+
+def per_channel_fp8(v: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+    """vendor/sageattention/quant.py:134-166 with MeanScaleKernel (csrc/fused/fused.cu:381-428), smooth_v off:
+    ``scale[b,h,d] = max_n |v| / 448``; codes ``e4m3(v * (448 / max))``.  v [B,H,N,D] -> (codes as float32 holding
+    e4m3-exact values [B,H,N,D], scale float32 [B,H,D])."""
+    vf = v.astype(np.float32)
+    amax = np.abs(vf).max(axis=2)
+    scale = (amax / np.float32(448.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        recip = np.where(amax > 0, np.float32(448.0) / amax, np.float32(0)).astype(np.float32)
+    return e4m3_round(vf * recip[:, :, None, :]), scale
+
+
+def fp8_pv_attention_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray, window_size: int = 0,
+                               sm_scale: Optional[float] = None, smooth_k: bool = True, round_fn=None) -> np.ndarray:
+    """Causal attention with the FP8 P V arithmetic of the reference's sm_90 kernel: per 64-key tile
+    ``m = max(m, rowmax)``; ``P~ = 2^(s - m + 8.807)`` (attn_utils.cuh:30,354-458), row sum in fp32 BEFORE the cast,
+    ``P~`` rounded to e4m3 (qk_int_sv_f8_cuda_sm90.cu:310-320), V in e4m3 with one scale per channel
+    (:func:`per_channel_fp8`), fp32 accumulation, ``O = acc / l * v_scale`` (:490-515).
+
+    The scores come from THIS library's Q K^T (the reference's per-thread INT8 granularity belongs to its sm_90 tiling):
+    K smoothed; for the 128-query block at s, keys below ``wla(s)`` INT8 with one scale per query row and per key row
+    (codes of :func:`quant_per_block_int8` with one-row blocks), keys in ``[wla(s), s + 128)`` in bf16 with the causal
+    mask; tiles of 64 keys in that order.  q [B,H_q,N,D], k/v [B,H_kv,N,D] float32 holding bf16-exact values."""
+    rf = (lambda a: a) if round_fn is None else round_fn
+    B, H_q, N, D = q.shape
+    H_kv = k.shape[1]
+    g = H_q // H_kv
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    sml = np.float32(np.float32(sm_scale) * np.float32(1.44269504))
+    km = rf(k.astype(np.float32).mean(axis=2, keepdims=True)) if smooth_k else np.zeros((B, H_kv, 1, D), np.float32)
+    k_sm = rf(k.astype(np.float32) - km)
+    q_i8, q_sc = quant_per_block_int8(q, 1, sm_scale * LOG2E)
+    k_i8, k_sc = quant_per_block_int8(k_sm, 1, 1.0)
+    v8, v_sc = per_channel_fp8(v)
+    out = np.zeros((B, H_q, N, D), dtype=np.float32)
+    off = np.float32(FP8_P_OFFSET)
+    for b in range(B):
+        for h in range(H_q):
+            hk = h // g
+            for s0 in range(0, N, 128):
+                rows = np.arange(s0, min(s0 + 128, N))
+                wla = int(window_lo_aligned(np.array(s0), window_size)) if window_size > 0 else s0
+                m = np.full(len(rows), -np.inf, dtype=np.float32)
+                l = np.zeros(len(rows), dtype=np.float32)
+                acc = np.zeros((len(rows), D), dtype=np.float32)
+                tiles = [(c0, True) for c0 in range(0, wla, 64)] + [(c0, False) for c0 in range(wla, min(s0 + 128, N), 64)]
+                for c0, is_i8 in tiles:
+                    cols = np.arange(c0, min(c0 + 64, N))
+                    if is_i8:
+                        dot = q_i8[b, h, rows].astype(np.float32) @ k_i8[b, hk, cols].astype(np.float32).T
+                        y = (dot * k_sc[b, hk, cols][None, :]).astype(np.float32) * q_sc[b, h, rows][:, None]
+                    else:
+                        y = (q[b, h, rows].astype(np.float32) @ k_sm[b, hk, cols].T).astype(np.float32) * sml
+                        y = np.where(rows[:, None] >= cols[None, :], y, -np.inf).astype(np.float32)
+                    m_new = np.maximum(m, y.max(axis=1))
+                    with np.errstate(invalid="ignore"):
+                        alpha = np.where(np.isneginf(m), np.float32(0), np.exp2(m - m_new)).astype(np.float32)
+                        pt = np.where(np.isneginf(y), np.float32(0), np.exp2(y - m_new[:, None] + off)).astype(np.float32)
+                    l = l * alpha + pt.sum(axis=1, dtype=np.float32)
+                    acc = acc * alpha[:, None] + e4m3_round(pt) @ v8[b, hk, cols]
+                    m = m_new
+                out[b, h, rows] = acc / l[:, None] * v_sc[b, hk][None, :]
+    return rf(out)
+
+
 def dense_causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray,
                            sm_scale: Optional[float] = None) -> np.ndarray:
     """float64 causal softmax(QK^T)V with GQA — the yardstick the prefill

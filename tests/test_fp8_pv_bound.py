@@ -1,4 +1,5 @@
-"""Why P·V stays in BF16: rounding P and V to FP8 (e4m3, the format of the reference's sm_90a FP8 path,
+"""Why BF16 P·V is the default of the hybrid prefill (FP8 P·V is built behind ``sage_fp8_attention``, the reference's
+FP8 entry point): rounding P and V to FP8 (e4m3, the format of the reference's sm_90a FP8 path,
 src/ops/sage_fp8_attention.py:15-45) on the synthetic prefill data misses the accuracy bar of this path
 (max-abs 2e-2, rel-MSE 1e-4 against 16-bit attention) by an order of magnitude, while BF16 operands stay
 two orders inside it.  Pure torch on CPU."""
