@@ -208,9 +208,11 @@ def time_kernel_steps(torch, layers, qs, steps, warmup, dist=None, flush=None, g
     return total, steps * len(plans)
 
 
-def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
+def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None, graph=True):
     """Per step: q/k/v of the new token for every layer from pinned host memory -> device; per layer append
-    to staging (flush when full) and decode attention; every layer's output back to the host."""
+    to staging (flush when full) and decode attention; every layer's output back to the host.
+    ``graph``: the step runs as one CUDA-graph replay (``DecodeStepGraph``: copy in, one fused append + attention launch
+    per layer with the cache lengths read from the copied message, copy out); else layer by layer from Python."""
     r = H_Q // H_KV
     n = len(layers)
     g = torch.Generator(); g.manual_seed(seed)
@@ -218,21 +220,33 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
     rows = B * (H_Q + 2 * H_KV)
     # one pinned message per step: the new token's q | k | v rows of every layer; one pinned result per step
     hin = torch.randn(tot, n, rows, D, generator=g).to(torch.bfloat16).pin_memory()
-    hout = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16).pin_memory()
-    dev = layers[0].k_window.device
-    xdev = torch.empty(n, rows, D, dtype=torch.bfloat16, device=dev)
-    odev = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16, device=dev)
-    qv = [xdev[li, :B * H_Q].view(B, H_Q, 1, D) for li in range(n)]
-    kv = [xdev[li, B * H_Q:B * (H_Q + H_KV)].view(B, H_KV, 1, D) for li in range(n)]
-    vv = [xdev[li, B * (H_Q + H_KV):].view(B, H_KV, 1, D) for li in range(n)]
-    ov = [odev[li] for li in range(n)]
+    h2d = n * (B * H_Q * D + 2 * B * H_KV * D) * 2
+    d2h = n * B * H_Q * D * 2
+    if graph:
+        from hyquant_b200.graph_decode import DecodeStepGraph
+        dg = DecodeStepGraph(layers, B, H_Q, H_KV)
+        msg = dg.host_in[:n * rows * D * 2].view(torch.bfloat16).view(n, rows, D)
+        h2d += n * 8                          # + (n_quant, n_staging) of every layer
 
-    def one_step(s):
-        xdev.copy_(hin[s], non_blocking=True)
-        for li, layer in enumerate(layers):
-            layer.decode_step(qv[li], kv[li], vv[li], r, out=ov[li])      # append + attention, one launch
-        hout.copy_(odev, non_blocking=True)
-        torch.cuda.synchronize()      # the step's result is on the host
+        def one_step(s):
+            msg.copy_(hin[s])                 # the host produces the step's inputs into the message
+            dg.step(synchronize=True)         # the step's result is on the host
+    else:
+        hout = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16).pin_memory()
+        dev = layers[0].k_window.device
+        xdev = torch.empty(n, rows, D, dtype=torch.bfloat16, device=dev)
+        odev = torch.empty(n, B, H_Q, 1, D, dtype=torch.bfloat16, device=dev)
+        qv = [xdev[li, :B * H_Q].view(B, H_Q, 1, D) for li in range(n)]
+        kv = [xdev[li, B * H_Q:B * (H_Q + H_KV)].view(B, H_KV, 1, D) for li in range(n)]
+        vv = [xdev[li, B * (H_Q + H_KV):].view(B, H_KV, 1, D) for li in range(n)]
+        ov = [odev[li] for li in range(n)]
+
+        def one_step(s):
+            xdev.copy_(hin[s], non_blocking=True)
+            for li, layer in enumerate(layers):
+                layer.decode_step(qv[li], kv[li], vv[li], r, out=ov[li])      # append + attention, one launch
+            hout.copy_(odev, non_blocking=True)
+            torch.cuda.synchronize()      # the step's result is on the host
 
     for s in range(warmup):
         one_step(s)
@@ -246,8 +260,8 @@ def time_e2e_steps(torch, hq, layers, steps, warmup, seed, dist=None):
     e1.record()
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
-    h2d = n * (B * H_Q * D + 2 * B * H_KV * D) * 2
-    d2h = n * B * H_Q * D * 2
+    if graph:
+        dg.close()
     return max(e0.elapsed_time(e1), wall_ms), h2d, d2h
 
 
@@ -665,7 +679,7 @@ def run_ours(args):
     if args.no_e2e:
         e2e_ms, h2d, d2h = float("nan"), 0, 0
     else:
-        e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, args.warmup, 99 + rank, dist)
+        e2e_ms, h2d, d2h = time_e2e_steps(torch, hq, layers, args.steps, max(args.warmup, 3), 99 + rank, dist, graph=not args.no_graph)
     clocks = sampler.stop()      # sampled every 2 ms over the three decode loops (graph, plain launches, e2e)
     e2e_bytes = sum(layer_bytes(l, B * H_Q) for l in layers)     # staging has grown by then; close enough per step
 
@@ -790,7 +804,8 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "path": "per step one pinned host message (q/k/v of every layer) to the device, DStageLayerCache.decode_step per layer (append_staging + decode_attention as one launch; the patched models' decode path), one message with every layer's output back to the host"},
+                    "path": "per step one pinned host message (q/k/v of every layer and every layer's cache lengths) to the device, one fused append_staging + decode_attention launch per layer (DStageLayerCache.decode_step), one message with every layer's output back to the host" +
+                            ("; the whole step is one CUDA-graph replay (DecodeStepGraph): the kernels read the lengths from the message" if not args.no_graph else "; launched layer by layer from Python")},
             "gpu_launches": launches,
             "launch_mode": ("python" if args.no_graph else "cuda graph replay of one token (32 launches)") +
                            ("" if args.no_overlap else "; programmatic dependent launch: a call's blocks start and fetch their first "

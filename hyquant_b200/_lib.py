@@ -59,6 +59,7 @@ class DecodeArgs(C.Structure):
         ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("kn_stride", C.c_int64), ("vn_stride", C.c_int64),
         ("peer_bufs", C.c_void_p), ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_seq", C.c_uint32),
         ("peer_reserved", C.c_int32), ("peer_timeout_ns", C.c_int64),
+        ("lengths", C.c_void_p),
     ]
 
 

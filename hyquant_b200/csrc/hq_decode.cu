@@ -92,7 +92,7 @@ struct DecodeParams {
   __nv_bfloat16* stage_k; __nv_bfloat16* stage_v;   // staging buffers, written only when the call carries a new token
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
   int overlap;                            // launched with programmatic stream serialisation
-  int uq_stable;                          // INT4 units [0, uq_stable) cannot have been written by the previous kernel
+  const int* lengths;                     // device {n_quant, n_staging} overriding the values above (or null)
   int* status; int* counters;             // workspace
   float* ws_m; float* ws_l; float* ws_acc;
 };
@@ -147,23 +147,31 @@ struct Unit {
   int tok0;       // first token within its segment
 };
 
+// The lengths that change from step to step.  They come with the launch (host values) or, when the call names a device
+// record, from there: a launch captured in a CUDA graph then stays valid while the cache grows.
+struct Lens {
+  int n_quant, n_stg;     // quantised prefix tokens, live staging tokens
+  int uq, useg1, units;   // quantised units, staging units, all units of a head
+  int uq_stable;          // quantised units that the kernel just before this one cannot have written
+};
+
 template <int KB, int VB>
-__device__ __forceinline__ Unit unit_of(const DecodeParams& p, int head, int u) {
+__device__ __forceinline__ Unit unit_of(const DecodeParams& p, const Lens& L, int head, int u) {
   Unit r;
-  if (u < p.uq) {
+  if (u < L.uq) {
     constexpr int kUnitQ = Fmt<KB, VB>::kUnitQ;
-    r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, p.n_quant - r.tok0);
+    r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, L.n_quant - r.tok0);
     r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowK;
     r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowV;
     return r;
   }
-  u -= p.uq;
+  u -= L.uq;
   int s = 0;
   if (u >= p.useg[0]) {
     u -= p.useg[0]; s = 1;
-    if (u >= p.useg[1]) { u -= p.useg[1]; s = 2; if (u >= p.useg[2]) { u -= p.useg[2]; s = 3; } }
+    if (u >= L.useg1) { u -= L.useg1; s = 2; if (u >= p.useg[2]) { u -= p.useg[2]; s = 3; } }
   }
-  r.kind = 1; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, p.nseg[s] - r.tok0);
+  r.kind = 1; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, (s == 1 ? L.n_stg : p.nseg[s]) - r.tok0);
   r.k = reinterpret_cast<const uint8_t*>(p.kseg[s] + head * p.kseg_stride[s] + (int64_t)r.tok0 * 128);
   r.v = reinterpret_cast<const uint8_t*>(p.vseg[s] + head * p.vseg_stride[s] + (int64_t)r.tok0 * 128);
   return r;
@@ -430,11 +438,20 @@ decode_splitk_kernel(const DecodeParams p) {
   // each do one large one.
   const int split = blockIdx.x / p.BH;
   const int head = blockIdx.x - split * p.BH;
+  Lens L;
+  L.n_quant = p.n_quant; L.n_stg = p.nseg[1];
+  if (p.lengths != nullptr) {       // written before the kernel that precedes this one started (see hq_decode_args.lengths)
+    L.n_quant = __ldg(p.lengths); L.n_stg = __ldg(p.lengths + 1);
+  }
+  L.uq = (L.n_quant + kUnitQ - 1) / kUnitQ;
+  L.useg1 = (L.n_stg + kUnitB - 1) / kUnitB;
+  L.units = L.uq + p.useg[0] + L.useg1 + p.useg[2] + p.useg[3];
+  L.uq_stable = L.n_quant > 128 ? (L.n_quant - 128) / kUnitQ : 0;
   int u_begin, u_end;
   {
     const int64_t parts = (int64_t)(p.nsplit - 1) * 256 + p.last_share;          // in 1/256 of an even share
-    u_begin = (int)(((int64_t)split * 256 * p.units) / parts);
-    u_end = split + 1 == p.nsplit ? p.units : (int)(((int64_t)(split + 1) * 256 * p.units) / parts);
+    u_begin = (int)(((int64_t)split * 256 * L.units) / parts);
+    u_end = split + 1 == p.nsplit ? L.units : (int)(((int64_t)(split + 1) * 256 * L.units) / parts);
   }
   const int n_my = (u_end - u_begin - warp + kWarps - 1) / kWarps;   // units u_begin + warp + kWarps i
   uint8_t* my_ring = ring + warp * (kSlots * kSlotBytes);
@@ -457,7 +474,7 @@ decode_splitk_kernel(const DecodeParams p) {
   const __half* const ks_base = p.k_scale + head * p.ks_stride_bh;
   const __half* const vs_base = p.v_scale + head * p.vs_stride_bh;
   const uint32_t ring_u32 = smem_u32(my_ring), bar_u32 = smem_u32(my_bar);
-  const int uq_full = p.n_quant / kUnitQ;            // quantised units with all their tokens
+  const int uq_full = L.n_quant / kUnitQ;            // quantised units with all their tokens
   auto bulk_raw = [](uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar) : "memory");
@@ -491,7 +508,7 @@ decode_splitk_kernel(const DecodeParams p) {
       if (kScaleTma && lane < kScaleLanes) scale_copies(slot, tok0, kUnitQ);
       return;
     }
-    const Unit un = unit_of<KB, VB>(p, head, u);
+    const Unit un = unit_of<KB, VB>(p, L, head, u);
     if (kScaleTma && lane < kScaleLanes) scale_copies(slot, un.kind == 0 ? un.tok0 : 0, un.kind == 0 ? un.ntok : 0);
     if (lane != 0) return;
     uint8_t* dst = my_ring + slot * kSlotBytes;
@@ -511,9 +528,9 @@ decode_splitk_kernel(const DecodeParams p) {
   // quantised tokens older than the newest 128, vertical-line tokens, window tokens (not staging, not the new token).
   auto stable = [&](int i) -> bool {
     const int u = u_begin + warp + kWarps * i;
-    if (u < p.uq) return u < p.uq_stable;
-    const int ub = u - p.uq;
-    return ub < p.useg[0] || (ub >= p.useg[0] + p.useg[1] && ub < p.useg[0] + p.useg[1] + p.useg[2]);
+    if (u < L.uq) return u < L.uq_stable;
+    const int ub = u - L.uq;
+    return ub < p.useg[0] || (ub >= p.useg[0] + L.useg1 && ub < p.useg[0] + L.useg1 + p.useg[2]);
   };
 
   // ---- 2. the query rows and the first bulk copies.
@@ -548,7 +565,7 @@ decode_splitk_kernel(const DecodeParams p) {
   if (p.nseg[3] > 0 && split == 0 && warp == 0) {
     const __nv_bfloat16* src = (lane < 16 ? p.kseg[3] : p.vseg[3]) + head * (lane < 16 ? p.kseg_stride[3] : p.vseg_stride[3]);
     __nv_bfloat16* dst = (lane < 16 ? p.stage_k : p.stage_v) + head * (lane < 16 ? p.kseg_stride[1] : p.vseg_stride[1]) +
-                         (int64_t)p.nseg[1] * 128;
+                         (int64_t)L.n_stg * 128;
     reinterpret_cast<uint4*>(dst)[lane & 15] = __ldg(reinterpret_cast<const uint4*>(src) + (lane & 15));
   }
 
@@ -645,9 +662,9 @@ decode_splitk_kernel(const DecodeParams p) {
     auto load_scales = [&](int ii) -> uint32_t {
       if (kScaleTma || ii >= n_my) return 0u;
       const int u = u_begin + warp + kWarps * ii;
-      if (u >= p.uq) return 0u;
+      if (u >= L.uq) return 0u;
       const int tok = u * kUnitQ + lane;
-      if (lane >= kUnitQ || tok >= p.n_quant) return 0u;
+      if (lane >= kUnitQ || tok >= L.n_quant) return 0u;
       const uint16_t ks = __half_as_ushort(p.k_scale[head * p.ks_stride_bh + tok]);
       const uint16_t vs = __half_as_ushort(p.v_scale[head * p.vs_stride_bh + tok]);
       return (uint32_t)ks | ((uint32_t)vs << 16);
@@ -656,8 +673,8 @@ decode_splitk_kernel(const DecodeParams p) {
 
     for (; i < n_my; ++i) {
       const int u = u_begin + warp + kWarps * i;
-      if (u >= p.uq) break;
-      const int ntok = min(kUnitQ, p.n_quant - u * kUnitQ);
+      if (u >= L.uq) break;
+      const int ntok = min(kUnitQ, L.n_quant - u * kUnitQ);
       const uint32_t sc_next = load_scales(i + 1);
       const int slot = i % kSlots;
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
@@ -905,7 +922,7 @@ decode_splitk_kernel(const DecodeParams p) {
         for (int r = 0; r < 2; ++r) Qb[nt][c][r] = fragB[((nt * 8 + c) * 2 + r) * 32 + lane];
 
     for (; i < n_my; ++i) {
-      const Unit un = unit_of<KB, VB>(p, head, u_begin + warp + kWarps * i);
+      const Unit un = unit_of<KB, VB>(p, L, head, u_begin + warp + kWarps * i);
       const int slot = i % kSlots;
       if (!mbar_wait_bounded(&my_bar[slot], (uint32_t)((i / kSlots) & 1))) { failed = true; break; }
       uint8_t* Ks = my_ring + slot * kSlotBytes;
@@ -1275,12 +1292,14 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   }
   HQ_REQUIRE((a->flags & ~HQ_DECODE_OVERLAP_PREVIOUS) == 0, HQ_ERR_INVALID, "hq_decode_splitk: unknown flags 0x%x", a->flags);
   p.overlap = (a->flags & HQ_DECODE_OVERLAP_PREVIOUS) ? 1 : 0;
-  p.uq_stable = a->n_quant > 128 ? (a->n_quant - 128) / kUnitQ : 0;
   p.R = a->kv_repeat;
   p.out_dtype = a->out_dtype;
   p.sml = a->sm_scale * 1.44269504f;
   p.out = a->out; p.out_stride = a->out_stride;
   p.pm = a->partial_m; p.pl = a->partial_l; p.pacc = a->partial_acc;
+  p.lengths = a->lengths;
+  HQ_REQUIRE(a->lengths == nullptr || (((uintptr_t)a->lengths & 3) == 0 && a->k_staging && a->v_staging), HQ_ERR_INVALID,
+             "hq_decode_splitk: lengths must be 4-byte aligned and needs the staging buffers");
   p.peer.world = 0;
   if (a->peer_world > 1) {
     HQ_REQUIRE(!partial && a->out != nullptr, HQ_ERR_INVALID, "hq_decode_splitk: a peer exchange writes the merged result to out");

@@ -77,6 +77,7 @@ class DStageLayerCache:
         self.vertical_indices: Optional[torch.Tensor] = None   # [B, H_KV, T] chosen at freeze
         self.overlap_previous: bool = True     # decode launches may overlap the end of the previous kernel
         self._plan_fresh: bool = False
+        self._lengths: Optional[torch.Tensor] = None   # device int32 [2] = (n_quant, n_staging) the kernel reads, if bound
 
     # ---- views of the live prefix (reference attribute names) -----------------
     @property
@@ -269,6 +270,7 @@ class DStageLayerCache:
             p.args.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS
         p.args.n_quant = self._n_quant
         p.args.n_staging = self._staging_ptr
+        p.args.lengths = None if self._lengths is None else self._lengths.data_ptr()
         return p
 
     def decode_attention(self, query_states: torch.Tensor, kv_repeat: int, *, partial=None,
@@ -318,6 +320,51 @@ class DStageLayerCache:
         if partial is not None:
             return None
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
+
+    # ---- decode launches that stay valid in a CUDA graph --------------------------------------------
+    def bind_lengths(self, record: Optional[torch.Tensor]):
+        """Make the decode kernel take ``(n_quant, n_staging)`` from ``record`` (device int32 [2], e.g. a slice of the buffer
+        the step's inputs are copied into) instead of from the launch arguments, so that a captured launch stays valid
+        while the cache grows.  The caller writes :meth:`step_lengths` into it before each step; ``None`` unbinds."""
+        if record is not None and (record.dtype != torch.int32 or record.numel() != 2 or not record.is_cuda):
+            raise HyQuantError("the length record must be a CUDA int32 tensor of two elements")
+        self._lengths = record
+        self._plan = None
+
+    def step_lengths(self) -> Tuple[int, int]:
+        """``(n_quant, n_staging)`` as the next :meth:`decode_step` has to see them (before its token is counted)."""
+        return self._n_quant, self._staging_ptr
+
+    def next_step_flushes(self) -> bool:
+        """True when the next appended token fills the staging buffer (that step quantises 128 tokens first)."""
+        return self._staging_ptr >= GROUP_SIZE - 1
+
+    def capture_decode_step(self, query_states, key_states, value_states, kv_repeat: int, out: torch.Tensor,
+                            overlap: bool = True):
+        """Issue the fused ``decode_step`` launch WITHOUT counting the token: for use inside a CUDA-graph capture
+        (lengths bound with :meth:`bind_lengths`; every tensor argument must keep its address across replays).
+        After each replay call :meth:`count_replayed_step`."""
+        if self._lengths is None:
+            raise HyQuantError("bind_lengths first: a captured launch must not carry the lengths in its arguments")
+        B, H_KV, S, D = key_states.shape
+        B_, H_Q_, _, D_ = query_states.shape
+        q2d = query_states.reshape(B_ * H_Q_, D_)
+        k2, v2 = key_states.reshape(B * H_KV, D), value_states.reshape(B * H_KV, D)
+        plan = self._decode_plan(q2d, kv_repeat)
+        a = plan.args
+        a.flags = _lib.HQ_DECODE_OVERLAP_PREVIOUS if (overlap and self.k_bits == 4 and self.v_bits == 4) else 0
+        a.k_new, a.v_new, a.kn_stride, a.vn_stride = k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0)
+        try:
+            plan.run(q2d, out=out.view(B_ * H_Q_, D_))
+        finally:
+            a.k_new = a.v_new = None
+
+    def count_replayed_step(self):
+        """Account for one replay of a launch captured by :meth:`capture_decode_step` (one token appended)."""
+        if self._staging_ptr >= GROUP_SIZE - 1:
+            raise HyQuantError("this step fills the staging buffer: it has to go through decode_step (flush), not a replay")
+        self._staging_ptr += 1
+        self._seq_len += 1
 
     def get_seq_length(self) -> int:
         return self._seq_len

@@ -164,6 +164,13 @@ typedef struct hq_decode_args {
    * with hq_peer_exchange_merge calls on the same buffers.  partial_* must be NULL. */
   void* const* peer_bufs; int32_t peer_world; int32_t peer_rank; uint32_t peer_seq; int32_t peer_reserved;
   int64_t peer_timeout_ns;     /* 0 = 2 s */
+  /* Optional: a device record {int32 n_quant, int32 n_staging} that overrides the two fields above when the kernel
+   * runs, so that a launch captured in a CUDA graph stays valid while the cache grows (the reference keeps both on
+   * the host and grows its tensors with torch.cat, src/ops/d_stage_kv_cache.py:195-217).  n_quant / n_staging above
+   * are then only used to choose the split count.  The record must be complete before the kernel launched just
+   * before this one starts (e.g. written by the copy that brings the step's inputs), because an overlapped launch
+   * (HQ_DECODE_OVERLAP_PREVIOUS) reads it at once; the staging pointers must be set. */
+  const int32_t* lengths;
 } hq_decode_args;
 
 int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);
