@@ -41,6 +41,7 @@ class DecodeStepGraph:
             return q, k, v, buf[n * self._row_bytes:].view(torch.int32).view(n, 2)
 
         self.host_q, self.host_k, self.host_v, self._host_len = views(self.host_in)     # the caller fills host_q/k/v
+        self._host_len_np = self._host_len.numpy()        # same memory; element-wise tensor writes would cost microseconds each
         self._q, self._k, self._v, self._len = views(self.dev_in)
         for i, layer in enumerate(layers):
             layer.bind_lengths(self._len[i])
@@ -69,12 +70,14 @@ class DecodeStepGraph:
         """Run one token: ``host_q / host_k / host_v`` hold the new rows of every layer; returns ``host_out``
         ([layers, B, H_Q, 1, D], valid after the stream has been synchronised)."""
         from .d_stage_kv_cache import GROUP_SIZE
-        flush = any(l.next_step_flushes() for l in self.layers)
-        for i, layer in enumerate(self.layers):
-            nq, ns = layer.step_lengths()
-            if layer.next_step_flushes():      # that layer appends, quantises its 128 staged tokens, then attends
-                nq, ns = nq + GROUP_SIZE, 0
-            self._host_len[i, 0], self._host_len[i, 1] = nq, ns
+        flush = False
+        lens = []
+        for layer in self.layers:
+            nq, ns = layer._n_quant, layer._staging_ptr
+            if ns >= GROUP_SIZE - 1:           # that layer appends, quantises its 128 staged tokens, then attends
+                nq, ns, flush = nq + GROUP_SIZE, 0, True
+            lens.append((nq, ns))
+        self._host_len_np[:] = lens
         if flush or not self._warm:
             self._eager()
             self._warm = True
