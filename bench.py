@@ -478,6 +478,35 @@ def bench_prefill_heads(torch, hq, dev, rank, world, dist, n=32768):
             "tflops_all_ranks": round(flops / float(ms[0]) / 1e9, 1)}
 
 
+def measure_tensor_peaks(torch, dev):
+    """TFLOP/s (TOP/s) of this GPU's tcgen05 pipe for kind::i8, kind::f8f6f4 (e4m3) and kind::f16 (bf16), from the
+    library's probe kernel: products issued back to back on every SM with the operands resident in shared memory (no
+    loads, no epilogue) - an upper bound measured here rather than a nominal figure.  Median of 5 launches of ~1 ms."""
+    import ctypes as C
+    from hyquant_b200 import _lib
+    lib = _lib.lib()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    sms = C.c_int(0)
+    out = {}
+    for kind, name, kdim in ((0, "i8", 128), (1, "f8f6f4_e4m3", 128), (2, "f16_bf16", 64)):
+        steps = 4096
+        st = _lib.stream_ptr(dev)
+        _lib.check(lib.hq_tc_peak(kind, 256, status.data_ptr(), C.byref(sms), st), "hq_tc_peak")
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(lib.hq_tc_peak(kind, steps, status.data_ptr(), C.byref(sms), st), "hq_tc_peak")
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = float(np.median(times))
+        out[name] = round(sms.value * steps * 2.0 * 128 * 256 * kdim / ms / 1e9, 1)
+    out["status"] = int(status.item())
+    out["how"] = "tcgen05.mma 128x256 products back to back on every SM, operands in shared memory, accumulators in tensor memory"
+    return out
+
+
 # ---------------------------------------------------------------------------
 # the reference's own kernels on this GPU (Triton, compiled for sm_100 by the installed Triton)
 # ---------------------------------------------------------------------------
@@ -665,6 +694,7 @@ def run_ours(args):
         layers.append(layer); qs.append(qd)
     call_bytes = layer_bytes(layers[0], B * H_Q)
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()      # a profiler started with its collection off (e.g. ncu --profile-from-start off) begins here, after the set-up
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -717,7 +747,9 @@ def run_ours(args):
             del ls, qq
         del flush
     prefill = []
+    tensor_peaks = None
     if rank == 0 and not args.no_prefill:
+        tensor_peaks = measure_tensor_peaks(torch, dev)
         from hyquant_b200.synth import gen_torch
         from hyquant_b200.sage_unified import PrefillPlan
         bf16_peak = None
@@ -767,6 +799,10 @@ def run_ours(args):
             prefill.append({"seq": n, "ms": round(ms_, 3), "tflops": round(plan.flops / ms_ / 1e9, 1),
                             "sage_fp8_attention_ms": pv,
                             "frac_of_measured_bf16_sustained": None if not bf16_peak else round(plan.flops / ms_ / 1e9 / bf16_peak, 3),
+                            # INT8 Q K^T and BF16 P V are half of the flops each: the time the two pipes would need at their
+                            # measured probe rates is the bound this fraction is taken against
+                            "frac_of_measured_i8_qk_bf16_pv_bound": round(
+                                (0.5 * plan.flops / tensor_peaks["i8"] + 0.5 * plan.flops / tensor_peaks["f16_bf16"]) / 1e9 / ms_, 3),
                             "ms_with_selection_and_preparation": round(ms_all, 3),
                             "tflops_with_selection_and_preparation": round(plan.flops / ms_all / 1e9, 1),
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
@@ -816,6 +852,7 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "sweep": sweep,
             "prefill": prefill,
+            "tensor_pipe_peaks_measured": tensor_peaks,
             "bit_width_decode": bit_widths,
             "batched_decode": batched,
             "long_context_decode": long_ctx,
@@ -831,9 +868,10 @@ def run_ours(args):
         raise SystemExit(f"sharded result differs from the single-GPU result (or a peer wait ran out) in: {bad}")
 
 
-# DRAM bytes per launch of the decode kernel from an ncu capture of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum, profiles/decode_splitk_cfg1_32k.md)
-TRAFFIC_BYTES_PER_LAUNCH = 40289792
+# DRAM bytes per launch of the decode kernel from an ncu capture of this workload (dram__bytes_read.sum +
+# dram__bytes_write.sum of hq::decode_splitk_kernel<1, true, 4, 4, false>, mean of two launches); to be taken again
+# whenever the kernel's loads change
+TRAFFIC_BYTES_PER_LAUNCH = 40293760
 
 
 def main():

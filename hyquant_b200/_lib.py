@@ -30,7 +30,7 @@ EXPORTS = [
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_quant_blocks", "hq_per_block_int8",
     "hq_prefill_vertical_prepare", "hq_prefill_transpose_v", "hq_prefill_quant_v_fp8",
-    "hq_prefill_hybrid",
+    "hq_prefill_hybrid", "hq_tc_peak",
     "hq_peer_exchange_bytes", "hq_peer_slot", "hq_peer_recv_slot", "hq_peer_exchange_merge", "hq_peer_status",
     "hq_peer_buffer_create", "hq_peer_buffer_open", "hq_peer_buffer_close", "hq_peer_buffer_destroy",
 ]
@@ -123,6 +123,7 @@ def _declare(lib):
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
     lib.hq_prefill_quant_v_fp8.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
+    lib.hq_tc_peak.argtypes = [i32, i32, vp, C.POINTER(C.c_int), vp]
     lib.hq_peer_exchange_bytes.argtypes = [i32, i32, C.POINTER(i64)]
     lib.hq_peer_slot.argtypes = [vp, i32, i32, C.c_uint32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
     lib.hq_peer_recv_slot.argtypes = [vp, i32, i32, C.c_uint32, i32, C.POINTER(vp)]

@@ -371,7 +371,10 @@ class DStageLayerCache:
 
 
 class DStageKVCache(_HF_Cache):
-    """HF-compatible KV cache with D-stage quantisation (reference :360-494)."""
+    """The Hugging Face ``Cache`` surface of the reference's ``DStageKVCache`` (src/ops/d_stage_kv_cache.py:360-494),
+    taken over method by method because generation code and the patched forwards call it by these names (``update``,
+    ``get_seq_length``, ``get_mask_sizes``, ``get_layer``, ``crop`` ...).  It holds no algorithm: every layer is a
+    :class:`DStageLayerCache`, whose freeze / append / attention run on this library's kernels."""
 
     is_compileable = False
 

@@ -61,49 +61,58 @@ def validate_patch_args(mode: str, window_size: int, top_ratio: float,
     return mode
 
 
+# Small Hugging Face glue the patched forwards need; names, arguments and results follow the reference's helpers
+# (src/patch/_common.py:80-141) so that code written against them keeps working.
+
 def repeat_interleave_manual(x: torch.Tensor, repeats: int, dim: int) -> torch.Tensor:
+    """Each slice along ``dim`` ``repeats`` times in a row (GQA expansion of K / V heads), as a contiguous tensor."""
     if repeats == 1:
         return x
-    x_exp = x.unsqueeze(dim + 1)
-    expanded = x_exp.expand(*x.shape[:dim], x.shape[dim], repeats, *x.shape[dim + 1:])
-    return expanded.reshape(*x.shape[:dim], x.shape[dim] * repeats, *x.shape[dim + 1:]).contiguous()
+    shape = list(x.shape)
+    expanded = x.unsqueeze(dim + 1).expand(*shape[:dim + 1], repeats, *shape[dim + 1:])
+    shape[dim] *= repeats
+    return expanded.reshape(shape).contiguous()
 
 
 def infer_kv_repeat(attn_module: torch.nn.Module) -> int:
-    """Reference _common.py:91-99."""
-    if hasattr(attn_module, "num_key_value_groups") and attn_module.num_key_value_groups is not None:
-        return max(int(attn_module.num_key_value_groups), 1)
-    if hasattr(attn_module, "num_heads") and hasattr(attn_module, "num_key_value_heads"):
-        return max(int(attn_module.num_heads) // max(int(attn_module.num_key_value_heads), 1), 1)
+    """Query heads per KV head of an attention module: its ``num_key_value_groups`` if it has one, else the ratio of
+    its head counts, else 1."""
+    groups = getattr(attn_module, "num_key_value_groups", None)
+    if groups is not None:
+        return max(1, int(groups))
+    heads, kv_heads = getattr(attn_module, "num_heads", None), getattr(attn_module, "num_key_value_heads", None)
+    if heads is not None and kv_heads is not None:
+        return max(1, int(heads) // max(1, int(kv_heads)))
     return 1
 
 
 def resolve_attention_interface(config: Any, eager_attention_forward: Callable[..., Any], *,
                                 output_attentions: bool = False) -> Callable[..., Any]:
-    implementation = getattr(config, "_attn_implementation", "eager")
-    if implementation == "eager":
-        return eager_attention_forward
-    if implementation == "sdpa" and output_attentions:
+    """The attention function transformers would use for ``config``; eager when it is asked for, when attention weights
+    are wanted from sdpa, or when the registry is not available."""
+    name = getattr(config, "_attn_implementation", "eager")
+    if name == "eager" or (name == "sdpa" and output_attentions):
         return eager_attention_forward
     try:
-        from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+        from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS as registry
     except Exception:
         return eager_attention_forward
-    return ALL_ATTENTION_FUNCTIONS.get(implementation, eager_attention_forward)
+    return registry.get(name, eager_attention_forward)
 
 
 def pop_past_key_value_aliases(past_key_value: Any, kwargs: dict) -> Any:
-    if past_key_value is None and "past_key_values" in kwargs:
-        past_key_value = kwargs.pop("past_key_values")
-    if past_key_value is None and "past_key_value" in kwargs:
-        past_key_value = kwargs.pop("past_key_value")
+    """The cache object, whichever keyword the transformers version passes it under (the alias is removed from kwargs)."""
+    for alias in ("past_key_values", "past_key_value"):
+        if past_key_value is None and alias in kwargs:
+            past_key_value = kwargs.pop(alias)
     return past_key_value
 
 
 def trim_4d_attention_mask(attention_mask: Any, key_states: Any) -> Any:
-    if attention_mask is not None and getattr(attention_mask, "ndim", None) == 4:
-        return attention_mask[:, :, :, : key_states.shape[-2]]
-    return attention_mask
+    """A 4-D mask cut to the key length; anything else is passed through."""
+    if attention_mask is None or getattr(attention_mask, "ndim", None) != 4:
+        return attention_mask
+    return attention_mask[..., : key_states.shape[-2]]
 
 
 # ----------------------------------------------------------------------------

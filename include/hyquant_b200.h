@@ -397,6 +397,14 @@ int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
 int hq_prefill_quant_v_fp8(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
                            void* v_t8, float* v_scale, void* amax_scratch, void* stream);
 
+/* --------------------------------------------------------------------------
+ * Tensor-pipe peak probe (no counterpart in the reference): runs tcgen05.mma products of `kind` (0 = kind::i8,
+ * 1 = kind::f8f6f4 on e4m3, 2 = kind::f16 on bf16) back to back on every SM, operands resident in shared memory,
+ * accumulators in tensor memory.  One launch does sms * steps products of 128 x 256 x K (K = 128 for the 8-bit kinds,
+ * 64 for bf16); the caller times it.  The benchmark uses the result as the measured denominator of the prefill
+ * kernel's tensor-pipe fraction.  status: device word, zeroed by the caller; bit 2 = a bounded wait expired. */
+int hq_tc_peak(int kind, int steps, int* status, int* sms_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,7 +24,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("HYQUANT_REFERENCE", "/root/reference")
+REF = os.environ.get("HYQUANT_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "src", "ops")):
+    sys.exit("set HYQUANT_REFERENCE to a checkout of the reference (the directory that holds src/ops)")
 sys.path.insert(0, REF)
 os.environ["HYBRID_ATTN_DECODE_KERNEL"] = "pytorch"
 
