@@ -29,7 +29,7 @@ EXPORTS = [
     "hq_topk",
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_quant_blocks", "hq_per_block_int8",
-    "hq_prefill_vertical_prepare", "hq_prefill_transpose_v", "hq_prefill_quant_v_fp8",
+    "hq_prefill_vertical_prepare", "hq_prefill_transpose_v", "hq_prefill_quant_v_fp8", "hq_prefill_vertical_gather_v_fp8",
     "hq_prefill_hybrid", "hq_tc_peak",
     "hq_peer_exchange_bytes", "hq_peer_slot", "hq_peer_recv_slot", "hq_peer_exchange_merge", "hq_peer_status",
     "hq_peer_buffer_create", "hq_peer_buffer_open", "hq_peer_buffer_close", "hq_peer_buffer_destroy",
@@ -60,6 +60,8 @@ class DecodeArgs(C.Structure):
         ("peer_bufs", C.c_void_p), ("peer_world", C.c_int32), ("peer_rank", C.c_int32), ("peer_seq", C.c_uint32),
         ("peer_reserved", C.c_int32), ("peer_timeout_ns", C.c_int64),
         ("lengths", C.c_void_p),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("rope_stride", C.c_int64),
+        ("rope_heads_per_batch", C.c_int32), ("rope_reserved", C.c_int32),
     ]
 
 
@@ -76,6 +78,7 @@ class PrefillArgs(C.Structure):
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_sn", C.c_int64),
         ("status", C.c_void_p),
         ("v_t8", C.c_void_p), ("v_scale8", C.c_void_p), ("pv_fp8", C.c_int32), ("reserved0", C.c_int32),
+        ("vert_vt8", C.c_void_p),
     ]
 
 
@@ -122,6 +125,7 @@ def _declare(lib):
                                                 vp, vp, vp, vp, vp, vp]
     lib.hq_prefill_transpose_v.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp]
     lib.hq_prefill_quant_v_fp8.argtypes = [vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]
+    lib.hq_prefill_vertical_gather_v_fp8.argtypes = [vp, i32, i32, i32, i32, i32, vp, i64, i64, i64, vp, vp, vp]
     lib.hq_prefill_hybrid.argtypes = [C.POINTER(PrefillArgs), vp]
     lib.hq_tc_peak.argtypes = [i32, i32, vp, C.POINTER(C.c_int), vp]
     lib.hq_peer_exchange_bytes.argtypes = [i32, i32, C.POINTER(i64)]

@@ -93,6 +93,8 @@ struct DecodeParams {
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
   int overlap;                            // launched with programmatic stream serialisation
   const int* lengths;                     // device {n_quant, n_staging} overriding the values above (or null)
+  const __nv_bfloat16* rope_cos; const __nv_bfloat16* rope_sin;   // [batch, 128] rotary factors of the step (or null)
+  int64_t rope_stride; int heads_per_batch;
   int* status; int* counters;             // workspace
   float* ws_m; float* ws_l; float* ws_acc;
 };
@@ -145,6 +147,7 @@ struct Unit {
   int kind;       // 0 = quantised, 1 = BF16
   int ntok;       // valid tokens
   int tok0;       // first token within its segment
+  int seg;        // BF16 units: 0 vertical lines, 1 staging, 2 window, 3 the step's new token
 };
 
 // The lengths that change from step to step.  They come with the launch (host values) or, when the call names a device
@@ -160,7 +163,7 @@ __device__ __forceinline__ Unit unit_of(const DecodeParams& p, const Lens& L, in
   Unit r;
   if (u < L.uq) {
     constexpr int kUnitQ = Fmt<KB, VB>::kUnitQ;
-    r.kind = 0; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, L.n_quant - r.tok0);
+    r.kind = 0; r.seg = -1; r.tok0 = u * kUnitQ; r.ntok = min(kUnitQ, L.n_quant - r.tok0);
     r.k = p.k_packed + head * p.kp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowK;
     r.v = p.v_packed + head * p.vp_stride_bh + (int64_t)r.tok0 * Fmt<KB, VB>::kRowV;
     return r;
@@ -171,7 +174,7 @@ __device__ __forceinline__ Unit unit_of(const DecodeParams& p, const Lens& L, in
     u -= p.useg[0]; s = 1;
     if (u >= L.useg1) { u -= L.useg1; s = 2; if (u >= p.useg[2]) { u -= p.useg[2]; s = 3; } }
   }
-  r.kind = 1; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, (s == 1 ? L.n_stg : p.nseg[s]) - r.tok0);
+  r.kind = 1; r.seg = s; r.tok0 = u * kUnitB; r.ntok = min(kUnitB, (s == 1 ? L.n_stg : p.nseg[s]) - r.tok0);
   r.k = reinterpret_cast<const uint8_t*>(p.kseg[s] + head * p.kseg_stride[s] + (int64_t)r.tok0 * 128);
   r.v = reinterpret_cast<const uint8_t*>(p.vseg[s] + head * p.vseg_stride[s] + (int64_t)r.tok0 * 128);
   return r;
@@ -392,6 +395,20 @@ __device__ __forceinline__ void peer_receive_all(const DecodeParams& p, float* s
   if (expired) atomicOr(reinterpret_cast<int*>(g.bufs[g.rank]), 2);
 }
 
+// Rotary position embedding as Hugging Face models apply it (rotate_half form, the arithmetic of apply_rotary_pos_emb
+// that the reference's patched forwards call before the cache, src/patch/patch_llama.py:58-65): out = x cos + rot sin with
+// rot[d] = -x[d + 64] for d < 64 and x[d - 64] otherwise, every product and the sum rounded to bf16 as eager bf16
+// arithmetic does.  `x`, `other`: two bf16 values each (this channel pair and the pair 64 channels away); `neg`: this pair is in
+// the lower half.
+__device__ __forceinline__ uint32_t rope_pair(uint32_t x, uint32_t other, uint32_t cs, uint32_t sn, bool neg) {
+  auto lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+  auto hi = [](uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); };
+  auto rb = [](float f) { return __bfloat162float(__float2bfloat16_rn(f)); };
+  const float r0 = neg ? -lo(other) : lo(other), r1 = neg ? -hi(other) : hi(other);
+  const float o0 = rb(rb(lo(x) * lo(cs)) + rb(r0 * lo(sn))), o1 = rb(rb(hi(x) * hi(cs)) + rb(r1 * hi(sn)));
+  return pack_bf16x2(o0, o1);
+}
+
 // ---- the kernel -------------------------------------------------------------
 
 // The four 16-bit-lane fields of a word as fp16 subnormals, offset binary: result k = ((nibble k) ^ 8) * 2^-24 for k = 0, 2
@@ -546,6 +563,14 @@ decode_splitk_kernel(const DecodeParams p) {
       qraw[k] = make_uint2(0u, 0u);
       if (hd < kQItems && hd < p.R)
         qraw[k] = __ldg(reinterpret_cast<const uint2*>(p.q + (int64_t)(head * p.R + hd) * p.q_stride) + lane);
+      if (p.rope_cos != nullptr) {     // the query arrives unrotated: this lane's channels 4 lane .. + 3 pair with lane ^ 16's
+        const int64_t ro = (int64_t)(head / p.heads_per_batch) * p.rope_stride;
+        const uint2 cs = __ldg(reinterpret_cast<const uint2*>(p.rope_cos + ro) + lane);
+        const uint2 sn = __ldg(reinterpret_cast<const uint2*>(p.rope_sin + ro) + lane);
+        const uint32_t ox = __shfl_xor_sync(0xffffffffu, qraw[k].x, 16), oy = __shfl_xor_sync(0xffffffffu, qraw[k].y, 16);
+        qraw[k].x = rope_pair(qraw[k].x, ox, cs.x, sn.x, lane < 16);
+        qraw[k].y = rope_pair(qraw[k].y, oy, cs.y, sn.y, lane < 16);
+      }
     }
   };
   if (!p.overlap) {
@@ -566,7 +591,20 @@ decode_splitk_kernel(const DecodeParams p) {
     const __nv_bfloat16* src = (lane < 16 ? p.kseg[3] : p.vseg[3]) + head * (lane < 16 ? p.kseg_stride[3] : p.vseg_stride[3]);
     __nv_bfloat16* dst = (lane < 16 ? p.stage_k : p.stage_v) + head * (lane < 16 ? p.kseg_stride[1] : p.vseg_stride[1]) +
                          (int64_t)L.n_stg * 128;
-    reinterpret_cast<uint4*>(dst)[lane & 15] = __ldg(reinterpret_cast<const uint4*>(src) + (lane & 15));
+    uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + (lane & 15));
+    if (p.rope_cos != nullptr) {       // the new K row is stored rotated (lanes 0..15 hold it, 8 channels each; V is left alone)
+      const int64_t ro = (int64_t)(head / p.heads_per_batch) * p.rope_stride;
+      const uint4 cs = __ldg(reinterpret_cast<const uint4*>(p.rope_cos + ro) + (lane & 15));
+      const uint4 sn = __ldg(reinterpret_cast<const uint4*>(p.rope_sin + ro) + (lane & 15));
+      const uint4 o = make_uint4(__shfl_xor_sync(0xffffffffu, w.x, 8), __shfl_xor_sync(0xffffffffu, w.y, 8),
+                                 __shfl_xor_sync(0xffffffffu, w.z, 8), __shfl_xor_sync(0xffffffffu, w.w, 8));
+      if (lane < 16) {
+        const bool neg = lane < 8;
+        w = make_uint4(rope_pair(w.x, o.x, cs.x, sn.x, neg), rope_pair(w.y, o.y, cs.y, sn.y, neg),
+                       rope_pair(w.z, o.z, cs.z, sn.z, neg), rope_pair(w.w, o.w, cs.w, sn.w, neg));
+      }
+    }
+    reinterpret_cast<uint4*>(dst)[lane & 15] = w;
   }
 
   // ---- 3. query fragments (B operands of S^T = K Q^T) scattered straight into fragment
@@ -934,6 +972,15 @@ decode_splitk_kernel(const DecodeParams p) {
           reinterpret_cast<uint4*>(Ks + un.ntok * 256)[x] = make_uint4(0, 0, 0, 0);
           reinterpret_cast<uint4*>(Vs + un.ntok * 256)[x] = make_uint4(0, 0, 0, 0);
         }
+        if (un.seg == 3 && p.rope_cos != nullptr) {     // the new token's K row came as the caller has it: rotate it here
+          const int64_t ro = (int64_t)(head / p.heads_per_batch) * p.rope_stride;
+          const uint2 cs = __ldg(reinterpret_cast<const uint2*>(p.rope_cos + ro) + lane);
+          const uint2 sn = __ldg(reinterpret_cast<const uint2*>(p.rope_sin + ro) + lane);
+          const uint2 mine = reinterpret_cast<const uint2*>(Ks)[lane], other = reinterpret_cast<const uint2*>(Ks)[lane ^ 16];
+          __syncwarp();
+          reinterpret_cast<uint2*>(Ks)[lane] = make_uint2(rope_pair(mine.x, other.x, cs.x, sn.x, lane < 16),
+                                                          rope_pair(mine.y, other.y, cs.y, sn.y, lane < 16));
+        }
         __syncwarp();
       }
       float s[NT][4];
@@ -1298,6 +1345,14 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.out = a->out; p.out_stride = a->out_stride;
   p.pm = a->partial_m; p.pl = a->partial_l; p.pacc = a->partial_acc;
   p.lengths = a->lengths;
+  p.rope_cos = (const __nv_bfloat16*)a->rope_cos; p.rope_sin = (const __nv_bfloat16*)a->rope_sin;
+  p.rope_stride = a->rope_stride; p.heads_per_batch = a->rope_heads_per_batch > 0 ? a->rope_heads_per_batch : 1;
+  HQ_REQUIRE((a->rope_cos == nullptr) == (a->rope_sin == nullptr), HQ_ERR_INVALID, "hq_decode_splitk: rope_cos and rope_sin go together");
+  if (a->rope_cos != nullptr) {
+    HQ_REQUIRE(aligned16(a->rope_cos) && aligned16(a->rope_sin) && a->rope_stride % 8 == 0 && a->rope_heads_per_batch > 0 &&
+                   a->BH_KV % a->rope_heads_per_batch == 0, HQ_ERR_INVALID,
+               "hq_decode_splitk: rotary factors must be 16-byte aligned rows, rope_heads_per_batch must divide BH_KV");
+  }
   HQ_REQUIRE(a->lengths == nullptr || (((uintptr_t)a->lengths & 3) == 0 && a->k_staging && a->v_staging), HQ_ERR_INVALID,
              "hq_decode_splitk: lengths must be 4-byte aligned and needs the staging buffers");
   p.peer.world = 0;

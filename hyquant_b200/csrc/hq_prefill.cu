@@ -57,6 +57,19 @@ int prefill_tc_prepare_vertical(const int32_t* vasc, int B, int H_Q, int H_KV, i
                                 int64_t v_sb, int64_t v_sh, int64_t v_sn, void* xk, void* xvt, cudaStream_t st);
 int prefill_tc_prepare_v_fp8(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t8, float* v_scale,
                              void* amax_scratch, cudaStream_t st);
+int prefill_tc_gather_v_fp8(const int32_t* vasc, int B, int H_Q, int H_KV, int N, int T, const void* v, int64_t v_sb, int64_t v_sh,
+                            int64_t v_sn, const float* v_scale, void* xvt8, cudaStream_t st);
+}
+
+extern "C" int hq_prefill_vertical_gather_v_fp8(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int T, const void* v,
+                                                int64_t v_sb, int64_t v_sh, int64_t v_sn, const float* v_scale, void* vert_vt8,
+                                                void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(vidx_asc && v && v_scale && vert_vt8 && B > 0 && H_Q > 0 && H_KV > 0 && N > 0 && T > 0 && H_Q % H_KV == 0, HQ_ERR_INVALID,
+             "hq_prefill_vertical_gather_v_fp8: bad arguments");
+  HQ_REQUIRE(aligned16(v) && aligned16(vert_vt8) && v_sb % 8 == 0 && v_sh % 8 == 0 && v_sn % 8 == 0, HQ_ERR_ALIGNMENT,
+             "hq_prefill_vertical_gather_v_fp8: rows must be 16-byte aligned");
+  return prefill_tc_gather_v_fp8(vidx_asc, B, H_Q, H_KV, N, T, v, v_sb, v_sh, v_sn, v_scale, vert_vt8, (cudaStream_t)stream);
 }
 
 extern "C" int hq_prefill_quant_v_fp8(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
@@ -110,11 +123,11 @@ extern "C" int hq_prefill_hybrid(const hq_prefill_args* a, void* stream) {
              HQ_ERR_INVALID, "hq_prefill_hybrid: null pointer");
   if (a->pv_fp8) {
     HQ_REQUIRE(a->v_t8 && a->v_scale8 && aligned16(a->v_t8), HQ_ERR_INVALID, "hq_prefill_hybrid: FP8 P V needs v_t8 (16-byte aligned) and v_scale8");
-    HQ_REQUIRE(a->T == 0, HQ_ERR_UNSUPPORTED, "hq_prefill_hybrid: FP8 P V is built without vertical lines (T must be 0)");
+    HQ_REQUIRE(a->T == 0 || (a->vert_vt8 && aligned16(a->vert_vt8)), HQ_ERR_INVALID, "hq_prefill_hybrid: FP8 P V with vertical lines needs vert_vt8");
   } else {
     HQ_REQUIRE(a->v_t != nullptr, HQ_ERR_INVALID, "hq_prefill_hybrid: v_t is null");
   }
-  HQ_REQUIRE(a->T == 0 || (a->vert_k && a->vert_vt && a->nv_valid), HQ_ERR_INVALID,
+  HQ_REQUIRE(a->T == 0 || (a->vert_k && (a->vert_vt || a->pv_fp8) && a->nv_valid), HQ_ERR_INVALID,
              "hq_prefill_hybrid: vertical arguments missing");
   HQ_REQUIRE(aligned16(a->q_i8) && aligned16(a->q_bf) && aligned16(a->k_i8) && aligned16(a->k_bf) && (a->pv_fp8 || aligned16(a->v_t)) &&
                  aligned16(a->k_scale) && aligned16(a->k_bias) && aligned16(a->out) && a->o_sn % 8 == 0 && a->o_sh % 8 == 0 && a->o_sb % 8 == 0,

@@ -682,8 +682,11 @@ int prefill_tc_launch(const hq_prefill_args* a, cudaStream_t st) {
                             (uint64_t)Npad * 4, 64, 1, false))) return rc;
   if (T > 0) {
     if ((rc = tc::make_map_2d(&mXk, a->vert_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, (uint64_t)a->B * a->H_Q * Tpad, 256, 64, 64))) return rc;
-    if ((rc = tc::make_map_2d(&mXv, a->vert_vt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Tpad, (uint64_t)a->B * a->H_Q * 128,
-                              (uint64_t)Tpad * 2, 64, 128))) return rc;
+    if (fp8) {
+      if ((rc = tc::make_map_2d(&mXv, a->vert_vt8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)Tpad, (uint64_t)a->B * a->H_Q * 128,
+                                (uint64_t)Tpad, 64, 128, 64))) return rc;
+    } else if ((rc = tc::make_map_2d(&mXv, a->vert_vt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Tpad, (uint64_t)a->B * a->H_Q * 128,
+                                     (uint64_t)Tpad * 2, 64, 128))) return rc;
   } else {
     mXk = mKb; mXv = mVt;
   }
@@ -754,6 +757,50 @@ transpose_v_fp8_kernel(const __nv_bfloat16* __restrict__ v, int64_t sb, int64_t 
                              tile[k16 + 4 * j + 3][d] * recip);
     *reinterpret_cast<uint4*>(vt8 + ((int64_t)bh * 128 + d) * Npad + key0 + k16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
+}
+
+// gathered vertical-line rows of V for FP8 P V: xvt8 [B,H_Q,128,Tpad] e4m3 (transposed; columns >= T zero), quantised with
+// the kv-head's channel scales like the rest of V
+__global__ void __launch_bounds__(256)
+vertical_gather_v_fp8_kernel(const int* __restrict__ vasc, int T, int Tpad, int N, int H_Q, int H_KV,
+                             const __nv_bfloat16* __restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sn,
+                             const float* __restrict__ v_scale, uint8_t* __restrict__ xvt8) {
+  __shared__ float tile[64][129];
+  const int64_t bhq = blockIdx.y;
+  const int b = (int)(bhq / H_Q), hq = (int)(bhq - (int64_t)b * H_Q), hkv = hq / (H_Q / H_KV);
+  const int j0 = blockIdx.x * 64, tid = threadIdx.x;
+  for (int x = tid; x < 64 * 16; x += 256) {
+    const int r = x >> 4, c = (x & 15) * 8;
+    uint4 vr = make_uint4(0, 0, 0, 0);
+    if (j0 + r < T) {
+      const int src = min(max(vasc[bhq * T + j0 + r], 0), N - 1);
+      vr = __ldg(reinterpret_cast<const uint4*>(v + b * v_sb + hkv * v_sh + (int64_t)src * v_sn + c));
+    }
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&vr);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[r][c + j] = __bfloat162float(e[j]);
+  }
+  __syncthreads();
+  for (int x = tid; x < 128 * 4; x += 256) {
+    const int d = x >> 2, k16 = (x & 3) * 16;
+    const float sc = v_scale[((int64_t)b * H_KV + hkv) * 128 + d];
+    const float recip = sc > 0.f ? 1.f / sc : 0.f;          // 448 / amax, the factor the V codes were formed with
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = tc::pack_e4m3x4(tile[k16 + 4 * j][d] * recip, tile[k16 + 4 * j + 1][d] * recip, tile[k16 + 4 * j + 2][d] * recip,
+                             tile[k16 + 4 * j + 3][d] * recip);
+    *reinterpret_cast<uint4*>(xvt8 + (bhq * 128 + d) * Tpad + j0 + k16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+int prefill_tc_gather_v_fp8(const int32_t* vasc, int B, int H_Q, int H_KV, int N, int T, const void* v, int64_t v_sb, int64_t v_sh,
+                            int64_t v_sn, const float* v_scale, void* xvt8, cudaStream_t st) {
+  const int Tpad = (T + 63) / 64 * 64;
+  vertical_gather_v_fp8_kernel<<<dim3(Tpad / 64, B * H_Q), 256, 0, st>>>(vasc, T, Tpad, N, H_Q, H_KV, (const __nv_bfloat16*)v, v_sb,
+                                                                        v_sh, v_sn, v_scale, (uint8_t*)xvt8);
+  HQ_CUDA(cudaGetLastError());
+  return HQ_OK;
 }
 
 int prefill_tc_prepare_v_fp8(const void* v, int64_t sb, int64_t sh, int64_t sn, int B, int H_KV, int N, void* v_t8, float* v_scale,

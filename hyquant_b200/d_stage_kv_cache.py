@@ -289,21 +289,41 @@ class DStageLayerCache:
             return None
         return out if out is not None else res.reshape(B_, H_Q_, 1, D_)
 
+    @staticmethod
+    def _rope_eager(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """x cos + rotate_half(x) sin in x's dtype, as Hugging Face's apply_rotary_pos_emb does ([B, H, 1, D] with [B, D])."""
+        half = x.shape[-1] // 2
+        rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+        return (x * cos[:, None, None, :]) + (rot * sin[:, None, None, :])
+
     def decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
-                    kv_repeat: int, *, out: Optional[torch.Tensor] = None, partial=None, peer=None) -> torch.Tensor:
+                    kv_repeat: int, *, out: Optional[torch.Tensor] = None, partial=None, peer=None, rope=None) -> torch.Tensor:
         """``append_staging(key_states, value_states)`` followed by ``decode_attention(query_states, kv_repeat)``
         (reference :195-303) as one kernel launch: the decode kernel attends to the new token from where it
         is and stores it into its staging slot on the way.  Same result as the two calls up to the order of
         the fp32 partial sums.  The step that fills the staging buffer takes the two-call route, because the
-        reference flushes (quantises the 128 staged tokens) before that step's attention."""
+        reference flushes (quantises the 128 staged tokens) before that step's attention.
+
+        ``rope=(cos, sin)`` (not in the reference, whose patched forwards rotate q and k with separate eager kernels before
+        the cache, src/patch/patch_llama.py:58-65): bf16 ``[B, D]`` or ``[B, 1, D]`` rotary factors of this step's position;
+        ``query_states`` and ``key_states`` are then given UNROTATED and the kernel rotates them itself."""
         B, H_KV, S, D = key_states.shape
+        cos = sin = None
+        if rope is not None:
+            cos, sin = (t.reshape(B, D) for t in rope)
         fused = (S == 1 and self._staging_ptr < GROUP_SIZE - 1
                  and key_states.dtype == torch.bfloat16 and value_states.dtype == torch.bfloat16
                  and self._staging_buf_k.dtype == torch.bfloat16 and key_states.stride(3) == 1 and value_states.stride(3) == 1)
         if fused:
             k2, v2 = key_states.reshape(B * H_KV, D), value_states.reshape(B * H_KV, D)
             fused = (k2.data_ptr() % 16 == 0 and v2.data_ptr() % 16 == 0 and k2.stride(0) % 8 == 0 and v2.stride(0) % 8 == 0)
+            if fused and cos is not None:
+                fused = (cos.dtype == torch.bfloat16 and sin.dtype == torch.bfloat16 and cos.stride(1) == 1 and sin.stride(1) == 1
+                         and cos.stride(0) == sin.stride(0) and cos.stride(0) % 8 == 0 and cos.data_ptr() % 16 == 0
+                         and sin.data_ptr() % 16 == 0 and query_states.dtype == torch.bfloat16)
         if not fused:
+            if cos is not None:
+                query_states, key_states = self._rope_eager(query_states, cos, sin), self._rope_eager(key_states, cos, sin)
             self.append_staging(key_states, value_states)
             return self.decode_attention(query_states, kv_repeat, out=out, partial=partial, peer=peer)
         B_, H_Q_, _, D_ = query_states.shape
@@ -311,10 +331,13 @@ class DStageLayerCache:
         plan = self._decode_plan(q2d, kv_repeat)
         a = plan.args
         a.k_new, a.v_new, a.kn_stride, a.vn_stride = k2.data_ptr(), v2.data_ptr(), k2.stride(0), v2.stride(0)
+        if cos is not None:
+            a.rope_cos, a.rope_sin, a.rope_stride, a.rope_heads_per_batch = cos.data_ptr(), sin.data_ptr(), cos.stride(0), H_KV
         try:
             res = plan.run(q2d, out=None if out is None else out.view(B_ * H_Q_, D_), partial=partial, peer=peer)
         finally:
             a.k_new = a.v_new = None
+            a.rope_cos = a.rope_sin = None
         self._staging_ptr += 1
         self._seq_len += 1
         if partial is not None:

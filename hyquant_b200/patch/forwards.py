@@ -45,6 +45,9 @@ def build_attention_forward(family: str, *, mode: str, window_size: int, top_rat
     apply_rotary_pos_emb = modeling.apply_rotary_pos_emb
     eager_attention_forward = modeling.eager_attention_forward
     del use_vertical_indices
+    # Llama and Qwen3 rotate with the half-split rotate_half over the whole head, which the decode kernel can apply itself;
+    # GLM-4's interleaved partial rotation stays on the eager path
+    fuse_rope = family in ("llama", "qwen")
 
     def patched_attention_forward(self, hidden_states: torch.Tensor, position_embeddings=None,
                                   attention_mask: Optional[torch.Tensor] = None, past_key_values: Optional[object] = None,
@@ -66,15 +69,20 @@ def build_attention_forward(family: str, *, mode: str, window_size: int, top_rat
         query_states, key_states = q.transpose(1, 2), k.transpose(1, 2)
         value_states = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
         cos, sin = position_embeddings
-        query_states, key_states = apply_rotary_pos_emb(query_states, key_states, cos, sin)
-
         q_len = int(query_states.shape[2])
         has_d_cache = (d_stage_decode and mode in D_STAGE_MODES and past_key_values is not None
                        and is_d_stage_cache(past_key_values))
         fused_step = None
+        rope_in_kernel = False
         if has_d_cache and q_len == 1 and past_key_values.get_layer(self.layer_idx).phase == "decode":
-            # decode step on a frozen cache: append + attention in one launch (DStageLayerCache.decode_step)
+            # decode step on a frozen cache: rotary embedding (where the family's form allows), append and attention in one
+            # launch (DStageLayerCache.decode_step with rope=); q and k then stay unrotated here
             fused_step = past_key_values.get_layer(self.layer_idx)
+            rope_in_kernel = fuse_rope and query_states.dtype == torch.bfloat16 and cos.shape[-1] == 128
+        if not rope_in_kernel:
+            query_states, key_states = apply_rotary_pos_emb(query_states, key_states, cos, sin)
+        if fused_step is not None:
+            pass
         elif has_d_cache:
             key_states, value_states = handle_d_stage_cache(self.layer_idx, past_key_values, query_states, key_states,
                                                             value_states, self, sin, cos, cache_position)
@@ -100,7 +108,8 @@ def build_attention_forward(family: str, *, mode: str, window_size: int, top_rat
                 raise HyQuantError(f"mode '{mode}' decodes against a DStageKVCache; pass one as past_key_values "
                                    "(the cache-less quantise/dequantise emulation is not built)")
             if fused_step is not None:
-                attn_output = finish(fused_step.decode_step(query_states, key_states, value_states, kv_repeat))
+                attn_output = finish(fused_step.decode_step(query_states, key_states, value_states, kv_repeat,
+                                                            rope=(cos, sin) if rope_in_kernel else None))
             else:
                 layer_cache = past_key_values.get_layer(self.layer_idx)
                 attn_output = finish(layer_cache.decode_attention(query_states, kv_repeat))

@@ -129,7 +129,7 @@ class PrefillPlan:
                  window_size: int, sm_scale: Optional[float], smooth_k: bool, scale_granularity: Optional[str] = None,
                  pv_fp8: bool = False):
         """``pv_fp8``: the P V product in FP8 E4M3 with the reference's ``sage_fp8_attention`` arithmetic (V^T quantised
-        per channel, P~ = 2^(s - m + 8.807) against the exact running maximum); not built together with vertical lines."""
+        per channel, P~ = 2^(s - m + 8.807) against the exact running maximum), for INT8, window and vertical tiles alike."""
         dtype = q.dtype
         qb, kb, vb, B, H_q, H_kv, N = _prep_inputs(q, k, v)
         dev = q.device
@@ -144,8 +144,6 @@ class PrefillPlan:
         Npad = (N + 63) // 64 * 64
         v_t = v_t8 = v_sc8 = None
         if pv_fp8:
-            if vertical_indices is not None and vertical_indices.shape[-1] > 0:
-                raise HyQuantError("FP8 P V is not built together with vertical lines")
             v_t8 = torch.empty(B, H_kv, 128, Npad, dtype=torch.uint8, device=dev)
             v_sc8 = torch.empty(B, H_kv, 128, dtype=torch.float32, device=dev)
             scratch = torch.empty(B * H_kv * 128, dtype=torch.int32, device=dev)
@@ -173,6 +171,12 @@ class PrefillPlan:
                                              vb.data_ptr(), vb.stride(0), vb.stride(1), vb.stride(2), k_sc.data_ptr(),
                                              ptr(vert_k), ptr(vert_vt), k_bias.data_ptr(), ptr(nvv), st)
         _lib.check(rc, "hq_prefill_vertical_prepare")
+        vert_vt8 = None
+        if pv_fp8 and T:
+            vert_vt8 = torch.empty(B, H_q, 128, (T + 63) // 64 * 64, dtype=torch.uint8, device=dev)
+            rc = lib.hq_prefill_vertical_gather_v_fp8(vasc.data_ptr(), B, H_q, H_kv, N, T, vb.data_ptr(), vb.stride(0), vb.stride(1),
+                                                      vb.stride(2), v_sc8.data_ptr(), vert_vt8.data_ptr(), st)
+            _lib.check(rc, "hq_prefill_vertical_gather_v_fp8")
         out = torch.empty(B, H_q, N, 128, dtype=dtype, device=dev)      # contiguous: rows 16-byte aligned
         a = PrefillArgs()
         a.struct_bytes = C.sizeof(PrefillArgs)
@@ -188,11 +192,13 @@ class PrefillPlan:
             a.v_t = v_t.data_ptr()
         if T:
             a.vert_k, a.vert_vt, a.nv_valid = vert_k.data_ptr(), vert_vt.data_ptr(), nvv.data_ptr()
+            if vert_vt8 is not None:
+                a.vert_vt8 = vert_vt8.data_ptr()
         a.out, a.o_sb, a.o_sh, a.o_sn = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         a.status = self.status.data_ptr()
         self.args, self.out, self.device = a, out, dev
-        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, k_bias, nvv, v_t, v_t8, v_sc8)
+        self._keep = (qb, kb, vb, q_i8, q_bf, q_sc, k_i8, k_bf, k_sc, k_mean, vert_k, vert_vt, k_bias, nvv, v_t, v_t8, v_sc8, vert_vt8)
         self.v_t8, self.v_scale8 = v_t8, v_sc8
         self.flops = 4.0 * B * H_q * 128 * N * (N + 1) / 2
 
@@ -217,10 +223,11 @@ def hybrid_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_i
 
 def sage_vertical_attention_v2(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, vertical_indices: torch.Tensor, *,
                                window_size: int = 256, sm_scale: Optional[float] = None,
-                               smooth_k: bool = True) -> torch.Tensor:
+                               smooth_k: bool = True, pv_fp8: bool = False) -> torch.Tensor:
     """int8 QK for the rest, 16-bit QK for vertical lines + window (reference sage_unified.py:550-622).
-    q [B,H_q,N,D], k/v [B,H_kv,N,D], vertical_indices [B,H_q,T] int64; returns q's dtype."""
-    return hybrid_prefill(q, k, v, vertical_indices, window_size, sm_scale, smooth_k)
+    q [B,H_q,N,D], k/v [B,H_kv,N,D], vertical_indices [B,H_q,T] int64; returns q's dtype.
+    ``pv_fp8`` (not in the reference's signature): the P V product in FP8 E4M3 as in :func:`sage_fp8_attention`."""
+    return hybrid_prefill(q, k, v, vertical_indices, window_size, sm_scale, smooth_k, pv_fp8=pv_fp8)
 
 
 def sage_unified_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, window_size: int = 0,

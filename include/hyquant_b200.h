@@ -171,6 +171,13 @@ typedef struct hq_decode_args {
    * before this one starts (e.g. written by the copy that brings the step's inputs), because an overlapped launch
    * (HQ_DECODE_OVERLAP_PREVIOUS) reads it at once; the staging pointers must be set. */
   const int32_t* lengths;
+  /* Optional: rotary position embedding applied inside the call (rotate_half form, bf16 arithmetic of Hugging Face's
+   * apply_rotary_pos_emb, which the reference's patched forwards run as separate eager kernels before the cache,
+   * src/patch/patch_llama.py:58-65): q and k_new arrive UNROTATED, the kernel rotates the query rows while it loads them
+   * and the new K row both where it attends to it and where it stores it into the staging buffer (V is not rotated).
+   * rope_cos / rope_sin: bf16 [batch, 128], rope_stride elements between batch rows; rope_heads_per_batch = kv heads
+   * per batch entry (head index / rope_heads_per_batch selects the row). */
+  const void* rope_cos; const void* rope_sin; int64_t rope_stride; int32_t rope_heads_per_batch; int32_t rope_reserved;
 } hq_decode_args;
 
 int hq_decode_workspace_bytes(int BH_KV, int kv_repeat, int64_t* bytes);
@@ -379,7 +386,7 @@ typedef struct hq_prefill_args {
   const int32_t* nv_valid;
   void* out; int64_t o_sb, o_sh, o_sn;         /* [B,H_Q,N,128], strides in elements (multiples of 8) */
   int32_t* status;             /* device word, zeroed by the caller; bit 1 = a bounded wait expired */
-  /* FP8 P V (pv_fp8 != 0; T must be 0): P~ = 2^(s - m + 8.807) rounded to e4m3 against the exact running maximum,
+  /* FP8 P V (pv_fp8 != 0): P~ = 2^(s - m + 8.807) rounded to e4m3 against the exact running maximum,
    * V^T as e4m3 with one scale per channel (hq_prefill_quant_v_fp8), the product on tcgen05 kind::f8f6f4, the row sum
    * in fp32 before the cast - the arithmetic of the reference's sage_fp8_attention
    * (src/ops/sage_fp8_attention.py:15-45 -> vendor/sageattention/core_sm90.py:116-165,
@@ -387,6 +394,7 @@ typedef struct hq_prefill_args {
   const void* v_t8;            /* e4m3 [B,H_KV,128,Npad] */
   const float* v_scale8;       /* fp32 [B,H_KV,128] */
   int32_t pv_fp8; int32_t reserved0;
+  const void* vert_vt8;        /* T > 0: e4m3 [B,H_Q,128,Tpad] from hq_prefill_vertical_gather_v_fp8 (vert_vt is not used then) */
 } hq_prefill_args;
 int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
 
@@ -396,6 +404,12 @@ int hq_prefill_hybrid(const hq_prefill_args* args, void* stream);
  *   max_n |v| / 448.  amax_scratch: B * H_KV * 128 * 4 bytes of device scratch (cleared here, in stream). */
 int hq_prefill_quant_v_fp8(const void* v, int64_t v_sb, int64_t v_sh, int64_t v_sn, int B, int H_KV, int N,
                            void* v_t8, float* v_scale, void* amax_scratch, void* stream);
+/* The vertical-line rows of V for FP8 P V: gathered per query head (vidx_asc as for hq_prefill_vertical_prepare),
+ * quantised with the kv head's channel scales (v_scale from hq_prefill_quant_v_fp8), transposed:
+ * vert_vt8 e4m3 [B,H_Q,128,Tpad], columns >= T zero. */
+int hq_prefill_vertical_gather_v_fp8(const int32_t* vidx_asc, int B, int H_Q, int H_KV, int N, int T, const void* v,
+                                     int64_t v_sb, int64_t v_sh, int64_t v_sn, const float* v_scale, void* vert_vt8,
+                                     void* stream);
 
 /* --------------------------------------------------------------------------
  * Tensor-pipe peak probe (no counterpart in the reference): runs tcgen05.mma products of `kind` (0 = kind::i8,

@@ -621,7 +621,8 @@ def per_channel_fp8(v: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
 
 
 def fp8_pv_attention_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray, window_size: int = 0,
-                               sm_scale: Optional[float] = None, smooth_k: bool = True, round_fn=None) -> np.ndarray:
+                               sm_scale: Optional[float] = None, smooth_k: bool = True, round_fn=None,
+                               vertical_indices: Optional[np.ndarray] = None) -> np.ndarray:
     """Causal attention with the FP8 P V arithmetic of the reference's sm_90 kernel: per 64-key tile
     ``m = max(m, rowmax)``; ``P~ = 2^(s - m + 8.807)`` (attn_utils.cuh:30,354-458), row sum in fp32 BEFORE the cast,
     ``P~`` rounded to e4m3 (qk_int_sv_f8_cuda_sm90.cu:310-320), V in e4m3 with one scale per channel
@@ -630,7 +631,10 @@ def fp8_pv_attention_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray, wind
     The scores come from THIS library's Q K^T (the reference's per-thread INT8 granularity belongs to its sm_90 tiling):
     K smoothed; for the 128-query block at s, keys below ``wla(s)`` INT8 with one scale per query row and per key row
     (codes of :func:`quant_per_block_int8` with one-row blocks), keys in ``[wla(s), s + 128)`` in bf16 with the causal
-    mask; tiles of 64 keys in that order.  q [B,H_q,N,D], k/v [B,H_kv,N,D] float32 holding bf16-exact values."""
+    mask; tiles of 64 keys in that order.  With ``vertical_indices`` [B,H_q,T] the head's vertical lines below
+    ``wla(s)`` leave the INT8 tiles and follow them as bf16 tiles of 64 in ascending position (the structure of
+    ``sage_vertical_attention_v2``, sage_unified.py:499-622).  q [B,H_q,N,D], k/v [B,H_kv,N,D] float32 holding
+    bf16-exact values."""
     rf = (lambda a: a) if round_fn is None else round_fn
     B, H_q, N, D = q.shape
     H_kv = k.shape[1]
@@ -654,12 +658,20 @@ def fp8_pv_attention_reference(q: np.ndarray, k: np.ndarray, v: np.ndarray, wind
                 m = np.full(len(rows), -np.inf, dtype=np.float32)
                 l = np.zeros(len(rows), dtype=np.float32)
                 acc = np.zeros((len(rows), D), dtype=np.float32)
-                tiles = [(c0, True) for c0 in range(0, wla, 64)] + [(c0, False) for c0 in range(wla, min(s0 + 128, N), 64)]
-                for c0, is_i8 in tiles:
-                    cols = np.arange(c0, min(c0 + 64, N))
-                    if is_i8:
+                vert = np.zeros(0, dtype=np.int64)
+                if vertical_indices is not None and vertical_indices.shape[-1] > 0 and N - window_size > 0:
+                    vert = np.sort(np.clip(vertical_indices[b, h].astype(np.int64), 0, N - window_size - 1))
+                    vert = vert[vert < wla]
+                tiles = [(np.arange(c0, min(c0 + 64, N)), 0) for c0 in range(0, wla, 64)]
+                tiles += [(vert[j:j + 64], 1) for j in range(0, len(vert), 64)]
+                tiles += [(np.arange(c0, min(c0 + 64, N)), 2) for c0 in range(wla, min(s0 + 128, N), 64)]
+                for cols, kind in tiles:
+                    if kind == 0:
                         dot = q_i8[b, h, rows].astype(np.float32) @ k_i8[b, hk, cols].astype(np.float32).T
                         y = (dot * k_sc[b, hk, cols][None, :]).astype(np.float32) * q_sc[b, h, rows][:, None]
+                        y = np.where(np.isin(cols, vert)[None, :], -np.inf, y).astype(np.float32)
+                    elif kind == 1:
+                        y = (q[b, h, rows].astype(np.float32) @ k_sm[b, hk, cols].T).astype(np.float32) * sml
                     else:
                         y = (q[b, h, rows].astype(np.float32) @ k_sm[b, hk, cols].T).astype(np.float32) * sml
                         y = np.where(rows[:, None] >= cols[None, :], y, -np.inf).astype(np.float32)

@@ -120,3 +120,19 @@ def test_reference_interface_names():
         validate_patch_args("d_k4v4", -1, 0.05)
     with pytest.raises(ValueError):
         validate_patch_args("d_k4v4", 1, 0.0)
+
+
+def test_integration_doc_struct_matches_the_binding():
+    """The ctypes mirror of hq_decode_args printed in INTEGRATION.md must be the one the package binds: a reader who
+    pastes it gets the size the library checks (struct_bytes)."""
+    import ctypes as C
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "INTEGRATION.md")).read()
+    m = re.search(r"class hq_decode_args\(C\.Structure\):.*?_fields_ = (\[.*?\])\n\ndef ", text, re.S)
+    assert m, "the struct listing is missing from INTEGRATION.md"
+    fields = eval(m.group(1), {"C": C})
+    Doc = type("Doc", (C.Structure,), {"_fields_": fields})
+    assert [f[0] for f in fields] == [f[0] for f in _lib.DecodeArgs._fields_]
+    assert C.sizeof(Doc) == C.sizeof(_lib.DecodeArgs)

@@ -56,11 +56,18 @@ def test_fp8_pv_against_oracle(B, H_Q, H_KV, N):
     assert orc.rel_mse(bf, dense) <= 1e-4
 
 
-def test_fp8_pv_refuses_vertical_lines():
-    q, k, v = make(1, 2, 1, 512, 1)
-    vidx = torch.zeros(1, 2, 4, dtype=torch.int64, device=DEV)
-    with pytest.raises(hq.HyQuantError):
-        su.hybrid_prefill(t_bf16(q), t_bf16(k), t_bf16(v), vidx, 128, None, True, pv_fp8=True)
+@pytest.mark.parametrize("B,H_Q,H_KV,N,W", [(1, 4, 2, 640, 128), (1, 8, 2, 1536, 64)])
+def test_fp8_pv_with_window_and_vertical_lines(B, H_Q, H_KV, N, W):
+    """The hybrid structure (INT8 rest, BF16 vertical lines and window for Q K^T) with every P V tile in FP8."""
+    q, k, v = make(B, H_Q, H_KV, N, N + 1)
+    vidx = hq.compute_vertical_indices(t_bf16(q), t_bf16(k), W, 0.05, kv_repeat=H_Q // H_KV)
+    out = hq.sage_vertical_attention_v2(t_bf16(q), t_bf16(k), t_bf16(v), vidx, window_size=W, pv_fp8=True).float().cpu().numpy()
+    ref8 = orc.fp8_pv_attention_reference(q, k, v, window_size=W, round_fn=orc.bf16_round, vertical_indices=vidx.cpu().numpy())
+    err, rm = np.abs(out - ref8).max(), orc.rel_mse(out, ref8)
+    assert np.isfinite(out).all() and err <= 2e-2 and rm <= 1e-4, (err, rm)
+    out_w = su.hybrid_prefill(t_bf16(q), t_bf16(k), t_bf16(v), None, W, None, True, pv_fp8=True).float().cpu().numpy()
+    ref_w = orc.fp8_pv_attention_reference(q, k, v, window_size=W, round_fn=orc.bf16_round)
+    assert np.abs(out_w - ref_w).max() <= 2e-2 and orc.rel_mse(out_w, ref_w) <= 1e-4
 
 
 def test_fp8_pv_at_8k_rows_against_dense():

@@ -83,3 +83,31 @@ def test_lengths_record_overrides_the_arguments():
     plan.run(q.reshape(8, 128), out=out3.view(8, 128))
     assert not torch.equal(out3, want)
     layer.bind_lengths(None)
+
+
+def test_rope_inside_the_decode_step_equals_eager_rope():
+    """decode_step(rope=(cos, sin)) on unrotated q / k against Hugging Face's eager rotation followed by the plain
+    decode_step: outputs and the stored K rows bit for bit (the kernel rounds every product and the sum to bf16 as the
+    eager bf16 arithmetic does), across a staging flush."""
+    B, H_Q, H_KV, N, W = 2, 8, 2, 700, 64
+    R = H_Q // H_KV
+    a, b = _layers(1, B, H_Q, H_KV, N, W)[0], _layers(1, B, H_Q, H_KV, N, W)[0]
+    gen = torch.Generator(device=DEV); gen.manual_seed(4)
+    inv = 1.0 / (10000 ** (torch.arange(0, 128, 2, device=DEV).float() / 128))
+    for step in range(140):
+        q = torch.randn(B, H_Q, 1, 128, generator=gen, device=DEV).to(torch.bfloat16)
+        k = torch.randn(B, H_KV, 1, 128, generator=gen, device=DEV).to(torch.bfloat16)
+        v = torch.randn(B, H_KV, 1, 128, generator=gen, device=DEV).to(torch.bfloat16)
+        pos = torch.tensor([N + step, N + step + 3], device=DEV).float()            # a position per batch entry
+        ang = pos[:, None] * inv[None, :]
+        cos = torch.cat((ang.cos(), ang.cos()), -1).to(torch.bfloat16)               # [B, 128] as HF's rotary module gives it
+        sin = torch.cat((ang.sin(), ang.sin()), -1).to(torch.bfloat16)
+
+        def eager(x):
+            rot = torch.cat((-x[..., 64:], x[..., :64]), dim=-1)
+            return (x * cos[:, None, None, :]) + (rot * sin[:, None, None, :])
+
+        want = a.decode_step(eager(q), eager(k), v, R)
+        got = b.decode_step(q, k, v, R, rope=(cos[:, None, :], sin[:, None, :]))
+        assert torch.equal(got, want), step
+    assert torch.equal(a._staging_buf_k, b._staging_buf_k) and torch.equal(a.k_quant_packed, b.k_quant_packed)

@@ -95,7 +95,11 @@ def test_window_only_full_and_int8_only_variants():
     tq, tk, tv = t_bf16(q), t_bf16(k), t_bf16(v)
     check(to_np(hq.sage_unified_attention(tq, tk, tv, window_size=128)), ref)
     check(to_np(hq.sage_unified_attention(tq, tk, tv, window_size=0)), ref)
-    check(to_np(hq.sage_fp8_attention(tq, tk, tv)), ref)
+    check(to_np(hq.sage_fp8_attention(tq, tk, tv, pv_fp8=False)), ref)
+    # FP8 P V (the entry point's default, checked against its own oracle in test_gpu_fp8_pv.py) is an order of magnitude
+    # further from exact attention: that is the format, not the kernel
+    fp8 = to_np(hq.sage_fp8_attention(tq, tk, tv))
+    assert np.isfinite(fp8).all() and 1e-4 < orc.rel_mse(fp8, ref) < 5e-3
     full = to_np(hq.full_attention_fp16_triton(tq, tk, tv))
     check(full, ref)
     assert orc.rel_mse(full, ref) < 2e-5          # no quantisation at all on this path
