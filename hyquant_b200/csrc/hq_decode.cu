@@ -83,6 +83,7 @@ struct DecodeParams {
   int nsplit;
   int BH;                                 // heads of the call (grid = BH * nsplit blocks, split-major)
   int last_share;                         // share of a head's last split in 1/256 of an even share
+  int cluster;                            // > 1: the nsplit (= cluster) blocks of a head are one thread-block cluster
   int R;                                  // kv_repeat
   int out_dtype;
   float sml;                              // sm_scale * log2(e)
@@ -428,9 +429,26 @@ __device__ __forceinline__ void cvt_crumbs_subnormal(uint32_t w, uint32_t (&h)[4
   h[3] = lop3_and_xor(w, 0x00C000C0u, 0x00800080u);
 }
 
-template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
+// Cluster-wide barrier: orders the blocks' shared-memory writes before it against the other blocks' reads after it.
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// fp32 at shared-memory address `addr` (of this block's window) in block `rank` of the cluster
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// kMode: 0 = the splits of a head merge through the workspace; 1 = the same, followed by the exchange with the other
+// sequence shards over peer memory; 2 = the splits of a head are one thread-block cluster and merge through
+// distributed shared memory.  Instantiated apart, so that each form costs the others no registers.
+template <int NT, bool kScaleTma, int KB, int VB, int kMode>
 __global__ void __launch_bounds__(warps_of(NT) * 32, 1)
 decode_splitk_kernel(const DecodeParams p) {
+  constexpr bool kPeer = kMode == 1, kCluster = kMode == 2;
   using F = Fmt<KB, VB>;
   using VF = VFmt<VB>;
   constexpr int kWarps = warps_of(NT), kThreads = kWarps * 32;
@@ -453,8 +471,9 @@ decode_splitk_kernel(const DecodeParams p) {
   // that split may be a small one (p.last_share / 256 of an even share, the other splits the rest): when the heads
   // do not fill the SMs evenly (128 heads on 148 SMs), the SMs left over work through the small splits while the others
   // each do one large one.
-  const int split = blockIdx.x / p.BH;
-  const int head = blockIdx.x - split * p.BH;
+  // In cluster mode the splits of a head are the blocks of one cluster (consecutive block numbers).
+  const int split = kCluster ? (int)(blockIdx.x % p.cluster) : (int)(blockIdx.x / p.BH);
+  const int head = kCluster ? (int)(blockIdx.x / p.cluster) : (int)(blockIdx.x - split * p.BH);
   Lens L;
   L.n_quant = p.n_quant; L.n_stg = p.nseg[1];
   if (p.lengths != nullptr) {       // written before the kernel that precedes this one started (see hq_decode_args.lengths)
@@ -1104,6 +1123,54 @@ decode_splitk_kernel(const DecodeParams p) {
       l += mrg_l[w * NT * 8 + hd];
     }
   };
+  if constexpr (kCluster) {
+    // ======================= merge the splits inside the cluster ==============
+    // Every block leaves its rows (position order) and their (m, l) in its own shared memory; after a cluster barrier
+    // block r merges elements [r per, (r + 1) per) of the head's R x 128 outputs, reading the C blocks' values with
+    // ld.shared::cluster (all in flight together), and writes them out.  A second barrier keeps every block's shared
+    // memory alive until its readers are done.  Nothing goes through the workspace.
+    const int C = p.cluster;
+    float* cl_o = mrg_o + (size_t)kWarps * NT * 8 * kMrgStride;      // [R][128]
+    float* cl_ml = cl_o + NT * 8 * 128;                              // [R][2]
+    for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
+      float M, l, acc;
+      cta_row(hd, d, M, l, acc);
+      cl_o[hd * 128 + d] = acc;
+      if (d == 0) { cl_ml[2 * hd] = M; cl_ml[2 * hd + 1] = l; }
+    }
+    cluster_barrier();
+    const int per = (p.R * 128 + C - 1) / C;
+    for (int x = tid; x < per; x += kThreads) {
+      const int e = split * per + x;
+      if (e >= p.R * 128) break;
+      const int hd = e >> 7, dd = e & 127;
+      const uint32_t a_ml = smem_u32(cl_ml + 2 * hd), a_o = smem_u32(cl_o + e);
+      float mc[8], lc[8], oc[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        mc[c] = -INFINITY; lc[c] = 0.f; oc[c] = 0.f;
+        if (c < C) {
+          mc[c] = ld_cluster_f32(a_ml, c);
+          lc[c] = ld_cluster_f32(a_ml + 4, c);
+          oc[c] = ld_cluster_f32(a_o, c);
+        }
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) M = fmaxf(M, mc[c]);
+      float den = 0.f, acc = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float wt = (mc[c] == -INFINITY) ? 0.f : ex2f(mc[c] - M);
+        den = fmaf(wt, lc[c], den);
+        acc = fmaf(wt, oc[c], acc);
+      }
+      const int64_t qrow = (int64_t)head * p.R + hd;
+      store_out(p.out, qrow * p.out_stride + chan_of_pos(dd), den > 0.f ? acc / den : 0.f, p.out_dtype);
+    }
+    cluster_barrier();
+    return;
+  }
   for (int hd = tid < kRowThreads ? tid >> 7 : p.R; hd < p.R; hd += kRowThreads / 128) {
     float M, l, acc;
     cta_row(hd, d, M, l, acc);
@@ -1218,14 +1285,14 @@ static size_t decode_smem_bytes(int NT, int slot_bytes) {
   return (size_t)w * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 + (size_t)w * kSlots * 8;
 }
 
-template <int NT, bool kScaleTma, int KB, int VB, bool kPeer>
-static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+template <int NT, bool kScaleTma, int KB, int VB, int kMode>
+static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st, int* clusters_out) {
   const size_t smem = decode_smem_bytes(NT, Fmt<KB, VB>::kSlot);
   static thread_local int attr_dev = -1;
   int dev = 0;
   HQ_CUDA(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma, KB, VB, kPeer>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HQ_CUDA(cudaFuncSetAttribute(decode_splitk_kernel<NT, kScaleTma, KB, VB, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
     attr_dev = dev;
   }
@@ -1234,23 +1301,59 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   cfg.blockDim = dim3(warps_of(NT) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.overlap) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.cluster > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)p.cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = p.overlap ? 1 : 0;
-  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB, kPeer>, p));
+  cfg.numAttrs = na;
+  if (clusters_out != nullptr) {       // query only: how many clusters of this size the device holds at once
+    *clusters_out = 0;
+    if (kMode != 2) return HQ_OK;
+    static thread_local int cached_dev = -1;
+    static thread_local int cached[9];       // cluster sizes 2..8 (the portable ones)
+    if (cached_dev != dev) { for (int i = 0; i < 9; ++i) cached[i] = -1; cached_dev = dev; }
+    if (p.cluster > 8) return HQ_OK;
+    if (cached[p.cluster] < 0) {
+      int n = 0;
+      cfg.numAttrs = 1;                 // the cluster dimension alone
+      cudaLaunchAttribute only[1] = {attr[na - 1]};
+      cfg.attrs = only;
+      if (cudaOccupancyMaxActiveClusters(&n, decode_splitk_kernel<NT, kScaleTma, KB, VB, kMode>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      cached[p.cluster] = n;
+    }
+    *clusters_out = cached[p.cluster];
+    return HQ_OK;
+  }
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB, kMode>, p));
   return HQ_OK;
 }
 
 #ifndef HQ_DEC_FAST_BUILD
 template <int KB, int VB>
-static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st) {
+static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st, int* clusters_out) {
   if (p.peer.world > 1) {   // the exchanging instantiations exist with directly loaded scales only (any alignment)
-    return NT == 1 ? launch_decode<1, false, KB, VB, true>(p, grid, st) : launch_decode<2, false, KB, VB, true>(p, grid, st);
+    return NT == 1 ? launch_decode<1, false, KB, VB, 1>(p, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 1>(p, grid, st, clusters_out);
   }
-  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, false>(p, grid, st) : launch_decode<1, false, KB, VB, false>(p, grid, st);
-  return p.scale_tma ? launch_decode<2, true, KB, VB, false>(p, grid, st) : launch_decode<2, false, KB, VB, false>(p, grid, st);
+  if (p.cluster > 1) {      // the cluster instantiations exist with scales riding in the bulk copies only
+    if (!p.scale_tma) { if (clusters_out) *clusters_out = 0; return clusters_out ? HQ_OK : HQ_ERR_INVALID; }
+    return NT == 1 ? launch_decode<1, true, KB, VB, 2>(p, grid, st, clusters_out) : launch_decode<2, true, KB, VB, 2>(p, grid, st, clusters_out);
+  }
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, 0>(p, grid, st, clusters_out) : launch_decode<1, false, KB, VB, 0>(p, grid, st, clusters_out);
+  return p.scale_tma ? launch_decode<2, true, KB, VB, 0>(p, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 0>(p, grid, st, clusters_out);
 }
 #endif
 
@@ -1380,11 +1483,17 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   bool force_direct_scales = false;
   int nsplit = a->num_splits;
   int last_share = 256;
+  int cluster = 1;                 // candidate cluster size (checked against the device below)
   if (nsplit <= 0) {
     const int by_grid = sms / a->BH_KV;
     const int by_work = (p.units + kWarps - 1) / kWarps;
     nsplit = by_grid < by_work ? by_grid : by_work;
     if (nsplit > split_cap) nsplit = split_cap;
+    // A head's splits as one thread-block cluster (at most 8 blocks) merge through distributed shared memory, which
+    // saves the partial store, the ticket and the last block's merge: taken when the plain plan has no more splits
+    // than a cluster has blocks (short prefixes, or enough heads).
+    // Not in partial mode: a sequence shard's state is bit for bit what the exchanging kernel sends, in either form.
+    if (nsplit >= 2 && nsplit <= 8 && p.peer.world <= 1 && !partial) cluster = nsplit;
     // SMs left over by an even split (sms - BH * nsplit) take one more, small split of every head: a fraction
     // 0.8 * spare / sms of the head (the 0.8 pays for the fixed cost of the extra blocks), if that is worth a block
     const int spare = sms - a->BH_KV * nsplit;
@@ -1407,6 +1516,7 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.nsplit = nsplit;
   p.BH = a->BH_KV;
   p.last_share = last_share;
+  p.cluster = 1;
 #ifdef HQ_DEC_FAST_BUILD
   if (const char* e = getenv("HQ_DEC_LAST")) p.last_share = atoi(e);
 #endif
@@ -1430,24 +1540,45 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   p.scale_tma = !force_direct_scales && a->n_quant > 0 && aligned16(a->k_scale) && aligned16(a->v_scale) && a->ks_stride_bh % 8 == 0 &&
                 a->vs_stride_bh % 8 == 0 && a->ks_stride_bh >= nq8 && a->vs_stride_bh >= nq8;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid((unsigned)(a->BH_KV * nsplit));
+  auto dispatch = [&](const DecodeParams& pp, dim3 grid, int* clusters_out) -> int {
+    const DecodeParams& p = pp;
 #ifdef HQ_DEC_FAST_BUILD      // development builds: the K4/V4 instantiations only
-  HQ_REQUIRE(k_bits == 4 && v_bits == 4 && p.peer.world <= 1, HQ_ERR_UNSUPPORTED, "hq_decode_splitk: development build (K4/V4, no peers)");
-  if (NT == 1) return p.scale_tma ? launch_decode<1, true, 4, 4, false>(p, grid, st) : launch_decode<1, false, 4, 4, false>(p, grid, st);
-  return p.scale_tma ? launch_decode<2, true, 4, 4, false>(p, grid, st) : launch_decode<2, false, 4, 4, false>(p, grid, st);
+    HQ_REQUIRE(k_bits == 4 && v_bits == 4 && p.peer.world <= 1, HQ_ERR_UNSUPPORTED, "hq_decode_splitk: development build (K4/V4, no peers)");
+    if (p.cluster > 1) {
+      if (!p.scale_tma) { if (clusters_out) *clusters_out = 0; return clusters_out ? HQ_OK : HQ_ERR_INVALID; }
+      return NT == 1 ? launch_decode<1, true, 4, 4, 2>(p, grid, st, clusters_out) : launch_decode<2, true, 4, 4, 2>(p, grid, st, clusters_out);
+    }
+    if (NT == 1) return p.scale_tma ? launch_decode<1, true, 4, 4, 0>(p, grid, st, clusters_out) : launch_decode<1, false, 4, 4, 0>(p, grid, st, clusters_out);
+    return p.scale_tma ? launch_decode<2, true, 4, 4, 0>(p, grid, st, clusters_out) : launch_decode<2, false, 4, 4, 0>(p, grid, st, clusters_out);
 #else
-  switch (k_bits * 16 + v_bits) {
-    case 0x44: return launch_decode_bits<4, 4>(p, NT, grid, st);
-    case 0x88: return launch_decode_bits<8, 8>(p, NT, grid, st);
-    case 0x84: return launch_decode_bits<8, 4>(p, NT, grid, st);
-    case 0x82: return launch_decode_bits<8, 2>(p, NT, grid, st);
-    case 0x48: return launch_decode_bits<4, 8>(p, NT, grid, st);
-    case 0x42: return launch_decode_bits<4, 2>(p, NT, grid, st);
-    case 0x28: return launch_decode_bits<2, 8>(p, NT, grid, st);
-    case 0x24: return launch_decode_bits<2, 4>(p, NT, grid, st);
-    default: return launch_decode_bits<2, 2>(p, NT, grid, st);
-  }
+    switch (k_bits * 16 + v_bits) {
+      case 0x44: return launch_decode_bits<4, 4>(p, NT, grid, st, clusters_out);
+      case 0x88: return launch_decode_bits<8, 8>(p, NT, grid, st, clusters_out);
+      case 0x84: return launch_decode_bits<8, 4>(p, NT, grid, st, clusters_out);
+      case 0x82: return launch_decode_bits<8, 2>(p, NT, grid, st, clusters_out);
+      case 0x48: return launch_decode_bits<4, 8>(p, NT, grid, st, clusters_out);
+      case 0x42: return launch_decode_bits<4, 2>(p, NT, grid, st, clusters_out);
+      case 0x28: return launch_decode_bits<2, 8>(p, NT, grid, st, clusters_out);
+      case 0x24: return launch_decode_bits<2, 4>(p, NT, grid, st, clusters_out);
+      default: return launch_decode_bits<2, 2>(p, NT, grid, st, clusters_out);
+    }
 #endif
+  };
+#ifdef HQ_DEC_FAST_BUILD
+  if (const char* e = getenv("HQ_DEC_CLUSTER")) cluster = atoi(e);
+#endif
+  if (cluster > 1 && cluster <= p.units) {
+    // the device must hold every head's cluster at once (one block per SM, clusters do not span GPCs)
+    DecodeParams pc = p;
+    pc.cluster = cluster;
+    pc.nsplit = cluster;
+    pc.last_share = 256;
+    int held = 0;
+    const int rq = dispatch(pc, dim3((unsigned)(a->BH_KV * cluster)), &held);
+    if (rq != HQ_OK) return rq;
+    if (held >= a->BH_KV) return dispatch(pc, dim3((unsigned)(a->BH_KV * cluster)), nullptr);
+  }
+  return dispatch(p, dim3((unsigned)(a->BH_KV * nsplit)), nullptr);
 }
 
 // ---- decode without caller-provided scratch -----------------------------------------------

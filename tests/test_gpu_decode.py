@@ -172,6 +172,21 @@ def test_decode_empty_segments(segs):
     check_close(run_gpu(c, q, 4), ref)
 
 
+@pytest.mark.parametrize("R,heads,nq", [(4, 8, 900), (4, 8, 1900), (4, 8, 3400), (8, 4, 2500), (16, 8, 1100), (16, 2, 2300),
+                                        (4, 32, 20000), (1, 64, 9000)])
+def test_decode_cluster_merge_against_workspace_merge(R, heads, nq):
+    """Shapes whose automatic plan has 2 to 8 splits per head: the splits of a head run as one thread-block cluster
+    and merge through distributed shared memory.  Same result as the workspace merge with as many explicit splits
+    (fp32 summation order apart), and as the oracle."""
+    c, q = build_case(heads, R, nq, 40, 17, 128, seed=heads * 1000 + nq)
+    ref = orc.decode_attention_exact(q, c, R).reshape(-1, 128)
+    out = run_gpu(c, q, R)
+    check_close(out, ref)
+    for s in (2, 3, 5, 8):
+        plain = run_gpu(c, q, R, num_splits=s)
+        assert np.all(np.abs(out - plain) <= 2e-3 + 2.0 ** -7 * np.abs(plain))
+
+
 def test_decode_split_invariance_and_partials():
     c, q = build_case(4, 4, 5000, 250, 77, 128, seed=9)
     ref = orc.decode_attention_exact(q, c, 4).reshape(-1, 128)
