@@ -25,7 +25,7 @@ EXPORTS = [
     "hq_quant_pack", "hq_quant_pack_int4", "hq_staging_append",
     "hq_decode_workspace_bytes", "hq_decode_splitk", "hq_decode_splitk_static", "hq_decode_static_status",
     "hq_lse_merge", "hq_lse_merge_strided",
-    "hq_vertical_scores",
+    "hq_vertical_scores", "hq_vertical_scores_grouped",
     "hq_topk",
     "hq_cache_reorganize", "hq_cache_reorganize_bits", "hq_lse_merge_partial",
     "hq_prefill_quant_workspace_bytes", "hq_prefill_quant", "hq_prefill_quant_blocks", "hq_per_block_int8",
@@ -111,6 +111,8 @@ def _declare(lib):
     lib.hq_lse_merge_strided.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp, i32, i64, vp]
     lib.hq_vertical_scores.argtypes = [vp, i32, i64, i64, i64, i32, i32, i32, i32,
                                        vp, i64, i64, i64, i32, i32, i32, i32, vp, vp, vp]
+    lib.hq_vertical_scores_grouped.argtypes = [vp, i32, i64, i64, i64, i32, i32, i32, i32, i32,
+                                               vp, i64, i64, i64, i32, i32, i32, vp, vp, vp]
     lib.hq_topk.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp]
     lib.hq_cache_reorganize.argtypes = [vp, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp,
                                         vp, vp, i64, vp, vp, i64, i32, vp]

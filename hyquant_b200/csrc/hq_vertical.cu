@@ -17,13 +17,24 @@
 namespace hq {
 
 // ------------------------------------------------------------------ pooling
+// `group` > 1: output head h is the mean of the input heads h group .. h group + group - 1, taken per token and rounded
+// to the input dtype (what a 16-bit mean over the head axis gives) before the tokens are pooled.
 template <typename T>
 __global__ void pool_query_kernel(const T* __restrict__ q, int64_t sb, int64_t sh, int64_t sn, int H_Q, int n_q,
-                                  int tail_len, int round_mode /*-1 none, else dtype*/, float* __restrict__ pooled) {
+                                  int tail_len, int round_mode /*-1 none, else dtype*/, int group, int group_dtype,
+                                  float* __restrict__ pooled) {
   const int bh = blockIdx.x, b = bh / H_Q, h = bh - b * H_Q, d = threadIdx.x;
-  const T* base = q + b * sb + h * sh + (int64_t)(n_q - tail_len) * sn + d;
+  const T* base = q + b * sb + (int64_t)h * group * sh + (int64_t)(n_q - tail_len) * sn + d;
   float acc = 0.f;
-  for (int i = 0; i < tail_len; ++i) acc += load_as_float<T>(base + i * sn);
+  if (group <= 1) {
+    for (int i = 0; i < tail_len; ++i) acc += load_as_float<T>(base + i * sn);
+  } else {
+    for (int i = 0; i < tail_len; ++i) {
+      float s = 0.f;
+      for (int r = 0; r < group; ++r) s += load_as_float<T>(base + r * sh + i * sn);
+      acc += out_round(s / (float)group, group_dtype);
+    }
+  }
   float m = acc / (float)tail_len;
   if (round_mode >= 0) m = out_round(m, round_mode);
   pooled[(int64_t)bh * 128 + d] = m;
@@ -271,12 +282,12 @@ topk_kernel(const float* __restrict__ scores, int64_t stride, int n, int k, int 
 
 }  // namespace hq
 
-extern "C" int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
-                                  int B, int H_Q, int n_q, int tail_len,
-                                  const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
-                                  int H_KV, int n_cand, int round_mean, int round_scores,
-                                  float* pooled, float* scores, void* stream) {
-  using namespace hq;
+namespace hq {
+static int vertical_scores_impl(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                int B, int H_Q, int n_q, int tail_len, int group,
+                                const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                int H_KV, int n_cand, int round_mean, int round_scores,
+                                float* pooled, float* scores, void* stream) {
   HQ_REQUIRE(B >= 0 && H_Q > 0 && H_KV > 0 && n_q > 0 && n_cand >= 0, HQ_ERR_INVALID, "hq_vertical_scores: bad sizes");
   HQ_REQUIRE(H_Q % H_KV == 0, HQ_ERR_INVALID, "hq_vertical_scores: H_Q %d not a multiple of H_KV %d", H_Q, H_KV);
   const int R = H_Q / H_KV;
@@ -292,10 +303,10 @@ extern "C" int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_
   const int rm = round_mean ? io_dtype : -1;
   if (io_dtype == HQ_BF16)
     pool_query_kernel<__nv_bfloat16><<<B * H_Q, 128, 0, st>>>((const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_n, H_Q,
-                                                              n_q, tail_len, rm, pooled);
+                                                              n_q, tail_len, rm, group, io_dtype, pooled);
   else
     pool_query_kernel<__half><<<B * H_Q, 128, 0, st>>>((const __half*)q, q_stride_b, q_stride_h, q_stride_n, H_Q, n_q,
-                                                       tail_len, rm, pooled);
+                                                       tail_len, rm, group, io_dtype, pooled);
   HQ_CUDA(cudaGetLastError());
   const int tiles = (n_cand + 15) / 16;
   int chunks = (2 * sm_count() + B * H_KV - 1) / (B * H_KV);
@@ -314,6 +325,29 @@ extern "C" int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_
   }
   HQ_CUDA(cudaGetLastError());
   return HQ_OK;
+}
+}  // namespace hq
+
+extern "C" int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                  int B, int H_Q, int n_q, int tail_len,
+                                  const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                  int H_KV, int n_cand, int round_mean, int round_scores,
+                                  float* pooled, float* scores, void* stream) {
+  return hq::vertical_scores_impl(q, io_dtype, q_stride_b, q_stride_h, q_stride_n, B, H_Q, n_q, tail_len, 1, k, k_stride_b,
+                                  k_stride_h, k_stride_n, H_KV, n_cand, round_mean, round_scores, pooled, scores, stream);
+}
+
+// The selection of the cache's freeze: the saved queries of the `group` query heads of a kv-head are averaged first
+// (per token, rounded to io_dtype), then pooled and scored per KV head.  q is [B, H_KV * group, n_q, 128].
+extern "C" int hq_vertical_scores_grouped(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                                          int B, int H_KV, int group, int n_q, int tail_len,
+                                          const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                                          int n_cand, int round_mean, int round_scores,
+                                          float* pooled, float* scores, void* stream) {
+  using namespace hq;
+  HQ_REQUIRE(group >= 1 && group <= 64, HQ_ERR_INVALID, "hq_vertical_scores_grouped: group %d outside 1..64", group);
+  return vertical_scores_impl(q, io_dtype, q_stride_b, q_stride_h, q_stride_n, B, H_KV, n_q, tail_len, group, k, k_stride_b,
+                              k_stride_h, k_stride_n, H_KV, n_cand, round_mean, round_scores, pooled, scores, stream);
 }
 
 extern "C" int hq_topk(const float* scores, int64_t scores_stride, int rows, int n, int k,

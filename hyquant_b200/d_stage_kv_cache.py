@@ -168,10 +168,14 @@ class DStageLayerCache:
                 and kv_repeat >= 1:
             cand = max(0, prefix_len - self.window_size)
             if cand > 0:
-                # group mean of the saved queries, in the input dtype like the reference (:131-133)
-                q_kv = self._query_tail.reshape(B, H_KV, kv_repeat, -1, D).mean(dim=2)
-                scores = vertical_scores(q_kv.to(keys.dtype), keys.reshape(B, H_KV, N, D)[:, :, :prefix_len],
-                                         self.window_size, 1)
+                # group mean of the saved queries, in the input dtype like the reference (:131-133): inside the
+                # scoring call when the queries already have the keys' 16-bit dtype
+                kpre = keys.reshape(B, H_KV, N, D)[:, :, :prefix_len]
+                if kv_repeat > 1 and self._query_tail.dtype == keys.dtype:
+                    scores = vertical_scores(self._query_tail, kpre, self.window_size, 1, group_mean=kv_repeat)
+                else:
+                    q_kv = self._query_tail.reshape(B, H_KV, kv_repeat, -1, D).mean(dim=2)
+                    scores = vertical_scores(q_kv.to(keys.dtype), kpre, self.window_size, 1)
                 T = vertical_topk_count(cand, self.top_ratio)
                 vidx, vasc = topk_indices(scores, T, want_ascending=True)       # [B, H_KV, T]
         self.vertical_indices = vidx

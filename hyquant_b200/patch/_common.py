@@ -120,11 +120,16 @@ def trim_4d_attention_mask(attention_mask: Any, key_states: Any) -> Any:
 # ----------------------------------------------------------------------------
 
 def vertical_scores(query_states: torch.Tensor, key_states: torch.Tensor, window_size: int,
-                    kv_repeat: int = 1, *, round_like_reference: bool = False) -> Optional[torch.Tensor]:
+                    kv_repeat: int = 1, *, round_like_reference: bool = False,
+                    group_mean: int = 1) -> Optional[torch.Tensor]:
     """fp32 scores [B, H_Q, P] of the pooled last-``window_size`` queries against
     the prefix keys (reference _common.py:161-185).  ``round_like_reference``
     rounds the pooled query and the scores to the input dtype as the reference's
-    in-dtype mean / matmul do; by default both stay fp32."""
+    in-dtype mean / matmul do; by default both stay fp32.
+
+    ``group_mean`` = G > 1 is the selection of the cache's freeze: ``query_states`` holds
+    G query heads per kv-head, which are averaged first (per token, in the input dtype,
+    reference d_stage_kv_cache.py:131-133); the scores are then [B, H_KV, P]."""
     _lib.require_cuda(query_states, "query_states")
     B, H_Q, n_q, D = query_states.shape
     if D != 128:
@@ -134,6 +139,10 @@ def vertical_scores(query_states: torch.Tensor, key_states: torch.Tensor, window
     if P == 0:
         return None
     H = int(key_states.shape[1])
+    if group_mean > 1:
+        if H * group_mean != H_Q:
+            raise AssertionError(f"H_Q ({H_Q}) != H_KV ({H}) * group_mean ({group_mean})")
+        H_Q = H
     if not (H == H_Q or H * kv_repeat == H_Q):
         raise AssertionError(f"H_Q ({H_Q}) != H_KV ({H}) * kv_repeat ({kv_repeat})")
     if key_states.dtype not in (torch.bfloat16, torch.float16):
@@ -150,6 +159,13 @@ def vertical_scores(query_states: torch.Tensor, key_states: torch.Tensor, window
     pooled = torch.empty(B, H_Q, D, dtype=torch.float32, device=q.device)
     scores = torch.empty(B, H_Q, P, dtype=torch.float32, device=q.device)
     rl = 1 if round_like_reference else 0
+    if group_mean > 1:
+        rc = _lib.lib().hq_vertical_scores_grouped(
+            q.data_ptr(), _lib.dtype_code(k.dtype), q.stride(0), q.stride(1), q.stride(2), B, H, group_mean, n_q, tail_len,
+            k.data_ptr(), k.stride(0), k.stride(1), k.stride(2), P, rl, rl,
+            pooled.data_ptr(), scores.data_ptr(), _lib.stream_ptr(q.device))
+        _lib.check(rc, "hq_vertical_scores_grouped")
+        return scores
     rc = _lib.lib().hq_vertical_scores(
         q.data_ptr(), _lib.dtype_code(k.dtype), q.stride(0), q.stride(1), q.stride(2), B, H_Q, n_q, tail_len,
         k.data_ptr(), k.stride(0), k.stride(1), k.stride(2), H, P, rl, rl,

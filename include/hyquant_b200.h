@@ -265,6 +265,16 @@ int hq_vertical_scores(const void* q, int io_dtype, int64_t q_stride_b, int64_t 
                        int H_KV, int n_cand, int round_mean, int round_scores,
                        float* pooled, float* scores, void* stream);
 
+/* The same for the selection inside DStageLayerCache.freeze (src/ops/d_stage_kv_cache.py:131-136): the saved
+ * queries q [B, H_KV * group, n_q, 128] are first averaged over the `group` query heads of each kv-head (per token,
+ * rounded to io_dtype like the reference's in-dtype mean), then pooled and scored per KV head:
+ * pooled fp32 [B, H_KV, 128], scores fp32 [B, H_KV, n_cand]. */
+int hq_vertical_scores_grouped(const void* q, int io_dtype, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_n,
+                               int B, int H_KV, int group, int n_q, int tail_len,
+                               const void* k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_n,
+                               int n_cand, int round_mean, int round_scores,
+                               float* pooled, float* scores, void* stream);
+
 /* Top-k of each row of `scores` ([rows, n] fp32, row stride `scores_stride`),
  * descending, ties towards the lower index.  Replaces torch.topk(..., sorted=True)
  * in compute_vertical_indices (src/patch/_common.py:187-190).  idx_desc int64

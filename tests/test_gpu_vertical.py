@@ -44,6 +44,23 @@ def test_vertical_scores_and_topk(B, H_Q, H_KV, N, W, nq):
         assert max_abs(s_exp.cpu().numpy(), sg) <= 1e-4 * max(1.0, np.abs(sg).max())
 
 
+@pytest.mark.parametrize("B,H_KV,R,N,W,nq", [(1, 8, 4, 1024, 128, 128), (2, 2, 16, 600, 64, 64), (1, 4, 7, 300, 32, 5)])
+def test_vertical_scores_with_group_mean_inside(B, H_KV, R, N, W, nq):
+    """The freeze-side selection: the mean over a kv-head's query heads taken inside the scoring call equals the
+    eager mean in the input dtype followed by the plain call."""
+    case = gen_numpy(B, H_KV * R, H_KV, N, 128, W, 0.05, 33, n_qry=nq)
+    q, k = t_bf16(case.q), t_bf16(case.k)
+    fused = hq.vertical_scores(q, k, W, 1, group_mean=R)
+    eager = hq.vertical_scores(q.reshape(B, H_KV, R, nq, 128).mean(dim=2), k, W, 1)
+    assert fused.shape == eager.shape == (B, H_KV, N - W)
+    # the same numbers up to a rare last-bit difference of a 16-bit mean (fp32 summation order over the heads)
+    assert max_abs(fused.cpu().numpy(), eager.cpu().numpy()) <= 2e-3 * float(eager.abs().max())
+    kk = orc.vertical_topk_count(N - W, 0.05)
+    a, b = hq.topk_indices(fused, kk), hq.topk_indices(eager, kk)
+    same = np.mean([len(set(x.tolist()) & set(y.tolist())) / kk for x, y in zip(a.reshape(-1, kk).cpu().numpy(), b.reshape(-1, kk).cpu().numpy())])
+    assert same >= 0.95
+
+
 def test_vertical_reference_rounding_mode_and_empty_prefix():
     case = gen_numpy(1, 8, 2, 512, 128, 64, 0.05, 5)
     q, k = orc.bf16_round(case.q), orc.bf16_round(case.k)
