@@ -42,6 +42,8 @@
 
 #include "hq_common.cuh"
 #include "hq_peer.cuh"
+#include "hq_tc05.cuh"      // the tensor-map encoder
+#include <string.h>
 
 namespace hq {
 
@@ -92,6 +94,7 @@ struct DecodeParams {
   PeerGroup peer;                         // peer.world > 1: exchange the state with the other sequence shards and merge
   __nv_bfloat16* stage_k; __nv_bfloat16* stage_v;   // staging buffers, written only when the call carries a new token
   int scale_tma;                          // scales ride in the bulk copies (aligned rows) or are loaded directly
+  int kv_fused;                           // K and V codes of a head are two planes of one tensor: one request per unit
   int overlap;                            // launched with programmatic stream serialisation
   const int* lengths;                     // device {n_quant, n_staging} overriding the values above (or null)
   const __nv_bfloat16* rope_cos; const __nv_bfloat16* rope_sin;   // [batch, 128] rotary factors of the step (or null)
@@ -447,7 +450,7 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
 // distributed shared memory.  Instantiated apart, so that each form costs the others no registers.
 template <int NT, bool kScaleTma, int KB, int VB, int kMode>
 __global__ void __launch_bounds__(warps_of(NT) * 32, 1)
-decode_splitk_kernel(const DecodeParams p) {
+decode_splitk_kernel(const __grid_constant__ CUtensorMap kv_map, const DecodeParams p) {
   constexpr bool kPeer = kMode == 1, kCluster = kMode == 2;
   using F = Fmt<KB, VB>;
   using VF = VFmt<VB>;
@@ -538,8 +541,15 @@ decode_splitk_kernel(const DecodeParams p) {
         const uint32_t dst = ring_u32 + slot * kSlotBytes, bar = bar_u32 + slot * 8;
         constexpr uint32_t kb = kUnitQ * F::kRowK, vb = kUnitQ * F::kRowV;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kb + vb) : "memory");
-        bulk_raw(dst, kq_base + tok0 * F::kRowK, kb, bar);
-        bulk_raw(dst + F::kVOff, vq_base + tok0 * F::kRowV, vb, bar);
+        if (KB == VB && p.kv_fused) {
+          // the unit's K rows and V rows are one box {unit bytes, 1 unit, 2 planes} of the head's code tensor:
+          // one request to the copy engine instead of two, landing as [K rows | V rows] like the two bulk copies
+          asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                       ::"r"(dst), "l"(&kv_map), "r"(0), "r"(u), "r"(2 * head), "r"(bar) : "memory");
+        } else {
+          bulk_raw(dst, kq_base + tok0 * F::kRowK, kb, bar);
+          bulk_raw(dst + F::kVOff, vq_base + tok0 * F::kRowV, vb, bar);
+        }
       }
       if (kScaleTma && lane < kScaleLanes) scale_copies(slot, tok0, kUnitQ);
       return;
@@ -1285,8 +1295,36 @@ static size_t decode_smem_bytes(int NT, int slot_bytes) {
   return (size_t)w * kSlots * slot_bytes + (size_t)NT * 512 * 4 * 2 + (size_t)NT * 8 * 4 + (size_t)w * kSlots * 8;
 }
 
+// Tensor map of the code planes as {unit bytes (in 8-byte elements, so that a whole unit of up to 2 KB is one row of
+// the box), units per plane, planes}, box {unit, 1, 2}, no swizzle.  The last few maps are kept (a cache's buffers change only when it grows), since encoding one costs about as much
+// host time as the launch.
+static int kv_tensor_map(CUtensorMap* out, const void* base, int row_bytes, int64_t plane_tokens, int64_t planes, int unit_tokens) {
+  struct Entry { const void* base; int row; int64_t tokens, planes; int unit; CUtensorMap map; };
+  constexpr int kKeep = 8;
+  static thread_local Entry kept[kKeep];
+  static thread_local int next = 0;
+  for (int i = 0; i < kKeep; ++i)
+    if (kept[i].base == base && kept[i].row == row_bytes && kept[i].tokens == plane_tokens && kept[i].planes == planes &&
+        kept[i].unit == unit_tokens) { *out = kept[i].map; return HQ_OK; }
+  tc::EncodeTiledFn fn = tc::encode_fn();
+  HQ_REQUIRE(fn != nullptr, HQ_ERR_CUDA, "hq_decode_splitk: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t unit_bytes = (cuuint64_t)row_bytes * (cuuint64_t)unit_tokens;
+  const cuuint64_t dims[3] = {unit_bytes / 8, (cuuint64_t)plane_tokens / (cuuint64_t)unit_tokens, (cuuint64_t)planes};
+  const cuuint64_t strides[2] = {unit_bytes, (cuuint64_t)row_bytes * (cuuint64_t)plane_tokens};
+  const cuuint32_t box[3] = {(cuuint32_t)(unit_bytes / 8), 1u, 2u};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HQ_REQUIRE(r == CUDA_SUCCESS, HQ_ERR_CUDA, "hq_decode_splitk: cuTensorMapEncodeTiled failed with %d (row %d, %lld tokens, %lld planes)",
+             (int)r, row_bytes, (long long)plane_tokens, (long long)planes);
+  kept[next] = Entry{base, row_bytes, plane_tokens, planes, unit_tokens, *out};
+  next = (next + 1) % kKeep;
+  return HQ_OK;
+}
+
 template <int NT, bool kScaleTma, int KB, int VB, int kMode>
-static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st, int* clusters_out) {
+static int launch_decode(const DecodeParams& p, const CUtensorMap& kv_map, dim3 grid, cudaStream_t st, int* clusters_out) {
   const size_t smem = decode_smem_bytes(NT, Fmt<KB, VB>::kSlot);
   static thread_local int attr_dev = -1;
   int dev = 0;
@@ -1338,22 +1376,22 @@ static int launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st, int*
     *clusters_out = cached[p.cluster];
     return HQ_OK;
   }
-  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB, kMode>, p));
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, decode_splitk_kernel<NT, kScaleTma, KB, VB, kMode>, kv_map, p));
   return HQ_OK;
 }
 
 #ifndef HQ_DEC_FAST_BUILD
 template <int KB, int VB>
-static int launch_decode_bits(const DecodeParams& p, int NT, dim3 grid, cudaStream_t st, int* clusters_out) {
+static int launch_decode_bits(const DecodeParams& p, const CUtensorMap& kv_map, int NT, dim3 grid, cudaStream_t st, int* clusters_out) {
   if (p.peer.world > 1) {   // the exchanging instantiations exist with directly loaded scales only (any alignment)
-    return NT == 1 ? launch_decode<1, false, KB, VB, 1>(p, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 1>(p, grid, st, clusters_out);
+    return NT == 1 ? launch_decode<1, false, KB, VB, 1>(p, kv_map, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 1>(p, kv_map, grid, st, clusters_out);
   }
   if (p.cluster > 1) {      // the cluster instantiations exist with scales riding in the bulk copies only
     if (!p.scale_tma) { if (clusters_out) *clusters_out = 0; return clusters_out ? HQ_OK : HQ_ERR_INVALID; }
-    return NT == 1 ? launch_decode<1, true, KB, VB, 2>(p, grid, st, clusters_out) : launch_decode<2, true, KB, VB, 2>(p, grid, st, clusters_out);
+    return NT == 1 ? launch_decode<1, true, KB, VB, 2>(p, kv_map, grid, st, clusters_out) : launch_decode<2, true, KB, VB, 2>(p, kv_map, grid, st, clusters_out);
   }
-  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, 0>(p, grid, st, clusters_out) : launch_decode<1, false, KB, VB, 0>(p, grid, st, clusters_out);
-  return p.scale_tma ? launch_decode<2, true, KB, VB, 0>(p, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 0>(p, grid, st, clusters_out);
+  if (NT == 1) return p.scale_tma ? launch_decode<1, true, KB, VB, 0>(p, kv_map, grid, st, clusters_out) : launch_decode<1, false, KB, VB, 0>(p, kv_map, grid, st, clusters_out);
+  return p.scale_tma ? launch_decode<2, true, KB, VB, 0>(p, kv_map, grid, st, clusters_out) : launch_decode<2, false, KB, VB, 0>(p, kv_map, grid, st, clusters_out);
 }
 #endif
 
@@ -1480,7 +1518,7 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   const int NT = a->kv_repeat <= 8 ? 1 : 2;
   const int kWarps = warps_of(NT);
   const int split_cap = (int)(((int64_t)a->BH_KV + max_ctas()) / a->BH_KV);
-  bool force_direct_scales = false;
+  bool force_direct_scales = false, force_split_kv = false;
   int nsplit = a->num_splits;
   int last_share = 256;
   int cluster = 1;                 // candidate cluster size (checked against the device below)
@@ -1508,6 +1546,7 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
 #ifdef HQ_DEC_FAST_BUILD
   if (const char* e = getenv("HQ_DEC_NSPLIT")) nsplit = atoi(e);
   if (getenv("HQ_DEC_NOSCALETMA")) force_direct_scales = true;
+  if (getenv("HQ_DEC_SPLITKV")) force_split_kv = true;
 #endif
   if (nsplit < 1) nsplit = 1;
   if (nsplit > p.units && p.units > 0) nsplit = p.units;
@@ -1539,6 +1578,22 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
   const int64_t nq8 = ((int64_t)a->n_quant + 7) & ~(int64_t)7;
   p.scale_tma = !force_direct_scales && a->n_quant > 0 && aligned16(a->k_scale) && aligned16(a->v_scale) && a->ks_stride_bh % 8 == 0 &&
                 a->vs_stride_bh % 8 == 0 && a->ks_stride_bh >= nq8 && a->vs_stride_bh >= nq8;
+  // K and V codes as two planes of one tensor (what DStageLayerCache allocates when K and V have the same width):
+  // v_packed lies one plane after k_packed and a head is two planes.  Then a unit's codes are one box of a 3-D
+  // tensor map {row bytes, tokens of a plane, 2 * BH planes}.
+  CUtensorMap kv_map;
+  memset(&kv_map, 0, sizeof(kv_map));
+  p.kv_fused = 0;
+  if (k_bits == v_bits && a->n_quant >= kUnitQ && p.peer.world <= 1 && !force_split_kv) {
+    const int64_t row = 16 * k_bits;
+    const int64_t plane = (const uint8_t*)a->v_packed - (const uint8_t*)a->k_packed;
+    if (plane > 0 && plane % row == 0 && plane % 16 == 0 && a->kp_stride_bh == 2 * plane && a->vp_stride_bh == 2 * plane &&
+        plane / row >= a->n_quant && plane / row < (1ll << 31) && (kUnitQ * row) % 16 == 0 && kUnitQ * row <= 2048) {
+      const int rm = kv_tensor_map(&kv_map, a->k_packed, (int)row, plane / row, 2 * (int64_t)a->BH_KV, kUnitQ);
+      if (rm != HQ_OK) return rm;
+      p.kv_fused = 1;
+    }
+  }
   cudaStream_t st = (cudaStream_t)stream;
   auto dispatch = [&](const DecodeParams& pp, dim3 grid, int* clusters_out) -> int {
     const DecodeParams& p = pp;
@@ -1546,21 +1601,21 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
     HQ_REQUIRE(k_bits == 4 && v_bits == 4 && p.peer.world <= 1, HQ_ERR_UNSUPPORTED, "hq_decode_splitk: development build (K4/V4, no peers)");
     if (p.cluster > 1) {
       if (!p.scale_tma) { if (clusters_out) *clusters_out = 0; return clusters_out ? HQ_OK : HQ_ERR_INVALID; }
-      return NT == 1 ? launch_decode<1, true, 4, 4, 2>(p, grid, st, clusters_out) : launch_decode<2, true, 4, 4, 2>(p, grid, st, clusters_out);
+      return NT == 1 ? launch_decode<1, true, 4, 4, 2>(p, kv_map, grid, st, clusters_out) : launch_decode<2, true, 4, 4, 2>(p, kv_map, grid, st, clusters_out);
     }
-    if (NT == 1) return p.scale_tma ? launch_decode<1, true, 4, 4, 0>(p, grid, st, clusters_out) : launch_decode<1, false, 4, 4, 0>(p, grid, st, clusters_out);
-    return p.scale_tma ? launch_decode<2, true, 4, 4, 0>(p, grid, st, clusters_out) : launch_decode<2, false, 4, 4, 0>(p, grid, st, clusters_out);
+    if (NT == 1) return p.scale_tma ? launch_decode<1, true, 4, 4, 0>(p, kv_map, grid, st, clusters_out) : launch_decode<1, false, 4, 4, 0>(p, kv_map, grid, st, clusters_out);
+    return p.scale_tma ? launch_decode<2, true, 4, 4, 0>(p, kv_map, grid, st, clusters_out) : launch_decode<2, false, 4, 4, 0>(p, kv_map, grid, st, clusters_out);
 #else
     switch (k_bits * 16 + v_bits) {
-      case 0x44: return launch_decode_bits<4, 4>(p, NT, grid, st, clusters_out);
-      case 0x88: return launch_decode_bits<8, 8>(p, NT, grid, st, clusters_out);
-      case 0x84: return launch_decode_bits<8, 4>(p, NT, grid, st, clusters_out);
-      case 0x82: return launch_decode_bits<8, 2>(p, NT, grid, st, clusters_out);
-      case 0x48: return launch_decode_bits<4, 8>(p, NT, grid, st, clusters_out);
-      case 0x42: return launch_decode_bits<4, 2>(p, NT, grid, st, clusters_out);
-      case 0x28: return launch_decode_bits<2, 8>(p, NT, grid, st, clusters_out);
-      case 0x24: return launch_decode_bits<2, 4>(p, NT, grid, st, clusters_out);
-      default: return launch_decode_bits<2, 2>(p, NT, grid, st, clusters_out);
+      case 0x44: return launch_decode_bits<4, 4>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x88: return launch_decode_bits<8, 8>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x84: return launch_decode_bits<8, 4>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x82: return launch_decode_bits<8, 2>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x48: return launch_decode_bits<4, 8>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x42: return launch_decode_bits<4, 2>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x28: return launch_decode_bits<2, 8>(p, kv_map, NT, grid, st, clusters_out);
+      case 0x24: return launch_decode_bits<2, 4>(p, kv_map, NT, grid, st, clusters_out);
+      default: return launch_decode_bits<2, 2>(p, kv_map, NT, grid, st, clusters_out);
     }
 #endif
   };

@@ -116,8 +116,15 @@ class DStageLayerCache:
     def _alloc_prefix(self, BH: int, n: int, device):
         cap = n + max(8 * GROUP_SIZE, n // 8)
         cap = (cap + GROUP_SIZE - 1) // GROUP_SIZE * GROUP_SIZE
-        self._kq = torch.empty(BH, cap, self._D * self.k_bits // 8, dtype=torch.int8, device=device)
-        self._vq = torch.empty(BH, cap, self._D * self.v_bits // 8, dtype=torch.int8, device=device)
+        if self.k_bits == self.v_bits:
+            # K and V codes of a head as two planes of one tensor [BH, 2, cap, row]: the decode kernel then fetches a
+            # unit's K rows and V rows with one tensor-map request instead of two copies (hq_decode_splitk looks for
+            # this layout through the pointers and strides it is given)
+            kv = torch.empty(BH, 2, cap, self._D * self.k_bits // 8, dtype=torch.int8, device=device)
+            self._kq, self._vq = kv[:, 0], kv[:, 1]
+        else:
+            self._kq = torch.empty(BH, cap, self._D * self.k_bits // 8, dtype=torch.int8, device=device)
+            self._vq = torch.empty(BH, cap, self._D * self.v_bits // 8, dtype=torch.int8, device=device)
         self._ks = torch.empty(BH, cap, dtype=torch.float16, device=device)
         self._vs = torch.empty(BH, cap, dtype=torch.float16, device=device)
 

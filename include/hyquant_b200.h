@@ -122,7 +122,10 @@ typedef struct hq_decode_args {
   const void* q;               /* bf16 [BH_KV*kv_repeat, 128] */
   int64_t q_stride;            /* elements between query rows */
   const void* k_packed;        /* int8 [BH_KV, n_quant, 16 * k_bits] (4 bits: 64 bytes per token) */
-  const void* v_packed;
+  const void* v_packed;        /* Any placement works.  When k_bits == v_bits and the two are planes of one
+                                * tensor [BH_KV, 2, cap, row] (v_packed = k_packed + cap * row bytes, both head
+                                * strides = 2 * cap * row), a unit's K and V rows are fetched with one tensor-map
+                                * request instead of two copies; results are the same bit for bit. */
   int64_t kp_stride_bh;        /* BYTES between heads */
   int64_t vp_stride_bh;
   const void* k_scale;         /* fp16 [BH_KV, n_quant] */

@@ -583,3 +583,34 @@ def test_decode_step_equals_append_then_decode(bits):
 def decode_status_of(layer):
     from hyquant_b200.decode_d_stage import decode_status
     return decode_status(layer._plan.ws)
+
+
+@pytest.mark.parametrize("bits", [(4, 4), (8, 8), (2, 2)])
+@pytest.mark.parametrize("heads,N", [((1, 8, 2), 3000), ((2, 32, 8), 9000)])
+def test_codes_as_planes_of_one_tensor_equal_separate_tensors(bits, heads, N):
+    """The cache class keeps K and V codes of equal width as two planes of one tensor, which the decode kernel reads with
+    one tensor-map request per unit; the same cache handed over as separate contiguous tensors takes two bulk copies
+    per unit.  Same bytes in shared memory, so the outputs are equal bit for bit."""
+    import hyquant_b200 as hq
+    from hyquant_b200 import decode_d_stage as dds
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV = heads
+    R, W = H_Q // H_KV, 128
+    t = gen_torch(B, H_Q, H_KV, N, 128, W, 0.05, 5 + N, n_qry=W, device="cuda")
+    layer = hq.DStageLayerCache(0, k_bits=bits[0], v_bits=bits[1], window_size=W, top_ratio=0.05, use_vert=True)
+    layer.update_prefill(t["k"], t["v"]); layer.save_query_tail(t["q"]); layer.freeze(kv_repeat=R)
+    assert layer._vq.data_ptr() - layer._kq.data_ptr() == layer._kq.shape[1] * layer._kq.shape[2]      # planes of one tensor
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for step in range(3):
+        kn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        vn = torch.randn(B, H_KV, 1, 128, generator=g, device="cuda").bfloat16()
+        layer.append_staging(kn, vn)
+    q = torch.randn(B, H_Q, 1, 128, generator=g, device="cuda").bfloat16()
+    planes = layer.decode_attention(q, R)
+    S = layer._staging_ptr
+    apart = dds.fused_d_stage_decode(q.reshape(-1, 128), layer.k_quant_packed.contiguous(), layer.v_quant_packed.contiguous(),
+                                     layer.k_scale.contiguous(), layer.v_scale.contiguous(), layer.k_topk, layer.v_topk,
+                                     layer._staging_buf_k[:, :S], layer._staging_buf_v[:, :S], layer.k_window, layer.v_window,
+                                     bits[0], bits[1], kv_repeat=R)
+    assert torch.equal(planes.reshape(-1, 128), apart)
+    assert decode_status_of(layer) == 0
