@@ -233,10 +233,14 @@ class DStageLayerCache:
             return
         k = key_states.reshape(BH, S, D)
         v = value_states.reshape(BH, S, D)
-        for i in range(S):
-            self._staging_buf_k[:, self._staging_ptr, :] = k[:, i, :]
-            self._staging_buf_v[:, self._staging_ptr, :] = v[:, i, :]
-            self._staging_ptr += 1
+        # several tokens (or another dtype): one copy per run of tokens up to the next flush, not one per token
+        i = 0
+        while i < S:
+            r = min(GROUP_SIZE - self._staging_ptr, S - i)
+            self._staging_buf_k[:, self._staging_ptr:self._staging_ptr + r].copy_(k[:, i:i + r])
+            self._staging_buf_v[:, self._staging_ptr:self._staging_ptr + r].copy_(v[:, i:i + r])
+            self._staging_ptr += r
+            i += r
             if self._staging_ptr >= GROUP_SIZE:
                 self._flush_staging_buffer()
         self._seq_len += S

@@ -614,3 +614,29 @@ def test_codes_as_planes_of_one_tensor_equal_separate_tensors(bits, heads, N):
                                      bits[0], bits[1], kv_repeat=R)
     assert torch.equal(planes.reshape(-1, 128), apart)
     assert decode_status_of(layer) == 0
+
+
+def test_multi_token_append_equals_token_by_token():
+    """append_staging with several tokens at once (a chunked prefill continuation) leaves the cache exactly as the same
+    tokens appended one by one do, across two flushes of the staging buffer."""
+    import hyquant_b200 as hq
+    from hyquant_b200.synth import gen_torch
+    B, H_Q, H_KV, N, W = 1, 8, 2, 700, 64
+    t = gen_torch(B, H_Q, H_KV, N, 128, W, 0.05, 91, n_qry=W, device="cuda")
+    a, b = [hq.DStageLayerCache(0, window_size=W, top_ratio=0.05) for _ in range(2)]
+    for layer in (a, b):
+        layer.update_prefill(t["k"], t["v"]); layer.save_query_tail(t["q"]); layer.freeze(kv_repeat=4)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    kn = torch.randn(B, H_KV, 300, 128, generator=g, device="cuda").bfloat16()
+    vn = torch.randn(B, H_KV, 300, 128, generator=g, device="cuda").bfloat16()
+    for lo, hi in ((0, 7), (7, 130), (130, 131), (131, 300)):
+        a.append_staging(kn[:, :, lo:hi], vn[:, :, lo:hi])
+    for i in range(300):
+        b.append_staging(kn[:, :, i:i + 1], vn[:, :, i:i + 1])
+    assert a._staging_ptr == b._staging_ptr == 300 - 256 and a._n_quant == b._n_quant
+    assert a.get_seq_length() == b.get_seq_length() == N + 300
+    assert torch.equal(a.k_quant_packed, b.k_quant_packed) and torch.equal(a.v_quant_packed, b.v_quant_packed)
+    assert torch.equal(a.k_scale, b.k_scale) and torch.equal(a.v_scale, b.v_scale)
+    assert torch.equal(a._staging_buf_k[:, :44], b._staging_buf_k[:, :44]) and torch.equal(a._staging_buf_v[:, :44], b._staging_buf_v[:, :44])
+    q = torch.randn(B, H_Q, 1, 128, generator=g, device="cuda").bfloat16()
+    assert torch.equal(a.decode_attention(q, 4), b.decode_attention(q, 4))
