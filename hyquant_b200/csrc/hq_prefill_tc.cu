@@ -509,20 +509,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mQi, const __grid_constant
           const float2 esc2 = make_float2(esc, esc), nmu2 = make_float2(-mu, -mu);
           float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
           if (is_i8) {
-  #pragma unroll
+            float* y = reinterpret_cast<float*>(sr);
+#pragma unroll
             for (int c4 = 0; c4 < 16; ++c4) {
               const float4 kk = ks4[c4], bb = kb4[c4];
-              // bits(i + 0x4B400000) = 12582912 + i for |i| < 2^22; the bias row carries -12582912 * scale (or -inf)
               const float2 a01 = make_float2(__int_as_float((int)sr[4 * c4] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 1] + 0x4B400000));
               const float2 a23 = make_float2(__int_as_float((int)sr[4 * c4 + 2] + 0x4B400000), __int_as_float((int)sr[4 * c4 + 3] + 0x4B400000));
               const float2 y01 = ffma2(ffma2(a01, make_float2(kk.x, kk.y), make_float2(bb.x, bb.y)), esc2, nmu2);
               const float2 y23 = ffma2(ffma2(a23, make_float2(kk.z, kk.w), make_float2(bb.z, bb.w)), esc2, nmu2);
-              const float2 p01 = make_float2(ex2f(y01.x), ex2f(y01.y)), p23 = make_float2(ex2f(y23.x), ex2f(y23.y));
-              rsa = fadd2(rsa, p01);
-              rsb = fadd2(rsb, p23);
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(p01.x, p01.y), h1 = __floats2bfloat162_rn(p23.x, p23.y);   // low half = even column
-              pk[2 * c4] = *reinterpret_cast<uint32_t*>(&h0);
-              pk[2 * c4 + 1] = *reinterpret_cast<uint32_t*>(&h1);
+              y[4 * c4] = y01.x; y[4 * c4 + 1] = y01.y; y[4 * c4 + 2] = y23.x; y[4 * c4 + 3] = y23.y;
+            }
+#pragma unroll
+            for (int c = 0; c < 64; ++c) y[c] = ex2f(y[c]);
+            float2 rsc = make_float2(0.f, 0.f), rsd = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+              rsa = fadd2(rsa, make_float2(y[8 * c8], y[8 * c8 + 1]));
+              rsb = fadd2(rsb, make_float2(y[8 * c8 + 2], y[8 * c8 + 3]));
+              rsc = fadd2(rsc, make_float2(y[8 * c8 + 4], y[8 * c8 + 5]));
+              rsd = fadd2(rsd, make_float2(y[8 * c8 + 6], y[8 * c8 + 7]));
+            }
+            rsa = fadd2(rsa, rsc); rsb = fadd2(rsb, rsd);
+#pragma unroll
+            for (int c2 = 0; c2 < 32; ++c2) {
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(y[2 * c2], y[2 * c2 + 1]);
+              pk[c2] = *reinterpret_cast<uint32_t*>(&h0);
             }
           } else {
   #pragma unroll
