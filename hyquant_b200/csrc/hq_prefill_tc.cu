@@ -103,8 +103,11 @@ struct TcItemIter {
     while (kind < 3 && !valid(pl)) step(pl);
   }
   __device__ __forceinline__ void next(const TcPlan& pl) {
-    do step(pl); while (kind < 3 && !valid(pl));
     if (++stage == depth) { stage = 0; par ^= 1u; }
+    // the common cases first (the lanes that walk the ring are single threads: every instruction here is latency)
+    if (kind == 0 && j + 1 < pl.n_rest) { ++j; return; }
+    if (kind == 2) { if (++j >= pl.n_win) kind = 3; return; }
+    do step(pl); while (kind < 3 && !valid(pl));
   }
   __device__ __forceinline__ bool done() const { return kind >= 3; }
   __device__ __forceinline__ bool feeds(int h) const { return kind != 1 || hh == h; }
