@@ -1531,7 +1531,15 @@ extern "C" int hq_decode_splitk(const hq_decode_args* a, void* stream) {
     // saves the partial store, the ticket and the last block's merge: taken when the plain plan has no more splits
     // than a cluster has blocks (short prefixes, or enough heads).
     // Not in partial mode: a sequence shard's state is bit for bit what the exchanging kernel sends, in either form.
-    if (nsplit >= 2 && nsplit <= 8 && p.peer.world <= 1 && !partial) cluster = nsplit;
+    // A short prefix is better off with eight blocks of half-empty warps than with four full ones (1K: 5.8 against
+    // 6.4 us), and even cluster sizes measured better than odd ones.
+    if (nsplit <= 8 && p.peer.world <= 1 && !partial) {
+      int c = by_grid < 8 ? by_grid : 8;
+      if (c > p.units) c = p.units;
+      if (c > split_cap) c = split_cap;
+      if (c > 2 && (c & 1)) --c;
+      if (c >= 2) cluster = c;
+    }
     // SMs left over by an even split (sms - BH * nsplit) take one more, small split of every head: a fraction
     // 0.8 * spare / sms of the head (the 0.8 pays for the fixed cost of the extra blocks), if that is worth a block
     const int spare = sms - a->BH_KV * nsplit;
