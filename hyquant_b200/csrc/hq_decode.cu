@@ -765,15 +765,6 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap kv_map, const DecodePar
           kw[ch][0] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g) * 64 + t * 16);
           kw[ch][1] = *reinterpret_cast<const uint4*>(Ks + (16 * ch + g + 8) * 64 + t * 16);
         }
-#ifdef HQ_DEC_SPLITCHAIN
-        float s2[kChunks][NT][4];        // second accumulator chain: halves the depth of dependent MMAs
-#pragma unroll
-        for (int ch = 0; ch < kChunks; ++ch)
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) s2[ch][nt][x] = 0.f;
-#endif
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
 #pragma unroll
@@ -785,24 +776,11 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap kv_map, const DecodePar
             cvt_nibbles_biased(wb, hb);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-#ifdef HQ_DEC_SPLITCHAIN
-              mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
-              mma_f16_16816(s2[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
-#else
               mma_f16_16816(s[ch][nt], ha[0], hb[0], ha[1], hb[1], Qh[nt][2 * w][0], Qh[nt][2 * w][1]);
               mma_f16_16816(s[ch][nt], ha[2], hb[2], ha[3], hb[3], Qh[nt][2 * w + 1][0], Qh[nt][2 * w + 1][1]);
-#endif
             }
           }
         }
-#ifdef HQ_DEC_SPLITCHAIN
-#pragma unroll
-        for (int ch = 0; ch < kChunks; ++ch)
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) s[ch][nt][x] += s2[ch][nt][x];
-#endif
       } else if constexpr (KB == 8) {
         // a 128-byte row: 16 bytes at 64 h + 16 t; word w of it holds channels 64 h + 16 t + 4 w + (0..3)
 #pragma unroll
