@@ -603,6 +603,8 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap kv_map, const DecodePar
     }
   };
   if (!p.overlap) {
+    // a kernel launched behind this one as a programmatic dependent (the exchange of sequence shards) may take its place
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     load_q();
     for (int i = 0; i < kSlots && i < n_my; ++i) issue(i);
   } else {

@@ -31,6 +31,9 @@ struct PeerParams {
 // then waits, so every rank's words are on their way without depending on anything another rank does.
 __global__ void __launch_bounds__(128)
 peer_exchange_merge_kernel(const PeerParams p) {
+  // Launched as a programmatic dependent of the kernel before it on the stream (the decode call that writes this
+  // rank's state): its blocks may be resident before that kernel ends and wait here for its completion.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int d = threadIdx.x;
   const PeerGroup& g = p.g;
   const PeerLayout L = peer_layout(g.world, g.rows);
@@ -102,8 +105,17 @@ extern "C" int hq_peer_exchange_merge(const hq_peer_exchange_args* a, void* stre
     if (per_sm < 1) per_sm = 1;
   }
   const int resident = per_sm * sm_count();
-  peer_exchange_merge_kernel<<<a->rows < resident ? a->rows : resident, 128, 0, (cudaStream_t)stream>>>(p);
-  HQ_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(a->rows < resident ? a->rows : resident));
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HQ_CUDA(cudaLaunchKernelEx(&cfg, peer_exchange_merge_kernel, p));
   return HQ_OK;
 }
 
