@@ -573,6 +573,91 @@ def bench_reference_triton(torch, hq, dev, layer, q_decode, prefill_seqs):
     return out
 
 
+def bench_cache_ops(torch, hq, dev, hbm_peak):
+    """The cache-side rows of the path at the headline shape (B = 1, 8 KV heads, 32K prefix): the prefill -> decode
+    reorganisation (``freeze``: vertical-line selection + gather + compaction + quantisation), the selection alone,
+    the per-token quantiser alone on the whole prefix, and one staging flush.  Each with its algorithmic bytes, and the
+    reference's own ``freeze`` (eager PyTorch on the same GPU) beside it when ``oracle/_ref`` is there."""
+    from hyquant_b200.synth import gen_torch, n_vertical
+    from hyquant_b200 import decode_d_stage as dd
+    r = H_Q // H_KV
+    t = gen_torch(B, H_Q, H_KV, N_PREFIX, D, W, RHO, 1015, n_qry=W, device=dev)
+    k, v, q = t["k"], t["v"], t["q"]
+
+    def timed(fn, reps, setup=None):
+        (setup or (lambda: None))()
+        fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            if setup is not None:
+                setup()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / reps
+
+    out = {"workload": f"B={B}, {H_KV} kv heads, d={D}, prefix {N_PREFIX}, W={W}, rho={RHO:.0%}; one layer"}
+    state = {}
+
+    def new_layer():
+        layer = hq.DStageLayerCache(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+        layer.update_prefill(k, v)
+        layer.save_query_tail(q)
+        state["layer"] = layer
+
+    ms = timed(lambda: state["layer"].freeze(kv_repeat=r), 5, setup=new_layer)
+    layer = state["layer"]
+    nq, nt = layer._n_quant, layer.k_topk.shape[1]
+    heads = B * H_KV
+    # K prefix read for the scores, K and V read once for the reorganisation, codes + scales and BF16 rows written
+    fr_bytes = heads * (256 * (N_PREFIX - W) + 512 * N_PREFIX + 132 * nq + 512 * (nt + W))
+    out["freeze"] = {"ms": round(ms, 4), "bytes": fr_bytes, "gbps": round(fr_bytes / ms / 1e6, 1),
+                     "frac_of_measured_hbm": None if not hbm_peak else round(fr_bytes / ms / 1e6 / hbm_peak, 3),
+                     "what": "DStageLayerCache.freeze: hq_vertical_scores_grouped + hq_topk + hq_cache_reorganize_bits, allocations included"}
+    ms = timed(lambda: hq.compute_vertical_indices(q, k, W, RHO, kv_repeat=r), 10)
+    sel_bytes = heads * 256 * (N_PREFIX - W)
+    out["vertical_selection"] = {"ms": round(ms, 4), "bytes": sel_bytes, "gbps": round(sel_bytes / ms / 1e6, 1),
+                                 "what": "compute_vertical_indices per query head: pooled scores over the prefix keys + exact top-k"}
+    x = k.reshape(heads, N_PREFIX, D)
+    ms = timed(lambda: dd.quantize_per_token(x, 4), 10)
+    qb = heads * N_PREFIX * (256 + 66)
+    out["quantize_per_token"] = {"ms": round(ms, 4), "bytes": qb, "gbps": round(qb / ms / 1e6, 1),
+                                 "frac_of_measured_hbm": None if not hbm_peak else round(qb / ms / 1e6 / hbm_peak, 3),
+                                 "what": "hq_quant_pack on the whole prefix of one layer (4 bits)"}
+    g = torch.Generator(device=dev).manual_seed(5)
+    kn = torch.randn(B, H_KV, 127, D, generator=g, device=dev).bfloat16()
+    layer.append_staging(kn, kn)
+
+    def refill():
+        layer._staging_ptr = 128
+
+    ms = timed(lambda: layer._flush_staging_buffer(), 10, setup=refill)
+    out["staging_flush"] = {"us": round(ms * 1e3, 2), "what": "128 staged tokens of every head quantised and appended in place (two launches)"}
+    ref = reference_dir()
+    if ref is not None:
+        try:
+            sys.path.insert(0, ref)
+            from src.ops.d_stage_kv_cache import DStageLayerCache as RefLayer
+
+            def new_ref():
+                rl = RefLayer(0, k_bits=4, v_bits=4, window_size=W, top_ratio=RHO, use_vert=True)
+                rl.update_prefill(k, v)
+                rl.save_query_tail(q)
+                state["ref"] = rl
+
+            out["reference_freeze_ms_same_gpu"] = round(timed(lambda: state["ref"].freeze(kv_repeat=r), 3, setup=new_ref), 3)
+            state.pop("ref", None)
+        except Exception as e:
+            out["reference_freeze_ms_same_gpu"] = f"unavailable: {type(e).__name__}: {e}"
+    del t, layer, state
+    torch.cuda.empty_cache()
+    return out
+
+
 def build_cpu_layer(seed=1015, n_prefix=N_PREFIX):
     from hyquant_b200.synth import gen_numpy, n_vertical
     from oracle import hq_oracle as orc
@@ -807,8 +892,11 @@ def run_ours(args):
                             "tflops_with_selection_and_preparation": round(plan.flops / ms_all / 1e9, 1),
                             "kernel": "hq::prefill_tc_kernel (tcgen05 kind::i8 QK^T + kind::f16 BF16 tiles and PV, TMEM accumulators)"})
             del plan, t
-    batched = long_ctx = bit_widths = prefill_heads = ref_triton = None
+    batched = long_ctx = bit_widths = prefill_heads = ref_triton = cache_ops = None
     legs = set() if args.no_extra else set(args.extra_legs.split(","))
+    if "cache" in legs and rank == 0:
+        cache_ops = bench_cache_ops(torch, hq, dev, peak if peak_src.startswith("measured") else None)
+        torch.cuda.empty_cache()
     if "reference" in legs and rank == 0:
         ref_triton = bench_reference_triton(torch, hq, dev, layers[0], qs[0], [int(x) for x in args.prefill_seq.split(",")])
         torch.cuda.empty_cache()
@@ -858,6 +946,7 @@ def run_ours(args):
             "long_context_decode": long_ctx,
             "prefill_kv_head_groups": prefill_heads,
             "reference_triton_sm100": ref_triton,
+            "cache_ops": cache_ops,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -890,7 +979,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="launch every decode call plainly (no programmatic dependent launch)")
     ap.add_argument("--no-extra", action="store_true", help="skip the bit-width, batched (64q/8kv x 16) and 128K long-context decode legs")
-    ap.add_argument("--extra-legs", default="bits,batched,long,prefill_heads,reference",
+    ap.add_argument("--extra-legs", default="bits,batched,long,prefill_heads,reference,cache",
                     help="which of those legs to run (comma-separated); prefill_heads = the 32K prefill with its KV-head groups "
                          "over the ranks (N > 1), reference = the reference's Triton kernels on the same inputs (needs oracle/_ref)")
     ap.add_argument("--prefill-heads-single", action="store_true", help="run the prefill_heads leg on one GPU too")
