@@ -63,6 +63,36 @@ def test_quantize_matches_oracle_bit_exact(shape, nbits):
     assert np.array_equal(pk.cpu().numpy(), po1) and np.array_equal(sc.cpu().numpy().view(np.uint16), so1.view(np.uint16))
 
 
+@pytest.mark.parametrize("nbits", [2, 4, 8])
+def test_quantize_ties_and_near_ties_bit_exact(nbits):
+    """Quotients x / scale on a half-integer, and one to three units in the last place beside it: where rounding the
+    product with the reciprocal could differ from rounding the IEEE quotient, the kernel has to take the division.
+    fp32 inputs, scales that are exact in fp16 (the row maximum is q_max times the scale)."""
+    qmax = 2 ** (nbits - 1) - 1
+    rng = np.random.Generator(np.random.PCG64(nbits))
+    rows = []
+    for s in [1.0, 0.5, 0.333251953125, 3.0517578125e-05, 1023.5, 0.0999755859375, 7.152557373046875e-07 * 64]:
+        s = np.float32(np.float16(s))
+        for rep in range(4):
+            row = np.zeros(128, dtype=np.float32)
+            row[0] = np.float32(qmax) * s                      # pins the scale (exactly q_max * s)
+            ks = rng.integers(-qmax - 1, qmax, size=127).astype(np.float32) + np.float32(0.5)
+            x = (ks * s).astype(np.float32)                    # quotient = k + 0.5 (exact for these scales where the product is exact)
+            ulps = rng.integers(-3, 4, size=127)
+            bits_ = x.view(np.int32) + ulps.astype(np.int32)   # a few units in the last place beside the tie
+            row[1:] = bits_.view(np.float32)
+            row[1:] = np.clip(row[1:], -row[0], row[0])        # keep row[0] the maximum
+            rows.append(row)
+    x = np.stack(rows)[None]                                   # [1, n, 128]
+    for mode in (0, 1):
+        pk = torch.empty(1, x.shape[1], 16 * nbits, dtype=torch.int8, device=DEV)
+        sc = torch.empty(1, x.shape[1], dtype=torch.float16, device=DEV)
+        dd.quantize_per_token_into(torch.from_numpy(x).to(DEV), pk, sc, 0, scale_mode=mode, nbits=nbits)
+        po, so = orc.quantize_per_token(x, nbits, reciprocal_scale=bool(mode))
+        assert np.array_equal(sc.cpu().numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(pk.cpu().numpy(), po)
+
+
 def test_quantize_empty_and_append_offset():
     p, s = hq.quantize_per_token(torch.zeros(4, 0, 128, dtype=torch.bfloat16, device=DEV), 4)
     assert p.shape == (4, 0, 64) and s.shape == (4, 0)
