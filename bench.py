@@ -327,6 +327,7 @@ def bench_batched_decode(torch, hq, dev, rank, world, dist, graph):
             "sharding": f"kv heads over {world} rank(s), {hkv_l} per rank, no collective", "scaling": "strong",
             "us_per_call": round(us, 2), "bytes_per_call_per_rank": bts,
             "gbps_all_ranks": round(bts * world / us / 1e3, 1), "caches_per_rank": caches,
+            "frac_of_hbm_peak_per_gpu": round(bts / us / 1e3 / measured_peak()[0], 3),
             "sharded_max_abs_err": err, "sharded_ok": err is None or err <= SHARD_TOL,
             "l2": "caches exceed L2" if flush is None else "flushed before each pass"}
 
@@ -425,6 +426,7 @@ def bench_long_context_decode(torch, hq, dev, rank, world, dist):
                        "buffers over NVLink, waits for theirs and merges",
            "scaling": "strong", "us_per_layer_token": round(us, 2), "cache_bytes_per_layer": full_bytes,
            "gbps_all_ranks": round(full_bytes / us / 1e3, 1),
+           "frac_of_hbm_peak_per_gpu": round(full_bytes / world / us / 1e3 / measured_peak()[0], 3),
            "launch_mode": "python, host-driven: " + ("two launches per layer and token (decode of the shard, taking the new token on the tail rank; exchange + merge)" if world > 1 else "decode_step (append + decode in one launch)"),
            "l2": "4 layer caches of 138 MB in turn; a layer's shard is re-read only after the other three"}
     out.update(res_extra)
