@@ -670,3 +670,33 @@ def test_multi_token_append_equals_token_by_token():
     assert torch.equal(a._staging_buf_k[:, :44], b._staging_buf_k[:, :44]) and torch.equal(a._staging_buf_v[:, :44], b._staging_buf_v[:, :44])
     q = torch.randn(B, H_Q, 1, 128, generator=g, device="cuda").bfloat16()
     assert torch.equal(a.decode_attention(q, 4), b.decode_attention(q, 4))
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_decode_random_shapes_both_code_layouts(seed):
+    """Random head counts, GQA ratios, bit widths and segment lengths: against the oracle, and with K / V codes handed over
+    as planes of one tensor (one request per unit) equal bit for bit to separate tensors (two requests)."""
+    rng = np.random.Generator(np.random.PCG64(1000 + seed))
+    bits = [(4, 4), (4, 4), (8, 8), (2, 2), (4, 2), (8, 4)][seed % 6]
+    BH = int(rng.choice([1, 2, 3, 8, 16, 40]))
+    R = int(rng.choice([1, 2, 4, 5, 8, 12, 16]))
+    nq = int(rng.choice([0, 17, 200, 1500, 6000])) + int(rng.integers(0, 40))
+    nt, ns, nw = int(rng.integers(0, 90)), int(rng.integers(0, 128)), int(rng.choice([0, 64, 128]))
+    if nq + nt + ns + nw == 0:
+        nw = 64
+    c, q = build_case(BH, R, nq, nt, ns, nw, seed=seed, k_bits=bits[0], v_bits=bits[1])
+    ref = orc.decode_attention_exact(q, c, R).reshape(-1, 128)
+    out = run_gpu(c, q, R)
+    check_close(out, ref)
+    if bits[0] == bits[1] and nq > 0:
+        row = 16 * bits[0]
+        cap = (nq + 127) // 128 * 128 + 128
+        kv = torch.zeros(BH, 2, cap, row, dtype=torch.int8, device=DEV)
+        kv[:, 0, :nq] = torch.from_numpy(np.ascontiguousarray(c.k_quant_packed)).to(DEV)
+        kv[:, 1, :nq] = torch.from_numpy(np.ascontiguousarray(c.v_quant_packed)).to(DEV)
+        ti = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+        S = c.staging_ptr
+        planes = hq.fused_d_stage_decode(t_bf16(q.reshape(-1, 128)), kv[:, 0, :nq], kv[:, 1, :nq], ti(c.k_scale), ti(c.v_scale),
+                                         t_bf16(c.k_topk), t_bf16(c.v_topk), t_bf16(c.staging_k)[:, :S], t_bf16(c.staging_v)[:, :S],
+                                         t_bf16(c.k_window), t_bf16(c.v_window), bits[0], bits[1], kv_repeat=R)
+        assert np.array_equal(to_np(planes), out)
