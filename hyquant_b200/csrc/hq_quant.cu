@@ -1,9 +1,9 @@
 // Per-token symmetric quantise + pack, 8 / 4 / 2 bits (flush of the staging buffer
 // and the quantisation step of the prefill->decode reorganisation).
 //
-// HBM-bound: reads 256 B (bf16) per token, writes 64 B codes + 2 B scale.  One
-// warp owns one token row at a time; lane l holds channels 4l..4l+3, so the
-// warp's loads are one 256-byte line and its stores one 64-byte line.
+// HBM-bound: reads 256 B (bf16) per token, writes 64 B codes + 2 B scale.  Eight
+// lanes own a token row (16 channels each), so a warp works on four rows at a time;
+// a row's loads are one 256-byte line and its stores one 64-byte line.
 #include "hq_quant.cuh"
 
 namespace hq {
@@ -14,20 +14,24 @@ quant_pack_kernel(const T* __restrict__ x, int64_t x_stride_bh, int64_t x_stride
                   uint8_t* __restrict__ packed, int64_t packed_stride_bh,
                   __half* __restrict__ scale, int64_t scale_stride_bh,
                   int64_t dst_off, int scale_mode) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane & 7;
   const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t rows = (int64_t)BH * n;
-  for (int64_t r = warp0; r < rows; r += nwarps) {
-    const int bh = (int)(r / n);
+  for (int64_t r0 = 4 * warp0; r0 < rows; r0 += 4 * nwarps) {
+    const int64_t mine = r0 + (lane >> 3);
+    const bool live = mine < rows;
+    const int64_t r = live ? mine : rows - 1;          // lanes past the end redo the last row and store nothing
+    const int bh = rows <= 0x7FFFFFFF ? (int)((uint32_t)r / (uint32_t)n) : (int)(r / n);
     const int tok = (int)(r - (int64_t)bh * n);
-    const T* src = x + bh * x_stride_bh + tok * x_stride_n + lane * 4;
-    float v[4];
-    load4(src, v);
-    uint32_t code;
-    __half s = quant_row_bits<BITS>(v, scale_mode, code);
-    store_codes<BITS>(packed + bh * packed_stride_bh + (dst_off + tok) * (16 * BITS), lane, code);
-    if (lane == 0) scale[bh * scale_stride_bh + dst_off + tok] = s;
+    float v[16];
+    load16(x + bh * x_stride_bh + tok * x_stride_n + sub * 16, v);
+    uint32_t code[BITS / 2];
+    const __half s = quant_row16<BITS>(v, scale_mode, code);
+    if (live) {
+      store_codes16<BITS>(packed + bh * packed_stride_bh + (dst_off + tok) * (16 * BITS), sub, code);
+      if (sub == 0) scale[bh * scale_stride_bh + dst_off + tok] = s;
+    }
   }
 }
 
@@ -94,16 +98,15 @@ extern "C" int hq_quant_pack(const void* x, int in_dtype, int64_t x_stride_bh, i
   if (BH == 0 || n == 0) return HQ_OK;
   HQ_REQUIRE(x && packed && scale, HQ_ERR_INVALID, "hq_quant_pack: null pointer");
   HQ_REQUIRE(scale_mode == 0 || scale_mode == 1, HQ_ERR_INVALID, "hq_quant_pack: scale_mode must be 0 or 1");
-  const int esz = in_dtype == HQ_F32 ? 4 : 2;
-  HQ_REQUIRE(((uintptr_t)x % (4 * esz)) == 0 && (x_stride_bh % 4) == 0 && (x_stride_n % 4) == 0, HQ_ERR_ALIGNMENT,
-             "hq_quant_pack: x rows must be aligned to 4 elements");
-  const int lane_bytes = nbits / 2;      // bytes one lane stores
+  HQ_REQUIRE(((uintptr_t)x % 16) == 0 && (x_stride_bh % 8) == 0 && (x_stride_n % 8) == 0, HQ_ERR_ALIGNMENT,
+             "hq_quant_pack: x rows must be 16-byte aligned (strides multiples of 8 elements)");
+  const int lane_bytes = 2 * nbits;      // bytes one lane stores
   HQ_REQUIRE(((uintptr_t)packed % lane_bytes) == 0 && (packed_stride_bh % lane_bytes) == 0, HQ_ERR_ALIGNMENT,
              "hq_quant_pack: packed rows must be %d-byte aligned", lane_bytes);
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows = (int64_t)BH * n;
   const int warps_per_block = 8;
-  int64_t blocks = (rows + warps_per_block - 1) / warps_per_block;
+  int64_t blocks = (rows + 4 * warps_per_block - 1) / (4 * warps_per_block);      // a warp takes four rows per trip
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   dim3 grid((unsigned)blocks);

@@ -11,63 +11,88 @@
 
 namespace hq {
 
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
-  uint2 u = *reinterpret_cast<const uint2*>(p);
-  v[0] = __uint_as_float(u.x << 16);
-  v[1] = __uint_as_float(u.x & 0xFFFF0000u);
-  v[2] = __uint_as_float(u.y << 16);
-  v[3] = __uint_as_float(u.y & 0xFFFF0000u);
+// Work split: EIGHT lanes per token row, sixteen channels per lane, so a warp works on four rows at a time and the
+// per-row overhead (row arithmetic, the maximum's shuffles, the scale) is paid once per four rows.  (With a whole warp
+// on one row the kernels were bound by instruction issue at a fifth of the memory bandwidth.)
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&v)[16]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p), b = *reinterpret_cast<const uint4*>(p + 8);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
 }
-__device__ __forceinline__ void load4(const __half* p, float (&v)[4]) {
-  uint2 u = *reinterpret_cast<const uint2*>(p);
-  __half2 a = *reinterpret_cast<__half2*>(&u.x), b = *reinterpret_cast<__half2*>(&u.y);
-  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+__device__ __forceinline__ void load16(const __half* p, float (&v)[16]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p), b = *reinterpret_cast<const uint4*>(p + 8);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+    v[2 * i] = __low2float(h); v[2 * i + 1] = __high2float(h);
+  }
 }
-__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
-  float4 f = *reinterpret_cast<const float4*>(p);
-  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+__device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 f = *reinterpret_cast<const float4*>(p + 4 * i);
+    v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+  }
 }
 
-// All 32 lanes call this with their 4 channels of one 128-channel token.  Returns the fp16 scale (same on
-// every lane) and this lane's 4 codes in the low bits of `code`: 4 bytes (BITS = 8), 16 bits (4) or one byte (2);
-// a token row is 16 * BITS bytes and lane l owns bytes [l * BITS / 2, (l + 1) * BITS / 2).
-// NaN inputs: 0/0 cannot happen (the scale is >= half(1e-5 / q_max) > 0); inf / inf gives NaN, which converts to code 0.
+// Called by all 32 lanes; lanes 8 g .. 8 g + 7 hold one 128-channel token (lane l: channels 16 (l & 7) .. + 15).
+// Returns the row's fp16 scale (the same on the row's eight lanes) and this lane's 16 codes packed in channel order
+// into `code` (BITS / 2 words: 16 bytes at 8 bits, 8 at 4, 4 at 2); a token row is 16 * BITS bytes and lane l owns
+// bytes [2 BITS (l & 7), 2 BITS ((l & 7) + 1)).
+// q = rint(x / sf) with the IEEE quotient without sixteen IEEE divisions per lane: the product with the correctly
+// rounded reciprocal is within 1.5 * 2^-23 (relative) of the rounded quotient, and |quotient| < 2^BITS, so the two round
+// to the same integer unless the product lies within kNearTie of a half-integer - only then the division is done.
+// Infinities and NaNs take the same values either way (x * 0 = x / inf = 0 or NaN alike, inf * r = inf / sf).
+// NaN inputs: 0/0 cannot happen (the scale is >= half(1e-5 / q_max) > 0); inf / inf gives NaN, which the clamp turns
+// into the lowest code.
 template <int BITS>
-__device__ __forceinline__ __half quant_row_bits(const float (&v)[4], int scale_mode, uint32_t& code) {
+__device__ __forceinline__ __half quant_row16(const float (&v)[16], int scale_mode, uint32_t (&code)[BITS / 2]) {
   constexpr float qmax = (float)((1 << (BITS - 1)) - 1), qmin = -(float)(1 << (BITS - 1));
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float amax = 0.f;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   amax = fmaxf(amax, 1e-5f);
   const float s32 = scale_mode == 0 ? __fdiv_rn(amax, qmax) : __fmul_rn(amax, __fdiv_rn(1.0f, qmax));
   const __half sh = __float2half_rn(s32);
   const float sf = __half2float(sh);
-  uint32_t c = 0;
+  const float rcp = __frcp_rn(sf);
+  constexpr float kNearTie = BITS == 8 ? 1.5e-4f : 6e-6f;      // > 4 x the largest possible difference of the two
+  constexpr int kPerWord = 32 / BITS;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float q = rintf(__fdiv_rn(v[i], sf));
-    q = fminf(fmaxf(q, qmin), qmax);
-    c |= ((uint32_t)(__float2int_rn(q)) & ((1u << BITS) - 1u)) << (BITS * i);
+  for (int w = 0; w < BITS / 2; ++w) {
+    uint32_t c = 0;
+#pragma unroll
+    for (int i = 0; i < kPerWord; ++i) {
+      const float x = v[w * kPerWord + i];
+      const float t = __fmul_rn(x, rcp);
+      float q = rintf(t);
+      if (0.5f - fabsf(t - q) < kNearTie) q = rintf(__fdiv_rn(x, sf));
+      q = fminf(fmaxf(q, qmin), qmax);
+      c |= ((uint32_t)(__float2int_rn(q)) & ((1u << BITS) - 1u)) << (BITS * i);
+    }
+    code[w] = c;
   }
-  code = c;
   return sh;
 }
 
-// store the lane's codes of a token row that starts at `prow`
+// store the lane's codes of a token row that starts at `prow` (sub = lane & 7)
 template <int BITS>
-__device__ __forceinline__ void store_codes(uint8_t* prow, int lane, uint32_t code) {
-  if (BITS == 8) reinterpret_cast<uint32_t*>(prow)[lane] = code;
-  else if (BITS == 4) reinterpret_cast<uint16_t*>(prow)[lane] = (uint16_t)code;
-  else prow[lane] = (uint8_t)code;
+__device__ __forceinline__ void store_codes16(uint8_t* prow, int sub, const uint32_t (&code)[BITS / 2]) {
+  if (BITS == 8) reinterpret_cast<uint4*>(prow)[sub] = make_uint4(code[0], code[1], code[2], code[3]);
+  else if (BITS == 4) reinterpret_cast<uint2*>(prow)[sub] = make_uint2(code[0], code[BITS == 4 ? 1 : 0]);
+  else reinterpret_cast<uint32_t*>(prow)[sub] = code[0];
 }
 
-// quantise one token row with a run-time bit width and store its codes; returns the scale
-__device__ __forceinline__ __half quant_store_row(int bits, const float (&v)[4], int scale_mode, uint8_t* prow, int lane) {
-  uint32_t c;
+// quantise one token row (eight lanes) with a run-time bit width and store its codes if `store`; returns the scale
+__device__ __forceinline__ __half quant_store_row16(int bits, const float (&v)[16], int scale_mode, uint8_t* prow, int sub, bool store) {
   __half s;
-  if (bits == 8) { s = quant_row_bits<8>(v, scale_mode, c); store_codes<8>(prow, lane, c); }
-  else if (bits == 4) { s = quant_row_bits<4>(v, scale_mode, c); store_codes<4>(prow, lane, c); }
-  else { s = quant_row_bits<2>(v, scale_mode, c); store_codes<2>(prow, lane, c); }
+  if (bits == 8) { uint32_t c[4]; s = quant_row16<8>(v, scale_mode, c); if (store) store_codes16<8>(prow, sub, c); }
+  else if (bits == 4) { uint32_t c[2]; s = quant_row16<4>(v, scale_mode, c); if (store) store_codes16<4>(prow, sub, c); }
+  else { uint32_t c[1]; s = quant_row16<2>(v, scale_mode, c); if (store) store_codes16<2>(prow, sub, c); }
   return s;
 }
 

@@ -56,28 +56,32 @@ cache_reorg_kernel(const __nv_bfloat16* __restrict__ keys, const __nv_bfloat16* 
     for (int i = threadIdx.x; i < cnt; i += blockDim.x) s_slice[i] = __ldg(asc + lo + i);
     __syncthreads();
     const int n_quant = prefix_len - T;
-    for (int p = p0 + warp; p < p1; p += kReorgWarps) {
+    // eight lanes per source row, four rows per warp and trip (every lane stays in step for the shuffles)
+    const int sub = lane & 7;
+    for (int pb = p0 + 4 * warp; pb < p1; pb += 4 * kReorgWarps) {
+      const int p = pb + (lane >> 3);
       // rank within the slice: entries < p; hit: an entry == p
       int below = 0, hit = 0;
-      for (int i = lane; i < cnt; i += 32) {
+      for (int i = sub; i < cnt; i += 8) {
         const int v = s_slice[i];
         below += v < p;
         hit |= v == p;
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
+      for (int o = 4; o > 0; o >>= 1) {
         below += __shfl_xor_sync(0xffffffffu, below, o);
         hit |= __shfl_xor_sync(0xffffffffu, hit, o);
       }
-      if (hit) continue;
       const int dst = p - (lo + below);
-      if (dst < 0 || dst >= n_quant) continue;   // cannot happen for a consistent index list
-      float kv[4], vv[4];
-      load4(K + (int64_t)p * 128 + lane * 4, kv);
-      load4(V + (int64_t)p * 128 + lane * 4, vv);
-      const __half sk = quant_store_row(k_bits, kv, scale_mode, k_packed + bh * kp_stride_bh + (int64_t)dst * (16 * k_bits), lane);
-      const __half sv = quant_store_row(v_bits, vv, scale_mode, v_packed + bh * vp_stride_bh + (int64_t)dst * (16 * v_bits), lane);
-      if (lane == 0) {
+      const bool live = p < p1 && !hit && dst >= 0 && dst < n_quant;     // dst out of range cannot happen for a consistent index list
+      const int ps = p < p1 ? p : p1 - 1;
+      float kv[16], vv[16];
+      load16(K + (int64_t)ps * 128 + sub * 16, kv);
+      load16(V + (int64_t)ps * 128 + sub * 16, vv);
+      const int64_t d = live ? dst : 0;
+      const __half sk = quant_store_row16(k_bits, kv, scale_mode, k_packed + bh * kp_stride_bh + d * (16 * k_bits), sub, live);
+      const __half sv = quant_store_row16(v_bits, vv, scale_mode, v_packed + bh * vp_stride_bh + d * (16 * v_bits), sub, live);
+      if (live && sub == 0) {
         k_scale[bh * scale_stride_bh + dst] = sk;
         v_scale[bh * scale_stride_bh + dst] = sv;
       }
@@ -153,6 +157,9 @@ extern "C" int hq_cache_reorganize_bits(const void* keys, const void* values, in
   HQ_REQUIRE(window == 0 || (k_window && v_window), HQ_ERR_INVALID, "hq_cache_reorganize: null window output");
   HQ_REQUIRE(prefix_len - T == 0 || (k_packed && v_packed && k_scale && v_scale), HQ_ERR_INVALID,
              "hq_cache_reorganize: null quantised output");
+  HQ_REQUIRE(((uintptr_t)k_packed % (2 * k_bits)) == 0 && ((uintptr_t)v_packed % (2 * v_bits)) == 0 && kp_stride_bh % (2 * k_bits) == 0 &&
+                 vp_stride_bh % (2 * v_bits) == 0, HQ_ERR_ALIGNMENT,
+             "hq_cache_reorganize: packed rows must be aligned to 2 * bits bytes (what one lane stores)");
   HQ_REQUIRE((T == 0 || (aligned16(k_topk) && aligned16(v_topk))) && (window == 0 || (aligned16(k_window) && aligned16(v_window))),
              HQ_ERR_ALIGNMENT, "hq_cache_reorganize: BF16 outputs must be 16-byte aligned");
   const int prefix_tiles = (prefix_len + kReorgTile - 1) / kReorgTile;

@@ -47,8 +47,8 @@ def quantize_per_token_into(x: torch.Tensor, packed: torch.Tensor, scale: torch.
     BH, n, D = x.shape
     if D != 128:
         raise HyQuantError(f"head_dim {D} is not built (128 only)")
-    if x.stride(2) != 1:
-        x = x.contiguous()
+    if x.stride(2) != 1 or x.stride(1) % 8 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()               # the kernel reads a row as 16-byte pieces
     if packed.dtype != torch.int8 or scale.dtype != torch.float16:
         raise HyQuantError("packed must be int8 and scale fp16")
     if packed.stride(2) != 1 or packed.stride(1) != 16 * nbits or scale.stride(1) != 1:

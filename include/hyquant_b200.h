@@ -53,8 +53,10 @@ const char* hq_last_error(void);
  * growth of the prefix (:213-216): rows are written at token `dst_token_offset`
  * of pre-allocated capacity buffers.
  *
- *   x        [BH, n, 128] in_dtype, row stride x_stride_n, head stride x_stride_bh (elements)
- *   packed   int8  [BH, cap, 16 * nbits] (64 bytes per token at 4 bits), head stride packed_stride_bh (bytes)
+ *   x        [BH, n, 128] in_dtype, row stride x_stride_n, head stride x_stride_bh (elements; rows 16-byte aligned,
+ *            strides multiples of 8 elements)
+ *   packed   int8  [BH, cap, 16 * nbits] (64 bytes per token at 4 bits), head stride packed_stride_bh (bytes; rows
+ *            aligned to 2 * nbits bytes)
  *   scale    fp16  [BH, cap],     head stride scale_stride_bh (elements)
  *   scale_mode 0: scale = half(max(|x|,1e-5) / 7)            (IEEE divide; CPU-eager PyTorch)
  *              1: scale = half(max(|x|,1e-5) * (1.0f/7.0f))  (CUDA-eager PyTorch)
